@@ -1,0 +1,210 @@
+#!/usr/bin/env python
+"""Headline benchmark: Llama-3-8B-shape training throughput (tokens/s) on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
+
+Model: vocab 128256, d_model 4096, 32 layers, 32 query / 8 KV heads (head_dim 128), SwiGLU FFN 14336,
+RoPE theta 500000, bf16, random-init N(0, 0.02); data: uniform random token ids, global batch 8 x seq
+4096 (synthetic). Every step is forward + backward (FlashAttention backward) + fused Adam.
+
+Two timed regions, each K steps after W warm-up steps, bracketed by a barrier and a device
+synchronise, timed with CUDA events, max over ranks:
+  * ``value``: steps fed from a device-resident batch;
+  * ``e2e``:   ``Trainer.train_step`` -- the public call -- fed from pinned host memory each step
+               (host-to-device copy of the tokens and device-to-host read of the loss included).
+Rank 0 prints ONE JSON line. ``--impl reference`` reports why the reference cannot be run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+REFERENCE_UNAVAILABLE = ("reference is a CMake/C++ project without setup.py or pyproject.toml: "
+                         "`pip install --no-index ... /root/reference` fails with 'Directory is not installable'")
+
+_SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while a timed region runs."""
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={_SMI_FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [c for c, p in zip(sm, power) if p > 0.5 * max(power)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(smax), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--global-batch", type=int, default=8)
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--micro-batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=32, help="(debug only) fewer layers; invalidates the metric")
+    ap.add_argument("--master-weights", action="store_true")
+    ap.add_argument("--parallelism", default="auto", help="auto | dp | tp  (auto: tensor+sequence parallel over all ranks)")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    from tesseract_b200 import _native
+    from tesseract_b200.models import LlamaConfig, LlamaModel
+    from tesseract_b200.training import TrainConfig, Trainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("bench.py --gpus N>1 must be launched with torch.distributed.run (one rank per GPU)")
+        args.gpus = world
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    from tesseract_b200.parallel import build_parallel_trainer  # noqa: WPS433 (after process group init)
+
+    cfg = LlamaConfig.llama_3_8b(dtype=torch.bfloat16, max_position_embeddings=args.seq_len)
+    cfg.num_hidden_layers = args.layers
+    tcfg = TrainConfig(lr=1e-4, micro_batch=args.micro_batch, grad_dtype=torch.bfloat16,
+                       master_weights=args.master_weights)
+    trainer, plan = build_parallel_trainer(cfg, tcfg, world, rank, device, args.parallelism, seed=1234)
+
+    B, S = args.global_batch, args.seq_len
+    if B % plan["dp"]:
+        raise SystemExit(f"global batch {B} is not divisible by the data-parallel degree {plan['dp']}")
+    local_b = B // plan["dp"]
+    gen = torch.Generator().manual_seed(1000 + plan["dp_rank"])
+    host_batches = [torch.randint(0, cfg.vocab_size, (local_b, S + 1), generator=gen, dtype=torch.int64).pin_memory()
+                    for _ in range(2)]
+    dev_batches = [b.to(device) for b in host_batches]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    last_loss = [0.0]
+
+    def dev_step(i):
+        last_loss[0] = trainer.step_on_device(dev_batches[i % 2])
+
+    def e2e_step(i):
+        last_loss[0] = trainer.train_step(host_batches[i % 2])
+
+    for i in range(args.warmup):
+        dev_step(i)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _native.launch_count()
+    ms_dev = timed(dev_step, args.steps)
+    launches = _native.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    status = _native.read_status(torch.cuda.current_stream().cuda_stream)
+
+    e2e = None
+    if not args.no_e2e:
+        e2e_step(0)
+        ms_e2e = timed(e2e_step, args.steps)
+        tok_e2e = B * S * args.steps / (ms_e2e / 1e3)
+        e2e = {"value": tok_e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+               "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4 * world}
+
+    if rank == 0:
+        tok_s = B * S * args.steps / (ms_dev / 1e3)
+        loss_val = float(last_loss[0]) if not isinstance(last_loss[0], float) else last_loss[0]
+        out = {
+            "metric": "Llama-3-8B-shape training tokens/s (fwd+bwd+Adam, max over ranks)",
+            "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform random token ids; random-init N(0,0.02) weights",
+            "config": {"model": "llama-3-8b-shape" + ("" if args.layers == 32 else f"-DEBUG-{args.layers}-layers"),
+                       "global_batch": B, "seq_len": S, "parallelism": plan["name"], "micro_batch": args.micro_batch,
+                       "optimizer": "Adam fp32 m/v" + (" + fp32 master" if args.master_weights else ""),
+                       "grad_dtype": "bf16", "l2_hygiene": "inputs_larger_than_l2 (16 GB of weights streamed per pass)",
+                       "gemm": os.environ.get("TESSERACT_GEMM", "tcgen05"),
+                       "attention": os.environ.get("TESSERACT_ATTN", "tcgen05"),
+                       "fused_comm": plan.get("fused_comm", False)},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
+            "kernel_status": status,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,387 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] (+)= op(A) * op(B), fp32 accumulation in TMEM.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles of A and B into a 128-byte-swizzled smem ring
+//   warp 1      allocates TMEM; one thread issues tcgen05.mma (128 x BN x 16) and tcgen05.commit
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (double-buffered in TMEM), convert, store
+// Operands may be K-major (row-major [rows, K]) or M/N-major (row-major [K, rows]); the second form is
+// what the backward GEMMs of a Linear layer need (dX = dY * W, dW = dY^T * X) without any transposes.
+//
+// Replaces the cuBLASLt bridge of the reference (src/cuda/MatMul.cpp:422-490) for every dense
+// Linear forward/backward.
+#include "common.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace tsb {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStageBytesA = BM * BK * 2;
+  static constexpr int kStageBytesB = BN * BK * 2;
+  static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+};
+
+struct TileCoord {
+  int m_blk, n_blk;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
+  constexpr int GM = 16;
+  const int group_size = GM * num_n;
+  const int group_id = t / group_size;
+  const int first_m = group_id * GM;
+  const int gm = min(num_m - first_m, GM);
+  const int r = t - group_id * group_size;
+  return {first_m + r % gm, r / gm};
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ C,
+                 int M, int N, int K, long long ldc, int* status) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ volatile int cta_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (M + BM - 1) / BM;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    cta_abort = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_smem, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, num_m, num_n);
+        const int m0 = tc.m_blk * BM;
+        const int n0 = tc.n_blk * BN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &cta_abort, status);
+          if (!ok) break;
+          uint8_t* sA = smem + stage * Cfg::kStageBytes;
+          uint8_t* sB = sA + Cfg::kStageBytesA;
+          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          if (!A_MN) {
+            tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sA + i * 8192, &tmA, &full_bar[stage], m0 + i * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sB + i * 8192, &tmB, &full_bar[stage], n0 + i * 64, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        bool ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, &cta_abort, status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, &cta_abort, status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t b_base = a_base + Cfg::kStageBytesA;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? umma_smem_desc_sw128(a_base + k * 2048, 8192, 1024)
+                                        : umma_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
+                                        : umma_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full_bar[acc]);  // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const int row_in_tile = q * 32 + lane;
+    const bool vec_ok = (ldc % (16 / sizeof(OutT)) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const TileCoord tc = tile_coord(t, num_m, num_n);
+      const int m0 = tc.m_blk * BM;
+      const int n0 = tc.n_blk * BN;
+      if (!mbar_wait(&tmem_full_bar[acc], acc_phase, &cta_abort, status)) break;
+      tc_fence_after();
+      const int row = m0 + row_in_tile;
+      OutT* crow = C + static_cast<long long>(row) * ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN + c * 32), r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          if (vec_ok && col0 + 32 <= N) {
+            if constexpr (sizeof(OutT) == 2) {
+              uint4* dst = reinterpret_cast<uint4*>(crow + col0);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+                if constexpr (ACCUM) {
+                  const uint4 old = dst[v];
+                  const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 of = __bfloat1622float2(o2[j]);
+                    f[2 * j] += of.x;
+                    f[2 * j + 1] += of.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]);
+                o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]);
+                o.w = pack_bf16x2(f[6], f[7]);
+                dst[v] = o;
+              }
+            } else {
+              float4* dst = reinterpret_cast<float4*>(crow + col0);
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 o = make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
+                                       __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
+                if constexpr (ACCUM) {
+                  const float4 old = dst[v];
+                  o.x += old.x;
+                  o.y += old.y;
+                  o.z += old.z;
+                  o.w += old.w;
+                }
+                dst[v] = o;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < N) {
+                float v = __uint_as_float(r[j]);
+                if constexpr (ACCUM) v += to_f32<OutT>(crow[col0 + j]);
+                crow[col0 + j] = from_f32<OutT>(v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------ tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (cta_abort) {
+      // Give copies and MMAs that are still in flight a bounded moment to land before TMEM goes away.
+      for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- tensor-map cache
+struct TmapKey {
+  const void* p;
+  uint64_t rows, cols, stride;
+  uint32_t br, bc;
+  bool operator==(const TmapKey& o) const {
+    return p == o.p && rows == o.rows && cols == o.cols && stride == o.stride && br == o.br && bc == o.bc;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.p) * 0x9E3779B97F4A7C15ull;
+    h ^= k.rows * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= k.cols * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
+    h ^= k.stride + (h << 6) + (h >> 2);
+    h ^= (static_cast<size_t>(k.br) << 32 | k.bc) + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmaps;
+std::mutex g_tmap_mu;
+
+bool cached_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t stride_bytes,
+                    uint32_t box_rows, uint32_t box_cols) {
+  TmapKey key{base, rows, cols, stride_bytes, box_rows, box_cols};
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  auto it = g_tmaps.find(key);
+  if (it != g_tmaps.end()) {
+    *out = it->second;
+    return true;
+  }
+  if (!make_tmap_2d(out, base, 2, rows, cols, stride_bytes, box_rows, box_cols, true)) return false;
+  if (g_tmaps.size() > 8192) g_tmaps.clear();
+  g_tmaps.emplace(key, *out);
+  return true;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
+int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int max_ctas,
+               cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT, ACCUM>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int grid = sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (tiles < grid) grid = tiles;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(C), M, N, K, ldc,
+                                                        device_status_word());
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int out_f32,
+               int accumulate, int max_ctas, cudaStream_t s) {
+  if (out_f32) {
+    return accumulate ? launch_cfg<BN, A_MN, B_MN, float, true>(ta, tb, C, M, N, K, ldc, max_ctas, s)
+                      : launch_cfg<BN, A_MN, B_MN, float, false>(ta, tb, C, M, N, K, ldc, max_ctas, s);
+  }
+  return accumulate ? launch_cfg<BN, A_MN, B_MN, __nv_bfloat16, true>(ta, tb, C, M, N, K, ldc, max_ctas, s)
+                    : launch_cfg<BN, A_MN, B_MN, __nv_bfloat16, false>(ta, tb, C, M, N, K, ldc, max_ctas, s);
+}
+
+template <int BN>
+int launch_major(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int a_mn,
+                 int b_mn, int out_f32, int accumulate, int max_ctas, cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch_out<BN, false, false>(ta, tb, C, M, N, K, ldc, out_f32, accumulate, max_ctas, s);
+  if (!a_mn && b_mn) return launch_out<BN, false, true>(ta, tb, C, M, N, K, ldc, out_f32, accumulate, max_ctas, s);
+  if (a_mn && !b_mn) return launch_out<BN, true, false>(ta, tb, C, M, N, K, ldc, out_f32, accumulate, max_ctas, s);
+  return launch_out<BN, true, true>(ta, tb, C, M, N, K, ldc, out_f32, accumulate, max_ctas, s);
+}
+
+}  // namespace
+}  // namespace tsb
+
+// C[M,N] (+)= op(A) * op(B) with bf16 inputs and fp32 accumulation.
+//   a_mn == 0: A is row-major [M, K] (row stride lda elements);  a_mn == 1: A is row-major [K, M].
+//   b_mn == 0: B is row-major [N, K] (row stride ldb elements);  b_mn == 1: B is row-major [K, N].
+//   C is row-major [M, N] with row stride ldc; bf16, or fp32 when out_f32 != 0; accumulate != 0 adds
+//   into the existing contents of C.
+// Requirements: A and B 16-byte aligned with row strides that are multiples of 8 elements.
+// block_n: 0 = choose, else 64 / 128 / 256. max_ctas: 0 = one CTA per SM, else a cap (used when some SMs are
+// reserved for a concurrent communication kernel).
+// Returns 0, a cudaError_t, or -2 (bad argument) / -3 (tensor map encoding failed).
+TSB_EXPORT int tsb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                             long long ldb, long long ldc, int a_mn, int b_mn, int out_f32, int accumulate,
+                             int block_n, int max_ctas, void* stream) {
+  using namespace tsb;
+  if (M <= 0 || N <= 0 || K <= 0) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % 8) || (ldb % 8))
+    return -2;
+  int bn = block_n;
+  if (bn == 0) {
+    const int sms = sm_count();
+    const long long t256 = static_cast<long long>((M + BM - 1) / BM) * ((N + 255) / 256);
+    const long long t128 = static_cast<long long>((M + BM - 1) / BM) * ((N + 127) / 128);
+    if (N >= 256 && t256 >= sms) bn = 256;
+    else if (N >= 128 && t128 >= sms / 2) bn = 128;
+    else bn = (N >= 128 && t128 * 2 > ((M + BM - 1) / BM) * ((N + 63) / 64)) ? 128 : 64;
+  }
+  if (bn != 64 && bn != 128 && bn != 256) return -2;
+  CUtensorMap ta, tb;
+  bool ok;
+  if (!a_mn) ok = cached_tmap_2d(&ta, A, M, K, lda * 2, BM, BK);
+  else ok = cached_tmap_2d(&ta, A, K, M, lda * 2, BK, 64);
+  if (!ok) return -3;
+  if (!b_mn) ok = cached_tmap_2d(&tb, B, N, K, ldb * 2, bn, BK);
+  else ok = cached_tmap_2d(&tb, B, K, N, ldb * 2, BK, 64);
+  if (!ok) return -3;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (bn) {
+    case 256: return launch_major<256>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
+    case 128: return launch_major<128>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
+    default: return launch_major<64>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
+  }
+}

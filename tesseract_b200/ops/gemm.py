@@ -1,0 +1,132 @@
+"""Dense GEMM entry points: the tcgen05 bf16 kernel for CUDA bf16 tensors, torch elsewhere.
+
+``linear`` is the autograd-aware op every projection of the model goes through. Its backward issues
+the two transposed GEMMs directly on the row-major operands (M/N-major UMMA descriptors), and can
+accumulate the weight gradient straight into a caller-owned ``main_grad`` buffer.
+
+Reference counterpart: ``ops::matmul`` -> cuBLASLt (src/ops/cpu/MatMul.cpp:424-435,
+src/cuda/MatMul.cpp:422-490) and ``MatMulBackward`` (src/ops/cpu/MatMul.cpp:400-420).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from .. import _native
+
+
+def _use_native(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and os.environ.get("TESSERACT_GEMM", "tcgen05") != "cublas"
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+              out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, accumulate: bool = False,
+              block_n: int = 0, max_ctas: int = 0) -> torch.Tensor:
+    """C[M,N] (+)= op(A) @ op(B)^T on the tcgen05 kernel.
+
+    ``a`` is [M,K] (``a_mn=False``) or [K,M] (``a_mn=True``); ``b`` is [N,K] or [K,N] (``b_mn=True``).
+    Rows must be contiguous (stride 1 in the last dimension), row strides multiples of 8 elements.
+    """
+    assert a.dim() == 2 and b.dim() == 2 and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(1) == 1 and b.stride(1) == 1, "gemm_bf16 needs unit stride in the last dimension"
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"gemm_bf16: inner dimensions differ ({K} vs {Kb})")
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype or torch.bfloat16)
+        if accumulate:
+            raise ValueError("accumulate=True needs an existing `out`")
+    else:
+        assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    rc = _native.lib().tsb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+        int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), block_n, max_ctas,
+        _native.stream_ptr(a.device))
+    _native.check(rc, "tsb_gemm_bf16")
+    return out
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a [M,K] @ b[N,K]^T without autograd."""
+    if _use_native(a):
+        return gemm_bf16(a, b)
+    return a @ b.t()
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, wgrad_buf, force_wgrad):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(1) != 1 or x2.stride(0) % 8:
+            x2 = x2.contiguous()
+        y = gemm_bf16(x2, w)
+        ctx.save_for_backward(x2, w)
+        ctx.wgrad_buf = wgrad_buf
+        ctx.force_wgrad = force_wgrad
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1 or dy2.stride(0) % 8:
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_bf16(dy2, w, b_mn=True).view(ctx.x_shape)           # dX = dY @ W
+        if ctx.needs_input_grad[1] or ctx.force_wgrad:
+            buf = ctx.wgrad_buf
+            if buf is not None:
+                gemm_bf16(dy2, x2, a_mn=True, b_mn=True, out=buf, accumulate=True)   # dW += dY^T @ X
+            else:
+                dw = gemm_bf16(dy2, x2, a_mn=True, b_mn=True)
+        return dx, dw, None, None
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           wgrad_buf: torch.Tensor | None = None, force_wgrad: bool = False) -> torch.Tensor:
+    """y = x @ weight^T (+ bias). ``weight`` is [out, in].
+
+    With ``wgrad_buf`` (same shape as ``weight``, bf16 or fp32) the backward pass adds the weight
+    gradient into that buffer and reports no gradient for ``weight`` to autograd. ``force_wgrad``
+    computes it even when ``weight`` itself is not an autograd leaf (a fused view over several
+    parameters that share one arena).
+    """
+    if _use_native(x) and weight.dtype == torch.bfloat16 and weight.stride(-1) == 1:
+        y = _LinearFn.apply(x, weight, wgrad_buf, bool(force_wgrad and wgrad_buf is not None))
+        if bias is not None:
+            y = y + bias
+        return y
+    if wgrad_buf is not None and torch.is_grad_enabled() and (weight.requires_grad or force_wgrad):
+        return _AccumLinearFn.apply(x, weight, bias, wgrad_buf)
+    return torch.nn.functional.linear(x, weight, bias)
+
+
+class _AccumLinearFn(torch.autograd.Function):
+    """Library-GEMM twin of _LinearFn (CPU tensors, fp32 CUDA tensors) with the same main_grad contract."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, wgrad_buf):
+        ctx.save_for_backward(x, w)
+        ctx.wgrad_buf = wgrad_buf
+        ctx.has_bias = bias is not None
+        return torch.nn.functional.linear(x, w, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = (dy2 @ w).view(x.shape) if ctx.needs_input_grad[0] else None
+        ctx.wgrad_buf.add_((dy2.t() @ x2).to(ctx.wgrad_buf.dtype))
+        db = dy2.sum(0) if ctx.has_bias else None
+        return dx, None, db, None

@@ -1,0 +1,246 @@
+"""Numerics of the native sm_100a kernels against plain PyTorch fp32 references of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from tesseract_b200 import _native
+    assert _native.available(), "native library missing on a GPU machine"
+    _native.lib()
+    return torch.device("cuda", 0)
+
+
+def _status_ok():
+    from tesseract_b200 import _native
+    assert _native.read_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
+def test_probe(dev):
+    from tesseract_b200 import _native
+    out = torch.zeros(1, dtype=torch.int32, device=dev)
+    _native.check(_native.lib().tsb_probe(out.data_ptr(), _native.stream_ptr(dev)), "probe")
+    assert int(out.item()) == 100
+
+
+def _rel_err(got, ref):
+    return ((got.float() - ref.float()).norm() / ref.float().norm().clamp_min(1e-12)).item()
+
+
+GEMM_SHAPES = [(128, 128, 64), (128, 256, 128), (256, 512, 256), (384, 640, 192), (1024, 1024, 1024),
+               (200, 264, 136), (4096, 768, 512), (64, 4096, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_layouts(dev, M, N, K, a_mn, b_mn):
+    from tesseract_b200.ops import gemm_bf16
+    g = torch.Generator(device=dev).manual_seed(M * 7 + N * 3 + K)
+    A = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    B = torch.randn(N, K, device=dev, generator=g).bfloat16()
+    ref = A.float() @ B.float().t()
+    a_in = A.t().contiguous() if a_mn else A
+    b_in = B.t().contiguous() if b_mn else B
+    out = gemm_bf16(a_in, b_in, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_err(out, ref) < 6e-3, (M, N, K, a_mn, b_mn)
+
+
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+def test_gemm_block_sizes_and_fp32_accumulate(dev, block_n):
+    from tesseract_b200.ops import gemm_bf16
+    M, N, K = 512, 768, 320
+    A = torch.randn(M, K, device=dev).bfloat16()
+    B = torch.randn(N, K, device=dev).bfloat16()
+    ref = A.float() @ B.float().t()
+    out = torch.ones(M, N, device=dev, dtype=torch.float32)
+    gemm_bf16(A, B, out=out, accumulate=True, block_n=block_n)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_err(out - 1.0, ref) < 1e-3
+    outb = torch.full((M, N), 2.0, device=dev, dtype=torch.bfloat16)
+    gemm_bf16(A, B, out=outb, accumulate=True, block_n=block_n)
+    assert _rel_err(outb.float() - 2.0, ref) < 2e-2
+
+
+def test_gemm_persistent_many_tiles(dev):
+    """More tiles than SMs: exercises the smem ring / TMEM double-buffer phase flips."""
+    from tesseract_b200.ops import gemm_bf16
+    M, N, K = 4096, 4096, 1024
+    A = torch.randn(M, K, device=dev).bfloat16() * 0.1
+    B = torch.randn(N, K, device=dev).bfloat16() * 0.1
+    out = gemm_bf16(A, B)
+    ref = A.float() @ B.float().t()
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_err(out, ref) < 6e-3
+    out2 = gemm_bf16(A, B)
+    assert torch.equal(out, out2), "GEMM is not run-to-run deterministic"
+
+
+def test_linear_autograd(dev):
+    from tesseract_b200 import ops
+    x = torch.randn(3, 128, 256, device=dev).bfloat16().requires_grad_()
+    w = (torch.randn(384, 256, device=dev) * 0.05).bfloat16().requires_grad_()
+    y = ops.linear(x, w)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 6e-3
+    assert _rel_err(x.grad, xr.grad) < 8e-3
+    assert _rel_err(w.grad, wr.grad) < 8e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,D", [(37, 256), (512, 4096), (5, 8192)])
+def test_rmsnorm_fwd_bwd(dev, dtype, rows, D):
+    from tesseract_b200 import ops
+    x = torch.randn(rows, D, device=dev).to(dtype).requires_grad_()
+    r = torch.randn(rows, D, device=dev).to(dtype).requires_grad_()
+    w = (1 + 0.1 * torch.randn(D, device=dev)).to(dtype).requires_grad_()
+    y, h = ops.rms_norm(x, w, 1e-5, residual=r)
+    gy, gh = torch.randn_like(y), torch.randn_like(h)
+    (y.float() * gy.float()).sum().add((h.float() * gh.float()).sum()).backward()
+    xr, rr, wr = [t.detach().float().requires_grad_() for t in (x, r, w)]
+    hr = (xr + rr).to(dtype).float() if dtype != torch.float32 else xr + rr
+    hr_full = xr + rr
+    yr = ops.rms_norm_ref(hr_full, wr, 1e-5)
+    ((yr * gy.float()).sum() + (hr_full * gh.float()).sum()).backward()
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel_err(y, yr) < tol and _rel_err(h, hr_full) < tol
+    assert _rel_err(x.grad, xr.grad) < tol and _rel_err(r.grad, rr.grad) < tol
+    assert _rel_err(w.grad, wr.grad) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_swiglu_fwd_bwd(dev, dtype):
+    from tesseract_b200 import ops
+    gu = torch.randn(77, 2 * 1376, device=dev).to(dtype).requires_grad_()
+    out = ops.swiglu(gu)
+    g = torch.randn_like(out)
+    out.backward(g)
+    gr = gu.detach().float().requires_grad_()
+    outr = ops.swiglu_ref(gr)
+    outr.backward(g.float())
+    tol = 1.5e-2 if dtype == torch.bfloat16 else 1e-5
+    assert _rel_err(out, outr) < tol and _rel_err(gu.grad, gr.grad) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rope_qkv(dev, dtype):
+    from tesseract_b200 import ops
+    H, Hkv, D, S, B = 4, 2, 64, 48, 3
+    cos, sin = ops.rope_tables(128, D, 10000.0, dev)
+    qkv = torch.randn(B * S, (H + 2 * Hkv) * D, device=dev).to(dtype)
+    ref = ops.rope_qkv(qkv.cpu().float(), cos.cpu(), sin.cpu(), num_heads=H, num_kv_heads=Hkv, head_dim=D, seq_len=S,
+                       pos_offset=5)
+    x = qkv.clone().requires_grad_()
+    got = ops.rope_qkv(x * 1.0, cos, sin, num_heads=H, num_kv_heads=Hkv, head_dim=D, seq_len=S, pos_offset=5)
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    assert _rel_err(got.cpu(), ref) < tol
+    # backward = inverse rotation: rotating the gradient back must return the upstream gradient's preimage
+    g = torch.randn_like(got)
+    got.backward(g)
+    xr = qkv.cpu().float().requires_grad_()
+    refr = ops.rope_qkv(xr, cos.cpu(), sin.cpu(), num_heads=H, num_kv_heads=Hkv, head_dim=D, seq_len=S, pos_offset=5)
+    refr.backward(g.cpu().float())
+    assert _rel_err(x.grad.cpu(), xr.grad) < tol
+
+
+def test_embedding_fwd_bwd(dev):
+    from tesseract_b200 import ops
+    V, D = 1000, 256
+    table = torch.randn(V, D, device=dev).bfloat16().requires_grad_()
+    ids = torch.randint(0, V, (4, 33), device=dev)
+    out = ops.embedding(ids, table)
+    assert torch.equal(out, table.detach()[ids])
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref = torch.zeros(V, D, device=dev).index_add_(0, ids.reshape(-1), g.reshape(-1, D).float())
+    assert _rel_err(table.grad, ref) < 1e-2
+
+
+@pytest.mark.parametrize("dtype,V", [(torch.bfloat16, 4096), (torch.float32, 1000), (torch.bfloat16, 128256)])
+def test_cross_entropy(dev, dtype, V):
+    from tesseract_b200 import ops
+    N = 64
+    logits = (torch.randn(N, V, device=dev) * 3).to(dtype).requires_grad_()
+    tgt = torch.randint(0, V, (N,), device=dev)
+    loss = ops.cross_entropy(logits, tgt)
+    loss.backward()
+    lr = logits.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(lr, tgt)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-3 * max(1.0, abs(ref.item()))
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel_err(logits.grad, lr.grad) < tol
+
+
+def test_vocab_parallel_ce_stats_merge(dev):
+    from tesseract_b200 import ops
+    N, V = 32, 2048
+    logits = (torch.randn(N, V, device=dev) * 2).bfloat16()
+    tgt = torch.randint(0, V, (N,), device=dev)
+    halves = [logits[:, :1024].contiguous(), logits[:, 1024:].contiguous()]
+    stats = ops.merge_ce_stats([ops.ce_stats(h, tgt, vocab_start=i * 1024) for i, h in enumerate(halves)])
+    losses = ops.ce_loss_and_grad_(halves[0], tgt, stats, 1.0, vocab_start=0, write_grad=False)
+    ref = torch.nn.functional.cross_entropy(logits.float(), tgt, reduction="none")
+    assert torch.allclose(losses, ref, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("use_arena", [True, False])
+def test_adam_matches_reference_formula(dev, use_arena):
+    from tesseract_b200.optim import Adam, ParamArena
+    torch.manual_seed(0)
+    ps = [torch.nn.Parameter(torch.randn(n, device=dev)) for n in (1000, 70001, 129)]
+    ref = [p.detach().clone() for p in ps]
+    m = [torch.zeros_like(p) for p in ref]
+    v = [torch.zeros_like(p) for p in ref]
+    arena = ParamArena(ps) if use_arena else None
+    opt = Adam(arena if use_arena else ps, lr=1e-2)
+    for t in range(1, 4):
+        grads = [torch.randn_like(p) for p in ref]
+        for p, g in zip(ps, grads):
+            if use_arena:
+                p.main_grad.copy_(g)
+            else:
+                p.grad = g.clone()
+        opt.step()
+        for i, g in enumerate(grads):
+            m[i] = 0.9 * m[i] + 0.1 * g
+            v[i] = 0.999 * v[i] + 0.001 * g * g
+            ref[i] -= 1e-2 * (m[i] / (1 - 0.9 ** t)) / ((v[i] / (1 - 0.999 ** t)).sqrt() + 1e-8)
+    for p, r in zip(ps, ref):
+        assert torch.allclose(p.detach(), r, atol=1e-5, rtol=1e-5)
+
+
+def test_tiny_llama_train_step_matches_cpu(dev):
+    """bf16 GPU step through every native kernel vs the fp32 CPU restatement of the same model."""
+    from tesseract_b200.models import LlamaConfig, LlamaModel
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, intermediate_size=512, max_position_embeddings=128, dtype=torch.float32)
+    cpu = LlamaModel(cfg, init_std=0.02, seed=3)
+    cfg_g = LlamaConfig(**{**cfg.__dict__, "dtype": torch.bfloat16})
+    gpu = LlamaModel(cfg_g, device=dev)
+    gpu.load_hf_state_dict({k: v for k, v in cpu.hf_state_dict().items()})
+    tok = torch.randint(0, 512, (2, 128))
+    tgt = torch.randint(0, 512, (2, 128))
+    lc = cpu.loss(tok, tgt)
+    lc.backward()
+    lg = gpu.loss(tok.to(dev), tgt.to(dev))
+    lg.backward()
+    _status_ok()
+    assert abs(lc.item() - lg.item()) < 3e-2
+    gc = dict(cpu.named_parameters())
+    worst = 0.0
+    for n, p in gpu.named_parameters():
+        worst = max(worst, _rel_err(p.grad, gc[n].grad))
+    assert worst < 8e-2, worst
