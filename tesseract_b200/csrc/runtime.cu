@@ -4,6 +4,7 @@
 #include "common.cuh"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -19,6 +20,7 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
+int g_last_encode_result = 0;
 
 EncodeTiledFn resolve_encode() {
   if (g_encode) return g_encode;
@@ -76,6 +78,13 @@ bool make_tmap_nd(CUtensorMap* out, const void* base, int elem_bytes, int rank, 
                   const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
   EncodeTiledFn enc = resolve_encode();
   if (!enc) return false;
+  // The driver call needs a current context. A thread that has only ever been handed work by another
+  // runtime instance (e.g. an autograd worker) may not have bound one yet; a runtime call binds it.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   CUtensorMapDataType dt;
   switch (elem_bytes) {
     case 1: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
@@ -93,10 +102,22 @@ bool make_tmap_nd(CUtensorMap* out, const void* base, int elem_bytes, int rank, 
     estride[i] = 1;
     if (i > 0) gstride[i - 1] = strides_bytes[i];
   }
+  g_last_encode_result = 0;
   CUresult r = enc(out, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstride, bdim, estride,
                    CU_TENSOR_MAP_INTERLEAVE_NONE,
                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_encode_result = static_cast<int>(r);
+    if (getenv("TESSERACT_DEBUG")) {
+      fprintf(stderr, "[tesseract_b200] cuTensorMapEncodeTiled failed: result=%d base=%p elem=%d rank=%d", (int)r,
+              base, elem_bytes, rank);
+      for (int i = 0; i < rank; ++i)
+        fprintf(stderr, " dim%d=%llu box%d=%u stride%d=%llu", i, (unsigned long long)dims[i], i, box[i], i,
+                (unsigned long long)(i ? strides_bytes[i] : (uint64_t)elem_bytes));
+      fprintf(stderr, "\n");
+    }
+  }
   return r == CUDA_SUCCESS;
 }
 
@@ -119,6 +140,9 @@ __global__ void probe_kernel(int* out) {
 TSB_EXPORT int tsb_read_status(void* stream) {
   return tsb::read_and_clear_status(static_cast<cudaStream_t>(stream));
 }
+
+// CUresult of the most recent failed tensor-map encoding (0 if the last one succeeded).
+TSB_EXPORT int tsb_last_tmap_error() { return tsb::g_last_encode_result; }
 
 TSB_EXPORT int tsb_sm_count() { return tsb::sm_count(); }
 

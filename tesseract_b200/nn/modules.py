@@ -249,7 +249,7 @@ class MultiHeadAttention(Module):
         qkv = ops.rope_qkv(qkv, self.rope.cos, self.rope.sin, num_heads=H, num_kv_heads=Hkv, head_dim=D, seq_len=S,
                            pos_offset=pos)
         qkv = qkv.view(B, S, H + 2 * Hkv, D)
-        o = ops.flash_attention(qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:], causal=self.causal)
+        o = ops.flash_attention_packed(qkv, H, Hkv, causal=self.causal)
         return self.o_proj(o.reshape(B, S, H * D))
 
 

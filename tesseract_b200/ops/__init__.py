@@ -1,13 +1,13 @@
 """Functional ops. CUDA tensors are served by the native sm_100a kernels; CPU tensors by the torch
 restatement of the reference's CPU math (which doubles as the test oracle)."""
-from .attention import attention_ref, flash_attention
+from .attention import attention_ref, flash_attention, flash_attention_packed
 from .fused import (ce_loss_and_grad_, ce_stats, cross_entropy, cross_entropy_ref, embedding, grad_to_buf,
                     merge_ce_stats, rms_norm, rms_norm_ref, rope_qkv, rope_ref, rope_tables, swiglu, swiglu_ref,
                     swiglu_silu_gate)
 from .gemm import gemm_bf16, linear, matmul_nt
 
 __all__ = [
-    "attention_ref", "flash_attention", "ce_loss_and_grad_", "ce_stats", "cross_entropy", "cross_entropy_ref",
+    "attention_ref", "flash_attention", "flash_attention_packed", "ce_loss_and_grad_", "ce_stats", "cross_entropy", "cross_entropy_ref",
     "embedding", "grad_to_buf", "merge_ce_stats", "rms_norm", "rms_norm_ref", "rope_qkv", "rope_ref",
     "rope_tables", "swiglu", "swiglu_ref", "swiglu_silu_gate", "gemm_bf16", "linear", "matmul_nt",
 ]

@@ -18,7 +18,9 @@ from .._native import check, lib, stream_ptr
 _native.register_signatures({
     "tsb_flash_fwd": [_native.P] * 5 + [_native.I] * 6 + [_native.L] * 12 + [_native.F, _native.I, _native.P],
     "tsb_flash_bwd": [_native.P] * 10 + [_native.I] * 6 + [_native.L] * 12 + [_native.F, _native.I, _native.P],
+    "tsb_flash_bwd_scratch_bytes": [_native.I] * 4,
 })
+_native._RESTYPES["tsb_flash_bwd_scratch_bytes"] = _native.L
 
 
 def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,
@@ -85,16 +87,74 @@ class _FlashFn(torch.autograd.Function):
             packed = torch.empty((B, Sq, H + 2 * Hkv, D), device=q.device, dtype=q.dtype)
             dq, dk, dv = packed[:, :, :H], packed[:, :, H:H + Hkv], packed[:, :, H + Hkv:]
         else:
-            dq = torch.empty((B, Sq, H, D), device=q.device, dtype=q.dtype)
-            dk = torch.empty((B, Sk, Hkv, D), device=q.device, dtype=q.dtype)
-            dv = torch.empty((B, Sk, Hkv, D), device=q.device, dtype=q.dtype)
+            # one allocation with a common (batch, seq, head) stride triple for the three gradients
+            Sm = max(Sq, Sk)
+            packed = torch.empty((B, Sm, H + 2 * Hkv, D), device=q.device, dtype=q.dtype)
+            dq, dk, dv = packed[:, :Sq, :H], packed[:, :Sk, H:H + Hkv], packed[:, :Sk, H + Hkv:]
+        scratch = torch.empty(lib().tsb_flash_bwd_scratch_bytes(B, Sq, H, D), device=q.device, dtype=torch.uint8)
+        if dk.stride() != dq.stride():
+            raise RuntimeError("flash_attention backward: dq/dk/dv must share batch/seq/head strides")
         check(lib().tsb_flash_bwd(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                                  lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), None,
+                                  lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(),
                                   B, Sq, Sk, H, Hkv, D,
                                   q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
                                   v.stride(0), v.stride(1), v.stride(2), dq.stride(0), dq.stride(1), dq.stride(2),
                                   ctx.scale, int(ctx.causal), stream_ptr(q.device)), "tsb_flash_bwd")
+        _native.add_launches(3)
         return dq, dk, dv, None, None
+
+
+class _FlashPackedFn(torch.autograd.Function):
+    """Self-attention over a packed projection output qkv [B, S, H + 2 Hkv, D]; the gradient comes back in
+    the same packed layout, ready for the QKV GEMM's backward (no slicing / concatenation passes)."""
+
+    @staticmethod
+    def forward(ctx, qkv, H, Hkv, causal, scale):
+        q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+        B, S, _, D = qkv.shape
+        o = torch.empty((B, S, H, D), device=qkv.device, dtype=qkv.dtype)
+        lse = torch.empty((B, H, S), device=qkv.device, dtype=torch.float32)
+        check(lib().tsb_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                  B, S, S, H, Hkv, D,
+                                  q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                  v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
+                                  scale, int(causal), stream_ptr(qkv.device)), "tsb_flash_fwd")
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.args = (H, Hkv, causal, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse = ctx.saved_tensors
+        H, Hkv, causal, scale = ctx.args
+        B, S, _, D = qkv.shape
+        q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+        do = do.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[:, :, :H], dqkv[:, :, H:H + Hkv], dqkv[:, :, H + Hkv:]
+        scratch = torch.empty(lib().tsb_flash_bwd_scratch_bytes(B, S, H, D), device=qkv.device, dtype=torch.uint8)
+        check(lib().tsb_flash_bwd(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                  lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr(),
+                                  B, S, S, H, Hkv, D,
+                                  q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                  v.stride(0), v.stride(1), v.stride(2), dq.stride(0), dq.stride(1), dq.stride(2),
+                                  scale, int(causal), stream_ptr(qkv.device)), "tsb_flash_bwd")
+        _native.add_launches(3)
+        return dqkv, None, None, None, None
+
+
+def flash_attention_packed(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, causal: bool = True,
+                           scale: float | None = None) -> torch.Tensor:
+    """Self-attention on a packed [B, S, H + 2 Hkv, D] tensor (queries, then keys, then values along the
+    head axis) -> [B, S, H, D]."""
+    D = qkv.shape[-1]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    H, Hkv = num_heads, num_kv_heads
+    if (qkv.is_cuda and qkv.dtype == torch.bfloat16 and D in (64, 128) and qkv.is_contiguous()
+            and _native_flash_available()):
+        return _FlashPackedFn.apply(qkv, H, Hkv, bool(causal), float(scale))
+    return flash_attention(qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:], causal=causal, scale=scale)
 
 
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,

@@ -37,11 +37,11 @@ class _RMSNormFn(torch.autograd.Function):
         D = x.shape[-1]
         x2 = x.reshape(-1, D).contiguous()
         rows = x2.shape[0]
-        y = torch.empty_like(x2)
+        y = torch.empty(x.shape, device=x.device, dtype=x.dtype)
         rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
         if residual is not None:
             r2 = residual.reshape(-1, D).contiguous()
-            h = torch.empty_like(x2)
+            h = torch.empty(x.shape, device=x.device, dtype=x.dtype)
             check(lib().tsb_rmsnorm_fwd(x2.data_ptr(), r2.data_ptr(), weight.data_ptr(), y.data_ptr(), h.data_ptr(),
                                         rstd.data_ptr(), rows, D, eps, dtype_code(x.dtype), stream_ptr(x.device)),
                   "tsb_rmsnorm_fwd")
@@ -54,12 +54,13 @@ class _RMSNormFn(torch.autograd.Function):
         ctx.has_res = residual is not None
         ctx.wgrad_buf = wgrad_buf
         ctx.shape = x.shape
-        return y.view(x.shape), (h.view(x.shape) if residual is not None else None)
+        return y, (h if residual is not None else None)
 
     @staticmethod
     def backward(ctx, dy, dh):
         h, weight, rstd = ctx.saved_tensors
         D = h.shape[-1]
+        h = h.reshape(-1, D)
         rows = h.shape[0]
         if dy is None:
             dy = torch.zeros(ctx.shape, device=h.device, dtype=h.dtype)

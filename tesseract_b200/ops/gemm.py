@@ -67,12 +67,15 @@ class _LinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         if x2.stride(1) != 1 or x2.stride(0) % 8:
             x2 = x2.contiguous()
-        y = gemm_bf16(x2, w)
+        # allocate the result in its final shape: a view made inside a Function may not be modified in
+        # place downstream (RoPE rotates the packed QKV projection in place)
+        y = torch.empty(*x.shape[:-1], w.shape[0], device=x.device, dtype=torch.bfloat16)
+        gemm_bf16(x2, w, out=y.view(-1, w.shape[0]))
         ctx.save_for_backward(x2, w)
         ctx.wgrad_buf = wgrad_buf
         ctx.force_wgrad = force_wgrad
         ctx.x_shape = x.shape
-        return y.view(*x.shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -82,7 +85,8 @@ class _LinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gemm_bf16(dy2, w, b_mn=True).view(ctx.x_shape)           # dX = dY @ W
+            dx = torch.empty(ctx.x_shape, device=dy.device, dtype=torch.bfloat16)
+            gemm_bf16(dy2, w, b_mn=True, out=dx.view(-1, w.shape[1]))     # dX = dY @ W
         if ctx.needs_input_grad[1] or ctx.force_wgrad:
             buf = ctx.wgrad_buf
             if buf is not None:

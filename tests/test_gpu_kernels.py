@@ -244,3 +244,56 @@ def test_tiny_llama_train_step_matches_cpu(dev):
     for n, p in gpu.named_parameters():
         worst = max(worst, _rel_err(p.grad, gc[n].grad))
     assert worst < 8e-2, worst
+
+
+@pytest.mark.parametrize("B,H,Hkv,S,D", [(1, 2, 2, 128, 128), (2, 4, 2, 256, 128), (1, 4, 1, 384, 64),
+                                          (2, 8, 2, 1000, 128), (1, 2, 1, 77, 64)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_flash_attention_forward(dev, B, H, Hkv, S, D, causal):
+    from tesseract_b200 import ops
+    g = torch.Generator(device=dev).manual_seed(S + D)
+    qkv = torch.randn(B, S, H + 2 * Hkv, D, device=dev, generator=g).bfloat16()
+    q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+    o = ops.flash_attention(q, k, v, causal=causal)
+    torch.cuda.synchronize()
+    _status_ok()
+    ref = ops.attention_ref(q.transpose(1, 2).float(), k.transpose(1, 2).float(), v.transpose(1, 2).float(),
+                            causal=causal).transpose(1, 2)
+    assert _rel_err(o, ref) < 1.5e-2, _rel_err(o, ref)
+
+
+def test_flash_attention_rectangular_causal(dev):
+    """Chunked prefill: 128 new queries against 384 keys, last query sees every key."""
+    from tesseract_b200 import ops
+    q = torch.randn(1, 128, 4, 128, device=dev).bfloat16()
+    k = torch.randn(1, 384, 2, 128, device=dev).bfloat16()
+    v = torch.randn(1, 384, 2, 128, device=dev).bfloat16()
+    o = ops.flash_attention(q, k, v, causal=True)
+    ref = ops.attention_ref(q.transpose(1, 2).float(), k.transpose(1, 2).float(), v.transpose(1, 2).float(),
+                            causal=True).transpose(1, 2)
+    _status_ok()
+    assert _rel_err(o, ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("B,H,Hkv,S,D", [(1, 2, 2, 128, 128), (2, 4, 2, 256, 128), (1, 4, 1, 384, 64),
+                                          (1, 8, 2, 600, 128)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_flash_attention_backward(dev, B, H, Hkv, S, D, causal):
+    from tesseract_b200 import ops
+    g = torch.Generator(device=dev).manual_seed(S * 3 + D)
+    qkv = (torch.randn(B, S, H + 2 * Hkv, D, device=dev, generator=g)).bfloat16().requires_grad_()
+    o = ops.flash_attention_packed(qkv, H, Hkv, causal=causal)
+    do = torch.randn(o.shape, device=dev, generator=g).bfloat16()
+    o.backward(do)
+    torch.cuda.synchronize()
+    _status_ok()
+    ref_in = qkv.detach().float().requires_grad_()
+    q, k, v = ref_in[:, :, :H], ref_in[:, :, H:H + Hkv], ref_in[:, :, H + Hkv:]
+    ref = ops.attention_ref(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=causal).transpose(1, 2)
+    ref.backward(do.float())
+    assert _rel_err(o, ref) < 1.5e-2
+    gq, gk, gv = qkv.grad[:, :, :H], qkv.grad[:, :, H:H + Hkv], qkv.grad[:, :, H + Hkv:]
+    rq, rk, rv = ref_in.grad[:, :, :H], ref_in.grad[:, :, H:H + Hkv], ref_in.grad[:, :, H + Hkv:]
+    assert _rel_err(gv, rv) < 2e-2, ("dv", _rel_err(gv, rv))
+    assert _rel_err(gk, rk) < 2e-2, ("dk", _rel_err(gk, rk))
+    assert _rel_err(gq, rq) < 2e-2, ("dq", _rel_err(gq, rq))
