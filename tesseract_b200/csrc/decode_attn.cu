@@ -1,0 +1,477 @@
+// Decode-time attention over a paged KV pool (split-K, GQA-grouped, bf16/fp16 or INT8 KV) and the
+// fused RoPE + KV-append (+ INT8 quantisation) kernel that feeds it.
+//
+// Pool layout [num_blocks, Hkv, block_size, D] (+ fp32 scales [num_blocks, Hkv, block_size] for INT8),
+// block_tables int32 [A, max_logical], lens int32 [A]: the reference's layout (src/nn/PagedKVPool.cpp:27-29,
+// src/cuda/PagedAttention.cu:88-262). A contiguous cache [B, Hkv, max_len, D] is the special case
+// block_size = max_len with block table {b}.
+//
+// Differences from the reference kernels (one CTA per (request, query head), no split over keys):
+//   * one CTA per (split, KV head, request) serves all G = H / Hkv query heads of the group, so K and V
+//     are read from HBM once per KV head instead of once per query head;
+//   * the key range of a request is split across CTAs (flash-decoding) and merged by a second kernel, so
+//     a few long requests still fill 148 SMs;
+//   * 128-bit loads: 8 lanes cover one D = 128 row, 4 tokens per warp per step, two steps in flight.
+// The INT8 path dequantises in registers: s = (q . kq) * k_scale, o += p * v_scale * vq
+// (per-(token, head) symmetric scales, src/cuda/QuantizeKV.cu:51-72).
+#include "common.cuh"
+
+namespace tsb {
+namespace {
+
+constexpr int kDecThreads = 128;
+constexpr int kDecWarps = 4;
+
+template <typename T>
+__device__ __forceinline__ void cvt16(const uint4& a, const uint4& b, float (&f)[16]) {
+  const T* pa = reinterpret_cast<const T*>(&a);
+  const T* pb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    f[i] = to_f32<T>(pa[i]);
+    f[8 + i] = to_f32<T>(pb[i]);
+  }
+}
+__device__ __forceinline__ void cvt16_i8(const uint4& a, float (&f)[16]) {
+  const int8_t* p = reinterpret_cast<const int8_t*>(&a);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) f[i] = static_cast<float>(p[i]);
+}
+
+struct DecParams {
+  const void* q;        // [A, H, D]
+  const void* k_pool;   // [nb, Hkv, bs, D]
+  const void* v_pool;
+  const float* k_scale; // [nb, Hkv, bs] or null
+  const float* v_scale;
+  const int* tables;    // [A, max_logical]
+  const int* lens;      // [A]
+  void* out;            // [A, H, D]
+  float* part_o;        // [A, H, splits, D]
+  float* part_ml;       // [A, H, splits, 2]
+  int A, H, Hkv, bs, nb, max_logical, splits;
+  float scale_log2;
+};
+
+// EPL = elements per lane (D / 8): 16 for D = 128, 8 for D = 64. GH = query heads handled per CTA.
+template <typename T, bool INT8, int D, int GH>
+__global__ void __launch_bounds__(kDecThreads)
+paged_decode_kernel(DecParams p) {
+  constexpr int EPL = D / 8;
+  const int split = blockIdx.x;
+  const int hgrp = blockIdx.y;  // index over Hkv * (G / GH)
+  const int a = blockIdx.z;
+  const int G = p.H / p.Hkv;
+  const int sub = G / GH;
+  const int hk = hgrp / sub;
+  const int h0 = hk * G + (hgrp % sub) * GH;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane >> 3;   // token slot within the warp step (0..3)
+  const int gl = lane & 7;     // lane within the 8-lane group: covers elements [gl*EPL, gl*EPL+EPL)
+
+  const int len = p.lens[a];
+  const int chunk = ((len + p.splits - 1) / p.splits + 15) & ~15;
+  const int t_begin = split * chunk;
+  const int t_end = min(len, t_begin + chunk);
+
+  // q slices in registers (fp32), pre-scaled by softmax scale * log2(e)
+  float qf[GH][EPL];
+  {
+    const T* qbase = static_cast<const T*>(p.q) + (static_cast<long long>(a) * p.H + h0) * D + gl * EPL;
+#pragma unroll
+    for (int g = 0; g < GH; ++g) {
+#pragma unroll
+      for (int i = 0; i < EPL; i += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(qbase + g * D + i);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qf[g][i + j] = to_f32<T>(e[j]) * p.scale_log2;
+      }
+    }
+  }
+  float o[GH][EPL];
+  float m[GH], l[GH];
+#pragma unroll
+  for (int g = 0; g < GH; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) o[g][i] = 0.f;
+  }
+
+  const int* table = p.tables + static_cast<long long>(a) * p.max_logical;
+  const int esz = INT8 ? 1 : static_cast<int>(sizeof(T));
+  // each warp step covers 4 tokens; the 4 warps interleave steps
+  for (int t0 = t_begin + warp * 4; t0 < t_end; t0 += kDecWarps * 4) {
+    const int t = t0 + grp;
+    const bool valid = t < t_end;
+    float kf[EPL], vf[EPL];
+    float ks = 1.f, vs = 1.f;
+    if (valid) {
+      int blk = table[t / p.bs];
+      blk = (blk < 0 || blk >= p.nb) ? 0 : blk;  // defence in depth, as in the reference kernels
+      const long long row = (static_cast<long long>(blk) * p.Hkv + hk) * p.bs + (t % p.bs);
+      const char* kp = static_cast<const char*>(p.k_pool) + (row * D + gl * EPL) * esz;
+      const char* vp = static_cast<const char*>(p.v_pool) + (row * D + gl * EPL) * esz;
+      if constexpr (INT8) {
+        if constexpr (EPL == 16) {
+          const uint4 kr = *reinterpret_cast<const uint4*>(kp);
+          const uint4 vr = *reinterpret_cast<const uint4*>(vp);
+          cvt16_i8(kr, kf);
+          cvt16_i8(vr, vf);
+        } else {
+          const uint2 kr = *reinterpret_cast<const uint2*>(kp);
+          const uint2 vr = *reinterpret_cast<const uint2*>(vp);
+          const int8_t* k8 = reinterpret_cast<const int8_t*>(&kr);
+          const int8_t* v8 = reinterpret_cast<const int8_t*>(&vr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            kf[i] = static_cast<float>(k8[i]);
+            vf[i] = static_cast<float>(v8[i]);
+          }
+        }
+        ks = p.k_scale[row];
+        vs = p.v_scale[row];
+      } else {
+        if constexpr (EPL == 16) {
+          const uint4 k0 = *reinterpret_cast<const uint4*>(kp);
+          const uint4 k1 = *reinterpret_cast<const uint4*>(kp + 16);
+          const uint4 v0 = *reinterpret_cast<const uint4*>(vp);
+          const uint4 v1 = *reinterpret_cast<const uint4*>(vp + 16);
+          cvt16<T>(k0, k1, kf);
+          cvt16<T>(v0, v1, vf);
+        } else {
+          const uint4 k0 = *reinterpret_cast<const uint4*>(kp);
+          const uint4 v0 = *reinterpret_cast<const uint4*>(vp);
+          const T* ke = reinterpret_cast<const T*>(&k0);
+          const T* ve = reinterpret_cast<const T*>(&v0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            kf[i] = to_f32<T>(ke[i]);
+            vf[i] = to_f32<T>(ve[i]);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        kf[i] = 0.f;
+        vf[i] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < GH; ++g) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) s = fmaf(qf[g][i], kf[i], s);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s *= ks;
+      if (valid) {
+        if (s > m[g]) {
+          const float corr = exp2f(m[g] - s);  // 0 when m was -inf
+          l[g] *= corr;
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) o[g][i] *= corr;
+          m[g] = s;
+        }
+        const float pr = exp2f(s - m[g]);
+        l[g] += pr;
+        const float pv = pr * vs;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) o[g][i] = fmaf(pv, vf[i], o[g][i]);
+      }
+    }
+  }
+
+  // merge the 4 token groups of the warp (lanes with equal gl), then the 4 warps through shared memory
+#pragma unroll
+  for (int off = 8; off <= 16; off <<= 1) {
+#pragma unroll
+    for (int g = 0; g < GH; ++g) {
+      const float om = __shfl_xor_sync(0xffffffffu, m[g], off);
+      const float ol = __shfl_xor_sync(0xffffffffu, l[g], off);
+      const float nm = fmaxf(m[g], om);
+      const float c0 = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - nm);
+      const float c1 = (om == -INFINITY) ? 0.f : exp2f(om - nm);
+      l[g] = l[g] * c0 + ol * c1;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const float oo = __shfl_xor_sync(0xffffffffu, o[g][i], off);
+        o[g][i] = o[g][i] * c0 + oo * c1;
+      }
+      m[g] = nm;
+    }
+  }
+  __shared__ float sm_o[kDecWarps][GH][D];
+  __shared__ float sm_m[kDecWarps][GH];
+  __shared__ float sm_l[kDecWarps][GH];
+  if (grp == 0) {
+#pragma unroll
+    for (int g = 0; g < GH; ++g) {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) sm_o[warp][g][gl * EPL + i] = o[g][i];
+      if (gl == 0) {
+        sm_m[warp][g] = m[g];
+        sm_l[warp][g] = l[g];
+      }
+    }
+  }
+  __syncthreads();
+  // thread tid handles (g, d) pairs
+  for (int idx = threadIdx.x; idx < GH * D; idx += kDecThreads) {
+    const int g = idx / D, d = idx % D;
+    float nm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) nm = fmaxf(nm, sm_m[w][g]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float c = (sm_m[w][g] == -INFINITY) ? 0.f : exp2f(sm_m[w][g] - nm);
+      acc += sm_o[w][g][d] * c;
+      ll += sm_l[w][g] * c;
+    }
+    const int h = h0 + g;
+    if (p.splits == 1) {
+      const float inv = ll > 0.f ? 1.f / ll : 0.f;
+      static_cast<T*>(p.out)[(static_cast<long long>(a) * p.H + h) * D + d] = from_f32<T>(acc * inv);
+    } else {
+      const long long pi = (static_cast<long long>(a) * p.H + h) * p.splits + split;
+      p.part_o[pi * D + d] = acc;
+      if (d == 0) {
+        p.part_ml[pi * 2] = nm;
+        p.part_ml[pi * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(D)
+decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, T* __restrict__ out,
+                    int splits) {
+  const long long ah = blockIdx.x;  // a * H + h
+  const int d = threadIdx.x;
+  float nm = -INFINITY;
+  for (int s = 0; s < splits; ++s) nm = fmaxf(nm, part_ml[(ah * splits + s) * 2]);
+  float acc = 0.f, ll = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(ah * splits + s) * 2];
+    const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - nm);
+    acc += part_o[(ah * splits + s) * D + d] * c;
+    ll += part_ml[(ah * splits + s) * 2 + 1] * c;
+  }
+  out[ah * D + d] = from_f32<T>(ll > 0.f ? acc / ll : 0.f);
+}
+
+int choose_splits(int A, int Hkv_groups, int max_len) {
+  const int target = sm_count() * 3;
+  int s = (target + A * Hkv_groups - 1) / (A * Hkv_groups);
+  const int max_s = max_len / 128 > 0 ? max_len / 128 : 1;
+  if (s > max_s) s = max_s;
+  if (s > 64) s = 64;
+  if (s < 1) s = 1;
+  return s;
+}
+
+template <typename T, bool INT8, int D>
+int launch_decode(DecParams p, int G, cudaStream_t s) {
+  const int GH = G >= 4 ? 4 : G;  // G in {1, 2, 4, 8, 16, ...}: groups of at most 4 heads per CTA
+  if (G % GH) return -2;
+  dim3 grid(p.splits, p.Hkv * (G / GH), p.A);
+  switch (GH) {
+    case 4: paged_decode_kernel<T, INT8, D, 4><<<grid, kDecThreads, 0, s>>>(p); break;
+    case 2: paged_decode_kernel<T, INT8, D, 2><<<grid, kDecThreads, 0, s>>>(p); break;
+    case 1: paged_decode_kernel<T, INT8, D, 1><<<grid, kDecThreads, 0, s>>>(p); break;
+    default: return -2;
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (p.splits > 1) {
+    decode_merge_kernel<T, D><<<p.A * p.H, D, 0, s>>>(p.part_o, p.part_ml, static_cast<T*>(p.out), p.splits);
+    e = cudaGetLastError();
+  }
+  return static_cast<int>(e);
+}
+
+// ------------------------------------------------------------------ RoPE + KV append (+ INT8 quant)
+// One warp per (token, head) over the H + 2 Hkv heads of a packed projection row.
+//   query heads: rotated, written to q_out (or in place);
+//   key heads:   rotated, then stored to the pool slot of the token (quantised if the pool is INT8);
+//   value heads: stored to the pool.
+template <typename T, bool INT8, int D>
+__global__ void __launch_bounds__(256)
+kv_append_kernel(T* __restrict__ qkv, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                 const int* __restrict__ positions, const int* __restrict__ slots, void* __restrict__ k_pool,
+                 void* __restrict__ v_pool, float* __restrict__ k_scale, float* __restrict__ v_scale,
+                 T* __restrict__ q_out, int tokens, int H, int Hkv, int bs, int rotate) {
+  constexpr int EPL = D / 32;  // 4 (D=128) or 2 (D=64): an even count, so rotation pairs stay in-lane
+  const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int HT = H + 2 * Hkv;
+  if (wid >= static_cast<long long>(tokens) * HT) return;
+  const int head = static_cast<int>(wid % HT);
+  const int t = static_cast<int>(wid / HT);
+  T* src = qkv + (static_cast<long long>(t) * HT + head) * D + lane * EPL;
+  float x[EPL];
+  if constexpr (EPL == 4) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = to_f32<T>(e[i]);
+  } else {
+    const uint32_t raw = *reinterpret_cast<const uint32_t*>(src);
+    const T* e = reinterpret_cast<const T*>(&raw);
+    x[0] = to_f32<T>(e[0]);
+    x[1] = to_f32<T>(e[1]);
+  }
+  const bool is_q = head < H;
+  const bool is_k = !is_q && head < H + Hkv;
+  if (rotate && (is_q || is_k)) {
+    const int pos = positions[t];
+    const float* c = cos_t + static_cast<long long>(pos) * (D / 2) + lane * (EPL / 2);
+    const float* s = sin_t + static_cast<long long>(pos) * (D / 2) + lane * (EPL / 2);
+#pragma unroll
+    for (int i = 0; i < EPL; i += 2) {
+      const float a = x[i], b = x[i + 1], cc = c[i / 2], ss = s[i / 2];
+      x[i] = a * cc - b * ss;
+      x[i + 1] = a * ss + b * cc;
+    }
+  }
+  if (is_q) {
+    T* dst = (q_out ? q_out + (static_cast<long long>(t) * H + head) * D : qkv + (static_cast<long long>(t) * HT + head) * D) +
+             lane * EPL;
+    if constexpr (EPL == 4) {
+      uint2 o;
+      T* e = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) e[i] = from_f32<T>(x[i]);
+      *reinterpret_cast<uint2*>(dst) = o;
+    } else {
+      uint32_t o;
+      T* e = reinterpret_cast<T*>(&o);
+      e[0] = from_f32<T>(x[0]);
+      e[1] = from_f32<T>(x[1]);
+      *reinterpret_cast<uint32_t*>(dst) = o;
+    }
+    return;
+  }
+  const int slot = slots[t];
+  if (slot < 0) return;  // token without a cache slot (padding)
+  const int kvh = is_k ? head - H : head - H - Hkv;
+  const int blk = slot / bs, off = slot % bs;
+  const long long row = (static_cast<long long>(blk) * Hkv + kvh) * bs + off;
+  void* pool = is_k ? k_pool : v_pool;
+  if constexpr (INT8) {
+    // the model dtype round trip first: what is quantised is what a full-precision cache would hold
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      x[i] = to_f32<T>(from_f32<T>(x[i]));
+      amax = fmaxf(amax, fabsf(x[i]));
+    }
+    amax = warp_max(amax);
+    const float scale = amax > 0.f ? amax / 127.f : 1.f;
+    int8_t qv[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      float r = rintf(x[i] / scale);
+      r = fminf(127.f, fmaxf(-127.f, r));
+      qv[i] = static_cast<int8_t>(r);
+    }
+    int8_t* dst = static_cast<int8_t*>(pool) + row * D + lane * EPL;
+    if constexpr (EPL == 4) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<uint32_t*>(qv);
+    else *reinterpret_cast<uint16_t*>(dst) = *reinterpret_cast<uint16_t*>(qv);
+    if (lane == 0) (is_k ? k_scale : v_scale)[row] = scale;
+  } else {
+    T* dst = static_cast<T*>(pool) + row * D + lane * EPL;
+    if constexpr (EPL == 4) {
+      uint2 o;
+      T* e = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) e[i] = from_f32<T>(x[i]);
+      *reinterpret_cast<uint2*>(dst) = o;
+    } else {
+      uint32_t o;
+      T* e = reinterpret_cast<T*>(&o);
+      e[0] = from_f32<T>(x[0]);
+      e[1] = from_f32<T>(x[1]);
+      *reinterpret_cast<uint32_t*>(dst) = o;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace tsb
+
+// fp32 scratch elements tsb_paged_decode may use for A requests, H query heads, head_dim D and a
+// longest sequence of max_len tokens (split partials: A * H * splits * (D + 2)).
+TSB_EXPORT long long tsb_paged_decode_scratch_floats(int A, int H, int D, int max_len) {
+  const long long splits = 64;
+  (void)max_len;
+  return static_cast<long long>(A) * H * splits * (D + 2);
+}
+
+// out[a, h, :] = attention of query q[a, h, :] over the first lens[a] pooled tokens of request a.
+//   dtype: 1 = bf16, 2 = fp16 (q, out, and the pool unless k_scale != NULL, in which case the pool is INT8).
+//   max_len: upper bound of lens (sizes the key split); scratch: tsb_paged_decode_scratch_floats() floats.
+TSB_EXPORT int tsb_paged_decode(const void* q, const void* k_pool, const void* v_pool, const float* k_scale,
+                                const float* v_scale, const int* tables, const int* lens, void* out, float* scratch,
+                                int A, int H, int Hkv, int D, int bs, int nb, int max_logical, float scale,
+                                int max_len, int dtype, void* stream) {
+  using namespace tsb;
+  if (A <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || (D != 64 && D != 128) || bs <= 0) return -2;
+  const int G = H / Hkv;
+  const int GH = G >= 4 ? 4 : G;
+  DecParams p;
+  p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.tables = tables; p.lens = lens; p.out = out;
+  p.A = A; p.H = H; p.Hkv = Hkv; p.bs = bs; p.nb = nb; p.max_logical = max_logical;
+  p.splits = choose_splits(A, Hkv * (G / GH), max_len);
+  p.part_o = scratch;
+  p.part_ml = scratch + static_cast<long long>(A) * H * p.splits * D;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool i8 = k_scale != nullptr;
+  if (dtype == 1) {
+    if (D == 128) return i8 ? launch_decode<__nv_bfloat16, true, 128>(p, G, s) : launch_decode<__nv_bfloat16, false, 128>(p, G, s);
+    return i8 ? launch_decode<__nv_bfloat16, true, 64>(p, G, s) : launch_decode<__nv_bfloat16, false, 64>(p, G, s);
+  }
+  if (dtype == 2) {
+    if (D == 128) return i8 ? launch_decode<__half, true, 128>(p, G, s) : launch_decode<__half, false, 128>(p, G, s);
+    return i8 ? launch_decode<__half, true, 64>(p, G, s) : launch_decode<__half, false, 64>(p, G, s);
+  }
+  return -2;
+}
+
+// Rotate (adjacent-pair RoPE at positions[t]) the query and key heads of packed qkv [tokens, (H + 2 Hkv) * D],
+// write queries to q_out [tokens, H, D] (in place when NULL) and scatter keys / values into the pool at
+// slots[t] = block * block_size + offset (negative = skip). With k_scale != NULL the pool is INT8 and
+// the per-(token, head) scales are written too. rotate = 0 skips RoPE.
+TSB_EXPORT int tsb_kv_append_paged(void* qkv, const float* cos_t, const float* sin_t, const int* positions,
+                                   const int* slots, void* k_pool, void* v_pool, float* k_scale, float* v_scale,
+                                   void* q_out, int tokens, int H, int Hkv, int D, int bs, int dtype, int rotate,
+                                   void* stream) {
+  using namespace tsb;
+  if (tokens <= 0 || (D != 64 && D != 128) || bs <= 0) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long warps = static_cast<long long>(tokens) * (H + 2 * Hkv);
+  const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
+  const bool i8 = k_scale != nullptr;
+#define TSB_KVA(TT, I8, DD)                                                                                      \
+  kv_append_kernel<TT, I8, DD><<<blocks, 256, 0, s>>>(static_cast<TT*>(qkv), cos_t, sin_t, positions, slots, k_pool, \
+                                                      v_pool, k_scale, v_scale, static_cast<TT*>(q_out), tokens, H, \
+                                                      Hkv, bs, rotate)
+  if (dtype == 1) {
+    if (D == 128) { if (i8) TSB_KVA(__nv_bfloat16, true, 128); else TSB_KVA(__nv_bfloat16, false, 128); }
+    else { if (i8) TSB_KVA(__nv_bfloat16, true, 64); else TSB_KVA(__nv_bfloat16, false, 64); }
+  } else if (dtype == 2) {
+    if (D == 128) { if (i8) TSB_KVA(__half, true, 128); else TSB_KVA(__half, false, 128); }
+    else { if (i8) TSB_KVA(__half, true, 64); else TSB_KVA(__half, false, 64); }
+  } else {
+    return -2;
+  }
+#undef TSB_KVA
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,3 +1,5 @@
-from .llama import LlamaConfig, LlamaModel, llama_local_to_hf_name
+from .llama import GenerateConfig, LlamaConfig, LlamaModel, llama_local_to_hf_name
+from .sampler import MT19937_64, Sampler, SamplingParams, sample_from_logits
 
-__all__ = ["LlamaConfig", "LlamaModel", "llama_local_to_hf_name"]
+__all__ = ["GenerateConfig", "LlamaConfig", "LlamaModel", "llama_local_to_hf_name", "MT19937_64", "Sampler",
+           "SamplingParams", "sample_from_logits"]

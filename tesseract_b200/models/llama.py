@@ -161,6 +161,30 @@ class _FusedLMHeadCE(torch.autograd.Function):
         return dh * g.to(dh.dtype), dw, None, None, None, None, None
 
 
+@dataclass
+class GenerateConfig:
+    """include/tesseract/models/Llama.hpp `GenerateConfig`."""
+
+    max_new_tokens: int = 32
+    eos_token_id: int = -1
+    do_sample: bool = False
+    sampling: "SamplingParams" = None
+    seed: int = 0
+    kv_int8: bool = False
+
+    def __post_init__(self):
+        if self.sampling is None:
+            from .sampler import SamplingParams
+            self.sampling = SamplingParams()
+
+
+def pick_next_token(logits_row: torch.Tensor, sampler, history) -> int:
+    """Greedy argmax (lowest index on ties) or a draw from ``sampler`` on the host copy of one logits row."""
+    if sampler is None:
+        return int(torch.argmax(logits_row.float()).item())
+    return sampler.sample(logits_row.float().cpu().numpy(), history)
+
+
 class LlamaModel(Module):
     def __init__(self, config: LlamaConfig, device=None, init_std: Optional[float] = None, seed: int = 0):
         super().__init__()
@@ -234,6 +258,123 @@ class LlamaModel(Module):
         w = self.lm_head.weight
         return _FusedLMHeadCE.apply(h2, w, targets.reshape(-1), _main_grad(w), chunk_rows, float(loss_scale),
                                     int(total_rows))
+
+    # ------------------------------------------------------------------ incremental decode
+    def _device(self):
+        return self.embed_tokens.weight.device
+
+    @torch.no_grad()
+    def forward_step(self, tokens: torch.Tensor, caches: list) -> torch.Tensor:
+        """tokens [B, S_new] (int64) through one cache per layer -> logits [B, S_new, V]. Inference only
+        (src/models/Llama.cpp:352-375)."""
+        if len(caches) != len(self.layers):
+            raise ValueError(f"forward_step needs {len(self.layers)} caches, got {len(caches)}")
+        x = self.embed_tokens(tokens)
+        for blk, cache in zip(self.layers, caches):
+            x = blk.forward_step(x, cache)
+        return self.lm_head(self.norm(x))
+
+    @torch.no_grad()
+    def forward_step_batched(self, tokens: torch.Tensor, caches: list) -> torch.Tensor:
+        """tokens [A, S_new]; ``caches[sequence][layer]`` -- A independent sequences, each with its own
+        per-layer (batch 1) caches at its own length (src/models/Llama.cpp:377-415)."""
+        A = tokens.shape[0]
+        if len(caches) != A or any(len(c) != len(self.layers) for c in caches):
+            raise ValueError("forward_step_batched: caches must be indexed [sequence][layer]")
+        x = self.embed_tokens(tokens)
+        for li, blk in enumerate(self.layers):
+            x = blk.forward_step_batched(x, [caches[a][li] for a in range(A)])
+        return self.lm_head(self.norm(x))
+
+    # cache factories (src/models/Llama.cpp:417-475)
+    def make_kv_caches(self, batch: int, max_len: int) -> list:
+        from ..nn.kv_cache import KVCache
+        c = self.config
+        return [KVCache(batch, c.kv_heads(), max_len, c.head_dim, c.dtype, self._device()) for _ in self.layers]
+
+    def make_quantized_kv_caches(self, batch: int, max_len: int) -> list:
+        from ..nn.kv_cache import QuantizedKVCache
+        c = self.config
+        return [QuantizedKVCache(batch, c.kv_heads(), max_len, c.head_dim, c.dtype, self._device()) for _ in self.layers]
+
+    def make_layer_pools(self, num_blocks: int, block_size: int) -> list:
+        from ..nn.kv_cache import PagedKVPool
+        c = self.config
+        return [PagedKVPool(num_blocks, c.kv_heads(), block_size, c.head_dim, c.dtype, self._device()) for _ in self.layers]
+
+    def make_paged_kv_caches(self, pools: list, max_len: int) -> list:
+        from ..nn.kv_cache import PagedKVCache
+        return [PagedKVCache(p, max_len) for p in pools]
+
+    def make_quantized_layer_pools(self, num_blocks: int, block_size: int) -> list:
+        from ..nn.kv_cache import QuantizedPagedKVPool
+        c = self.config
+        return [QuantizedPagedKVPool(num_blocks, c.kv_heads(), block_size, c.head_dim, c.dtype, self._device())
+                for _ in self.layers]
+
+    def make_quantized_paged_kv_caches(self, pools: list, max_len: int) -> list:
+        from ..nn.kv_cache import QuantizedPagedKVCache
+        return [QuantizedPagedKVCache(p, max_len) for p in pools]
+
+    # ------------------------------------------------------------------ generation
+    @torch.no_grad()
+    def generate(self, prompt_ids, cfg: Optional["GenerateConfig"] = None) -> list:
+        """Prefill ``prompt_ids`` then decode token by token until ``max_new_tokens`` or EOS (appended, then
+        stop). Returns prompt + generated ids (src/models/Llama.cpp:513-575)."""
+        from .sampler import Sampler
+        cfg = cfg or GenerateConfig()
+        prompt = [int(t) for t in prompt_ids]
+        if not prompt:
+            raise ValueError("generate: empty prompt")
+        V = self.config.vocab_size
+        if any(t < 0 or t >= V for t in prompt):
+            raise ValueError("generate: prompt id outside [0, vocab_size)")
+        if cfg.max_new_tokens < 0:
+            raise ValueError("generate: max_new_tokens must be >= 0")
+        total = len(prompt) + cfg.max_new_tokens
+        if total > self.config.max_position_embeddings:
+            raise ValueError("generate: prompt + max_new_tokens exceeds max_position_embeddings")
+        caches = (self.make_quantized_kv_caches(1, total) if cfg.kv_int8 else self.make_kv_caches(1, total))
+        sampler = Sampler(cfg.sampling, cfg.seed) if cfg.do_sample else None
+        out = list(prompt)
+        if cfg.max_new_tokens == 0:
+            return out
+        dev = self._device()
+        logits = self.forward_step(torch.tensor([prompt], dtype=torch.int64, device=dev), caches)
+        for step in range(cfg.max_new_tokens):
+            nxt = pick_next_token(logits[0, -1], sampler, out)
+            out.append(nxt)
+            if cfg.eos_token_id >= 0 and nxt == cfg.eos_token_id:
+                break
+            if step + 1 < cfg.max_new_tokens:
+                logits = self.forward_step(torch.tensor([[nxt]], dtype=torch.int64, device=dev), caches)
+        return out
+
+    def quantize_(self, scheme) -> None:
+        """Weight-only quantisation of every attention / FFN projection and of lm_head; embedding and norm
+        weights stay in floating point (include/tesseract/models/Llama.hpp `quantize_`)."""
+        from ..quant import quantize_linear
+        for blk in self.layers:
+            blk.attn.quantize_(scheme)
+            if hasattr(blk.ffn, "quantize_"):
+                blk.ffn.quantize_(scheme)
+        self.replace_module("lm_head", quantize_linear(self.lm_head, scheme))
+
+    def load_safetensors(self, path: str) -> list:
+        """Load a Hugging Face-format safetensors file in place; returns the unmatched keys."""
+        from ..io.safetensors import SafeTensors
+        st = SafeTensors.open(path)
+        return self.load_hf_state_dict({k: st.load(k) for k in st.keys()})
+
+    @staticmethod
+    def from_pretrained(path: str, config: LlamaConfig, device=None) -> "LlamaModel":
+        m = LlamaModel(config, device=device)
+        m.load_safetensors(path)
+        return m
+
+    def save_safetensors(self, path: str, metadata: Optional[dict] = None) -> None:
+        from ..io.safetensors import save_file
+        save_file({k: v.cpu() for k, v in self.hf_state_dict().items()}, path, metadata or {"format": "pt"})
 
     # ------------------------------------------------------------------ weights by HF name
     def hf_state_dict(self) -> dict:

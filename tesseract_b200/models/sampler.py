@@ -1,0 +1,132 @@
+"""Host sampler: repetition penalty -> temperature -> top-k -> top-p -> multinomial draw.
+
+Order and tie rules are the reference's (src/models/Sampler.cpp:29-116): the penalty is applied once per
+occurrence in ``prev_tokens`` (x > 0 ? x / pen : x * pen); temperature <= 1e-6 means argmax (lowest index
+on ties) and bypasses top-k / top-p; top-k keeps ties at the k-th value; top-p keeps the smallest prefix
+(by descending logit) whose cumulative mass reaches p and always the first token; the draw walks the
+survivors in index order against ``u * denom`` with ``u`` from ``uniform_real_distribution<double>`` on a
+``mt19937_64`` seeded with ``seed``. The generator is re-implemented here (and natively in the host
+runtime) so that seeded sequences are reproducible bit for bit; greedy decoding never touches it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0         # <= 0 => greedy
+    top_k: int = 0                   # 0 => disabled
+    top_p: float = 1.0               # 1.0 => disabled
+    repetition_penalty: float = 1.0  # 1.0 => disabled
+
+
+class MT19937_64:
+    """std::mt19937_64 (Matsumoto & Nishimura, 64-bit variant)."""
+
+    NN, MM = 312, 156
+    MATRIX_A = 0xB5026F5AA96619E9
+    UM, LM = 0xFFFFFFFF80000000, 0x7FFFFFFF
+    MASK = 0xFFFFFFFFFFFFFFFF
+
+    def __init__(self, seed: int = 5489):
+        self.seed(seed)
+
+    def seed(self, seed: int) -> None:
+        mt = [0] * self.NN
+        mt[0] = seed & self.MASK
+        for i in range(1, self.NN):
+            mt[i] = (6364136223846793005 * (mt[i - 1] ^ (mt[i - 1] >> 62)) + i) & self.MASK
+        self.mt, self.idx = mt, self.NN
+
+    def _twist(self) -> None:
+        mt, NN, MM = self.mt, self.NN, self.MM
+        for i in range(NN):
+            x = (mt[i] & self.UM) | (mt[(i + 1) % NN] & self.LM)
+            mt[i] = mt[(i + MM) % NN] ^ (x >> 1) ^ (self.MATRIX_A if x & 1 else 0)
+        self.idx = 0
+
+    def next_u64(self) -> int:
+        if self.idx >= self.NN:
+            self._twist()
+        x = self.mt[self.idx]
+        self.idx += 1
+        x ^= (x >> 29) & 0x5555555555555555
+        x ^= (x << 17) & 0x71D67FFFEDA60000
+        x ^= (x << 37) & 0xFFF7EEE000000000
+        x ^= x >> 43
+        return x & self.MASK
+
+    def uniform_double(self) -> float:
+        """libstdc++ ``uniform_real_distribution<double>(0, 1)``: one 64-bit draw scaled by 2^-64, clamped
+        below 1."""
+        r = float(self.next_u64()) / 18446744073709551616.0
+        if r >= 1.0:
+            r = float(np.nextafter(1.0, 0.0))
+        return r
+
+
+def argmax_lowest_index(x: np.ndarray) -> int:
+    return int(np.argmax(x))  # numpy returns the first maximal index
+
+
+def sample_from_logits(logits: np.ndarray, params: SamplingParams, prev_tokens: Sequence[int],
+                       rng: MT19937_64) -> int:
+    work = np.array(logits, dtype=np.float32, copy=True).reshape(-1)
+    V = work.shape[0]
+    if V == 0:
+        raise ValueError("sample_from_logits: empty logits")
+    if params.repetition_penalty != 1.0 and len(prev_tokens):
+        pen = np.float32(params.repetition_penalty)
+        for t in prev_tokens:
+            if 0 <= t < V:
+                work[t] = work[t] / pen if work[t] > 0 else work[t] * pen
+    if params.temperature <= 1e-6:
+        return argmax_lowest_index(work)
+    work *= np.float32(1.0 / params.temperature)
+    ninf = np.float32(-np.inf)
+    if 0 < params.top_k < V:
+        kth = np.partition(work, V - params.top_k)[V - params.top_k]
+        work[work < kth] = ninf
+    if params.top_p < 1.0:
+        order = np.argsort(-work, kind="stable")
+        sw = work[order]
+        finite = sw != ninf
+        maxv = sw.max()
+        e = np.where(finite, np.exp((sw - maxv).astype(np.float64)), 0.0)
+        denom = float(np.cumsum(e)[-1])
+        cum = np.cumsum(e / denom)
+        hit = np.nonzero(finite & (cum >= params.top_p))[0]
+        if hit.size:
+            cut = int(hit[0]) + 1
+            drop = order[cut:]
+            work[drop] = ninf
+    maxv = work.max()
+    finite = work != ninf
+    e = np.where(finite, np.exp((work - maxv).astype(np.float64)), 0.0)
+    denom = float(np.cumsum(e)[-1])
+    if not denom > 0.0:
+        raise RuntimeError("sample_from_logits: degenerate distribution")
+    r = rng.uniform_double() * denom
+    rem = np.subtract.accumulate(np.concatenate(([r], e)))[1:]
+    hit = np.nonzero(finite & (rem <= 0.0))[0]
+    if hit.size:
+        return int(hit[0])
+    return argmax_lowest_index(work)
+
+
+class Sampler:
+    """Owns the RNG of one request (src/models/Sampler.hpp `Sampler`)."""
+
+    def __init__(self, params: Optional[SamplingParams] = None, seed: int = 0):
+        self.params = params or SamplingParams()
+        self.rng = MT19937_64(seed)
+
+    def sample(self, logits, prev_tokens: Sequence[int] = ()) -> int:
+        return sample_from_logits(np.asarray(logits, dtype=np.float32), self.params, prev_tokens, self.rng)
+
+    def reseed(self, seed: int) -> None:
+        self.rng.seed(seed)

@@ -240,7 +240,10 @@ class MultiHeadAttention(Module):
             object.__setattr__(self, "rope", rope)
 
     def qkv(self, x2: torch.Tensor) -> torch.Tensor:
-        return _FusedProj.run(x2, [self.q_proj, self.k_proj, self.v_proj])
+        projs = [self.q_proj, self.k_proj, self.v_proj]
+        if all(isinstance(p, Linear) for p in projs):
+            return _FusedProj.run(x2, projs)
+        return torch.cat([p(x2) for p in projs], dim=-1)   # quantised projections
 
     def forward(self, x: torch.Tensor, pos: int = 0) -> torch.Tensor:
         B, S, Dm = x.shape
@@ -251,6 +254,85 @@ class MultiHeadAttention(Module):
         qkv = qkv.view(B, S, H + 2 * Hkv, D)
         o = ops.flash_attention_packed(qkv, H, Hkv, causal=self.causal)
         return self.o_proj(o.reshape(B, S, H * D))
+
+
+    # ------------------------------------------------------------------ incremental decode
+    def _project_step(self, x: torch.Tensor, positions: torch.Tensor):
+        """x [T, Dm], positions [T] -> rotated q [T, H, D], rotated k [T, Hkv, D], v [T, Hkv, D]."""
+        H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = self.qkv(x)
+        qkv = ops.rope_qkv(qkv, self.rope.cos, self.rope.sin, num_heads=H, num_kv_heads=Hkv, head_dim=D,
+                           seq_len=1, positions=positions)
+        qkv = qkv.view(-1, H + 2 * Hkv, D)
+        return qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
+
+    @torch.no_grad()
+    def forward_step(self, x: torch.Tensor, cache) -> torch.Tensor:
+        """x [B, S_new, Dm]: project, rotate at positions cache.current_len() .., append K/V to ``cache`` and
+        attend over the whole prefix (src/nn/MultiHeadAttention.cpp:234-363). S_new == 1 is decode,
+        S_new > 1 on an empty cache is prefill, anything else is chunked prefill (last query sees all keys)."""
+        B, Sn, Dm = x.shape
+        H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        pos = cache.current_len()
+        if pos + Sn > self.rope.max_seq_len:
+            raise ValueError("forward_step: position beyond the rotary table")
+        positions = (pos + torch.arange(Sn, device=x.device)).repeat(B)
+        q, k, v = self._project_step(x.reshape(B * Sn, Dm), positions)
+        q = q.reshape(B, Sn, H, D)
+        k = k.reshape(B, Sn, Hkv, D).transpose(1, 2)
+        v = v.reshape(B, Sn, Hkv, D).transpose(1, 2)
+        cache.append(k.contiguous(), v.contiguous())
+        keys, vals = cache.keys_view(), cache.values_view()          # [B, Hkv, L, D]
+        o = ops.flash_attention(q, keys.transpose(1, 2), vals.transpose(1, 2), causal=Sn > 1)
+        return self.o_proj(o.reshape(B, Sn, H * D))
+
+    @torch.no_grad()
+    def forward_step_batched(self, x: torch.Tensor, caches: list) -> torch.Tensor:
+        """x [A, S_new, Dm] with one (batch-1) cache per sequence, each possibly at a different length.
+        Projections run once over all A * S_new rows; attention threads every sequence through its own
+        cache, or runs as ONE ragged kernel when all caches are paged views of the same pool
+        (src/nn/MultiHeadAttention.cpp:365-649)."""
+        from .kv_cache import PagedKVCache
+        A, Sn, Dm = x.shape
+        H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        if len(caches) != A:
+            raise ValueError("forward_step_batched: one cache per sequence is required")
+        starts = [c.current_len() for c in caches]
+        positions = torch.cat([s + torch.arange(Sn) for s in starts]).to(x.device)
+        q, k, v = self._project_step(x.reshape(A * Sn, Dm), positions)
+        q = q.reshape(A, Sn, H, D)
+        k = k.reshape(A, Sn, Hkv, D).transpose(1, 2)
+        v = v.reshape(A, Sn, Hkv, D).transpose(1, 2)
+        for a, c in enumerate(caches):
+            c.append(k[a:a + 1].contiguous(), v[a:a + 1].contiguous())
+        same_pool = all(isinstance(c, PagedKVCache) for c in caches) and len({id(c.pool) for c in caches}) == 1
+        if same_pool:
+            pool = caches[0].pool
+            max_blocks = max(len(c.block_table) for c in caches)
+            tables = torch.zeros((A, max_blocks), dtype=torch.int32)
+            for a, c in enumerate(caches):
+                tables[a, :len(c.block_table)] = torch.tensor(c.block_table, dtype=torch.int32)
+            tables = tables.to(x.device)
+            lens = torch.tensor([c.current_len() for c in caches], dtype=torch.int32, device=x.device)
+            ks = getattr(pool, "k_scale", None)
+            vs = getattr(pool, "v_scale", None)
+            if Sn == 1:
+                o = ops.paged_decode_attention(q[:, 0].contiguous(), pool.k, pool.v, tables, lens, None, ks, vs).unsqueeze(1)
+            else:
+                o = ops.paged_prefill_attention(q, pool.k, pool.v, tables, lens, None, ks, vs)
+        else:
+            outs = []
+            for a, c in enumerate(caches):
+                keys, vals = c.keys_view(), c.values_view()
+                outs.append(ops.flash_attention(q[a:a + 1], keys.transpose(1, 2), vals.transpose(1, 2), causal=Sn > 1))
+            o = torch.cat(outs, dim=0)
+        return self.o_proj(o.reshape(A, Sn, H * D))
+
+    def quantize_(self, scheme) -> None:
+        """Swap the four projections for their weight-only quantised variants (src/nn/MultiHeadAttention.cpp:651-673)."""
+        from ..quant import quantize_linear
+        for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            self.replace_module(name, quantize_linear(getattr(self, name), scheme))
 
 
 class FeedForward(Module):
@@ -265,8 +347,17 @@ class FeedForward(Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
-        gu = _FusedProj.run(x.reshape(-1, shape[-1]), [self.gate_proj, self.up_proj])
+        x2 = x.reshape(-1, shape[-1])
+        if isinstance(self.gate_proj, Linear) and isinstance(self.up_proj, Linear):
+            gu = _FusedProj.run(x2, [self.gate_proj, self.up_proj])
+        else:
+            gu = torch.cat([self.gate_proj(x2), self.up_proj(x2)], dim=-1)
         return self.down_proj(ops.swiglu(gu)).view(shape)
+
+    def quantize_(self, scheme) -> None:
+        from ..quant import quantize_linear
+        for name in ("gate_proj", "up_proj", "down_proj"):
+            self.replace_module(name, quantize_linear(getattr(self, name), scheme))
 
 
 class TransformerBlock(Module):
@@ -298,3 +389,13 @@ class TransformerBlock(Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         out, res = self.forward_fused(x, None)
         return out + res
+
+    @torch.no_grad()
+    def forward_step(self, x: torch.Tensor, cache) -> torch.Tensor:
+        h = x + self.attn.forward_step(self.norm_1(x), cache)
+        return h + self.ffn(self.norm_2(h))
+
+    @torch.no_grad()
+    def forward_step_batched(self, x: torch.Tensor, caches: list) -> torch.Tensor:
+        h = x + self.attn.forward_step_batched(self.norm_1(x), caches)
+        return h + self.ffn(self.norm_2(h))
