@@ -262,17 +262,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_arrive(&dq_read);
     }
     // ---------------------------------------------------------------- dK, dV out
+    // tcgen05.ld is warp-collective (.sync.aligned): every lane of the warp issues it, and only the global
+    // stores are predicated on the row being inside the sequence.
     const int kr = c0 + row;
-    if (ok && kr < p.Sk) {
-      __nv_bfloat16* dk_row = p.dk + b * p.dk_sb + static_cast<long long>(kr) * p.dk_ss + hk * p.dk_sh;
-      __nv_bfloat16* dv_row = p.dv + b * p.dv_sb + static_cast<long long>(kr) * p.dv_ss + hk * p.dv_sh;
-      if (n_iter > 0) {
-        // the last dq_full wait above covered every MMA issued before it, including the dK / dV updates
+    const bool in_range = kr < p.Sk;
+    const bool warp_ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+    __nv_bfloat16* dk_row = p.dk + b * p.dk_sb + static_cast<long long>(in_range ? kr : 0) * p.dk_ss + hk * p.dk_sh;
+    __nv_bfloat16* dv_row = p.dv + b * p.dv_sb + static_cast<long long>(in_range ? kr : 0) * p.dv_ss + hk * p.dv_sh;
+    if (warp_ok && n_iter > 0) {
+      // the last dq_full wait above covered every MMA issued before it, including the dK / dV updates
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + lane_addr + Cfg::kColDK + c * 32, r);
-          tmem_ld_wait();
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + lane_addr + Cfg::kColDK + c * 32, r);
+        tmem_ld_wait();
+        if (in_range) {
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
             uint4 v;
@@ -282,8 +286,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             v.w = pack_bf16x2(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
             *reinterpret_cast<uint4*>(dk_row + c * 32 + e) = v;
           }
-          tmem_ld_32x32(tmem_base + lane_addr + Cfg::kColDV + c * 32, r);
-          tmem_ld_wait();
+        }
+        tmem_ld_32x32(tmem_base + lane_addr + Cfg::kColDV + c * 32, r);
+        tmem_ld_wait();
+        if (in_range) {
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
             uint4 v;
@@ -294,13 +300,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             *reinterpret_cast<uint4*>(dv_row + c * 32 + e) = v;
           }
         }
-      } else {
-        const uint4 z = make_uint4(0, 0, 0, 0);
+      }
+    } else if (warp_ok && in_range) {
+      const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
-          *reinterpret_cast<uint4*>(dk_row + c * 8) = z;
-          *reinterpret_cast<uint4*>(dv_row + c * 8) = z;
-        }
+      for (int c = 0; c < D / 8; ++c) {
+        *reinterpret_cast<uint4*>(dk_row + c * 8) = z;
+        *reinterpret_cast<uint4*>(dv_row + c * 8) = z;
       }
     }
   }

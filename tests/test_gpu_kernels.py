@@ -297,3 +297,84 @@ def test_flash_attention_backward(dev, B, H, Hkv, S, D, causal):
     assert _rel_err(gv, rv) < 2e-2, ("dv", _rel_err(gv, rv))
     assert _rel_err(gk, rk) < 2e-2, ("dk", _rel_err(gk, rk))
     assert _rel_err(gq, rq) < 2e-2, ("dq", _rel_err(gq, rq))
+
+
+def _make_paged(dev, A, Hkv, D, bs, lens, dtype, int8):
+    from tesseract_b200.nn.kv_cache import quantize_kv_per_token
+    nb = sum((l + bs - 1) // bs for l in lens) + 3
+    perm = torch.randperm(nb)
+    k_pool = torch.zeros(nb, Hkv, bs, D, device=dev, dtype=dtype)
+    v_pool = torch.zeros_like(k_pool)
+    max_blocks = max((l + bs - 1) // bs for l in lens)
+    tables = torch.zeros(A, max_blocks, dtype=torch.int32)
+    nxt = 0
+    for a, l in enumerate(lens):
+        n = (l + bs - 1) // bs
+        tables[a, :n] = perm[nxt:nxt + n].to(torch.int32)
+        nxt += n
+        k = torch.randn(Hkv, n * bs, D, device=dev).to(dtype)
+        v = torch.randn(Hkv, n * bs, D, device=dev).to(dtype)
+        for i in range(n):
+            k_pool[tables[a, i]] = k[:, i * bs:(i + 1) * bs]
+            v_pool[tables[a, i]] = v[:, i * bs:(i + 1) * bs]
+    ks = vs = None
+    if int8:
+        k_pool, ks = quantize_kv_per_token(k_pool)
+        v_pool, vs = quantize_kv_per_token(v_pool)
+    return k_pool, v_pool, ks, vs, tables.to(dev), torch.tensor(lens, dtype=torch.int32, device=dev)
+
+
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("A,H,Hkv,D,bs,lens", [(3, 8, 2, 128, 16, [37, 500, 1]), (2, 4, 4, 64, 16, [100, 33]),
+                                                 (5, 4, 1, 128, 16, [2000, 17, 256, 1024, 999]),
+                                                 (1, 16, 2, 128, 32, [4096])])
+def test_paged_decode_attention(dev, A, H, Hkv, D, bs, lens, int8):
+    from tesseract_b200 import ops
+    k_pool, v_pool, ks, vs, tables, lens_t = _make_paged(dev, A, Hkv, D, bs, lens, torch.bfloat16, int8)
+    q = torch.randn(A, H, D, device=dev).bfloat16()
+    got = ops.paged_decode_attention(q, k_pool, v_pool, tables, lens_t, None, ks, vs)
+    torch.cuda.synchronize()
+    _status_ok()
+    ref = ops.paged_attention_ref(q.float().unsqueeze(1), k_pool, v_pool, tables, lens_t, None, ks, vs).squeeze(1)
+    assert (got.float() - ref).abs().max() < 3e-3 * max(1.0, ref.abs().max().item()) + 2e-2, (got.float() - ref).abs().max()
+
+
+@pytest.mark.parametrize("int8", [False, True])
+def test_kv_append_paged_rope_and_quant(dev, int8):
+    from tesseract_b200 import _native, ops
+    from tesseract_b200.nn.kv_cache import quantize_kv_per_token
+    T, H, Hkv, D, bs, nb = 37, 4, 2, 128, 16, 8
+    cos, sin = ops.rope_tables(256, D, 10000.0, dev)
+    qkv = torch.randn(T, (H + 2 * Hkv) * D, device=dev).bfloat16()
+    positions = torch.randint(0, 200, (T,), device=dev, dtype=torch.int32)
+    slots = torch.randperm(nb * bs, device=dev)[:T].to(torch.int32)
+    if int8:
+        k_pool = torch.zeros(nb, Hkv, bs, D, device=dev, dtype=torch.int8)
+        k_scale = torch.ones(nb, Hkv, bs, device=dev)
+        v_scale = torch.ones_like(k_scale)
+    else:
+        k_pool = torch.zeros(nb, Hkv, bs, D, device=dev, dtype=torch.bfloat16)
+        k_scale = v_scale = None
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty(T, H, D, device=dev, dtype=torch.bfloat16)
+    work = qkv.clone()
+    _native.check(_native.lib().tsb_kv_append_paged(
+        work.data_ptr(), cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), slots.data_ptr(), k_pool.data_ptr(),
+        v_pool.data_ptr(), k_scale.data_ptr() if int8 else None, v_scale.data_ptr() if int8 else None, q_out.data_ptr(),
+        T, H, Hkv, D, bs, 1, 1, _native.stream_ptr(dev)), "tsb_kv_append_paged")
+    torch.cuda.synchronize()
+    x = qkv.float().view(T, H + 2 * Hkv, D)
+    rot = ops.rope_ref(x[:, :H + Hkv], cos, sin, positions.long())
+    assert _rel_err(q_out, rot[:, :H]) < 1e-2
+    k_ref = rot[:, H:].bfloat16().float()
+    v_ref = x[:, H + Hkv:]
+    blk, off = (slots // bs).long(), (slots % bs).long()
+    if int8:
+        kq, ksr = quantize_kv_per_token(k_ref)
+        got_k = k_pool[blk, :, off].float() * k_scale[blk, :, off][..., None]
+        got_v = v_pool[blk, :, off].float() * v_scale[blk, :, off][..., None]
+        assert (got_k - k_ref).abs().max() <= ksr.max() * 1.01 + 1e-3
+        assert (got_v - v_ref).abs().max() <= v_scale.max() * 1.01 + 1e-3
+    else:
+        assert _rel_err(k_pool[blk, :, off], k_ref) < 1e-2
+        assert torch.equal(v_pool[blk, :, off], qkv.view(T, H + 2 * Hkv, D)[:, H + Hkv:])
