@@ -15,9 +15,15 @@
 // The INT8 path dequantises in registers: s = (q . kq) * k_scale, o += p * v_scale * vq
 // (per-(token, head) symmetric scales, src/cuda/QuantizeKV.cu:51-72).
 #include "common.cuh"
+#include "tsb_no_alloc.h"
+
+#include <mutex>
 
 namespace tsb {
 namespace {
+
+// Scratch of tsb_paged_decode_static: lives in the library image, one copy per GPU that loads it.
+static __device__ __align__(256) float g_static_decode_scratch[TSB_STATIC_DECODE_SCRATCH_FLOATS];
 
 constexpr int kDecThreads = 128;
 constexpr int kDecWarps = 4;
@@ -475,3 +481,41 @@ TSB_EXPORT int tsb_kv_append_paged(void* qkv, const float* cos_t, const float* s
 #undef TSB_KVA
   return static_cast<int>(cudaGetLastError());
 }
+
+// See tsb_no_alloc.h for the contract. The address of the file-scope array is looked up once per device
+// (with that device current) and cached; host code must never hand the symbol itself to a kernel.
+TSB_EXPORT int tsb_paged_decode_static(const void* q, const void* k_pool, const void* v_pool, const float* k_scale,
+                                       const float* v_scale, const int* tables, const int* lens, void* out, int A,
+                                       int H, int Hkv, int D, int bs, int nb, int max_logical, float scale,
+                                       int max_len, int dtype, void* stream) {
+  using namespace tsb;
+  static float* scratch_of_device[64] = {nullptr};
+  static std::mutex mu;
+  if (A <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || (D != 64 && D != 128) || bs <= 0) return -2;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return -2;
+  float* scratch = scratch_of_device[dev];
+  if (!scratch) {
+    std::lock_guard<std::mutex> lk(mu);
+    scratch = scratch_of_device[dev];
+    if (!scratch) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_decode_scratch);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      scratch = static_cast<float*>(p);
+      scratch_of_device[dev] = scratch;
+    }
+  }
+  const int G = H / Hkv;
+  const int GH = G >= 4 ? 4 : G;
+  const int splits = choose_splits(A, Hkv * (G / GH), max_len);
+  const long long need = splits > 1 ? static_cast<long long>(A) * H * splits * (D + 2) : 0;
+  if (need > TSB_STATIC_DECODE_SCRATCH_FLOATS) return TSB_ERR_STATIC_SCRATCH_TOO_SMALL;
+  // Same code path as tsb_paged_decode from here on: identical split count, identical kernels.
+  return tsb_paged_decode(q, k_pool, v_pool, k_scale, v_scale, tables, lens, out, scratch, A, H, Hkv, D, bs, nb,
+                          max_logical, scale, max_len, dtype, stream);
+}
+
+TSB_EXPORT long long tsb_paged_decode_static_capacity_floats() { return TSB_STATIC_DECODE_SCRATCH_FLOATS; }
