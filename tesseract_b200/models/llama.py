@@ -238,7 +238,13 @@ class LlamaModel(Module):
             raise ValueError("LlamaModel: sequence longer than max_position_embeddings")
         x = self.embed_tokens(tokens)
         res = None
-        for blk in self.layers:
+        red = getattr(self, "grad_reducer", None)
+        for li, blk in enumerate(self.layers):
+            if red is not None:
+                # fires (in backward) once this block's weight gradients are complete
+                x = red.mark(x, red.block_bucket0 + li)
+                if res is not None:
+                    res = red.mark(res, red.block_bucket0 + li)
             x, res = blk.forward_fused(x, res)
         if res is None:
             return self.norm(x)

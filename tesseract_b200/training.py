@@ -71,6 +71,9 @@ class Trainer:
                                    loss_scale=1.0 / n_micro)
             loss.backward()
             total += loss.detach()
+        if hasattr(self.model, "sync_replicated_grads"):
+            self.arena.fold_autograd_grads()
+            self.model.sync_replicated_grads()
         if self.grad_reducer is not None:
             self.grad_reducer.finish_step()
         elif self.dp_group is not None:

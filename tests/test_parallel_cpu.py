@@ -1,0 +1,183 @@
+"""Parallel layers without a cluster: the in-process simulation backend (TP=1 vs TP=2/3 parity, forward and
+backward) and real multi-process runs over gloo CPU ranks (TP+SP Llama vs dense, DP gradient reducer,
+rank-local collectives)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tesseract_b200.nn import Linear
+from tesseract_b200.parallel import ColumnParallelLinear, RowParallelLinear, SimCommBackend
+
+
+def test_column_parallel_matches_dense_exactly():
+    torch.manual_seed(0)
+    dense = Linear(12, 18, bias=True)
+    x = torch.randn(5, 12, requires_grad=True)
+    for world in (2, 3):
+        col = ColumnParallelLinear.from_dense(dense, SimCommBackend(world))
+        assert [n for n, _ in col.named_parameters()][:2] == ["shard.0.weight", "shard.0.bias"]
+        y = col(x)
+        assert torch.equal(y, dense(x))
+        g = torch.randn_like(y)
+        y.backward(g)
+        xg = x.grad.clone()
+        x.grad = None
+        dense.zero_grad()
+        dense(x).backward(g)
+        wg = torch.cat([p.grad for p in col.weight_shards])
+        assert torch.allclose(wg, dense.weight.grad, atol=0) and torch.allclose(xg, x.grad, atol=1e-6)
+        x.grad = None
+
+
+def test_row_parallel_and_megatron_mlp():
+    torch.manual_seed(1)
+    up, down = Linear(8, 24, bias=False), Linear(24, 8, bias=True)
+    x = torch.randn(4, 8, requires_grad=True)
+    ref = down(torch.relu(up(x)))
+    for world in (2, 3):
+        comm = SimCommBackend(world)
+        col = ColumnParallelLinear.from_dense(up, comm)
+        row = RowParallelLinear.from_dense(down, comm)
+        shards = [torch.relu(s) for s in col.forward_shards(x)]
+        y = row.forward_shards(shards)
+        assert (y - ref).abs().max() < 1e-5
+        y.sum().backward()
+        wg = torch.cat([p.grad for p in row.weight_shards], dim=1)
+        down.zero_grad(); up.zero_grad()
+        xg = x.grad.clone(); x.grad = None
+        down(torch.relu(up(x))).sum().backward()
+        assert (wg - down.weight.grad).abs().max() < 1e-5 and (row.bias.grad - down.bias.grad).abs().max() < 1e-5
+        assert (xg - x.grad).abs().max() < 1e-5
+        x.grad = None
+    with pytest.raises(ValueError):
+        RowParallelLinear(10, 4, SimCommBackend(3))
+    with pytest.raises(ValueError):
+        row.forward_shards([x])
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run_ranks(fn, world, *args):
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q) + args) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    bad = [r for r in results if r[1] is not None]
+    assert not bad, bad[0][1]
+    return {r[0]: r[2] for r in results}
+
+
+def _entry(fn, rank, world, port, q, *args):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(2)
+    try:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        out = fn(rank, world, *args)
+        dist.barrier()
+        q.put((rank, None, out))
+    except Exception:  # pragma: no cover - reported to the parent
+        import traceback
+        q.put((rank, traceback.format_exc(), None))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _tp_llama_worker(rank, world):
+    from tesseract_b200.models import LlamaConfig, LlamaModel
+    from tesseract_b200.parallel.tp_layers import TPContext
+    from tesseract_b200.parallel.tp_model import TPLlamaModel
+    from tesseract_b200.optim import ParamArena
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                      num_key_value_heads=2, intermediate_size=688, max_position_embeddings=128, rope_theta=10000.0)
+    dense = LlamaModel(cfg, init_std=0.02, seed=7)
+    g = torch.Generator().manual_seed(3)
+    tok = torch.randint(0, 512, (4, 128), generator=g)
+    tgt = torch.randint(0, 512, (4, 128), generator=g)
+    ref_loss = dense.loss(tok, tgt)
+    ref_loss.backward()
+    tp = TPContext(dist.group.WORLD, rank, world, impl="nccl")
+    model = TPLlamaModel(cfg, tp)
+    model.load_dense_state_dict(dense.hf_state_dict())
+    ParamArena.from_module(model)
+    loss = model.loss(tok, tgt)
+    loss.backward()
+    model.sync_replicated_grads()
+    assert abs(loss.item() - ref_loss.item()) < 1e-5, (loss.item(), ref_loss.item())
+    worst = 0.0
+    dgrads = dict(dense.named_parameters())
+    for name, p in model.named_parameters():
+        want = model._shard_of(name, dgrads[name].grad)
+        worst = max(worst, (p.main_grad - want).abs().max().item())
+    assert worst < 1e-5, worst
+    full = model.gather_dense_state_dict()
+    for k, v in dense.hf_state_dict().items():
+        assert torch.equal(full[k], v), k
+    return worst
+
+
+def test_tp_sp_llama_matches_dense_over_gloo_ranks():
+    _run_ranks(_tp_llama_worker, 2)
+
+
+def _dp_worker(rank, world):
+    from tesseract_b200.models import LlamaConfig
+    from tesseract_b200.parallel import build_parallel_trainer
+    from tesseract_b200.training import TrainConfig
+    cfg = LlamaConfig(vocab_size=64, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                      intermediate_size=128, max_position_embeddings=32)
+    out = {}
+    for mode in ("dp", "tp"):
+        trainer, plan = build_parallel_trainer(cfg, TrainConfig(lr=1e-3, micro_batch=1), world, rank, "cpu", mode, seed=5)
+        g = torch.Generator().manual_seed(100 + plan["dp_rank"])
+        batch = torch.randint(0, 64, (2, 17), generator=g)
+        l0 = trainer.train_step(batch)
+        l1 = trainer.train_step(batch)
+        assert l1 < l0
+        flat = trainer.arena.flat.clone()
+        if mode == "dp":
+            gathered = [torch.empty_like(flat) for _ in range(world)]
+            dist.all_gather(gathered, flat)
+            assert all(torch.equal(gathered[0], t) for t in gathered), "replicas diverged"
+            assert trainer.grad_reducer.overlapped_bytes > 0
+        out[mode] = (l0, l1, plan["name"])
+    return out
+
+
+def test_dp_reducer_and_tp_trainer_over_gloo_ranks():
+    res = _run_ranks(_dp_worker, 2)
+    assert res[0]["dp"][2] == "dp2" and res[0]["tp"][2] == "tp2+sp"
+    assert abs(res[0]["tp"][0] - res[1]["tp"][0]) < 1e-6
+
+
+def _collectives_worker(rank, world):
+    from tesseract_b200.parallel import NcclCommBackend
+    c = NcclCommBackend()
+    x = torch.full((2, 3), float(rank + 1))
+    assert torch.equal(c.all_reduce_sum(x), torch.full((2, 3), float(sum(range(1, world + 1)))))
+    g = c.all_gather(x, dim=-1)
+    assert g.shape == (2, 3 * world) and float(g[0, -1]) == world
+    rs = c.reduce_scatter(torch.arange(world * 2, dtype=torch.float32).view(world * 2, 1))
+    assert torch.equal(rs, world * torch.arange(rank * 2, rank * 2 + 2, dtype=torch.float32).view(2, 1))
+    a2a = c.all_to_all(torch.arange(world, dtype=torch.float32).view(world, 1) + 10 * rank)
+    assert torch.equal(a2a.view(-1), torch.tensor([10.0 * r + rank for r in range(world)]))
+    return True
+
+
+def test_rank_local_collectives_over_gloo():
+    _run_ranks(_collectives_worker, 3)
