@@ -1,0 +1,186 @@
+"""Fused tensor-parallel primitives over peer-mapped ("symmetric") device memory.
+
+``SymmetricMemory`` allocates the same buffer on every rank of a group with ``cudaMalloc``, exchanges CUDA IPC
+handles over the process group and maps every peer's buffer into this process (NVLink P2P through NVSwitch).
+``FusedTP`` owns the buffers the two fused kernels of ``csrc/gemm_fused_comm.cu`` need and drives them:
+
+* ``gemm_rs``  row-parallel GEMM whose epilogue pushes each tile to the owning rank's staging slot, then one
+               cross-rank barrier kernel and a local sum of the ``world`` slots;
+* ``ag_gemm``  copy of the local token shard into the send buffer, one barrier kernel, then ONE kernel in which
+               copy CTAs land the remote shards locally while the other CTAs run the GEMM behind per-block flags.
+
+Send and staging buffers are double-buffered by call parity: a buffer is written again only two calls later, and
+every call contains a barrier that a rank can pass only after all its earlier kernels on the stream (its reads of
+the previous buffer generation included) have been issued before it -- so no second barrier per call is needed.
+All device-side waits are bounded and report through the status word (``_native.read_status``).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List
+
+import torch
+
+from .. import _native
+from .._native import check, lib
+
+P, I, L, F = _native.P, _native.I, _native.L, _native.F
+PP = ctypes.POINTER(ctypes.c_void_p)
+_native.register_signatures({
+    "tsb_symm_alloc": [L, PP],
+    "tsb_symm_free": [P],
+    "tsb_ipc_export": [P, P],
+    "tsb_ipc_open": [P, PP],
+    "tsb_ipc_close": [P],
+    "tsb_symm_barrier": [PP, I, I, I, P],
+    "tsb_reduce_slots": [P, P, I, L, P],
+    "tsb_gemm_rs": [P, P, PP, I, I, I, L, L, I, I, I, I, P],
+    "tsb_gemm_ag": [PP, P, P, P, P, I, I, I, I, I, L, L, I, I, I, I, P],
+})
+
+
+class _RawCuda:
+    """Exposes a raw device allocation to torch through ``__cuda_array_interface__`` (zero copy)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+class SymmetricMemory:
+    """One equally-sized buffer per rank; ``ptrs[r]`` is rank r's buffer as mapped in THIS process."""
+
+    def __init__(self, group, rank: int, world: int, nbytes: int, device):
+        import torch.distributed as dist
+        self.group, self.rank, self.world, self.nbytes = group, rank, world, nbytes
+        local = ctypes.c_void_p()
+        check(lib().tsb_symm_alloc(nbytes, ctypes.byref(local)), "tsb_symm_alloc")
+        self.local_ptr = local.value
+        handle = ctypes.create_string_buffer(64)
+        check(lib().tsb_ipc_export(self.local_ptr, handle), "tsb_ipc_export")
+        handles: List[bytes] = [None] * world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.ptrs: List[int] = []
+        self._opened: List[int] = []
+        for r in range(world):
+            if r == rank:
+                self.ptrs.append(self.local_ptr)
+                continue
+            out = ctypes.c_void_p()
+            check(lib().tsb_ipc_open(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(out)), "tsb_ipc_open")
+            self.ptrs.append(out.value)
+            self._opened.append(out.value)
+        self.ptr_array = (ctypes.c_void_p * world)(*self.ptrs)
+        self.local = torch.as_tensor(_RawCuda(self.local_ptr, nbytes), device=device)   # uint8 view
+
+    def offset_ptr_array(self, byte_offset: int):
+        return (ctypes.c_void_p * self.world)(*[p + byte_offset for p in self.ptrs])
+
+    def close(self) -> None:
+        for p in self._opened:
+            lib().tsb_ipc_close(p)
+        self._opened = []
+        if self.local_ptr:
+            lib().tsb_symm_free(self.local_ptr)
+            self.local_ptr = 0
+
+
+class FusedTP:
+    def __init__(self, group, rank: int, world: int, device, comm_ctas: int = 16):
+        if world > 8:
+            raise ValueError("FusedTP supports at most 8 ranks (one NVSwitch domain)")
+        self.group, self.rank, self.world, self.device = group, rank, world, torch.device(device)
+        self.comm_ctas = comm_ctas
+        self.pads = SymmetricMemory(group, rank, world, 256, device)
+        self.epoch = 0
+        self._send: SymmetricMemory = None     # 2 x [rows_per_rank, K] bf16
+        self._stage: SymmetricMemory = None    # 2 x [world, rows_per_rank, N] bf16
+        self._send_half = self._stage_half = 0
+        self._send_calls = self._stage_calls = 0
+        self._flags: Dict[int, list] = {}
+        self.calls = {"gemm_rs": 0, "ag_gemm": 0, "barrier": 0}
+
+    # ------------------------------------------------------------------ plumbing
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def barrier(self) -> None:
+        self.epoch += 1
+        check(lib().tsb_symm_barrier(self.pads.ptr_array, self.rank, self.world, self.epoch, self._stream()),
+              "tsb_symm_barrier")
+        self.calls["barrier"] += 1
+
+    def _ensure(self, which: str, half_bytes: int) -> SymmetricMemory:
+        cur = getattr(self, which)
+        if cur is None or cur.nbytes < 2 * half_bytes:
+            # (re)allocation is collective: every rank reaches this with the same sizes
+            torch.cuda.synchronize(self.device)
+            if cur is not None:
+                import torch.distributed as dist
+                dist.barrier(group=self.group)
+                cur.close()
+            cur = SymmetricMemory(self.group, self.rank, self.world, 2 * half_bytes, self.device)
+            setattr(self, which, cur)
+            setattr(self, which + "_half", half_bytes)
+        return cur
+
+    # ------------------------------------------------------------------ GEMM -> reduce-scatter
+    def gemm_rs(self, x: torch.Tensor, w: torch.Tensor, b_mn: bool = False) -> torch.Tensor:
+        """reduce_scatter_rows(x [M, K] @ op(w)^T) -> [M / world, N]."""
+        M, K = x.shape
+        N = w.shape[1] if b_mn else w.shape[0]
+        if M % (128 * self.world) or N % 8 or x.stride(1) != 1 or w.stride(1) != 1:
+            raise ValueError("gemm_rs: M must be a multiple of 128 * world and N of 8, rows contiguous")
+        rpr = M // self.world
+        stage = self._ensure("_stage", M * N * 2)
+        parity = self._stage_calls & 1
+        self._stage_calls += 1
+        off = parity * self._stage_half
+        check(lib().tsb_gemm_rs(x.data_ptr(), w.data_ptr(), stage.offset_ptr_array(off), M, N, K, x.stride(0),
+                                w.stride(0), int(b_mn), rpr, self.rank, self.world, self._stream()), "tsb_gemm_rs")
+        self.barrier()
+        out = torch.empty((rpr, N), device=x.device, dtype=torch.bfloat16)
+        check(lib().tsb_reduce_slots(stage.local_ptr + off, out.data_ptr(), self.world, rpr * N, self._stream()),
+              "tsb_reduce_slots")
+        self.calls["gemm_rs"] += 1
+        return out
+
+    # ------------------------------------------------------------------ all-gather -> GEMM
+    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False):
+        """(all_gather_rows(x_local [M / world, K]) @ op(w)^T, gathered x [M, K])."""
+        rpr, K = x_local.shape
+        M = rpr * self.world
+        N = w.shape[1] if b_mn else w.shape[0]
+        if rpr % 128 or N % 8 or w.stride(1) != 1:
+            raise ValueError("ag_gemm: rows per rank must be a multiple of 128 and N of 8")
+        send = self._ensure("_send", rpr * K * 2)
+        parity = self._send_calls & 1
+        self._send_calls += 1
+        off = parity * self._send_half
+        send.local[off:off + rpr * K * 2].view(torch.bfloat16).view(rpr, K).copy_(x_local)
+        self.barrier()                                     # every rank's shard is in its send buffer
+        num_m = M // 128
+        ent = self._flags.get(num_m)
+        if ent is None:
+            ent = [torch.zeros(num_m, dtype=torch.int32, device=self.device), 0]
+            self._flags[num_m] = ent
+        ent[1] += 1
+        cc = self.comm_ctas
+        while (128 * K * 2) % (16 * cc):
+            cc //= 2
+        # the counters advance by `cc` per call; keep cc fixed per flags buffer
+        if len(ent) == 2:
+            ent.append(cc)
+        cc = ent[2]
+        x_full = torch.empty((M, K), device=x_local.device, dtype=torch.bfloat16)
+        y = torch.empty((M, N), device=x_local.device, dtype=torch.bfloat16)
+        check(lib().tsb_gemm_ag(send.offset_ptr_array(off), x_full.data_ptr(), w.data_ptr(), y.data_ptr(),
+                                ent[0].data_ptr(), ent[1] * cc, cc, M, N, K, w.stride(0), y.stride(0), int(b_mn), rpr,
+                                self.rank, self.world, self._stream()), "tsb_gemm_ag")
+        self.calls["ag_gemm"] += 1
+        return y, x_full
+
+    def close(self) -> None:
+        for m in (self.pads, self._send, self._stage):
+            if m is not None:
+                m.close()

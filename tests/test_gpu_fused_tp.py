@@ -1,0 +1,164 @@
+"""Fused TP kernels. On one GPU the ranks of a group are emulated by launching each rank's kernel in turn over
+buffers that all live on that GPU (the kernels of different ranks never wait on one another: only the barrier
+kernel does, and it is not used here). With >= 2 GPUs the real peer-memory path runs in child processes."""
+import ctypes
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ptr_array(tensors):
+    return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-9)).item()
+
+
+@pytest.mark.parametrize("world,rpr,N,K,b_mn", [(1, 256, 512, 256, False), (4, 128, 256, 192, False),
+                                                 (2, 256, 384, 512, True), (8, 128, 4096, 512, False)])
+def test_gemm_rs_emulated_ranks(world, rpr, N, K, b_mn):
+    from tesseract_b200 import _native
+    from tesseract_b200.parallel import fused_tp  # noqa: F401 (registers the signatures)
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    M = rpr * world
+    g = torch.Generator(device=dev).manual_seed(world * 100 + N)
+    xs = [torch.randn(M, K, device=dev, generator=g).bfloat16() for _ in range(world)]
+    ws = [(torch.randn(N, K, device=dev, generator=g) * 0.1).bfloat16() for _ in range(world)]
+    staging = [torch.full((world, rpr, N), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    pa = _ptr_array(staging)
+    stream = torch.cuda.current_stream().cuda_stream
+    for r in range(world):
+        w_in = ws[r].t().contiguous() if b_mn else ws[r]
+        _native.check(lib.tsb_gemm_rs(xs[r].data_ptr(), w_in.data_ptr(), pa, M, N, K, xs[r].stride(0), w_in.stride(0),
+                                      int(b_mn), rpr, r, world, stream), "tsb_gemm_rs")
+    torch.cuda.synchronize()
+    assert _native.read_status(stream) == 0
+    total = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
+    for r in range(world):
+        assert torch.isfinite(staging[r].float()).all(), "a staging slot was not written"
+        out = torch.empty(rpr, N, device=dev, dtype=torch.bfloat16)
+        _native.check(lib.tsb_reduce_slots(staging[r].data_ptr(), out.data_ptr(), world, rpr * N, stream), "reduce")
+        assert _rel(out, total[r * rpr:(r + 1) * rpr]) < 1e-2
+        for src in range(world):  # each slot holds exactly that source rank's partial product
+            part = xs[src][r * rpr:(r + 1) * rpr].float() @ ws[src].float().t()
+            assert _rel(staging[r][src], part) < 1e-2
+
+
+@pytest.mark.parametrize("world,rpr,N,K,b_mn", [(1, 256, 512, 256, False), (4, 128, 256, 512, False),
+                                                 (2, 512, 768, 1024, True), (8, 128, 3584, 4096, False)])
+def test_ag_gemm_emulated_ranks(world, rpr, N, K, b_mn):
+    from tesseract_b200 import _native
+    from tesseract_b200.parallel import fused_tp  # noqa: F401
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    M = rpr * world
+    g = torch.Generator(device=dev).manual_seed(world * 7 + K)
+    shards = [torch.randn(rpr, K, device=dev, generator=g).bfloat16() for _ in range(world)]
+    full = torch.cat(shards)
+    pa = _ptr_array(shards)
+    stream = torch.cuda.current_stream().cuda_stream
+    cc = 16
+    while (128 * K * 2) % (16 * cc):
+        cc //= 2
+    for r in range(world):
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.1).bfloat16()
+        w_in = w.t().contiguous() if b_mn else w
+        flags = torch.zeros(M // 128, dtype=torch.int32, device=dev)
+        for call in (1, 2):   # the counters keep counting across calls
+            x_full = torch.full((M, K), float("nan"), device=dev, dtype=torch.bfloat16)
+            y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            _native.check(lib.tsb_gemm_ag(pa, x_full.data_ptr(), w_in.data_ptr(), y.data_ptr(), flags.data_ptr(),
+                                          call * cc, cc, M, N, K, w_in.stride(0), y.stride(0), int(b_mn), rpr, r, world,
+                                          stream), "tsb_gemm_ag")
+            torch.cuda.synchronize()
+            assert _native.read_status(stream) == 0
+            assert torch.equal(x_full, full), "gathered activations differ from the concatenated shards"
+            assert _rel(y, full.float() @ w.float().t()) < 1e-2
+        assert int(flags.min()) == 2 * cc and int(flags.max()) == 2 * cc
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    try:
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from tesseract_b200 import _native
+        from tesseract_b200.models import LlamaConfig
+        from tesseract_b200.parallel.fused_tp import FusedTP
+        from tesseract_b200.parallel.tp_layers import TPContext, ag_matmul, matmul_rs
+        fused = FusedTP(dist.group.WORLD, rank, world, dev)
+        ctx_f = TPContext(dist.group.WORLD, rank, world, impl="fused", fused=fused)
+        ctx_n = TPContext(dist.group.WORLD, rank, world, impl="nccl")
+        g = torch.Generator(device=dev).manual_seed(11 + rank)
+        errs = []
+        for it in range(3):
+            x = torch.randn(256 * world, 512, device=dev, generator=g).bfloat16()
+            w = (torch.randn(1024, 512, device=dev, generator=g) * 0.05).bfloat16()
+            a, b = matmul_rs(ctx_f, x, w), matmul_rs(ctx_n, x, w)
+            errs.append(((a.float() - b.float()).norm() / b.float().norm()).item())
+            xl = torch.randn(256, 512, device=dev, generator=g).bfloat16()
+            (ya, xa), (yb, xb) = ag_matmul(ctx_f, xl, w), ag_matmul(ctx_n, xl, w)
+            assert torch.equal(xa, xb)
+            errs.append(((ya.float() - yb.float()).norm() / yb.float().norm()).item())
+        torch.cuda.synchronize()
+        status = _native.read_status(torch.cuda.current_stream().cuda_stream)
+        # one optimizer step of a small TP+SP Llama: fused communication vs NCCL
+        from tesseract_b200.parallel import build_parallel_trainer
+        from tesseract_b200.training import TrainConfig
+        cfg = LlamaConfig(vocab_size=1024, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
+                          num_key_value_heads=4, intermediate_size=1024, max_position_embeddings=256,
+                          dtype=torch.bfloat16)
+        losses = {}
+        for impl in ("fused", "nccl"):
+            os.environ["TESSERACT_TP_COMM"] = impl
+            trainer, plan = build_parallel_trainer(cfg, TrainConfig(lr=1e-3, micro_batch=2), world, rank, dev, "tp", seed=3)
+            batch = torch.randint(0, 1024, (2, 257), generator=torch.Generator().manual_seed(5)).pin_memory()
+            losses[impl] = (trainer.train_step(batch), trainer.train_step(batch), plan["fused_comm"])
+        dist.barrier()
+        q.put((rank, None, (errs, status, losses)))
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, traceback.format_exc(), None))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_fused_tp_matches_nccl_on_real_peers():
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    bad = [r for r in results if r[1] is not None]
+    assert not bad, bad[0][1]
+    for _, _, (errs, status, losses) in results:
+        assert status == 0
+        assert max(errs) < 1e-2, errs
+        assert losses["fused"][2] is True and losses["nccl"][2] is False
+        assert abs(losses["fused"][0] - losses["nccl"][0]) < 2e-2
+        assert losses["fused"][1] < losses["fused"][0]
