@@ -87,7 +87,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--global-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=4096)
-    ap.add_argument("--micro-batch", type=int, default=1)
+    ap.add_argument("--micro-batch", type=int, default=0, help="sequences per forward/backward pass (0 = choose)")
+    ap.add_argument("--serve", type=int, default=-1, help="also run the serving benchmark (1 GPU only; -1 = auto)")
+    ap.add_argument("--serve-requests", type=int, default=256)
     ap.add_argument("--layers", type=int, default=32, help="(debug only) fewer layers; invalidates the metric")
     ap.add_argument("--master-weights", action="store_true")
     ap.add_argument("--parallelism", default="auto", help="auto | dp | tp  (auto: tensor+sequence parallel over all ranks)")
@@ -124,6 +126,11 @@ def main():
 
     cfg = LlamaConfig.llama_3_8b(dtype=torch.bfloat16, max_position_embeddings=args.seq_len)
     cfg.num_hidden_layers = args.layers
+    if args.micro_batch <= 0:
+        # one sequence per pass on a single GPU (activations of 32 layers next to 96 GB of model state); with the
+        # model sharded over >= 2 ranks there is room for larger passes, which means larger GEMMs and fewer launches
+        tp_like = world > 1 and args.parallelism in ("auto", "tp")
+        args.micro_batch = min(args.global_batch, 4 if world < 8 else 8) if tp_like else 1
     tcfg = TrainConfig(lr=1e-4, micro_batch=args.micro_batch, grad_dtype=torch.bfloat16,
                        master_weights=args.master_weights)
     trainer, plan = build_parallel_trainer(cfg, tcfg, world, rank, device, args.parallelism, seed=1234)
@@ -182,6 +189,21 @@ def main():
         e2e = {"value": tok_e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4 * world}
 
+    serve = None
+    want_serve = args.serve == 1 or (args.serve == -1 and world == 1 and args.layers == 32)
+    if want_serve and world == 1:
+        # free the training state first: the serving model and its KV pool need the memory
+        del trainer, dev_batches
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "benchmarks"))
+            from bench_serving import run_serving_bench
+            serve = run_serving_bench(requests=args.serve_requests, layers=args.layers, device=device)
+        except Exception as e:  # the training number stands on its own
+            serve = {"error": f"{type(e).__name__}: {e}"[:300]}
+
     if rank == 0:
         tok_s = B * S * args.steps / (ms_dev / 1e3)
         loss_val = float(last_loss[0]) if not isinstance(last_loss[0], float) else last_loss[0]
@@ -197,7 +219,7 @@ def main():
                        "gemm": os.environ.get("TESSERACT_GEMM", "tcgen05"),
                        "attention": os.environ.get("TESSERACT_ATTN", "tcgen05"),
                        "fused_comm": plan.get("fused_comm", False)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val, "serve": serve,
             "kernel_status": status,
         }
         print(json.dumps(out))

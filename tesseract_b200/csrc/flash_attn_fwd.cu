@@ -203,17 +203,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (p.causal) lim = min(lim, row_limit - c0 + 1);
         vis = max(0, min(BKV, lim));
       }
-      // pass 1: row maximum
+      // pass 1: row maximum (tiles that need no masking skip the per-element visibility test)
       float m_tile = -INFINITY;
+      if (need_mask) {
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(s_addr + c * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(r[i]);
-          if (c * 32 + i < vis) m_tile = fmaxf(m_tile, s);
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < vis) m_tile = fmaxf(m_tile, __uint_as_float(r[i]));
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(s_addr + c * 32, r);
+          tmem_ld_wait();
+          float m0 = fmaxf(__uint_as_float(r[0]), __uint_as_float(r[1]));
+          float m1 = fmaxf(__uint_as_float(r[2]), __uint_as_float(r[3]));
+#pragma unroll
+          for (int i = 4; i < 32; i += 4) {
+            m0 = fmaxf(m0, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+            m1 = fmaxf(m1, fmaxf(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])));
+          }
+          m_tile = fmaxf(m_tile, fmaxf(m0, m1));
         }
       }
       const float m_new = fmaxf(m_run, m_tile);
@@ -240,15 +255,31 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(s_addr + c * 32, r);
         tmem_ld_wait();
         uint32_t packed[16];
+        const float mneg = -m_use * p.scale_log2;
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = (c * 32 + i < vis) ? exp2f((__uint_as_float(r[i]) - m_use) * p.scale_log2) : 0.f;
-          float p1 = (c * 32 + i + 1 < vis) ? exp2f((__uint_as_float(r[i + 1]) - m_use) * p.scale_log2) : 0.f;
-          // the denominator sums what the tensor core will actually multiply (bf16-rounded P)
-          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-          const float2 pf = __bfloat1622float2(pb);
-          l_tile += pf.x + pf.y;
-          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = (c * 32 + i < vis) ? exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, mneg)) : 0.f;
+            float p1 = (c * 32 + i + 1 < vis) ? exp2f(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, mneg)) : 0.f;
+            // the denominator sums what the tensor core will actually multiply (bf16-rounded P)
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            const float2 pf = __bfloat1622float2(pb);
+            l_tile += pf.x + pf.y;
+            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+          }
+        } else {
+          float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, mneg));
+            const float p1 = exp2f(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, mneg));
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            const float2 pf = __bfloat1622float2(pb);
+            l0 += pf.x;
+            l1 += pf.y;
+            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+          }
+          l_tile += l0 + l1;
         }
         // columns [c*32, c*32+32) = four 16-byte chunks of row `row` in half (c >> 1)
         const int half = c >> 1;

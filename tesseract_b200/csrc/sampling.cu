@@ -1,0 +1,194 @@
+// Device-side token selection so that a decode step needs no logits transfer:
+//   * tsb_argmax_rows        greedy: index of the row maximum (lowest index on ties, like the host sampler)
+//   * tsb_sample_top_p_rows  temperature + nucleus sampling without sorting: the probability threshold of the
+//                            nucleus is found by bisection over the row (kept hot in L2), then one uniform draw
+//                            picks a token among the survivors in index order.
+// The host sampler (repetition penalty -> temperature -> top-k -> top-p -> mt19937_64 draw,
+// src/models/Sampler.cpp:29-116) stays the bit-exact path for seeded tests; these kernels are the serving fast
+// path. The reference copies the whole logits row to the host for every token (src/models/Llama.cpp:481-509).
+#include "common.cuh"
+
+namespace tsb {
+namespace {
+
+constexpr int kSampThreads = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(kSampThreads)
+argmax_rows_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, long long ld) {
+  __shared__ float sv[kSampThreads / 32];
+  __shared__ int si[kSampThreads / 32];
+  const T* x = logits + blockIdx.x * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int j = threadIdx.x; j < V; j += blockDim.x) {
+    const float f = to_f32<T>(x[j]);
+    if (f > best) {
+      best = f;
+      bi = j;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < kSampThreads / 32 ? sv[lane] : -INFINITY;
+    bi = lane < kSampThreads / 32 ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) out[blockIdx.x] = bi;
+  }
+}
+
+__device__ __forceinline__ float block_reduce_sum(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_reduce_max(float v, float* red) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : -INFINITY;
+  return warp_max(t);
+}
+
+// splitmix64 -> uniform in [0, 1)
+__device__ __forceinline__ float uniform_from(unsigned long long seed, unsigned long long row, unsigned long long step) {
+  unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (row * 0x100000001B3ull + step + 1);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return static_cast<float>(z >> 40) * (1.0f / 16777216.0f);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kSampThreads)
+sample_top_p_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, long long ld, float inv_temp,
+                    float top_p, unsigned long long seed, unsigned long long step) {
+  __shared__ float red[32];
+  __shared__ float s_scan[kSampThreads];
+  const T* x = logits + blockIdx.x * ld;
+  float m = -INFINITY;
+  for (int j = threadIdx.x; j < V; j += blockDim.x) m = fmaxf(m, to_f32<T>(x[j]) * inv_temp);
+  m = block_reduce_max(m, red);
+  float s = 0.f;
+  for (int j = threadIdx.x; j < V; j += blockDim.x) s += __expf(to_f32<T>(x[j]) * inv_temp - m);
+  const float denom = block_reduce_sum(s, red);
+  // bisection on the probability threshold t: mass(p >= t) is non-increasing in t; find the largest t whose
+  // mass still reaches top_p (the smallest nucleus). p is in (0, 1]; the top token has p_max = 1 / denom.
+  float lo = 0.f, hi = 1.f / denom;
+  if (top_p < 1.f) {
+    for (int it = 0; it < 24; ++it) {
+      const float mid = 0.5f * (lo + hi);
+      float mass = 0.f;
+      for (int j = threadIdx.x; j < V; j += blockDim.x) {
+        const float p = __expf(to_f32<T>(x[j]) * inv_temp - m) / denom;
+        if (p >= mid) mass += p;
+      }
+      mass = block_reduce_sum(mass, red);
+      if (mass >= top_p) lo = mid; else hi = mid;
+    }
+  }
+  const float thr = lo;
+  // mass of the survivors, then an inverse-CDF walk in index order
+  float keep = 0.f;
+  for (int j = threadIdx.x; j < V; j += blockDim.x) {
+    const float p = __expf(to_f32<T>(x[j]) * inv_temp - m) / denom;
+    if (p >= thr) keep += p;
+  }
+  const float total = block_reduce_sum(keep, red);
+  const float target = uniform_from(seed, blockIdx.x, step) * total;
+  // each thread owns a contiguous span so that the walk is in index order
+  const int per = (V + blockDim.x - 1) / blockDim.x;
+  const int j0 = threadIdx.x * per, j1 = min(V, j0 + per);
+  float mine = 0.f;
+  for (int j = j0; j < j1; ++j) {
+    const float p = __expf(to_f32<T>(x[j]) * inv_temp - m) / denom;
+    if (p >= thr) mine += p;
+  }
+  s_scan[threadIdx.x] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float acc = 0.f;
+    int owner = blockDim.x - 1;
+    for (int t = 0; t < static_cast<int>(blockDim.x); ++t) {
+      if (acc + s_scan[t] >= target && s_scan[t] > 0.f) {
+        owner = t;
+        break;
+      }
+      acc += s_scan[t];
+    }
+    // walk inside the owner's span
+    const int a0 = owner * per, a1 = min(V, a0 + per);
+    int pick = -1, last = -1;
+    for (int j = a0; j < a1; ++j) {
+      const float p = __expf(to_f32<T>(x[j]) * inv_temp - m) / denom;
+      if (p >= thr) {
+        last = j;
+        acc += p;
+        if (acc >= target) {
+          pick = j;
+          break;
+        }
+      }
+    }
+    if (pick < 0) pick = last >= 0 ? last : 0;
+    out[blockIdx.x] = pick;
+  }
+}
+
+}  // namespace
+}  // namespace tsb
+
+#define TSB_DISPATCH_FLOAT(dtype, ...)                      \
+  switch (dtype) {                                          \
+    case 0: { using T = float; __VA_ARGS__; } break;        \
+    case 1: { using T = __nv_bfloat16; __VA_ARGS__; } break; \
+    case 2: { using T = __half; __VA_ARGS__; } break;       \
+    default: return -2;                                     \
+  }
+
+// out[row] = argmax_j logits[row, j] (int32), lowest index on ties.
+TSB_EXPORT int tsb_argmax_rows(const void* logits, int* out, int rows, int V, long long ld, int dtype, void* stream) {
+  if (rows <= 0 || V <= 0) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TSB_DISPATCH_FLOAT(dtype, (tsb::argmax_rows_kernel<T><<<rows, tsb::kSampThreads, 0, s>>>(
+                                static_cast<const T*>(logits), out, V, ld)));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out[row] ~ softmax(logits[row] / temperature) restricted to its top_p nucleus. The draw for (row, step) is a
+// pure function of (seed, row, step).
+TSB_EXPORT int tsb_sample_top_p_rows(const void* logits, int* out, int rows, int V, long long ld, float temperature,
+                                     float top_p, unsigned long long seed, unsigned long long step, int dtype,
+                                     void* stream) {
+  if (rows <= 0 || V <= 0 || temperature <= 0.f || top_p <= 0.f) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TSB_DISPATCH_FLOAT(dtype, (tsb::sample_top_p_kernel<T><<<rows, tsb::kSampThreads, 0, s>>>(
+                                static_cast<const T*>(logits), out, V, ld, 1.f / temperature, top_p, seed, step)));
+  return static_cast<int>(cudaGetLastError());
+}

@@ -73,11 +73,14 @@ def _native_decode_ok(q: torch.Tensor, k_pool: torch.Tensor) -> bool:
 
 
 _scratch_cache: dict = {}
+_scratch_retired: list = []   # outgrown buffers stay alive: captured CUDA graphs may still point at them
 
 
 def _decode_scratch(device, floats: int) -> torch.Tensor:
     t = _scratch_cache.get(device)
     if t is None or t.numel() < floats:
+        if t is not None:
+            _scratch_retired.append(t)
         t = torch.empty(max(floats, 1 << 20), device=device, dtype=torch.float32)
         _scratch_cache[device] = t
     return t
@@ -97,12 +100,14 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         floats = lib().tsb_paged_decode_scratch_floats(A, H, D, max_len)
         scratch = _decode_scratch(q.device, floats)
         bt = block_tables if block_tables.dtype == torch.int32 else block_tables.to(torch.int32)
+        if bt.stride(1) != 1:
+            bt = bt.contiguous()
         ln = lens if lens.dtype == torch.int32 else lens.to(torch.int32)
         check(lib().tsb_paged_decode(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                      k_scale.data_ptr() if k_scale is not None else None,
                                      v_scale.data_ptr() if v_scale is not None else None,
                                      bt.data_ptr(), ln.data_ptr(), out.data_ptr(), scratch.data_ptr(),
-                                     A, H, Hkv, D, bs, nb, bt.shape[1], float(scale), max_len,
+                                     A, H, Hkv, D, bs, nb, bt.stride(0), float(scale), max_len,
                                      1 if q.dtype == torch.bfloat16 else 2, stream_ptr(q.device)), "tsb_paged_decode")
         _native.add_launches(1)
         return out

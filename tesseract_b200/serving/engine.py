@@ -1,0 +1,395 @@
+"""Device-resident continuous-batching engine (the serving fast path on a GPU).
+
+Same scheduling contract as ``models.scheduler.ContinuousBatchingScheduler`` (FIFO admission against free KV
+blocks, one token per running request per step, blocks recycled on retirement) but the whole decode step stays on
+the device:
+
+* one K and one V pool tensor for all layers ([L, num_blocks, Hkv, block, D], bf16 or INT8 + scales) and ONE block
+  table [batch, max_blocks] shared by every layer, uploaded once per step (the reference rebuilds and uploads the
+  tables in every layer of every step, src/nn/MultiHeadAttention.cpp:519-580);
+* per layer: fused RMSNorm(+residual) -> one QKV GEMM -> fused RoPE + KV append (+INT8 quantisation) into the pool ->
+  split-K paged decode attention -> o_proj -> ... -> SwiGLU FFN, every op a native sm_100a kernel;
+* tokens are chosen on the device (argmax / nucleus sampling kernels); only ``batch`` int32 ids return to the host;
+* the decode step is captured into CUDA graphs per batch-size bucket, so a step costs one graph launch;
+* prompts admitted in the same step are prefilled together (projections and FFN batched over all their tokens,
+  FlashAttention per prompt), instead of one un-batched prefill per request (src/models/Scheduler.cpp:115-124).
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+
+import numpy as np
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional
+
+import torch
+
+from .. import _native, ops
+from .._native import check, lib, stream_ptr
+from ..models.llama import GenerateConfig, LlamaModel
+from ..models.scheduler import EngineConfig
+from ..nn.kv_cache import BlockAllocator
+
+P, I, L, F = _native.P, _native.I, _native.L, _native.F
+_native.register_signatures({
+    "tsb_argmax_rows": [P, P, I, I, L, I, P],
+    "tsb_sample_top_p_rows": [P, P, I, I, L, F, F, _native.ctypes.c_ulonglong, _native.ctypes.c_ulonglong, I, P],
+})
+
+
+@dataclass
+class _Req:
+    id: int
+    gen: GenerateConfig
+    tokens: List[int]
+    prompt_len: int
+    generated: int = 0
+    finished: bool = False
+    blocks: List[int] = field(default_factory=list)
+    table_row: Optional[np.ndarray] = None
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    t_done: float = 0.0
+
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    check(lib().tsb_argmax_rows(logits.data_ptr(), out.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0),
+                                _native.dtype_code(logits.dtype), stream_ptr(logits.device)), "tsb_argmax_rows")
+    return out
+
+
+def sample_top_p_rows(logits: torch.Tensor, temperature: float, top_p: float, seed: int, step: int) -> torch.Tensor:
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    check(lib().tsb_sample_top_p_rows(logits.data_ptr(), out.data_ptr(), logits.shape[0], logits.shape[1],
+                                      logits.stride(0), float(temperature), float(top_p), seed, step,
+                                      _native.dtype_code(logits.dtype), stream_ptr(logits.device)),
+          "tsb_sample_top_p_rows")
+    return out
+
+
+class ServingEngine:
+    BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+
+    def __init__(self, model: LlamaModel, cfg: Optional[EngineConfig] = None, use_cuda_graph: bool = True,
+                 temperature: float = 0.0, top_p: float = 1.0, seed: int = 0):
+        self.model, self.cfg = model, cfg or EngineConfig()
+        c, mc = self.cfg, model.config
+        self.device = model._device()
+        if self.device.type != "cuda" or mc.dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError("ServingEngine needs a bf16 / fp16 model on a CUDA device "
+                             "(use ContinuousBatchingScheduler for CPU or fp32 models)")
+        self.H, self.Hkv, self.D = mc.num_attention_heads, mc.kv_heads(), mc.head_dim
+        self.L = len(model.layers)
+        self.temperature, self.top_p, self.seed = temperature, top_p, seed
+        self.greedy = temperature <= 1e-6
+        kv_dtype = torch.int8 if c.kv_int8 else mc.dtype
+        shape = (self.L, c.num_blocks, self.Hkv, c.block_size, self.D)
+        self.k_pool = torch.zeros(shape, dtype=kv_dtype, device=self.device)
+        self.v_pool = torch.zeros(shape, dtype=kv_dtype, device=self.device)
+        self.k_scale = self.v_scale = None
+        if c.kv_int8:
+            self.k_scale = torch.ones(shape[:-1], dtype=torch.float32, device=self.device)
+            self.v_scale = torch.ones(shape[:-1], dtype=torch.float32, device=self.device)
+        self.allocator = BlockAllocator(c.num_blocks)
+        self.max_blocks = (c.max_seq_len + c.block_size - 1) // c.block_size
+        self._fuse_weights()
+        self.waiting: Deque[_Req] = deque()
+        self.running: List[_Req] = []
+        self.requests: Dict[int, _Req] = {}
+        self._next_id = 0
+        self.steps = 0
+        self.use_cuda_graph = use_cuda_graph
+        self._graphs: Dict[int, dict] = {}
+        self._host_inputs: Dict[int, torch.Tensor] = {}
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0}
+
+    # ------------------------------------------------------------------ weights
+    def _fuse_weights(self) -> None:
+        """q/k/v and gate/up become views of one concatenated tensor per layer (one GEMM each)."""
+        self.wqkv, self.wgu = [], []
+        with torch.no_grad():
+            for blk in self.model.layers:
+                a, f = blk.attn, blk.ffn
+                w = torch.cat([a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], dim=0).contiguous()
+                n0, n1 = a.q_proj.weight.shape[0], a.k_proj.weight.shape[0]
+                a.q_proj.weight.data, a.k_proj.weight.data, a.v_proj.weight.data = w[:n0], w[n0:n0 + n1], w[n0 + n1:]
+                self.wqkv.append(w)
+                g = torch.cat([f.gate_proj.weight, f.up_proj.weight], dim=0).contiguous()
+                nf = f.gate_proj.weight.shape[0]
+                f.gate_proj.weight.data, f.up_proj.weight.data = g[:nf], g[nf:]
+                self.wgu.append(g)
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_ids, gen: Optional[GenerateConfig] = None) -> int:
+        gen = gen or GenerateConfig()
+        prompt = [int(t) for t in prompt_ids]
+        if not prompt:
+            raise ValueError("add_request: empty prompt")
+        V = self.model.config.vocab_size
+        if any(t < 0 or t >= V for t in prompt):
+            raise ValueError("add_request: prompt id outside [0, vocab_size)")
+        if gen.max_new_tokens < 0 or len(prompt) + gen.max_new_tokens > self.cfg.max_seq_len:
+            raise ValueError("add_request: prompt + max_new_tokens exceeds max_seq_len")
+        r = _Req(self._next_id, gen, prompt, len(prompt), t_submit=time.perf_counter())
+        self._next_id += 1
+        self.waiting.append(r)
+        self.requests[r.id] = r
+        return r.id
+
+    def has_pending(self) -> bool:
+        return bool(self.waiting) or bool(self.running)
+
+    def num_running(self) -> int:
+        return len(self.running)
+
+    def num_waiting(self) -> int:
+        return len(self.waiting)
+
+    def free_blocks(self) -> int:
+        return self.allocator.num_free()
+
+    def allocated_blocks(self) -> int:
+        return self.allocator.num_used()
+
+    def is_finished(self, rid: int) -> bool:
+        return self.requests[rid].finished
+
+    def result(self, rid: int) -> List[int]:
+        r = self.requests[rid]
+        if not r.finished:
+            raise KeyError(f"request {rid} is not finished")
+        return list(r.tokens)
+
+    def _blocks_for(self, n: int) -> int:
+        return (n + self.cfg.block_size - 1) // self.cfg.block_size
+
+    def _grow(self, r: _Req, new_len: int) -> None:
+        if r.table_row is None:
+            r.table_row = np.zeros(self.max_blocks, dtype=np.int32)
+        while len(r.blocks) < self._blocks_for(new_len):
+            b = self.allocator.allocate()
+            r.table_row[len(r.blocks)] = b
+            r.blocks.append(b)
+
+    def _retire(self, r: _Req) -> None:
+        for b in r.blocks:
+            self.allocator.free(b)
+        r.blocks = []
+        r.finished = True
+        r.t_done = time.perf_counter()
+
+    # ------------------------------------------------------------------ model pieces
+    def _layer(self, li: int, x, res, positions, slots, tables, lens, prefill_bounds=None):
+        blk = self.model.layers[li]
+        H, Hkv, D = self.H, self.Hkv, self.D
+        if res is None:
+            h, res = ops.rms_norm(x, blk.norm_1.weight, blk.norm_1.eps), x
+        else:
+            h, res = ops.rms_norm(x, blk.norm_1.weight, blk.norm_1.eps, residual=res)
+        qkv = ops.gemm_bf16(h, self.wqkv[li]) if h.dtype == torch.bfloat16 else h @ self.wqkv[li].t()
+        T = qkv.shape[0]
+        ks = self.k_scale[li] if self.k_scale is not None else None
+        vs = self.v_scale[li] if self.v_scale is not None else None
+        rope = self.model.rope
+        dt = _native.dtype_code(qkv.dtype)
+        if prefill_bounds is None:
+            q = torch.empty((T, H, D), device=qkv.device, dtype=qkv.dtype)
+            check(lib().tsb_kv_append_paged(qkv.data_ptr(), rope.cos.data_ptr(), rope.sin.data_ptr(), positions.data_ptr(),
+                                            slots.data_ptr(), self.k_pool[li].data_ptr(), self.v_pool[li].data_ptr(),
+                                            ks.data_ptr() if ks is not None else None,
+                                            vs.data_ptr() if vs is not None else None, q.data_ptr(), T, H, Hkv, D,
+                                            self.cfg.block_size, dt, 1, stream_ptr(qkv.device)), "tsb_kv_append_paged")
+            o = ops.paged_decode_attention(q, self.k_pool[li], self.v_pool[li], tables, lens, None, ks, vs,
+                                           max_len_hint=self.cfg.max_seq_len)
+            o = o.view(T, H * D)
+        else:
+            qkv = ops.rope_qkv(qkv, rope.cos, rope.sin, num_heads=H, num_kv_heads=Hkv, head_dim=D, seq_len=1,
+                               positions=positions)
+            check(lib().tsb_kv_append_paged(qkv.data_ptr(), rope.cos.data_ptr(), rope.sin.data_ptr(), positions.data_ptr(),
+                                            slots.data_ptr(), self.k_pool[li].data_ptr(), self.v_pool[li].data_ptr(),
+                                            ks.data_ptr() if ks is not None else None,
+                                            vs.data_ptr() if vs is not None else None, None, T, H, Hkv, D,
+                                            self.cfg.block_size, dt, 0, stream_ptr(qkv.device)), "tsb_kv_append_paged")
+            outs = []
+            q4 = qkv.view(T, H + 2 * Hkv, D)
+            for (a, b) in prefill_bounds:
+                outs.append(ops.flash_attention_packed(q4[a:b].unsqueeze(0), H, Hkv, causal=True).view(b - a, H * D))
+            o = torch.cat(outs, dim=0) if len(outs) > 1 else outs[0]
+        a_out = ops.gemm_bf16(o, blk.attn.o_proj.weight)
+        h2, res = ops.rms_norm(a_out, blk.norm_2.weight, blk.norm_2.eps, residual=res)
+        gu = ops.gemm_bf16(h2, self.wgu[li])
+        f = ops.gemm_bf16(ops.swiglu(gu), blk.ffn.down_proj.weight)
+        return f, res
+
+    def _forward(self, tokens, positions, slots, tables, lens, prefill_bounds=None, last_rows=None):
+        m = self.model
+        x = ops.embedding(tokens, m.embed_tokens.weight)
+        res = None
+        for li in range(self.L):
+            x, res = self._layer(li, x, res, positions, slots, tables, lens, prefill_bounds)
+        h, _ = ops.rms_norm(x, m.norm.weight, m.norm.eps, residual=res)
+        if last_rows is not None:
+            h = h.index_select(0, last_rows)
+        return ops.gemm_bf16(h.contiguous(), m.lm_head.weight)
+
+    def _pick(self, logits: torch.Tensor) -> torch.Tensor:
+        if self.greedy:
+            return argmax_rows(logits)
+        return sample_top_p_rows(logits, self.temperature, self.top_p, self.seed, self.steps)
+
+    # ------------------------------------------------------------------ scheduling
+    def _admit(self) -> List[_Req]:
+        admitted, reserved = [], 0
+        while self.waiting and len(self.running) + len(admitted) < self.cfg.max_batch_size:
+            head = self.waiting[0]
+            need = self._blocks_for(head.prompt_len + 1)
+            if self.free_blocks() - reserved < need:
+                if not self.running and not admitted:
+                    raise RuntimeError("engine: the head request does not fit and nothing is running to reclaim from")
+                break
+            reserved += need
+            admitted.append(self.waiting.popleft())
+        return admitted
+
+    @torch.no_grad()
+    def _prefill(self, reqs: List[_Req]) -> None:
+        t0 = time.perf_counter()
+        bs = self.cfg.block_size
+        toks, pos, slots, bounds, last = [], [], [], [], []
+        off = 0
+        for r in reqs:
+            self._grow(r, r.prompt_len)
+            toks += r.tokens
+            pos += list(range(r.prompt_len))
+            slots += [r.blocks[p // bs] * bs + p % bs for p in range(r.prompt_len)]
+            bounds.append((off, off + r.prompt_len))
+            off += r.prompt_len
+            last.append(off - 1)
+        dev = self.device
+        tokens = torch.tensor(toks, dtype=torch.int64).to(dev, non_blocking=True)
+        meta = torch.tensor([pos, slots], dtype=torch.int32).to(dev, non_blocking=True)
+        last_rows = torch.tensor(last, dtype=torch.int64).to(dev, non_blocking=True)
+        logits = self._forward(tokens, meta[0], meta[1], None, None, prefill_bounds=bounds, last_rows=last_rows)
+        nxt = self._pick(logits).cpu().tolist()
+        now = time.perf_counter()
+        for r, t in zip(reqs, nxt):
+            r.t_first = now
+            self._emit(r, int(t))
+        self.stats["prefill_tokens"] += off
+        self.stats["prefill_s"] += now - t0
+
+    def _emit(self, r: _Req, tok: int) -> None:
+        if r.gen.max_new_tokens == 0:
+            self._retire(r)
+            return
+        r.tokens.append(tok)
+        r.generated += 1
+        if (r.gen.eos_token_id >= 0 and tok == r.gen.eos_token_id) or r.generated >= r.gen.max_new_tokens:
+            self._retire(r)
+
+    def _bucket(self, n: int) -> int:
+        for b in self.BUCKETS:
+            if b >= n:
+                return b
+        return n
+
+    def _decode_inputs(self, reqs: List[_Req], A: int) -> torch.Tensor:
+        """Packed int32 step inputs [A, 4 + max_blocks]: token, position, cache slot, length after the append,
+        then the block table row. Padded rows have slot -1 and length 0."""
+        bs = self.cfg.block_size
+        n = len(reqs)
+        buf = self._host_inputs.get(A)
+        if buf is None:
+            buf = torch.zeros((A, 4 + self.max_blocks), dtype=torch.int32).pin_memory()
+            self._host_inputs[A] = buf
+        arr = buf.numpy()
+        for r in reqs:
+            self._grow(r, len(r.tokens))
+        pos = np.fromiter((len(r.tokens) - 1 for r in reqs), dtype=np.int32, count=n)
+        arr[:n, 0] = np.fromiter((r.tokens[-1] for r in reqs), dtype=np.int32, count=n)
+        arr[:n, 1] = pos
+        arr[:n, 4:] = np.stack([r.table_row for r in reqs])
+        arr[:n, 2] = arr[np.arange(n), 4 + pos // bs] * bs + pos % bs
+        arr[:n, 3] = pos + 1
+        arr[n:, 0:2] = 0
+        arr[n:, 2] = -1
+        arr[n:, 3] = 0
+        return buf
+
+    def _run_packed(self, inp: torch.Tensor) -> torch.Tensor:
+        tokens = inp[:, 0].long()
+        positions, slots, lens = inp[:, 1].contiguous(), inp[:, 2].contiguous(), inp[:, 3].contiguous()
+        tables = inp[:, 4:]
+        return self._forward(tokens, positions, slots, tables, lens)
+
+    @torch.no_grad()
+    def _decode(self, reqs: List[_Req]) -> None:
+        t0 = time.perf_counter()
+        n = len(reqs)
+        A = self._bucket(n) if self.use_cuda_graph else n
+        host = self._decode_inputs(reqs, A)
+        if self.use_cuda_graph and self.greedy:
+            g = self._graphs.get(A)
+            if g is None:
+                g = self._capture(A, host)
+            g["inp"].copy_(host, non_blocking=True)
+            g["graph"].replay()
+            nxt = g["next"][:n].cpu().tolist()
+        else:
+            logits = self._run_packed(host.to(self.device, non_blocking=True))
+            nxt = self._pick(logits)[:n].cpu().tolist()
+        for r, t in zip(reqs, nxt):
+            self._emit(r, int(t))
+        self.stats["decode_tokens"] += n
+        self.stats["decode_s"] += time.perf_counter() - t0
+
+    def _capture(self, A: int, host: torch.Tensor) -> dict:
+        dev = self.device
+        g = {"inp": host.to(dev)}
+        stream = torch.cuda.Stream(device=dev)
+        stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(stream):
+            for _ in range(2):                                # warm-up: lazy allocations, attribute settings
+                logits = self._run_packed(g["inp"])
+                g["next"] = argmax_rows(logits)
+        torch.cuda.current_stream(dev).wait_stream(stream)
+        torch.cuda.synchronize(dev)
+        # the warm-up runs appended to the cache at the fed positions; the captured replay overwrites the same slots
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self._run_packed(g["inp"])
+            g["next"] = argmax_rows(logits)
+        g["graph"] = graph
+        self._graphs[A] = g
+        return g
+
+    def step(self) -> bool:
+        admitted = self._admit()
+        if admitted:
+            self._prefill(admitted)
+            self.running += [r for r in admitted if not r.finished]
+        live = [r for r in self.running if not r.finished]
+        if live:
+            self._decode(live)
+        self.running = [r for r in self.running if not r.finished]
+        self.steps += 1
+        return self.has_pending()
+
+    def run(self) -> None:
+        while self.has_pending():
+            self.step()
+
+    # ------------------------------------------------------------------ metrics
+    def metrics(self) -> dict:
+        done = [r for r in self.requests.values() if r.finished and r.t_first > 0]
+        ttft = sorted((r.t_first - r.t_submit) * 1e3 for r in done)
+        s = self.stats
+        return {
+            "requests": len(done),
+            "prefill_tok_s": s["prefill_tokens"] / s["prefill_s"] if s["prefill_s"] > 0 else 0.0,
+            "decode_tok_s": s["decode_tokens"] / s["decode_s"] if s["decode_s"] > 0 else 0.0,
+            "ttft_p50_ms": ttft[len(ttft) // 2] if ttft else 0.0,
+            "steps": self.steps,
+        }

@@ -378,3 +378,52 @@ def test_kv_append_paged_rope_and_quant(dev, int8):
     else:
         assert _rel_err(k_pool[blk, :, off], k_ref) < 1e-2
         assert torch.equal(v_pool[blk, :, off], qkv.view(T, H + 2 * Hkv, D)[:, H + Hkv:])
+
+
+def test_device_sampling_kernels(dev):
+    from tesseract_b200.serving import argmax_rows, sample_top_p_rows
+    logits = torch.randn(37, 5000, device=dev).bfloat16()
+    logits[3, 100] = logits[3, 4000] = 50.0
+    got = argmax_rows(logits)
+    ref = logits.float().argmax(-1)
+    assert int(got[3]) == 100
+    assert torch.equal(got.long(), ref) or (got.long() != ref).sum() <= 1
+    peaked = torch.full((8, 1000), -10.0, device=dev).bfloat16()
+    peaked[:, 7] = 5.0
+    peaked[:, 9] = 4.5
+    picks = torch.stack([sample_top_p_rows(peaked, 1.0, 0.9, 123, s) for s in range(40)])
+    assert set(picks.unique().tolist()) <= {7, 9} and (picks == 7).float().mean() > 0.4
+    a = sample_top_p_rows(logits, 0.8, 0.95, 5, 1)
+    b = sample_top_p_rows(logits, 0.8, 0.95, 5, 1)
+    assert torch.equal(a, b) and int(a.min()) >= 0 and int(a.max()) < 5000
+
+
+@pytest.mark.parametrize("kv_int8", [False, True])
+def test_serving_engine_graph_vs_eager_and_generate(dev, kv_int8):
+    from tesseract_b200.models import GenerateConfig, LlamaConfig, LlamaModel
+    from tesseract_b200.models.scheduler import EngineConfig
+    from tesseract_b200.serving import ServingEngine
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, intermediate_size=1024, max_position_embeddings=256, dtype=torch.bfloat16)
+    model = LlamaModel(cfg, device=dev, init_std=0.3, seed=2)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (5, 37, 64, 9, 130, 17)]
+    outs = {}
+    for graph in (True, False):
+        eng = ServingEngine(model, EngineConfig(block_size=16, num_blocks=64, max_seq_len=256, max_batch_size=4,
+                                                kv_int8=kv_int8), use_cuda_graph=graph)
+        ids = [eng.add_request(p, GenerateConfig(max_new_tokens=12)) for p in prompts]
+        eng.run()
+        assert eng.free_blocks() == 64
+        outs[graph] = [eng.result(i) for i in ids]
+        m = eng.metrics()
+        assert m["requests"] == len(prompts) and m["decode_tok_s"] > 0
+    assert outs[True] == outs[False]
+    _status_ok()
+    if not kv_int8:
+        agree = 0
+        for p, got in zip(prompts, outs[True]):
+            ref = model.generate(p, GenerateConfig(max_new_tokens=12))
+            assert len(got) == len(ref) and got[:len(p)] == p
+            agree += sum(int(a == b) for a, b in zip(got[len(p):], ref[len(p):]))
+        assert agree >= 0.7 * 12 * len(prompts), agree
