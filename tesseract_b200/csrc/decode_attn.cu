@@ -106,87 +106,99 @@ paged_decode_kernel(DecParams p) {
   }
 
   const int* table = p.tables + static_cast<long long>(a) * p.max_logical;
-  const int esz = INT8 ? 1 : static_cast<int>(sizeof(T));
-  // each warp step covers 4 tokens; the 4 warps interleave steps
-  for (int t0 = t_begin + warp * 4; t0 < t_end; t0 += kDecWarps * 4) {
-    const int t = t0 + grp;
-    const bool valid = t < t_end;
-    float kf[EPL], vf[EPL];
-    float ks = 1.f, vs = 1.f;
-    if (valid) {
-      int blk = table[t / p.bs];
-      blk = (blk < 0 || blk >= p.nb) ? 0 : blk;  // defence in depth, as in the reference kernels
-      const long long row = (static_cast<long long>(blk) * p.Hkv + hk) * p.bs + (t % p.bs);
-      const char* kp = static_cast<const char*>(p.k_pool) + (row * D + gl * EPL) * esz;
-      const char* vp = static_cast<const char*>(p.v_pool) + (row * D + gl * EPL) * esz;
-      if constexpr (INT8) {
-        if constexpr (EPL == 16) {
-          const uint4 kr = *reinterpret_cast<const uint4*>(kp);
-          const uint4 vr = *reinterpret_cast<const uint4*>(vp);
-          cvt16_i8(kr, kf);
-          cvt16_i8(vr, vf);
-        } else {
-          const uint2 kr = *reinterpret_cast<const uint2*>(kp);
-          const uint2 vr = *reinterpret_cast<const uint2*>(vp);
-          const int8_t* k8 = reinterpret_cast<const int8_t*>(&kr);
-          const int8_t* v8 = reinterpret_cast<const int8_t*>(&vr);
+  constexpr int kRaw = INT8 ? (EPL / 16 > 0 ? EPL / 16 : 1) : EPL / 8;  // 16-byte words per K (or V) slice
+  constexpr int U = 2;                                                   // tokens in flight per lane group
+  // Each warp iteration covers 8 tokens (two per 8-lane group). All loads of an iteration (K, V, scales, and
+  // the block ids of the NEXT iteration) are issued before any arithmetic, so ~128 B per lane are in flight.
+  auto block_of = [&](int t) -> int {
+    int blk = t < t_end ? table[t / p.bs] : 0;
+    return (blk < 0 || blk >= p.nb) ? 0 : blk;  // defence in depth, as in the reference kernels
+  };
+  int t0 = t_begin + warp * (4 * U);
+  int blk_next[U];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            kf[i] = static_cast<float>(k8[i]);
-            vf[i] = static_cast<float>(v8[i]);
+  for (int u = 0; u < U; ++u) blk_next[u] = block_of(t0 + u * 4 + grp);
+  for (; t0 < t_end; t0 += kDecWarps * 4 * U) {
+    uint4 kraw[U][kRaw], vraw[U][kRaw];
+    float ks[U], vs[U];
+    bool valid[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + u * 4 + grp;
+      valid[u] = t < t_end;
+      ks[u] = vs[u] = 1.f;
+      if (valid[u]) {
+        const long long row = (static_cast<long long>(blk_next[u]) * p.Hkv + hk) * p.bs + (t % p.bs);
+        const size_t off = (static_cast<size_t>(row) * D + gl * EPL) * (INT8 ? 1 : sizeof(T));
+        const char* kp = static_cast<const char*>(p.k_pool) + off;
+        const char* vp = static_cast<const char*>(p.v_pool) + off;
+        if constexpr (INT8 && EPL == 8) {
+          const uint2 k2 = *reinterpret_cast<const uint2*>(kp);
+          const uint2 v2 = *reinterpret_cast<const uint2*>(vp);
+          kraw[u][0] = make_uint4(k2.x, k2.y, 0, 0);
+          vraw[u][0] = make_uint4(v2.x, v2.y, 0, 0);
+        } else {
+#pragma unroll
+          for (int w = 0; w < kRaw; ++w) {
+            kraw[u][w] = *reinterpret_cast<const uint4*>(kp + w * 16);
+            vraw[u][w] = *reinterpret_cast<const uint4*>(vp + w * 16);
           }
         }
-        ks = p.k_scale[row];
-        vs = p.v_scale[row];
-      } else {
-        if constexpr (EPL == 16) {
-          const uint4 k0 = *reinterpret_cast<const uint4*>(kp);
-          const uint4 k1 = *reinterpret_cast<const uint4*>(kp + 16);
-          const uint4 v0 = *reinterpret_cast<const uint4*>(vp);
-          const uint4 v1 = *reinterpret_cast<const uint4*>(vp + 16);
-          cvt16<T>(k0, k1, kf);
-          cvt16<T>(v0, v1, vf);
-        } else {
-          const uint4 k0 = *reinterpret_cast<const uint4*>(kp);
-          const uint4 v0 = *reinterpret_cast<const uint4*>(vp);
-          const T* ke = reinterpret_cast<const T*>(&k0);
-          const T* ve = reinterpret_cast<const T*>(&v0);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            kf[i] = to_f32<T>(ke[i]);
-            vf[i] = to_f32<T>(ve[i]);
-          }
+        if constexpr (INT8) {
+          ks[u] = p.k_scale[row];
+          vs[u] = p.v_scale[row];
         }
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        kf[i] = 0.f;
-        vf[i] = 0.f;
       }
     }
 #pragma unroll
-    for (int g = 0; g < GH; ++g) {
-      float s = 0.f;
+    for (int u = 0; u < U; ++u) blk_next[u] = block_of(t0 + kDecWarps * 4 * U + u * 4 + grp);
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) s = fmaf(qf[g][i], kf[i], s);
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      s += __shfl_xor_sync(0xffffffffu, s, 4);
-      s *= ks;
-      if (valid) {
-        if (s > m[g]) {
-          const float corr = exp2f(m[g] - s);  // 0 when m was -inf
-          l[g] *= corr;
+    for (int u = 0; u < U; ++u) {
+      float kf[EPL], vf[EPL];
+      if constexpr (INT8) {
+        const int8_t* k8 = reinterpret_cast<const int8_t*>(&kraw[u][0]);
+        const int8_t* v8 = reinterpret_cast<const int8_t*>(&vraw[u][0]);
 #pragma unroll
-          for (int i = 0; i < EPL; ++i) o[g][i] *= corr;
-          m[g] = s;
+        for (int i = 0; i < EPL; ++i) {
+          kf[i] = valid[u] ? static_cast<float>(k8[i]) : 0.f;
+          vf[i] = valid[u] ? static_cast<float>(v8[i]) : 0.f;
         }
-        const float pr = exp2f(s - m[g]);
-        l[g] += pr;
-        const float pv = pr * vs;
+      } else {
+        const T* ke = reinterpret_cast<const T*>(&kraw[u][0]);
+        const T* ve = reinterpret_cast<const T*>(&vraw[u][0]);
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) o[g][i] = fmaf(pv, vf[i], o[g][i]);
+        for (int i = 0; i < EPL; ++i) {
+          kf[i] = valid[u] ? to_f32<T>(ke[i]) : 0.f;
+          vf[i] = valid[u] ? to_f32<T>(ve[i]) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GH; ++g) {
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; i += 2) {
+          s0 = fmaf(qf[g][i], kf[i], s0);
+          s1 = fmaf(qf[g][i + 1], kf[i + 1], s1);
+        }
+        float sc = s0 + s1;
+        sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+        sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+        sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+        sc *= ks[u];
+        if (valid[u]) {
+          if (sc > m[g]) {
+            const float corr = exp2f(m[g] - sc);  // 0 when m was -inf
+            l[g] *= corr;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) o[g][i] *= corr;
+            m[g] = sc;
+          }
+          const float pr = exp2f(sc - m[g]);
+          l[g] += pr;
+          const float pv = pr * vs[u];
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) o[g][i] = fmaf(pv, vf[i], o[g][i]);
+        }
       }
     }
   }
@@ -272,9 +284,10 @@ decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ 
 }
 
 int choose_splits(int A, int Hkv_groups, int max_len) {
-  const int target = sm_count() * 3;
+  // enough CTAs for ~6 per SM (they are latency-bound and small), but never chunks shorter than 256 keys
+  const int target = sm_count() * 6;
   int s = (target + A * Hkv_groups - 1) / (A * Hkv_groups);
-  const int max_s = max_len / 128 > 0 ? max_len / 128 : 1;
+  const int max_s = max_len / 256 > 0 ? max_len / 256 : 1;
   if (s > max_s) s = max_s;
   if (s > 64) s = 64;
   if (s < 1) s = 1;

@@ -26,7 +26,7 @@ struct GemmCfg {
   static constexpr int kStageBytesA = BM * BK * 2;
   static constexpr int kStageBytesB = BN * BK * 2;
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
-  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 8 : 10));
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
 };
@@ -48,7 +48,7 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
 template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ C,
-                 int M, int N, int K, long long ldc, int* status) {
+                 int M, int N, int K, long long ldc, int* status, int split_k) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
 
@@ -67,8 +67,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int num_m = (M + BM - 1) / BM;
   const int num_n = (N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
-  const int num_kb = (K + BK - 1) / BK;
+  // split_k > 1: work item t covers K slice (t % split_k) of output tile (t / split_k); slices are summed with
+  // fp32 atomics by the epilogue (ATOMIC_OUT instantiation, C zero-initialised by the caller)
+  const int num_tiles = num_m * num_n * split_k;
+  const int total_kb = (K + BK - 1) / BK;
+  const int kb_per = (total_kb + split_k - 1) / split_k;
 
   if (threadIdx.x == 0) {
     cta_abort = 0;
@@ -99,11 +102,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-        const TileCoord tc = tile_coord(t, num_m, num_n);
+        const TileCoord tc = tile_coord(t / split_k, num_m, num_n);
         const int m0 = tc.m_blk * BM;
         const int n0 = tc.n_blk * BN;
+        const int kb0 = (t % split_k) * kb_per;
+        const int kb1 = min(total_kb, kb0 + kb_per);
         bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &cta_abort, status);
           if (!ok) break;
           uint8_t* sA = smem + stage * Cfg::kStageBytes;
@@ -142,7 +147,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (t % split_k) * kb_per;
+        const int kb1 = min(total_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, &cta_abort, status);
           if (!ok) break;
           tc_fence_after();
@@ -154,7 +161,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                         : umma_smem_desc_sw128(a_base + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
                                         : umma_smem_desc_sw128(b_base + k * 32, 16, 1024);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
           if (++stage == STAGES) {
@@ -176,9 +183,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const TileCoord tc = tile_coord(t, num_m, num_n);
+      const TileCoord tc = tile_coord(t / split_k, num_m, num_n);
       const int m0 = tc.m_blk * BM;
       const int n0 = tc.n_blk * BN;
+      const bool empty_slice = (t % split_k) * kb_per >= total_kb;
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, &cta_abort, status)) break;
       tc_fence_after();
       const int row = m0 + row_in_tile;
@@ -221,6 +229,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int v = 0; v < 8; ++v) {
                 float4 o = make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
                                        __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
+                if (split_k > 1) {
+                  if (!empty_slice) atomicAdd(&dst[v], o);
+                  continue;
+                }
                 if constexpr (ACCUM) {
                   const float4 old = dst[v];
                   o.x += old.x;
@@ -236,6 +248,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int j = 0; j < 32; ++j) {
               if (col0 + j < N) {
                 float v = __uint_as_float(r[j]);
+                if constexpr (sizeof(OutT) == 4) {
+                  if (split_k > 1) {
+                    if (!empty_slice) atomicAdd(reinterpret_cast<float*>(crow) + col0 + j, v);
+                    continue;
+                  }
+                }
                 if constexpr (ACCUM) v += to_f32<OutT>(crow[col0 + j]);
                 crow[col0 + j] = from_f32<OutT>(v);
               }
@@ -303,7 +321,7 @@ bool cached_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
 
 template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
 int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int max_ctas,
-               cudaStream_t stream) {
+               cudaStream_t stream, int split_k = 1) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT, ACCUM>;
   static bool attr_set = false;
@@ -312,12 +330,12 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * split_k;
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(C), M, N, K, ldc,
-                                                        device_status_word());
+                                                        device_status_word(), split_k);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -350,7 +368,7 @@ int launch_major(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, i
 //   C is row-major [M, N] with row stride ldc; bf16, or fp32 when out_f32 != 0; accumulate != 0 adds
 //   into the existing contents of C.
 // Requirements: A and B 16-byte aligned with row strides that are multiples of 8 elements.
-// block_n: 0 = choose, else 64 / 128 / 256. max_ctas: 0 = one CTA per SM, else a cap (used when some SMs are
+// block_n: 0 = choose, else 32 / 64 / 128 / 256. max_ctas: 0 = one CTA per SM, else a cap (used when some SMs are
 // reserved for a concurrent communication kernel).
 // Returns 0, a cudaError_t, or -2 (bad argument) / -3 (tensor map encoding failed).
 TSB_EXPORT int tsb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
@@ -363,13 +381,18 @@ TSB_EXPORT int tsb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   int bn = block_n;
   if (bn == 0) {
     const int sms = sm_count();
-    const long long t256 = static_cast<long long>((M + BM - 1) / BM) * ((N + 255) / 256);
-    const long long t128 = static_cast<long long>((M + BM - 1) / BM) * ((N + 127) / 128);
-    if (N >= 256 && t256 >= sms) bn = 256;
-    else if (N >= 128 && t128 >= sms / 2) bn = 128;
-    else bn = (N >= 128 && t128 * 2 > ((M + BM - 1) / BM) * ((N + 63) / 64)) ? 128 : 64;
+    const long long mt = (M + BM - 1) / BM;
+    auto tiles = [&](int b) { return mt * ((N + b - 1) / b); };
+    // largest tile that still gives every SM work; decode-shaped calls (few rows) stream the weight matrix
+    // and want as many CTAs pulling on HBM as possible, so they go down to 32-column tiles
+    if (N >= 256 && tiles(256) >= sms) bn = 256;
+    else if (N >= 128 && tiles(128) >= sms) bn = 128;
+    else if (N >= 64 && tiles(64) >= sms) bn = 64;
+    else if (N >= 128 && tiles(128) * 2 >= sms && mt > 2) bn = 128;
+    else bn = (N >= 64 && tiles(32) > 2 * sms) ? 64 : 32;
   }
-  if (bn != 64 && bn != 128 && bn != 256) return -2;
+  if (bn == 32 && b_mn) bn = 64;  // an N-major B tile is built from 64-column (128-byte) boxes
+  if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return -2;
   CUtensorMap ta, tb;
   bool ok;
   if (!a_mn) ok = cached_tmap_2d(&ta, A, M, K, lda * 2, BM, BK);
@@ -382,6 +405,29 @@ TSB_EXPORT int tsb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   switch (bn) {
     case 256: return launch_major<256>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
     case 128: return launch_major<128>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
-    default: return launch_major<64>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
+    case 64: return launch_major<64>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
+    default: return launch_major<32>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
   }
+}
+
+// Split-K variant for decode-shaped calls (few rows, the weight matrix is streamed once): the K range is cut into
+// `split_k` slices that run as independent work items, so that all SMs pull on HBM, and their fp32 partial sums are
+// added into C32 with vector atomics. C32 (fp32 [M, N], row stride ldc) must be zero on entry. A is [M, K] row-major,
+// B is [N, K] (b_mn = 0) or [K, N] (b_mn = 1). block_n: 64 or 128.
+TSB_EXPORT int tsb_gemm_bf16_splitk(const void* A, const void* B, float* C32, int M, int N, int K, long long lda,
+                                    long long ldb, long long ldc, int b_mn, int split_k, int block_n, void* stream) {
+  using namespace tsb;
+  if (M <= 0 || N <= 0 || K <= 0 || split_k < 1 || split_k > 64) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % 8) || (ldb % 8) || (ldc % 4))
+    return -2;
+  const int bn = block_n == 64 ? 64 : 128;
+  CUtensorMap ta, tb;
+  if (!cached_tmap_2d(&ta, A, M, K, lda * 2, BM, BK)) return -3;
+  if (!(b_mn ? cached_tmap_2d(&tb, B, K, N, ldb * 2, BK, 64) : cached_tmap_2d(&tb, B, N, K, ldb * 2, bn, BK))) return -3;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 128)
+    return b_mn ? launch_cfg<128, false, true, float, false>(ta, tb, C32, M, N, K, ldc, 0, s, split_k)
+                : launch_cfg<128, false, false, float, false>(ta, tb, C32, M, N, K, ldc, 0, s, split_k);
+  return b_mn ? launch_cfg<64, false, true, float, false>(ta, tb, C32, M, N, K, ldc, 0, s, split_k)
+              : launch_cfg<64, false, false, float, false>(ta, tb, C32, M, N, K, ldc, 0, s, split_k);
 }

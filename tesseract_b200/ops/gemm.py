@@ -54,6 +54,35 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: boo
     return out
 
 
+_native.register_signatures({
+    "tsb_gemm_bf16_splitk": [_native.P, _native.P, _native.P, _native.I, _native.I, _native.I, _native.L, _native.L,
+                             _native.L, _native.I, _native.I, _native.I, _native.P],
+})
+
+
+def decode_linear(x: torch.Tensor, w: torch.Tensor, sm_count: int = 148) -> torch.Tensor:
+    """x [M, K] @ w [N, K]^T for decode-shaped calls (few rows): when the plain tiling would leave most SMs idle
+    the K range is split across CTAs (fp32 atomics into a zeroed buffer, then one cast), so that the whole GPU
+    streams the weight matrix."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not (_use_native(x) and M <= 512 and hasattr(_native.lib(), "tsb_gemm_bf16_splitk")):
+        return matmul_nt(x, w)
+    mt = (M + 127) // 128
+    tiles = mt * ((N + 127) // 128)
+    if tiles >= sm_count:
+        return gemm_bf16(x, w)
+    kb = (K + 63) // 64
+    split = max(1, min(kb // 4, (2 * sm_count + tiles - 1) // tiles, 16))
+    if split == 1:
+        return gemm_bf16(x, w, block_n=128)
+    out32 = torch.zeros((M, N), device=x.device, dtype=torch.float32)
+    rc = _native.lib().tsb_gemm_bf16_splitk(x.data_ptr(), w.data_ptr(), out32.data_ptr(), M, N, K, x.stride(0),
+                                            w.stride(0), N, 0, split, 128, _native.stream_ptr(x.device))
+    _native.check(rc, "tsb_gemm_bf16_splitk")
+    return out32.to(torch.bfloat16)
+
+
 def matmul_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """a [M,K] @ b[N,K]^T without autograd."""
     if _use_native(a):

@@ -188,7 +188,7 @@ class ServingEngine:
             h, res = ops.rms_norm(x, blk.norm_1.weight, blk.norm_1.eps), x
         else:
             h, res = ops.rms_norm(x, blk.norm_1.weight, blk.norm_1.eps, residual=res)
-        qkv = ops.gemm_bf16(h, self.wqkv[li]) if h.dtype == torch.bfloat16 else h @ self.wqkv[li].t()
+        qkv = self._mm(h, self.wqkv[li])
         T = qkv.shape[0]
         ks = self.k_scale[li] if self.k_scale is not None else None
         vs = self.v_scale[li] if self.v_scale is not None else None
@@ -217,11 +217,18 @@ class ServingEngine:
             for (a, b) in prefill_bounds:
                 outs.append(ops.flash_attention_packed(q4[a:b].unsqueeze(0), H, Hkv, causal=True).view(b - a, H * D))
             o = torch.cat(outs, dim=0) if len(outs) > 1 else outs[0]
-        a_out = ops.gemm_bf16(o, blk.attn.o_proj.weight)
+        a_out = self._mm(o, blk.attn.o_proj.weight)
         h2, res = ops.rms_norm(a_out, blk.norm_2.weight, blk.norm_2.eps, residual=res)
-        gu = ops.gemm_bf16(h2, self.wgu[li])
-        f = ops.gemm_bf16(ops.swiglu(gu), blk.ffn.down_proj.weight)
+        gu = self._mm(h2, self.wgu[li])
+        f = self._mm(ops.swiglu(gu), blk.ffn.down_proj.weight)
         return f, res
+
+    @staticmethod
+    def _mm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """x @ w^T: split-K streaming GEMM for decode-sized batches, the regular tcgen05 GEMM otherwise."""
+        if x.dtype != torch.bfloat16:
+            return x @ w.t()
+        return ops.decode_linear(x, w) if x.shape[0] <= 512 else ops.gemm_bf16(x, w)
 
     def _forward(self, tokens, positions, slots, tables, lens, prefill_bounds=None, last_rows=None):
         m = self.model
@@ -232,7 +239,7 @@ class ServingEngine:
         h, _ = ops.rms_norm(x, m.norm.weight, m.norm.eps, residual=res)
         if last_rows is not None:
             h = h.index_select(0, last_rows)
-        return ops.gemm_bf16(h.contiguous(), m.lm_head.weight)
+        return self._mm(h.contiguous(), m.lm_head.weight)
 
     def _pick(self, logits: torch.Tensor) -> torch.Tensor:
         if self.greedy:

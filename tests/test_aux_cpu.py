@@ -1,0 +1,93 @@
+"""Auxiliary subsystems on CPU: failure detection (host-injected faults only), checkpoints, metrics, graph capture."""
+import json
+
+import pytest
+import torch
+
+from tesseract_b200.graph import GraphScope, build_backward, run
+from tesseract_b200.models import LlamaConfig, LlamaModel
+from tesseract_b200.training import TrainConfig, Trainer
+from tesseract_b200.utils import checkpoint, env, metrics
+from tesseract_b200.utils.watchdog import DictStore, RankLost, RankWatchdog
+
+
+def test_watchdog_detects_silent_never_joined_and_failed_ranks():
+    store, now = DictStore(), [0.0]
+    clock = lambda: now[0]
+    a = RankWatchdog(store, 0, 3, timeout_s=5.0, clock=clock)
+    b = RankWatchdog(store, 1, 3, timeout_s=5.0, clock=clock)
+    a.check()                      # rank 2 has not joined yet: tolerated until the timeout
+    now[0] = 3.0
+    b.beat(); a.step()
+    now[0] = 6.0
+    b.beat()
+    with pytest.raises(RankLost) as e:   # rank 2 never joined
+        a.check()
+    assert e.value.rank == 2 and "never joined" in e.value.reason
+    c = RankWatchdog(store, 2, 3, timeout_s=5.0, clock=clock)
+    a._seen.clear(); a.check()
+    now[0] = 20.0
+    c.beat()
+    with pytest.raises(RankLost) as e:   # rank 1 stopped beating
+        a.check()
+    assert e.value.rank == 1
+    b.beat()
+    c.report_failure("ValueError: injected on the host")
+    with pytest.raises(RankLost) as e:   # rank 2 raised and told the others before their next launch
+        a.check()
+    assert e.value.rank == 2 and "injected" in e.value.reason
+
+
+def test_checkpoint_roundtrip_and_resume(tmp_path):
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, num_hidden_layers=2, num_attention_heads=4,
+                      intermediate_size=64, max_position_embeddings=32)
+    torch.manual_seed(0)
+    batch = torch.randint(0, 64, (2, 17))
+    m1 = LlamaModel(cfg, init_std=0.1, seed=1)
+    t1 = Trainer(m1, TrainConfig(lr=1e-2, micro_batch=2))
+    for _ in range(3):
+        t1.train_step(batch)
+    path = str(tmp_path / "ckpt.tsrct")
+    checkpoint.save_checkpoint(path, m1, t1)
+    man = json.load(open(path + "/manifest.json"))
+    assert man["format"] == "tsrct" and man["step"] == 3 and man["config"]["hidden_size"] == 32
+    after = [t1.train_step(batch) for _ in range(2)]
+    m2 = LlamaModel(cfg, init_std=0.1, seed=99)
+    t2 = Trainer(m2, TrainConfig(lr=1e-2, micro_batch=2))
+    checkpoint.load_checkpoint(path, m2, t2)
+    assert t2.steps_done == 3
+    resumed = [t2.train_step(batch) for _ in range(2)]
+    assert resumed == pytest.approx(after, abs=1e-6)
+
+
+def test_metrics_and_env(tmp_path):
+    p = str(tmp_path / "m.jsonl")
+    log = metrics.MetricsLogger(p)
+    log.log(step=1, tok_s=123.0)
+    line = log.bench_line("decode", tok_s=10, ttft_ms=1.5)
+    log.close()
+    rec = json.loads(open(p).read().strip())
+    assert rec["step"] == 1 and line.startswith("[bench] decode tok_s=10")
+    assert metrics.percentile([5, 1, 3], 50) == 3
+    assert env.get("TESSERACT_GEMM") in ("tcgen05", "cublas") and "TESSERACT_TP_COMM" in env.describe()
+
+
+def test_graph_capture_run_and_backward():
+    class MLP(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = torch.nn.Linear(4, 8), torch.nn.Linear(8, 2)
+
+        def forward(self, x):
+            return self.b(torch.relu(self.a(x))) + 1.0
+
+    m = MLP()
+    with GraphScope() as scope:
+        g = scope.trace(m)
+    assert g.op_kinds() == ["matmul", "relu", "matmul", "add"] and g.inputs == ["x"]
+    x = torch.randn(3, 4)
+    assert torch.equal(run(g, x), m(x))
+    (gx,) = build_backward(g)(x)
+    xr = x.clone().requires_grad_()
+    m(xr).sum().backward()
+    assert torch.allclose(gx, xr.grad)

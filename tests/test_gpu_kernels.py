@@ -31,7 +31,7 @@ def _rel_err(got, ref):
     return ((got.float() - ref.float()).norm() / ref.float().norm().clamp_min(1e-12)).item()
 
 
-GEMM_SHAPES = [(128, 128, 64), (128, 256, 128), (256, 512, 256), (384, 640, 192), (1024, 1024, 1024),
+GEMM_SHAPES = [(64, 4096, 512), (256, 6144, 1024), (128, 128, 64), (128, 256, 128), (256, 512, 256), (384, 640, 192), (1024, 1024, 1024),
                (200, 264, 136), (4096, 768, 512), (64, 4096, 4096)]
 
 
@@ -51,7 +51,7 @@ def test_gemm_layouts(dev, M, N, K, a_mn, b_mn):
     assert _rel_err(out, ref) < 6e-3, (M, N, K, a_mn, b_mn)
 
 
-@pytest.mark.parametrize("block_n", [64, 128, 256])
+@pytest.mark.parametrize("block_n", [32, 64, 128, 256])
 def test_gemm_block_sizes_and_fp32_accumulate(dev, block_n):
     from tesseract_b200.ops import gemm_bf16
     M, N, K = 512, 768, 320
@@ -427,3 +427,14 @@ def test_serving_engine_graph_vs_eager_and_generate(dev, kv_int8):
             assert len(got) == len(ref) and got[:len(p)] == p
             agree += sum(int(a == b) for a, b in zip(got[len(p):], ref[len(p):]))
         assert agree >= 0.7 * 12 * len(prompts), agree
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (64, 6144, 4096), (256, 4096, 14336), (37, 1000, 520)])
+def test_decode_linear_split_k(dev, M, N, K):
+    from tesseract_b200 import ops
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+    got = ops.decode_linear(x, w)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _rel_err(got, x.float() @ w.float().t()) < 8e-3
