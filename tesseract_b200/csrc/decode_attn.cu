@@ -20,6 +20,11 @@
 #include <mutex>
 
 namespace tsb {
+
+int paged_decode_mma_dispatch(const void* q, const void* k_pool, const void* v_pool, const int* tables, const int* lens,
+                              void* out, float* part_o, float* part_ml, int A, int H, int Hkv, int D, int bs, int nb,
+                              int max_logical, int splits, int gh, float scale_log2, int dtype, cudaStream_t s);
+
 namespace {
 
 // Scratch of tsb_paged_decode_static: lives in the library image, one copy per GPU that loads it.
@@ -294,10 +299,24 @@ int choose_splits(int A, int Hkv_groups, int max_len) {
   return s;
 }
 
+// Query heads per CTA and number of key splits for a problem; shared by both entry points so that they always
+// agree. Full-precision pools run on the tensor-core kernel (up to 8 heads per CTA), INT8 pools on the CUDA-core one.
+void decode_plan(int A, int H, int Hkv, int max_len, bool int8, int* gh, int* splits) {
+  const int G = H / Hkv;
+  int g;
+  if (int8) {
+    g = (G % 4 == 0) ? 4 : ((G % 2 == 0) ? 2 : 1);
+  } else {
+    g = G >= 8 ? 8 : G;
+    while (G % g) --g;
+  }
+  *gh = g;
+  *splits = choose_splits(A, Hkv * (G / g), max_len);
+}
+
 template <typename T, bool INT8, int D>
 int launch_decode(DecParams p, int G, cudaStream_t s) {
-  const int GH = G >= 4 ? 4 : G;  // G in {1, 2, 4, 8, 16, ...}: groups of at most 4 heads per CTA
-  if (G % GH) return -2;
+  const int GH = (G % 4 == 0) ? 4 : ((G % 2 == 0) ? 2 : 1);  // heads per CTA (decode_plan uses the same rule)
   dim3 grid(p.splits, p.Hkv * (G / GH), p.A);
   switch (GH) {
     case 4: paged_decode_kernel<T, INT8, D, 4><<<grid, kDecThreads, 0, s>>>(p); break;
@@ -442,17 +461,35 @@ TSB_EXPORT int tsb_paged_decode(const void* q, const void* k_pool, const void* v
   using namespace tsb;
   if (A <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || (D != 64 && D != 128) || bs <= 0) return -2;
   const int G = H / Hkv;
-  const int GH = G >= 4 ? 4 : G;
+  const bool i8 = k_scale != nullptr;
+  int gh = 1, splits = 1;
+  decode_plan(A, H, Hkv, max_len, i8, &gh, &splits);
+  float* part_o = scratch;
+  float* part_ml = scratch + static_cast<long long>(A) * H * splits * D;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!i8) {
+    int rc = paged_decode_mma_dispatch(q, k_pool, v_pool, tables, lens, out, part_o, part_ml, A, H, Hkv, D, bs, nb,
+                                       max_logical, splits, gh, scale * 1.4426950408889634f, dtype, s);
+    if (rc != -100) {
+      if (rc != 0 || splits == 1) return rc;
+      if (dtype == 1) {
+        if (D == 128) decode_merge_kernel<__nv_bfloat16, 128><<<A * H, 128, 0, s>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+        else decode_merge_kernel<__nv_bfloat16, 64><<<A * H, 64, 0, s>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+      } else {
+        if (D == 128) decode_merge_kernel<__half, 128><<<A * H, 128, 0, s>>>(part_o, part_ml, static_cast<__half*>(out), splits);
+        else decode_merge_kernel<__half, 64><<<A * H, 64, 0, s>>>(part_o, part_ml, static_cast<__half*>(out), splits);
+      }
+      return static_cast<int>(cudaGetLastError());
+    }
+  }
   DecParams p;
   p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.k_scale = k_scale; p.v_scale = v_scale;
   p.tables = tables; p.lens = lens; p.out = out;
   p.A = A; p.H = H; p.Hkv = Hkv; p.bs = bs; p.nb = nb; p.max_logical = max_logical;
-  p.splits = choose_splits(A, Hkv * (G / GH), max_len);
-  p.part_o = scratch;
-  p.part_ml = scratch + static_cast<long long>(A) * H * p.splits * D;
+  p.splits = splits;
+  p.part_o = part_o;
+  p.part_ml = part_ml;
   p.scale_log2 = scale * 1.4426950408889634f;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool i8 = k_scale != nullptr;
   if (dtype == 1) {
     if (D == 128) return i8 ? launch_decode<__nv_bfloat16, true, 128>(p, G, s) : launch_decode<__nv_bfloat16, false, 128>(p, G, s);
     return i8 ? launch_decode<__nv_bfloat16, true, 64>(p, G, s) : launch_decode<__nv_bfloat16, false, 64>(p, G, s);
@@ -521,9 +558,8 @@ TSB_EXPORT int tsb_paged_decode_static(const void* q, const void* k_pool, const 
       scratch_of_device[dev] = scratch;
     }
   }
-  const int G = H / Hkv;
-  const int GH = G >= 4 ? 4 : G;
-  const int splits = choose_splits(A, Hkv * (G / GH), max_len);
+  int gh = 1, splits = 1;
+  decode_plan(A, H, Hkv, max_len, k_scale != nullptr, &gh, &splits);
   const long long need = splits > 1 ? static_cast<long long>(A) * H * splits * (D + 2) : 0;
   if (need > TSB_STATIC_DECODE_SCRATCH_FLOATS) return TSB_ERR_STATIC_SCRATCH_TOO_SMALL;
   // Same code path as tsb_paged_decode from here on: identical split count, identical kernels.

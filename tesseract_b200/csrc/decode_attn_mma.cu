@@ -1,0 +1,314 @@
+// Split-K paged decode attention on tensor cores (warp-level mma.sync), full-precision KV.
+//
+// Decode attention is a stream over the KV cache: 512 bytes of K and V per (token, KV head) against a handful of
+// FMAs per byte. On CUDA cores those FMAs, the bf16 -> fp32 conversions and the shuffle reductions cost ~75 warp
+// instructions per token and cap the kernel near 2 TB/s; here the two products run on the tensor cores
+// (m16n8k16, the G <= 8 query heads of a GQA group padded to the 16-row M dimension) and K / V go global ->
+// shared with 16-byte cp.async in a three-stage per-warp ring, so the kernel is bound by HBM, not by issue slots.
+//
+// One CTA per (key split, KV head, request); its 4 warps take 16-token tiles round-robin. Per tile and warp:
+//   S[head, token]  = Q[head, :] . K[token, :]      ldmatrix (K row-major)       -> 2 x D/16 mma
+//   P               = exp2(S * c - m) with online (m, l) per head, kept in the accumulator layout,
+//                     which IS the A-operand layout of the next product (no shuffles, no shared memory)
+//   O[head, :]     += P[head, token] . V[token, :]   ldmatrix.trans (V row-major) -> D/8 mma
+// The warps' (m, l, O) are merged through shared memory and written as the split's partial (or the final output
+// when there is one split); the merge of splits is decode_merge_kernel of decode_attn.cu.
+// Same inputs, pool layout and clamping rules as tsb_paged_decode (src/cuda/PagedAttention.cu:88-171 is the
+// reference's one-CTA-per-(request, head) CUDA-core kernel).
+#include "common.cuh"
+
+namespace tsb {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kTile = 16;     // tokens per warp tile
+constexpr int kStagesD = 3;   // cp.async ring depth per warp
+
+template <typename T>
+struct MmaT;
+template <>
+struct MmaT<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) { return pack_bf16x2(lo, hi); }
+};
+template <>
+struct MmaT<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// 16-byte async copy; src_bytes = 0 zero-fills the destination (rows past the end of the sequence).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+struct MmaDecParams {
+  const void* q;
+  const void* k_pool;
+  const void* v_pool;
+  const int* tables;
+  const int* lens;
+  void* out;
+  float* part_o;
+  float* part_ml;
+  int A, H, Hkv, bs, nb, max_logical, splits, gh;  // gh = query heads per CTA (<= 8)
+  float scale_log2;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kWarps * 32)
+paged_decode_mma_kernel(MmaDecParams p) {
+  constexpr int kRowBytes = D * 2 + 16;           // padded row: consecutive rows fall into different 16-byte bank groups
+  constexpr int kTileBytes = kTile * kRowBytes;   // one K (or V) tile
+  constexpr int kStageBytes = 2 * kTileBytes;     // K then V
+  constexpr int kChunks = D * 2 / 16;             // 16-byte pieces per row
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+
+  const int split = blockIdx.x;
+  const int hgrp = blockIdx.y;
+  const int a = blockIdx.z;
+  const int G = p.H / p.Hkv;
+  const int sub = G / p.gh;
+  const int hk = hgrp / sub;
+  const int h0 = hk * G + (hgrp % sub) * p.gh;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  const int len = p.lens[a];
+  const int chunk = ((len + p.splits - 1) / p.splits + 15) & ~15;
+  const int t_begin = split * chunk;
+  const int t_end = min(len, t_begin + chunk);
+  const int n_tiles = t_end > t_begin ? (t_end - t_begin + kTile - 1) / kTile : 0;
+
+  uint8_t* wsmem = smem + warp * (kStagesD * kStageBytes);
+  const uint32_t wsmem_u32 = smem_u32(wsmem);
+  const int* table = p.tables + static_cast<long long>(a) * p.max_logical;
+
+  // Q as the A operand (rows = heads, padded to 16 with zeros): per k-step a0 = (head g, d 2t..2t+1), a2 = (+8)
+  uint32_t qa[D / 16][2];
+  {
+    const T* qrow = static_cast<const T*>(p.q) + (static_cast<long long>(a) * p.H + h0 + g) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      if (g < p.gh) {
+        qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
+        qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8);
+      } else {
+        qa[ks][0] = qa[ks][1] = 0u;
+      }
+    }
+  }
+  float o[D / 8][2];  // O[head g][d = nb*8 + 2t, +1]
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = 0.f;
+  float m_run = -INFINITY, l_part = 0.f;  // l_part: this lane's share of the row sum (reduced at the end)
+
+  // tiles of this warp: warp, warp + 4, ... ; `issue(j)` starts the copies of this warp's j-th tile
+  const int my_tiles = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
+  auto issue = [&](int j) {
+    const int tile = warp + j * kWarps;
+    const int tok0 = t_begin + tile * kTile;
+    const uint32_t dstK = wsmem_u32 + (j % kStagesD) * kStageBytes;
+    const uint32_t dstV = dstK + kTileBytes;
+#pragma unroll
+    for (int i = 0; i < kTile * kChunks / 32; ++i) {
+      const int c = lane + 32 * i;
+      const int r = c / kChunks, piece = c % kChunks;
+      const int t = tok0 + r;
+      const bool valid = t < t_end;
+      int blk = valid ? table[t / p.bs] : 0;
+      blk = (blk < 0 || blk >= p.nb) ? 0 : blk;
+      const long long row = (static_cast<long long>(blk) * p.Hkv + hk) * p.bs + (valid ? t % p.bs : 0);
+      const size_t off = (static_cast<size_t>(row) * D) * sizeof(T) + piece * 16;
+      const uint32_t d = r * kRowBytes + piece * 16;
+      cp_async16(dstK + d, static_cast<const char*>(p.k_pool) + off, valid ? 16 : 0);
+      cp_async16(dstV + d, static_cast<const char*>(p.v_pool) + off, valid ? 16 : 0);
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < kStagesD - 1; ++j) {
+    if (j < my_tiles) issue(j);
+    cp_async_commit();
+  }
+
+  for (int j = 0; j < my_tiles; ++j) {
+    if (j + kStagesD - 1 < my_tiles) issue(j + kStagesD - 1);
+    cp_async_commit();
+    cp_async_wait<kStagesD - 1>();
+    __syncwarp();
+    const uint32_t sK = wsmem_u32 + (j % kStagesD) * kStageBytes;
+    const uint32_t sV = sK + kTileBytes;
+    const int tok0 = t_begin + (warp + j * kWarps) * kTile;
+
+    // ---- S = Q K^T : two 8-token column blocks
+    float s[2][4];
+#pragma unroll
+    for (int b = 0; b < 2; ++b) s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      // matrices: (tokens 0-7, d 0-7), (tokens 0-7, d 8-15), (tokens 8-15, d 0-7), (tokens 8-15, d 8-15)
+      uint32_t kb[4];
+      const int mat = lane >> 3;
+      const int r = (mat >> 1) * 8 + (lane & 7);
+      ldsm_x4(kb, sK + r * kRowBytes + ks * 32 + (mat & 1) * 16);
+      const uint32_t afrag[4] = {qa[ks][0], 0u, qa[ks][1], 0u};
+      MmaT<T>::mma(s[0], afrag, kb[0], kb[1]);
+      MmaT<T>::mma(s[1], afrag, kb[2], kb[3]);
+    }
+    // ---- online softmax for head row g (rows g + 8 are padding); this lane holds tokens b*8 + 2t, +1
+    float mx = -INFINITY;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int t = tok0 + b * 8 + 2 * t4 + e;
+        s[b][e] = t < t_end ? s[b][e] * p.scale_log2 : -INFINITY;
+        mx = fmaxf(mx, s[b][e]);
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    const float corr = m_run == -INFINITY ? 0.f : exp2f(m_run - m_use);
+    uint32_t pa[4];
+    {
+      const float p00 = exp2f(s[0][0] - m_use), p01 = exp2f(s[0][1] - m_use);
+      const float p10 = exp2f(s[1][0] - m_use), p11 = exp2f(s[1][1] - m_use);
+      l_part = l_part * corr + (p00 + p01 + p10 + p11);
+      pa[0] = MmaT<T>::pack(p00, p01);  // (head g, tokens 2t, 2t+1)
+      pa[1] = 0u;                       // heads g + 8: padding
+      pa[2] = MmaT<T>::pack(p10, p11);  // (head g, tokens 8 + 2t, +1)
+      pa[3] = 0u;
+    }
+    m_run = m_new;
+    // ---- O = O * corr + P V
+#pragma unroll
+    for (int nb2 = 0; nb2 < D / 16; ++nb2) {
+      // matrices (transposed on load): (tokens 0-7, d 0-7), (tokens 8-15, d 0-7), (tokens 0-7, d 8-15), (tokens 8-15, d 8-15)
+      uint32_t vb[4];
+      const int mat = lane >> 3;
+      const int r = (mat & 1) * 8 + (lane & 7);
+      ldsm_x4_trans(vb, sV + r * kRowBytes + nb2 * 32 + (mat >> 1) * 16);
+      float c0[4] = {o[2 * nb2][0] * corr, o[2 * nb2][1] * corr, 0.f, 0.f};
+      float c1[4] = {o[2 * nb2 + 1][0] * corr, o[2 * nb2 + 1][1] * corr, 0.f, 0.f};
+      MmaT<T>::mma(c0, pa, vb[0], vb[1]);
+      MmaT<T>::mma(c1, pa, vb[2], vb[3]);
+      o[2 * nb2][0] = c0[0];
+      o[2 * nb2][1] = c0[1];
+      o[2 * nb2 + 1][0] = c1[0];
+      o[2 * nb2 + 1][1] = c1[1];
+    }
+    __syncwarp();  // the stage may be overwritten by the copies issued in the next iteration
+  }
+  cp_async_wait<0>();
+
+  // ---- finish the row sums, merge the 4 warps through shared memory
+  float l_run = l_part;
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  __syncthreads();  // every warp is done with its ring: reuse the front of the buffer
+  float* sm_o = reinterpret_cast<float*>(smem);               // [kWarps][8][D]
+  float* sm_m = sm_o + kWarps * 8 * D;                        // [kWarps][8]
+  float* sm_l = sm_m + kWarps * 8;
+  if (g < p.gh) {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      sm_o[(warp * 8 + g) * D + i * 8 + 2 * t4] = o[i][0];
+      sm_o[(warp * 8 + g) * D + i * 8 + 2 * t4 + 1] = o[i][1];
+    }
+    if (t4 == 0) {
+      sm_m[warp * 8 + g] = m_run;
+      sm_l[warp * 8 + g] = l_run;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < p.gh * D; idx += kWarps * 32) {
+    const int hh = idx / D, d = idx % D;
+    float nm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) nm = fmaxf(nm, sm_m[w * 8 + hh]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float mw = sm_m[w * 8 + hh];
+      const float c = mw == -INFINITY ? 0.f : exp2f(mw - nm);
+      acc += sm_o[(w * 8 + hh) * D + d] * c;
+      ll += sm_l[w * 8 + hh] * c;
+    }
+    const int h = h0 + hh;
+    if (p.splits == 1) {
+      static_cast<T*>(p.out)[(static_cast<long long>(a) * p.H + h) * D + d] = from_f32<T>(ll > 0.f ? acc / ll : 0.f);
+    } else {
+      const long long pi = (static_cast<long long>(a) * p.H + h) * p.splits + split;
+      p.part_o[pi * D + d] = acc;
+      if (d == 0) {
+        p.part_ml[pi * 2] = nm;
+        p.part_ml[pi * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
+template <typename T, int D>
+int launch_mma(const MmaDecParams& p, cudaStream_t s) {
+  constexpr int kRowBytes = D * 2 + 16;
+  constexpr int ring = kWarps * kStagesD * 2 * kTile * kRowBytes;
+  constexpr int merge = (kWarps * 8 * D + 2 * kWarps * 8) * 4;
+  constexpr int smem = (ring > merge ? ring : merge) + 128;
+  auto kern = paged_decode_mma_kernel<T, D>;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr = true;
+  }
+  const int G = p.H / p.Hkv;
+  dim3 grid(p.splits, p.Hkv * (G / p.gh), p.A);
+  kern<<<grid, kWarps * 32, smem, s>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+// Called by tsb_paged_decode for bf16 / fp16 pools. Returns -100 when the shape is not covered here.
+int paged_decode_mma_dispatch(const void* q, const void* k_pool, const void* v_pool, const int* tables, const int* lens,
+                              void* out, float* part_o, float* part_ml, int A, int H, int Hkv, int D, int bs, int nb,
+                              int max_logical, int splits, int gh, float scale_log2, int dtype, cudaStream_t s) {
+  if (gh > 8 || (D != 64 && D != 128)) return -100;
+  MmaDecParams p;
+  p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.tables = tables; p.lens = lens; p.out = out;
+  p.part_o = part_o; p.part_ml = part_ml;
+  p.A = A; p.H = H; p.Hkv = Hkv; p.bs = bs; p.nb = nb; p.max_logical = max_logical; p.splits = splits; p.gh = gh;
+  p.scale_log2 = scale_log2;
+  if (dtype == 1) return D == 128 ? launch_mma<__nv_bfloat16, 128>(p, s) : launch_mma<__nv_bfloat16, 64>(p, s);
+  if (dtype == 2) return D == 128 ? launch_mma<__half, 128>(p, s) : launch_mma<__half, 64>(p, s);
+  return -100;
+}
+
+}  // namespace tsb

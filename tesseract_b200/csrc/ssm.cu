@@ -1,0 +1,226 @@
+// State-space kernels for the Mamba block: chunkwise selective scan (S6 recurrence) and depthwise causal conv1d
+// (optionally fused with SiLU).
+//
+//   h_t = exp(delta_t * A) * h_{t-1} + delta_t * B_t * u_t ;   y_t = <h_t, C_t> + D * u_t
+// u, delta, y: [B, L, d] (fp32 or bf16); A: [d, N] fp32; Bm, Cm: [B, L, N]; D: [d] fp32; state: [B, d, N] fp32.
+//
+// The recurrence is linear in h, so a sequence is cut into chunks of 64 steps that are scanned in parallel:
+//   pass 1  per (batch, chunk, channel): scan from a zero state -> local end state, sum of delta over the chunk
+//           (the chunk's decay is exp(A * sum delta), so one float per channel replaces N decay factors);
+//   pass 2  per (batch, channel, state): walk the chunks, turning local end states into chunk START states;
+//   pass 3  per (batch, chunk, channel): rescan from the start state and emit y.
+// Short sequences (decode steps, L <= 64) run as one pass with the state in registers. The reference has the same
+// three-pass structure with chunk 128 for fp32 prefill only (src/cuda/SelectiveScan.cu:95-228, N <= 32) and a
+// one-thread-per-output conv (src/cuda/CausalConv1d.cu:16-36).
+#include "common.cuh"
+
+namespace tsb {
+namespace {
+
+constexpr int kChunk = 64;
+constexpr int kScanThreads = 128;
+
+// Scan `steps` time steps of channel `ch` starting at t0 from the state in h[]; optionally emit y.
+template <typename T, int NMAX, bool EMIT>
+__device__ __forceinline__ float scan_steps(const T* __restrict__ u, const T* __restrict__ delta,
+                                            const float* __restrict__ Arow, const T* __restrict__ Bm,
+                                            const T* __restrict__ Cm, float Dval, T* __restrict__ y, float (&h)[NMAX],
+                                            long long base_bl, int t0, int steps, int d, int ch, int N) {
+  float sum_delta = 0.f;
+  float a[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) a[n] = n < N ? Arow[n] : 0.f;
+  for (int s = 0; s < steps; ++s) {
+    const long long bl = base_bl + t0 + s;  // flattened (batch, time)
+    const float dt = to_f32<T>(delta[bl * d + ch]);
+    const float uv = to_f32<T>(u[bl * d + ch]);
+    sum_delta += dt;
+    const float du = dt * uv;
+    float acc = 0.f;
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      if (n < N) {
+        h[n] = __expf(dt * a[n]) * h[n] + du * to_f32<T>(Bm[bl * N + n]);
+        if (EMIT) acc += h[n] * to_f32<T>(Cm[bl * N + n]);
+      }
+    }
+    if (EMIT) y[bl * d + ch] = from_f32<T>(acc + Dval * uv);
+  }
+  return sum_delta;
+}
+
+// One pass: thread per (batch, channel); state in registers. Used for L <= kChunk.
+template <typename T, int NMAX>
+__global__ void __launch_bounds__(kScanThreads)
+scan_direct_kernel(const T* u, const T* delta, const float* A, const T* Bm, const T* Cm, const float* Dv,
+                   const float* state_in, T* y, float* state_out, int Bsz, int L, int d, int N) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= Bsz * d) return;
+  const int b = idx / d, ch = idx % d;
+  float h[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) h[n] = (state_in && n < N) ? state_in[(static_cast<long long>(b) * d + ch) * N + n] : 0.f;
+  scan_steps<T, NMAX, true>(u, delta, A + static_cast<long long>(ch) * N, Bm, Cm, Dv[ch], y, h,
+                            static_cast<long long>(b) * L, 0, L, d, ch, N);
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n)
+    if (n < N) state_out[(static_cast<long long>(b) * d + ch) * N + n] = h[n];
+}
+
+// pass 1: h_loc[b, c, n, ch] = end state of chunk c scanned from zero; sdelta[b, c, ch] = sum of delta.
+template <typename T, int NMAX>
+__global__ void __launch_bounds__(kScanThreads)
+scan_local_kernel(const T* u, const T* delta, const float* A, const T* Bm, float* h_loc, float* sdelta, int Bsz, int L,
+                  int d, int N, int nC) {
+  const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (idx >= static_cast<long long>(Bsz) * nC * d) return;
+  const int ch = static_cast<int>(idx % d);
+  const int c = static_cast<int>((idx / d) % nC);
+  const int b = static_cast<int>(idx / (static_cast<long long>(d) * nC));
+  float h[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) h[n] = 0.f;
+  const int t0 = c * kChunk, steps = min(kChunk, L - t0);
+  const float sd = scan_steps<T, NMAX, false>(u, delta, A + static_cast<long long>(ch) * N, Bm, nullptr, 0.f, nullptr, h,
+                                              static_cast<long long>(b) * L, t0, steps, d, ch, N);
+  const long long bc = static_cast<long long>(b) * nC + c;
+  sdelta[bc * d + ch] = sd;
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n)
+    if (n < N) h_loc[(bc * N + n) * d + ch] = h[n];
+}
+
+// pass 2: sequential over chunks per (b, ch, n): local end states become chunk start states; final state out.
+__global__ void __launch_bounds__(kScanThreads)
+scan_combine_kernel(const float* A, float* h_loc, const float* sdelta, const float* state_in, float* state_out, int Bsz,
+                    int d, int N, int nC) {
+  const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (idx >= static_cast<long long>(Bsz) * N * d) return;
+  const int ch = static_cast<int>(idx % d);
+  const int n = static_cast<int>((idx / d) % N);
+  const int b = static_cast<int>(idx / (static_cast<long long>(d) * N));
+  const float a = A[static_cast<long long>(ch) * N + n];
+  float h = state_in ? state_in[(static_cast<long long>(b) * d + ch) * N + n] : 0.f;
+  for (int c = 0; c < nC; ++c) {
+    const long long bc = static_cast<long long>(b) * nC + c;
+    const long long at = (bc * N + n) * d + ch;
+    const float loc = h_loc[at];
+    h_loc[at] = h;
+    h = __expf(a * sdelta[bc * d + ch]) * h + loc;
+  }
+  state_out[(static_cast<long long>(b) * d + ch) * N + n] = h;
+}
+
+// pass 3: rescan every chunk from its start state and emit y.
+template <typename T, int NMAX>
+__global__ void __launch_bounds__(kScanThreads)
+scan_output_kernel(const T* u, const T* delta, const float* A, const T* Bm, const T* Cm, const float* Dv,
+                   const float* h_start, T* y, int Bsz, int L, int d, int N, int nC) {
+  const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (idx >= static_cast<long long>(Bsz) * nC * d) return;
+  const int ch = static_cast<int>(idx % d);
+  const int c = static_cast<int>((idx / d) % nC);
+  const int b = static_cast<int>(idx / (static_cast<long long>(d) * nC));
+  const long long bc = static_cast<long long>(b) * nC + c;
+  float h[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) h[n] = n < N ? h_start[(bc * N + n) * d + ch] : 0.f;
+  const int t0 = c * kChunk, steps = min(kChunk, L - t0);
+  scan_steps<T, NMAX, true>(u, delta, A + static_cast<long long>(ch) * N, Bm, Cm, Dv[ch], y, h,
+                            static_cast<long long>(b) * L, t0, steps, d, ch, N);
+}
+
+template <typename T, int NMAX>
+int run_scan(const void* u, const void* delta, const float* A, const void* Bm, const void* Cm, const float* Dv,
+             const float* state_in, void* y, float* state_out, float* scratch, int Bsz, int L, int d, int N,
+             cudaStream_t s) {
+  const T* u_ = static_cast<const T*>(u);
+  const T* dl = static_cast<const T*>(delta);
+  const T* b_ = static_cast<const T*>(Bm);
+  const T* c_ = static_cast<const T*>(Cm);
+  T* y_ = static_cast<T*>(y);
+  if (L <= kChunk) {
+    const int blocks = (Bsz * d + kScanThreads - 1) / kScanThreads;
+    scan_direct_kernel<T, NMAX><<<blocks, kScanThreads, 0, s>>>(u_, dl, A, b_, c_, Dv, state_in, y_, state_out, Bsz, L, d, N);
+    return static_cast<int>(cudaGetLastError());
+  }
+  const int nC = (L + kChunk - 1) / kChunk;
+  float* h_loc = scratch;
+  float* sdelta = scratch + static_cast<long long>(Bsz) * nC * N * d;
+  const long long work = static_cast<long long>(Bsz) * nC * d;
+  const unsigned blocks = static_cast<unsigned>((work + kScanThreads - 1) / kScanThreads);
+  scan_local_kernel<T, NMAX><<<blocks, kScanThreads, 0, s>>>(u_, dl, A, b_, h_loc, sdelta, Bsz, L, d, N, nC);
+  const long long work2 = static_cast<long long>(Bsz) * N * d;
+  scan_combine_kernel<<<static_cast<unsigned>((work2 + kScanThreads - 1) / kScanThreads), kScanThreads, 0, s>>>(
+      A, h_loc, sdelta, state_in, state_out, Bsz, d, N, nC);
+  scan_output_kernel<T, NMAX><<<blocks, kScanThreads, 0, s>>>(u_, dl, A, b_, c_, Dv, h_loc, y_, Bsz, L, d, N, nC);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// y[b, t, c] = bias[c] + sum_k w[c, k] * x[b, t - (K - 1) + k, c]   (+ SiLU)
+template <typename T>
+__global__ void __launch_bounds__(256)
+causal_conv1d_kernel(const T* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                     T* __restrict__ out, int Bsz, int L, int C, int K, int silu) {
+  const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long total = static_cast<long long>(Bsz) * L * C;
+  if (idx >= total) return;
+  const int c = static_cast<int>(idx % C);
+  const int t = static_cast<int>((idx / C) % L);
+  const long long b = idx / (static_cast<long long>(C) * L);
+  float acc = bias[c];
+  for (int k = 0; k < K; ++k) {
+    const int ts = t - (K - 1) + k;
+    if (ts >= 0) acc += w[c * K + k] * to_f32<T>(x[(b * L + ts) * C + c]);
+  }
+  if (silu) acc = acc / (1.f + __expf(-acc));
+  out[idx] = from_f32<T>(acc);
+}
+
+}  // namespace
+}  // namespace tsb
+
+// fp32 scratch elements tsb_selective_scan needs (0 for L <= 64).
+TSB_EXPORT long long tsb_selective_scan_scratch_floats(int Bsz, int L, int d, int N) {
+  if (L <= tsb::kChunk) return 0;
+  const long long nC = (L + tsb::kChunk - 1) / tsb::kChunk;
+  return static_cast<long long>(Bsz) * nC * d * (N + 1);
+}
+
+// dtype of u / delta / Bm / Cm / y: 0 = fp32, 1 = bf16. N <= 64. state_in may be NULL (zero state).
+TSB_EXPORT int tsb_selective_scan(const void* u, const void* delta, const float* A, const void* Bm, const void* Cm,
+                                  const float* Dv, const float* state_in, void* y, float* state_out, float* scratch,
+                                  int Bsz, int L, int d, int N, int dtype, int flags, void* stream) {
+  using namespace tsb;
+  (void)flags;
+  if (Bsz <= 0 || L <= 0 || d <= 0 || N <= 0 || N > 64) return -2;
+  if (L > kChunk && !scratch) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define TSB_SCAN(TT)                                                                                              \
+  (N <= 16 ? run_scan<TT, 16>(u, delta, A, Bm, Cm, Dv, state_in, y, state_out, scratch, Bsz, L, d, N, s)          \
+           : N <= 32 ? run_scan<TT, 32>(u, delta, A, Bm, Cm, Dv, state_in, y, state_out, scratch, Bsz, L, d, N, s) \
+                     : run_scan<TT, 64>(u, delta, A, Bm, Cm, Dv, state_in, y, state_out, scratch, Bsz, L, d, N, s))
+  if (dtype == 0) return TSB_SCAN(float);
+  if (dtype == 1) return TSB_SCAN(__nv_bfloat16);
+#undef TSB_SCAN
+  return -2;
+}
+
+// x, out: [B, L, C] (fp32 or bf16); w [C, K] fp32; bias [C] fp32. `state` is reserved (pass NULL).
+TSB_EXPORT int tsb_causal_conv1d(const void* x, const float* w, const float* bias, const void* state, void* out,
+                                 int Bsz, int L, int C, int K, int silu, int dtype, void* stream) {
+  using namespace tsb;
+  (void)state;
+  if (Bsz <= 0 || L <= 0 || C <= 0 || K <= 0) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long total = static_cast<long long>(Bsz) * L * C;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  if (dtype == 0)
+    causal_conv1d_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(x), w, bias, static_cast<float*>(out), Bsz, L, C, K, silu);
+  else if (dtype == 1)
+    causal_conv1d_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), w, bias,
+                                                                static_cast<__nv_bfloat16*>(out), Bsz, L, C, K, silu);
+  else
+    return -2;
+  return static_cast<int>(cudaGetLastError());
+}

@@ -24,6 +24,10 @@ from .modules import FeedForward, Linear, Module, ModuleList
 def route_topk(logits: torch.Tensor, k: int):
     """Router: returns (probs [T, E] fp32, top-k expert ids [T, k] sorted by (value desc, index asc),
     renormalised gates [T, k])."""
+    if (logits.is_cuda and not torch.is_grad_enabled() and logits.shape[-1] <= 256
+            and logits.dtype in (torch.float32, torch.bfloat16, torch.float16)):
+        probs, idx, gates, _ = ops.moe.route_native(logits, k)
+        return probs, idx, gates
     probs = torch.softmax(logits.float(), dim=-1)
     order = torch.sort(probs, dim=-1, descending=True, stable=True)
     idx = order.indices[:, :k]

@@ -10,8 +10,47 @@ from __future__ import annotations
 
 import torch
 
+from .. import _native
+from .._native import check, lib, stream_ptr
 from .gemm import gemm_bf16, linear
 from .fused import swiglu
+
+P, I = _native.P, _native.I
+_native.register_signatures({
+    "tsb_moe_route": [P, P, P, P, P, I, I, I, I, P],
+    "tsb_moe_sort": [P, P, P, P, P, P, I, I, I, P],
+})
+
+
+def route_native(logits: torch.Tensor, k: int, want_probs: bool = True):
+    """Device router (no autograd): returns (probs [T, E] fp32 or None, idx int64 [T, k], gates fp32 [T, k],
+    counts int32 [E])."""
+    T, E = logits.shape
+    lg = logits.contiguous()
+    idx = torch.empty((T, k), dtype=torch.int32, device=lg.device)
+    gates = torch.empty((T, k), dtype=torch.float32, device=lg.device)
+    probs = torch.empty((T, E), dtype=torch.float32, device=lg.device) if want_probs else None
+    counts = torch.zeros(E, dtype=torch.int32, device=lg.device)
+    check(lib().tsb_moe_route(lg.data_ptr(), idx.data_ptr(), gates.data_ptr(),
+                              probs.data_ptr() if probs is not None else None, counts.data_ptr(), T, E, k,
+                              _native.dtype_code(lg.dtype), stream_ptr(lg.device)), "tsb_moe_route")
+    return probs, idx.long(), gates, counts
+
+
+def sort_by_expert(idx: torch.Tensor, counts: torch.Tensor):
+    """Expert-sorted permutation of the T * k assignments, computed on the device.
+    Returns (offsets int32 [E + 1], sorted_pos int32 [T * k], sorted_token int32 [T * k])."""
+    T, k = idx.shape
+    E = counts.shape[0]
+    idx32 = idx.to(torch.int32).contiguous()
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=idx.device)
+    cursor = torch.empty(E, dtype=torch.int32, device=idx.device)
+    pos = torch.empty(T * k, dtype=torch.int32, device=idx.device)
+    tok = torch.empty(T * k, dtype=torch.int32, device=idx.device)
+    check(lib().tsb_moe_sort(idx32.data_ptr(), counts.data_ptr(), offsets.data_ptr(), cursor.data_ptr(), pos.data_ptr(),
+                             tok.data_ptr(), T, E, k, stream_ptr(idx.device)), "tsb_moe_sort")
+    _native.add_launches(1)
+    return offsets, pos, tok
 
 
 def grouped_path_ok(x2: torch.Tensor, moe) -> bool:

@@ -438,3 +438,79 @@ def test_decode_linear_split_k(dev, M, N, K):
     torch.cuda.synchronize()
     _status_ok()
     assert _rel_err(got, x.float() @ w.float().t()) < 8e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,L,d,N", [(2, 1, 64, 16), (1, 50, 96, 8), (2, 300, 128, 16), (1, 1000, 64, 32)])
+def test_selective_scan_and_conv1d(dev, dtype, B, L, d, N):
+    from tesseract_b200.ops import ssm
+    g = torch.Generator(device=dev).manual_seed(L + N)
+    u = torch.randn(B, L, d, device=dev, generator=g).to(dtype)
+    delta = torch.nn.functional.softplus(torch.randn(B, L, d, device=dev, generator=g)).to(dtype) * 0.1
+    A = -torch.exp(torch.randn(d, N, device=dev, generator=g) * 0.3)
+    Bm = torch.randn(B, L, N, device=dev, generator=g).to(dtype)
+    Cm = torch.randn(B, L, N, device=dev, generator=g).to(dtype)
+    D = torch.randn(d, device=dev, generator=g)
+    st = torch.randn(B, d, N, device=dev, generator=g)
+    y, s_out = ssm.selective_scan(u, delta, A, Bm, Cm, D, st)
+    yr, sr = ssm.selective_scan_ref(u.float(), delta.float(), A, Bm.float(), Cm.float(), D, st)
+    tol = 3e-2 if dtype == torch.bfloat16 else 2e-4
+    assert _rel_err(y, yr) < tol and _rel_err(s_out, sr) < tol
+    w = torch.randn(d, 4, device=dev, generator=g)
+    bias = torch.randn(d, device=dev, generator=g)
+    for silu in (False, True):
+        got = ssm.causal_conv1d(u, w, bias, silu=silu)
+        ref = ssm.causal_conv1d_ref(u.float(), w, bias, silu=silu)
+        assert _rel_err(got, ref) < (2e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M", [1, 3, 16])
+def test_quantized_gemv(dev, dtype, M):
+    from tesseract_b200.nn import Linear
+    from tesseract_b200.quant import QuantizedLinear, QuantizedLinearInt4G, unpack_int4_group
+    lin = Linear(1024, 768, bias=True)
+    x = torch.randn(M, 1024)
+    q8 = QuantizedLinear.from_linear(lin).to(dev)
+    q4 = QuantizedLinearInt4G.from_linear(lin, 128).to(dev)
+    if dtype != torch.float32:
+        q8.bias.data, q4.bias.data = q8.bias.data.to(dtype), q4.bias.data.to(dtype)
+    xd = x.to(dev).to(dtype)
+    w8 = q8.q_weight.float() * q8.weight_scale[:, None]
+    w4 = unpack_int4_group(q4.q_weight.cpu(), q4.weight_scale.cpu(), 128).to(dev)
+    tol = 1.5e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel_err(q8(xd), xd.float() @ w8.t() + q8.bias.float()) < tol
+    assert _rel_err(q4(xd), xd.float() @ w4.t() + q4.bias.float()) < tol
+
+
+def test_moe_router_and_sort(dev):
+    from tesseract_b200.nn.moe import route_topk
+    from tesseract_b200.ops import moe
+    T, E, k = 777, 8, 2
+    logits = torch.randn(T, E, device=dev)
+    logits[5, 3] = logits[5, 6] = 4.0          # tie: lower index first
+    probs, idx, gates, counts = moe.route_native(logits, k)
+    with torch.enable_grad():
+        pr, ir, gr = route_topk(logits.requires_grad_(), k)
+    assert torch.allclose(probs, pr, atol=1e-6) and torch.equal(idx, ir) and torch.allclose(gates, gr, atol=1e-6)
+    assert idx[5].tolist() == [3, 6]
+    assert torch.equal(counts.long(), torch.bincount(idx.reshape(-1), minlength=E))
+    offsets, pos, tok = moe.sort_by_expert(idx, counts)
+    assert offsets.tolist() == [0] + torch.cumsum(counts, 0).tolist()
+    flat_e = idx.reshape(-1)
+    assert sorted(pos.tolist()) == list(range(T * k))
+    assert torch.equal(tok[pos.long()].long(), torch.arange(T * k, device=dev) // k)
+    for e in range(E):
+        rows = pos[flat_e == e]
+        assert int(rows.min()) >= offsets[e] and int(rows.max()) < offsets[e + 1]
+
+
+def test_moe_layer_gpu_matches_dense_reference(dev):
+    from tesseract_b200.nn.moe import MoEFeedForward
+    torch.manual_seed(0)
+    moe_l = MoEFeedForward(256, 512, num_experts=4, num_experts_per_tok=2, dtype=torch.bfloat16, device=dev)
+    x = torch.randn(3, 40, 256, device=dev).bfloat16()
+    with torch.no_grad():
+        out = moe_l(x)
+        ref = moe_l.forward_dense_reference(x)
+    assert _rel_err(out, ref) < 3e-2
