@@ -21,8 +21,8 @@
 
 namespace tsb {
 
-int paged_decode_mma_dispatch(const void* q, const void* k_pool, const void* v_pool, const int* tables, const int* lens,
-                              void* out, float* part_o, float* part_ml, int A, int H, int Hkv, int D, int bs, int nb,
+int paged_decode_mma_dispatch(const void* q, const void* k_pool, const void* v_pool, const float* k_scale,
+                              const float* v_scale, const int* tables, const int* lens, void* out, float* part_o, float* part_ml, int A, int H, int Hkv, int D, int bs, int nb,
                               int max_logical, int splits, int gh, float scale_log2, int dtype, cudaStream_t s);
 
 namespace {
@@ -303,13 +303,9 @@ int choose_splits(int A, int Hkv_groups, int max_len) {
 // agree. Full-precision pools run on the tensor-core kernel (up to 8 heads per CTA), INT8 pools on the CUDA-core one.
 void decode_plan(int A, int H, int Hkv, int max_len, bool int8, int* gh, int* splits) {
   const int G = H / Hkv;
-  int g;
-  if (int8) {
-    g = (G % 4 == 0) ? 4 : ((G % 2 == 0) ? 2 : 1);
-  } else {
-    g = G >= 8 ? 8 : G;
-    while (G % g) --g;
-  }
+  (void)int8;  // both KV formats run on the tensor-core kernel: up to 8 query heads per CTA
+  int g = G >= 8 ? 8 : G;
+  while (G % g) --g;
   *gh = g;
   *splits = choose_splits(A, Hkv * (G / g), max_len);
 }
@@ -467,8 +463,8 @@ TSB_EXPORT int tsb_paged_decode(const void* q, const void* k_pool, const void* v
   float* part_o = scratch;
   float* part_ml = scratch + static_cast<long long>(A) * H * splits * D;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (!i8) {
-    int rc = paged_decode_mma_dispatch(q, k_pool, v_pool, tables, lens, out, part_o, part_ml, A, H, Hkv, D, bs, nb,
+  {
+    int rc = paged_decode_mma_dispatch(q, k_pool, v_pool, k_scale, v_scale, tables, lens, out, part_o, part_ml, A, H, Hkv, D, bs, nb,
                                        max_logical, splits, gh, scale * 1.4426950408889634f, dtype, s);
     if (rc != -100) {
       if (rc != 0 || splits == 1) return rc;

@@ -1,4 +1,4 @@
-// Split-K paged decode attention on tensor cores (warp-level mma.sync), full-precision KV.
+// Split-K paged decode attention on tensor cores (warp-level mma.sync), bf16 / fp16 or INT8 KV.
 //
 // Decode attention is a stream over the KV cache: 512 bytes of K and V per (token, KV head) against a handful of
 // FMAs per byte. On CUDA cores those FMAs, the bf16 -> fp32 conversions and the shuffle reductions cost ~75 warp
@@ -70,6 +70,8 @@ struct MmaDecParams {
   const void* q;
   const void* k_pool;
   const void* v_pool;
+  const float* k_scale;  // INT8 pools: per-(token, head) scales, else null
+  const float* v_scale;
   const int* tables;
   const int* lens;
   void* out;
@@ -79,13 +81,20 @@ struct MmaDecParams {
   float scale_log2;
 };
 
-template <typename T, int D>
+// INT8 pools: the raw int8 rows (and their scales) travel through the cp.async ring and are widened to T in a
+// per-warp conversion buffer right before the MMAs; int8 values are exact in bf16 / fp16, K scales multiply S after
+// the product and V scales multiply P before it, so no precision is lost to the staging.
+template <typename T, int D, bool INT8>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_mma_kernel(MmaDecParams p) {
   constexpr int kRowBytes = D * 2 + 16;           // padded row: consecutive rows fall into different 16-byte bank groups
-  constexpr int kTileBytes = kTile * kRowBytes;   // one K (or V) tile
-  constexpr int kStageBytes = 2 * kTileBytes;     // K then V
-  constexpr int kChunks = D * 2 / 16;             // 16-byte pieces per row
+  constexpr int kTileBytes = kTile * kRowBytes;   // one K (or V) tile as the tensor core reads it
+  constexpr int kRawRow = INT8 ? D : D * 2;       // bytes per pool row
+  constexpr int kRawTile = kTile * kRawRow;
+  constexpr int kStageBytes = INT8 ? (2 * kRawTile + 2 * kTile * 4) : 2 * kTileBytes;  // ring stage
+  constexpr int kConvBytes = INT8 ? 2 * kTileBytes : 0;                                // widened K, V
+  constexpr int kWarpBytes = kStagesD * kStageBytes + kConvBytes;
+  constexpr int kChunks = kRawRow / 16;           // 16-byte pieces per pool row
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
 
@@ -105,7 +114,7 @@ paged_decode_mma_kernel(MmaDecParams p) {
   const int t_end = min(len, t_begin + chunk);
   const int n_tiles = t_end > t_begin ? (t_end - t_begin + kTile - 1) / kTile : 0;
 
-  uint8_t* wsmem = smem + warp * (kStagesD * kStageBytes);
+  uint8_t* wsmem = smem + warp * kWarpBytes;
   const uint32_t wsmem_u32 = smem_u32(wsmem);
   const int* table = p.tables + static_cast<long long>(a) * p.max_logical;
 
@@ -134,20 +143,33 @@ paged_decode_mma_kernel(MmaDecParams p) {
     const int tile = warp + j * kWarps;
     const int tok0 = t_begin + tile * kTile;
     const uint32_t dstK = wsmem_u32 + (j % kStagesD) * kStageBytes;
-    const uint32_t dstV = dstK + kTileBytes;
+    const uint32_t dstV = dstK + (INT8 ? kRawTile : kTileBytes);
 #pragma unroll
-    for (int i = 0; i < kTile * kChunks / 32; ++i) {
+    for (int i = 0; i < (kTile * kChunks + 31) / 32; ++i) {
       const int c = lane + 32 * i;
+      if (c >= kTile * kChunks) break;
       const int r = c / kChunks, piece = c % kChunks;
       const int t = tok0 + r;
       const bool valid = t < t_end;
       int blk = valid ? table[t / p.bs] : 0;
       blk = (blk < 0 || blk >= p.nb) ? 0 : blk;
       const long long row = (static_cast<long long>(blk) * p.Hkv + hk) * p.bs + (valid ? t % p.bs : 0);
-      const size_t off = (static_cast<size_t>(row) * D) * sizeof(T) + piece * 16;
-      const uint32_t d = r * kRowBytes + piece * 16;
+      const size_t off = static_cast<size_t>(row) * kRawRow + piece * 16;
+      const uint32_t d = r * (INT8 ? kRawRow : kRowBytes) + piece * 16;
       cp_async16(dstK + d, static_cast<const char*>(p.k_pool) + off, valid ? 16 : 0);
       cp_async16(dstV + d, static_cast<const char*>(p.v_pool) + off, valid ? 16 : 0);
+    }
+    if constexpr (INT8) {
+      // scales: 16 K + 16 V floats per tile, 4 bytes each -> one 4-byte async copy per lane
+      const int r = lane & 15;
+      const int t = tok0 + r;
+      const bool valid = t < t_end;
+      int blk = valid ? table[t / p.bs] : 0;
+      blk = (blk < 0 || blk >= p.nb) ? 0 : blk;
+      const long long row = (static_cast<long long>(blk) * p.Hkv + hk) * p.bs + (valid ? t % p.bs : 0);
+      const float* src = (lane < 16 ? p.k_scale : p.v_scale) + row;
+      const uint32_t dst = dstK + 2 * kRawTile + lane * 4;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid ? 4 : 0) : "memory");
     }
   };
 #pragma unroll
@@ -161,8 +183,34 @@ paged_decode_mma_kernel(MmaDecParams p) {
     cp_async_commit();
     cp_async_wait<kStagesD - 1>();
     __syncwarp();
-    const uint32_t sK = wsmem_u32 + (j % kStagesD) * kStageBytes;
-    const uint32_t sV = sK + kTileBytes;
+    const uint32_t stage_u32 = wsmem_u32 + (j % kStagesD) * kStageBytes;
+    uint32_t sK = stage_u32, sV = stage_u32 + kTileBytes;
+    const float* sc = nullptr;
+    if constexpr (INT8) {
+      const uint8_t* raw = wsmem + (j % kStagesD) * kStageBytes;
+      uint8_t* conv = wsmem + kStagesD * kStageBytes;
+      sc = reinterpret_cast<const float*>(raw + 2 * kRawTile);
+      // widen 2 * kTile rows of D int8 to T: each lane converts 16-byte pieces
+#pragma unroll
+      for (int i = 0; i < (2 * kTile * kChunks + 31) / 32; ++i) {
+        const int c = lane + 32 * i;
+        if (c >= 2 * kTile * kChunks) break;
+        const int which = c / (kTile * kChunks);           // 0 = K, 1 = V
+        const int cc = c - which * kTile * kChunks;
+        const int r = cc / kChunks, piece = cc % kChunks;
+        const uint4 v = *reinterpret_cast<const uint4*>(raw + which * kRawTile + r * kRawRow + piece * 16);
+        const int8_t* e = reinterpret_cast<const int8_t*>(&v);
+        uint32_t w[8];
+#pragma unroll
+        for (int q2 = 0; q2 < 8; ++q2) w[q2] = MmaT<T>::pack(static_cast<float>(e[2 * q2]), static_cast<float>(e[2 * q2 + 1]));
+        uint8_t* dst = conv + which * kTileBytes + r * kRowBytes + piece * 32;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+      __syncwarp();
+      sK = smem_u32(conv);
+      sV = sK + kTileBytes;
+    }
     const int tok0 = t_begin + (warp + j * kWarps) * kTile;
 
     // ---- S = Q K^T : two 8-token column blocks
@@ -187,7 +235,9 @@ paged_decode_mma_kernel(MmaDecParams p) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int t = tok0 + b * 8 + 2 * t4 + e;
-        s[b][e] = t < t_end ? s[b][e] * p.scale_log2 : -INFINITY;
+        float sv = s[b][e] * p.scale_log2;
+        if constexpr (INT8) sv *= sc[b * 8 + 2 * t4 + e];
+        s[b][e] = t < t_end ? sv : -INFINITY;
         mx = fmaxf(mx, s[b][e]);
       }
     }
@@ -201,9 +251,16 @@ paged_decode_mma_kernel(MmaDecParams p) {
       const float p00 = exp2f(s[0][0] - m_use), p01 = exp2f(s[0][1] - m_use);
       const float p10 = exp2f(s[1][0] - m_use), p11 = exp2f(s[1][1] - m_use);
       l_part = l_part * corr + (p00 + p01 + p10 + p11);
-      pa[0] = MmaT<T>::pack(p00, p01);  // (head g, tokens 2t, 2t+1)
+      float w00 = p00, w01 = p01, w10 = p10, w11 = p11;
+      if constexpr (INT8) {  // V scales ride on P
+        w00 *= sc[16 + 2 * t4];
+        w01 *= sc[16 + 2 * t4 + 1];
+        w10 *= sc[16 + 8 + 2 * t4];
+        w11 *= sc[16 + 8 + 2 * t4 + 1];
+      }
+      pa[0] = MmaT<T>::pack(w00, w01);  // (head g, tokens 2t, 2t+1)
       pa[1] = 0u;                       // heads g + 8: padding
-      pa[2] = MmaT<T>::pack(p10, p11);  // (head g, tokens 8 + 2t, +1)
+      pa[2] = MmaT<T>::pack(w10, w11);  // (head g, tokens 8 + 2t, +1)
       pa[3] = 0u;
     }
     m_run = m_new;
@@ -275,13 +332,16 @@ paged_decode_mma_kernel(MmaDecParams p) {
   }
 }
 
-template <typename T, int D>
+template <typename T, int D, bool INT8>
 int launch_mma(const MmaDecParams& p, cudaStream_t s) {
   constexpr int kRowBytes = D * 2 + 16;
-  constexpr int ring = kWarps * kStagesD * 2 * kTile * kRowBytes;
+  constexpr int kTileBytes = kTile * kRowBytes;
+  constexpr int kRawTile = kTile * (INT8 ? D : D * 2);
+  constexpr int kStageBytes = INT8 ? (2 * kRawTile + 2 * kTile * 4) : 2 * kTileBytes;
+  constexpr int ring = kWarps * (kStagesD * kStageBytes + (INT8 ? 2 * kTileBytes : 0));
   constexpr int merge = (kWarps * 8 * D + 2 * kWarps * 8) * 4;
   constexpr int smem = (ring > merge ? ring : merge) + 128;
-  auto kern = paged_decode_mma_kernel<T, D>;
+  auto kern = paged_decode_mma_kernel<T, D, INT8>;
   static bool attr = false;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -297,17 +357,26 @@ int launch_mma(const MmaDecParams& p, cudaStream_t s) {
 }  // namespace
 
 // Called by tsb_paged_decode for bf16 / fp16 pools. Returns -100 when the shape is not covered here.
-int paged_decode_mma_dispatch(const void* q, const void* k_pool, const void* v_pool, const int* tables, const int* lens,
+int paged_decode_mma_dispatch(const void* q, const void* k_pool, const void* v_pool, const float* k_scale,
+                              const float* v_scale, const int* tables, const int* lens,
                               void* out, float* part_o, float* part_ml, int A, int H, int Hkv, int D, int bs, int nb,
                               int max_logical, int splits, int gh, float scale_log2, int dtype, cudaStream_t s) {
   if (gh > 8 || (D != 64 && D != 128)) return -100;
   MmaDecParams p;
-  p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.tables = tables; p.lens = lens; p.out = out;
+  p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.tables = tables; p.lens = lens; p.out = out;
   p.part_o = part_o; p.part_ml = part_ml;
   p.A = A; p.H = H; p.Hkv = Hkv; p.bs = bs; p.nb = nb; p.max_logical = max_logical; p.splits = splits; p.gh = gh;
   p.scale_log2 = scale_log2;
-  if (dtype == 1) return D == 128 ? launch_mma<__nv_bfloat16, 128>(p, s) : launch_mma<__nv_bfloat16, 64>(p, s);
-  if (dtype == 2) return D == 128 ? launch_mma<__half, 128>(p, s) : launch_mma<__half, 64>(p, s);
+  const bool i8 = k_scale != nullptr;
+  if (dtype == 1) {
+    if (D == 128) return i8 ? launch_mma<__nv_bfloat16, 128, true>(p, s) : launch_mma<__nv_bfloat16, 128, false>(p, s);
+    return i8 ? launch_mma<__nv_bfloat16, 64, true>(p, s) : launch_mma<__nv_bfloat16, 64, false>(p, s);
+  }
+  if (dtype == 2) {
+    if (D == 128) return i8 ? launch_mma<__half, 128, true>(p, s) : launch_mma<__half, 128, false>(p, s);
+    return i8 ? launch_mma<__half, 64, true>(p, s) : launch_mma<__half, 64, false>(p, s);
+  }
   return -100;
 }
 
