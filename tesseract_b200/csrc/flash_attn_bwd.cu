@@ -215,6 +215,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lse == -INFINITY) vis = 0;
         lse_l2 = lse * log2e;
       }
+      const bool all_full = __all_sync(0xffffffffu, vis == BT) != 0;
       if (!mbar_wait(&sdp_full, ph, &cta_abort, p.status)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll 1
@@ -224,15 +225,28 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(tmem_base + lane_addr + Cfg::kColDP + c * 32, rp);
         tmem_ld_wait();
         uint32_t pk[16], dsk[16];
+        if (all_full) {  // interior tile: no per-element visibility test
+          const float nd = -delta;
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = 0.f, p1 = 0.f;
-          if (c * 32 + e < vis) p0 = exp2f(__uint_as_float(rs[e]) * p.scale_log2 - lse_l2);
-          if (c * 32 + e + 1 < vis) p1 = exp2f(__uint_as_float(rs[e + 1]) * p.scale_log2 - lse_l2);
-          const float d0 = p0 * (__uint_as_float(rp[e]) - delta) * p.scale;
-          const float d1 = p1 * (__uint_as_float(rp[e + 1]) - delta) * p.scale;
-          pk[e >> 1] = pack_bf16x2(p0, p1);
-          dsk[e >> 1] = pack_bf16x2(d0, d1);
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(rs[e]), p.scale_log2, -lse_l2));
+            const float p1 = exp2f(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -lse_l2));
+            const float d0 = p0 * ((__uint_as_float(rp[e]) + nd) * p.scale);
+            const float d1 = p1 * ((__uint_as_float(rp[e + 1]) + nd) * p.scale);
+            pk[e >> 1] = pack_bf16x2(p0, p1);
+            dsk[e >> 1] = pack_bf16x2(d0, d1);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float p0 = 0.f, p1 = 0.f;
+            if (c * 32 + e < vis) p0 = exp2f(__uint_as_float(rs[e]) * p.scale_log2 - lse_l2);
+            if (c * 32 + e + 1 < vis) p1 = exp2f(__uint_as_float(rs[e + 1]) * p.scale_log2 - lse_l2);
+            const float d0 = p0 * (__uint_as_float(rp[e]) - delta) * p.scale;
+            const float d1 = p1 * (__uint_as_float(rp[e + 1]) - delta) * p.scale;
+            pk[e >> 1] = pack_bf16x2(p0, p1);
+            dsk[e >> 1] = pack_bf16x2(d0, d1);
+          }
         }
         store_row_chunk_sw128(sP, row, c, pk);
         store_row_chunk_sw128(sDS, row, c, dsk);

@@ -6,12 +6,15 @@
 //                 cores work on the next tile. Tiles owned by other ranks are computed first (rotated by rank,
 //                 so at any moment the ranks write to different peers), the local ones last. A small second
 //                 kernel sums the `world` slots after a cross-rank barrier.
-//   MODE_GATHER   all-gather -> column-parallel GEMM:    a few CTAs of the same persistent kernel pull the remote
-//                 token shards into this GPU's memory with bulk asynchronous copies (peer global -> shared ->
-//                 local global, 32 KB pieces, six in flight per CTA) and publish a per-128-row counter; the TMA
-//                 producer of every GEMM CTA waits (bounded) for the counter of the row block it is about to
-//                 load. The local shard is consumed first. Remote data crosses NVLink exactly once and the GEMM
-//                 reads only local memory (no TMA multicast, no remote operand reads).
+//   MODE_GATHER   all-gather -> column-parallel GEMM:    a few CTAs of the same persistent kernel PUSH this rank's
+//                 token shard into every rank's landing buffer (local bulk loads into shared memory, 16-byte
+//                 stores to the peer, one destination per time slot so the ranks never write to the same peer)
+//                 and bump a per-128-row counter on the receiver with a system-scope release; the TMA producer of
+//                 every GEMM CTA waits (bounded) for the counter of the row block it is about to load. The local
+//                 shard is consumed first, the others in arrival order. Remote data crosses NVLink exactly once,
+//                 as writes, and the GEMM reads only local memory (no TMA multicast, no remote operand reads).
+//                 When the caller keeps the gathered rows, the copy CTAs also move them from the landing buffer
+//                 to the caller's tensor as they arrive.
 //
 // The GEMM pipeline itself is the one of gemm_tcgen05.cu (TMA -> 128B-swizzled smem ring -> tcgen05.mma with
 // TMEM double buffering -> tcgen05.ld epilogue); here the epilogue goes through a per-warp shared-memory
@@ -33,7 +36,6 @@ constexpr int MODE_SCATTER = 1;
 constexpr int MODE_GATHER = 2;
 constexpr int kPiece = 32768;   // bytes per bulk copy
 constexpr int kCopyBufs = 6;
-constexpr int kCopyLag = 3;     // store groups allowed to be outstanding before a chunk is published
 
 template <int BN>
 struct Cfg {
@@ -47,12 +49,16 @@ struct Cfg {
 };
 
 struct TpArgs {
-  __nv_bfloat16* peer_out[kMaxWorld];        // SCATTER: staging base of every rank ([world][rows_per_rank][N])
-  const __nv_bfloat16* peer_src[kMaxWorld];  // GATHER: token shard of every rank ([rows_per_rank][K])
-  __nv_bfloat16* x_full;                     // GATHER: local [M][K] buffer the shards are landed in
-  int* chunk_flags;                          // GATHER: one counter per 128-row block
-  int flag_target;                           // GATHER: counter value meaning "all comm CTAs delivered the block"
-  int comm_ctas;                             // GATHER: CTAs [0, comm_ctas) copy, the rest multiply
+  __nv_bfloat16* peer_out[kMaxWorld];   // SCATTER: staging base of every rank ([world][rows_per_rank][N])
+  __nv_bfloat16* peer_land[kMaxWorld];  // GATHER: landing buffer [M][K] of every rank (peer_land[rank] is local)
+  int* peer_flags[kMaxWorld];           // GATHER: per-128-row-block arrival counters of every rank
+  const __nv_bfloat16* x_local;         // GATHER: this rank's token shard [rows_per_rank][K], contiguous, local
+  __nv_bfloat16* x_full;                // GATHER: optional local [M][K] copy of the gathered rows (may be null)
+  int* chunk_flags;                     // GATHER: == peer_flags[rank]
+  int flag_target;                      // GATHER: counter value meaning "the whole block has landed"
+  int comm_ctas;                        // GATHER: CTAs [0, comm_ctas) copy, the rest multiply
+  int parts;                            // GATHER: slices (= counter increments) per block and call
+  int phase_mask;                       // GATHER: bit 0 push the shard, bit 1 multiply (+ keep a copy)
   int rows_per_rank, rank, world;
 };
 
@@ -71,11 +77,6 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n, int
   return {m, r / gm};
 }
 
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(smem_dst)),
@@ -88,65 +89,162 @@ __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint3
                : "memory");
 }
 
-// Copy CTA of MODE_GATHER: lands this CTA's slice of every 128-row block (in consumption order) in x_full.
-__device__ void gather_copy_cta(uint8_t* smem, uint64_t* bars, const TpArgs& a, int num_m, int K, int m_rot,
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Copy CTA of MODE_GATHER, phase 1 (all threads): PUSH this rank's token shard into the landing buffer of every
+// rank. Time slot s sends the whole shard to rank (rank - s) mod world, so in every slot the ranks write to
+// distinct peers and each receiver gets the shards in the order its GEMM consumes them. A work item is one
+// 1 / parts slice of a 128-row block for one destination; items are dealt round-robin to the copy CTAs. The bytes
+// come through shared memory: one thread prefetches 32 KB pieces of the LOCAL shard with bulk copies (six in
+// flight), all threads store them to the peer with 16-byte stores, and after the last piece of an item one thread
+// issues a system-scope release increment of the receiver's counter for that block.
+__device__ bool gather_push_cta(uint8_t* smem, uint64_t* bars, const TpArgs& a, int K, volatile int* cta_abort,
+                                int* status, int* pieces_done) {
+  const int tid = threadIdx.x;
+  const long long chunk_bytes = static_cast<long long>(BM) * K * 2;
+  const int bpr = a.rows_per_rank / BM;
+  const long long slice = chunk_bytes / a.parts;
+  const int ppi = static_cast<int>((slice + kPiece - 1) / kPiece);
+  const int items_per_slot = bpr * a.parts;
+  const int n_items = a.world * items_per_slot;
+  const int cta = static_cast<int>(blockIdx.x);
+  const int my_items = cta < n_items ? (n_items - cta + a.comm_ctas - 1) / a.comm_ctas : 0;
+  const int n_pieces = my_items * ppi;
+  const uint8_t* shard = reinterpret_cast<const uint8_t*>(a.x_local);
+  const long long shard_off = static_cast<long long>(a.rank) * bpr * chunk_bytes;  // this shard inside [M][K]
+
+  auto decode = [&](int i, int& slot, int& blk, long long& off, uint32_t& bytes, bool& last) {
+    const int j = i / ppi, pi = i - j * ppi;
+    const int it = cta + j * a.comm_ctas;
+    slot = it / items_per_slot;
+    const int r = it - slot * items_per_slot;
+    blk = r / a.parts;
+    off = static_cast<long long>(blk) * chunk_bytes + static_cast<long long>(r - blk * a.parts) * slice +
+          static_cast<long long>(pi) * kPiece;
+    bytes = static_cast<uint32_t>(min(static_cast<long long>(kPiece), slice - static_cast<long long>(pi) * kPiece));
+    last = (pi == ppi - 1);
+  };
+  auto issue_load = [&](int i) {
+    int slot, blk;
+    long long off;
+    uint32_t bytes;
+    bool last;
+    decode(i, slot, blk, off, bytes, last);
+    const int s = i % kCopyBufs;
+    mbar_expect_tx(&bars[s], bytes);
+    bulk_g2s(smem + s * kPiece, shard + off, bytes, &bars[s]);
+  };
+
+  if (tid == 0)
+    for (int i = 0; i < n_pieces && i < kCopyBufs; ++i) issue_load(i);
+  bool good = true;
+  for (int i = 0; i < n_pieces; ++i) {
+    const int s = i % kCopyBufs;
+    const bool ok = mbar_wait(&bars[s], (i / kCopyBufs) & 1, cta_abort, status);
+    if (__syncthreads_or(ok ? 0 : 1)) {
+      good = false;
+      break;
+    }
+    int slot, blk;
+    long long off;
+    uint32_t bytes;
+    bool last;
+    decode(i, slot, blk, off, bytes, last);
+    int dst_rank = a.rank - slot;
+    if (dst_rank < 0) dst_rank += a.world;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(a.peer_land[dst_rank]) + shard_off + off;
+    uint8_t* dst2 = (slot == 0 && a.x_full) ? reinterpret_cast<uint8_t*>(a.x_full) + shard_off + off : nullptr;
+    const uint8_t* src = smem + s * kPiece;
+    for (uint32_t o = tid * 16; o < bytes; o += kThreads * 16) {
+      const uint4 v = *reinterpret_cast<const uint4*>(src + o);
+      *reinterpret_cast<uint4*>(dst + o) = v;
+      if (dst2) *reinterpret_cast<uint4*>(dst2 + o) = v;
+    }
+    __syncthreads();  // every thread has read the buffer and issued its stores
+    if (tid == 0) {
+      if (i + kCopyBufs < n_pieces) issue_load(i + kCopyBufs);
+      if (last) {
+        __threadfence_system();
+        red_release_sys_add(a.peer_flags[dst_rank] + a.rank * bpr + blk, 1);
+      }
+    }
+  }
+  *pieces_done = good ? n_pieces : 0;
+  return good;
+}
+
+// Copy CTA of MODE_GATHER, phase 2 (one thread): copies the remote shards from the landing buffer into x_full (the
+// tensor the caller keeps for the weight gradient) as they arrive, local memory to local memory through the same
+// ring of shared-memory buffers. `g0` pieces have already gone through the ring in this launch.
+__device__ void gather_keep_cta(uint8_t* smem, uint64_t* bars, const TpArgs& a, int num_m, int K, int g0,
                                 volatile int* cta_abort, int* status) {
   const long long chunk_bytes = static_cast<long long>(BM) * K * 2;
   const long long slice = chunk_bytes / a.comm_ctas;  // host guarantees divisibility and 16-byte multiples
   const int ppc = static_cast<int>((slice + kPiece - 1) / kPiece);
-  const int n_pieces = ppc * num_m;
   const int bpr = a.rows_per_rank / BM;
+  const int n_blocks = num_m - bpr;  // remote blocks, in consumption order
+  const int n_pieces = ppc * n_blocks;
   const long long cta_off = static_cast<long long>(blockIdx.x) * slice;
+  const uint8_t* land = reinterpret_cast<const uint8_t*>(a.peer_land[a.rank]);
+  uint8_t* keep = reinterpret_cast<uint8_t*>(a.x_full);
+  int waited_blocks = 0;
+  bool good = true;
 
-  auto piece_ptrs = [&](int i, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes) {
-    const int ci = i / ppc, pi = i - ci * ppc;
-    int mb = ci + m_rot;
+  auto piece_off = [&](int i, int& ci, uint32_t& bytes) -> long long {
+    ci = i / ppc;
+    const int pi = i - ci * ppc;
+    int mb = (a.rank + 1) * bpr + ci;
     if (mb >= num_m) mb -= num_m;
-    const int owner = mb / bpr;
-    const long long off = cta_off + static_cast<long long>(pi) * kPiece;
     bytes = static_cast<uint32_t>(min(static_cast<long long>(kPiece), slice - static_cast<long long>(pi) * kPiece));
-    src = reinterpret_cast<const uint8_t*>(a.peer_src[owner]) + static_cast<long long>(mb - owner * bpr) * chunk_bytes + off;
-    dst = reinterpret_cast<uint8_t*>(a.x_full) + static_cast<long long>(mb) * chunk_bytes + off;
+    return static_cast<long long>(mb) * chunk_bytes + cta_off + static_cast<long long>(pi) * kPiece;
   };
-  auto issue_load = [&](int i) {
-    const uint8_t* src;
-    uint8_t* dst;
+  auto issue_load = [&](int i) -> bool {
+    int ci;
     uint32_t bytes;
-    piece_ptrs(i, src, dst, bytes);
-    const int s = i % kCopyBufs;
-    mbar_expect_tx(&bars[s], bytes);
-    bulk_g2s(smem + s * kPiece, src, bytes, &bars[s]);
-  };
-  int published = 0;  // chunks [0, published) have been signalled
-  auto publish_upto_piece = [&](int done_pieces) {  // pieces [0, done_pieces) are complete in global memory
-    const int chunks_done = done_pieces / ppc;
-    while (published < chunks_done) {
-      int mb = published + m_rot;
+    const long long off = piece_off(i, ci, bytes);
+    while (waited_blocks <= ci) {  // the block's pushes must have landed
+      int mb = (a.rank + 1) * bpr + waited_blocks;
       if (mb >= num_m) mb -= num_m;
-      __threadfence();
-      atomicAdd(&a.chunk_flags[mb], 1);
-      ++published;
+      const long long t0 = clock64();
+      while (ld_acquire_sys(&a.chunk_flags[mb]) < a.flag_target) {
+        if (*cta_abort || clock64() - t0 > kWaitCycleLimit) {
+          if (!*cta_abort && status) atomicCAS(status, kStatusOk, kStatusFlagTimeout);
+          *cta_abort = 1;
+          return false;
+        }
+        __nanosleep(200);
+      }
+      fence_proxy_async_all();
+      ++waited_blocks;
     }
+    const int s = (g0 + i) % kCopyBufs;
+    mbar_expect_tx(&bars[s], bytes);
+    bulk_g2s(smem + s * kPiece, land + off, bytes, &bars[s]);
+    return true;
   };
 
-  for (int i = 0; i < n_pieces && i < kCopyBufs; ++i) issue_load(i);
-  for (int i = 0; i < n_pieces; ++i) {
-    const int s = i % kCopyBufs;
-    if (!mbar_wait(&bars[s], (i / kCopyBufs) & 1, cta_abort, status)) break;
-    const uint8_t* src;
-    uint8_t* dst;
+  int issued = 0;
+  for (; issued < n_pieces && issued < kCopyBufs && good; ++issued) good = issue_load(issued);
+  for (int i = 0; i < n_pieces && good; ++i) {
+    const int s = (g0 + i) % kCopyBufs;
+    if (!mbar_wait(&bars[s], ((g0 + i) / kCopyBufs) & 1, cta_abort, status)) break;
+    int ci;
     uint32_t bytes;
-    piece_ptrs(i, src, dst, bytes);
-    bulk_s2g(dst, smem + s * kPiece, bytes);
+    const long long off = piece_off(i, ci, bytes);
+    bulk_s2g(keep + off, smem + s * kPiece, bytes);
     tma_store_commit();
     // the buffer of the previous piece is free once its store has read shared memory
     tma_store_wait_read<1>();
-    if (i >= 1 && i - 1 + kCopyBufs < n_pieces) issue_load(i - 1 + kCopyBufs);
-    tma_store_wait_all<kCopyLag>();
-    publish_upto_piece(i + 1 - kCopyLag);
+    if (i >= 1 && i - 1 + kCopyBufs < n_pieces) good = issue_load(i - 1 + kCopyBufs);
   }
   tma_store_wait_all<0>();
-  if (!*cta_abort) publish_upto_piece(n_pieces);
 }
 
 template <int BN, bool B_MN, int MODE>
@@ -198,9 +296,14 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   if (is_copy_cta) {
     __syncthreads();
-    if (threadIdx.x == 0) gather_copy_cta(smem, copy_bar, args, num_m, K, m_rot, &cta_abort, status);
+    int g0 = 0;
+    bool good = true;
+    if (args.phase_mask & 1) good = gather_push_cta(smem, copy_bar, args, K, &cta_abort, status, &g0);
+    if (good && (args.phase_mask & 2) && args.x_full != nullptr && threadIdx.x == 0)
+      gather_keep_cta(smem, copy_bar, args, num_m, K, g0, &cta_abort, status);
     return;  // copy CTAs hold no TMEM
   }
+  if (MODE == MODE_GATHER && !(args.phase_mask & 2)) return;  // push-only launch (rank emulation on one GPU)
   if (warp == 1) {
     tmem_alloc(&tmem_base_smem, C_::kTmemCols);
     tmem_relinquish();
@@ -224,7 +327,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (MODE == MODE_GATHER && ready_blk != tc.m_blk) {
           // wait until the copy CTAs have landed this row block in local memory
           const long long t0 = clock64();
-          while (ld_acquire_gpu(&args.chunk_flags[tc.m_blk]) < args.flag_target) {
+          while (ld_acquire_sys(&args.chunk_flags[tc.m_blk]) < args.flag_target) {
             if (cta_abort) { ok = false; break; }
             if (clock64() - t0 > kWaitCycleLimit) {
               cta_abort = 1;
@@ -514,33 +617,50 @@ TSB_EXPORT int tsb_gemm_rs(const void* A, const void* B, void* const* peer_out, 
               : launch_tp<128, false, MODE_SCATTER>(ta, tb, nullptr, M, N, K, N, args, grid, s);
 }
 
-// All-gather fused with the column-parallel GEMM: C [M, N] = gather(peer_src)[M, K] * op(B).
-//   peer_src[r]: rank r's token shard [rows_per_rank][K] bf16 (peer mapping; peer_src[rank] is local).
-//   x_full [M][K]: local buffer that receives the gathered rows (kept by the caller for the weight gradient).
-//   flags: int32 [M / 128] counters in local memory, zero at allocation; flag_target = (#calls so far on this
-//   flags buffer, this one included) * comm_ctas. comm_ctas must divide 128 * K * 2 / 16.
-TSB_EXPORT int tsb_gemm_ag(void* const* peer_src, void* x_full, const void* B, void* C, int* flags, int flag_target,
-                           int comm_ctas, int M, int N, int K, long long ldb, long long ldc, int b_mn,
-                           int rows_per_rank, int rank, int world, void* stream) {
+// All-gather fused with the column-parallel GEMM: C [M, N] = gather(x_local)[M, K] * op(B).
+//   x_local [rows_per_rank][K] bf16 contiguous: this rank's token shard (any local memory).
+//   peer_land[r]: rank r's landing buffer [M][K] bf16 (peer mapping; peer_land[rank] is local and feeds the GEMM).
+//   peer_flags[r]: rank r's int32 [M / 128] arrival counters (peer mapping), zero at allocation;
+//   flag_target = (#calls so far on these counters, this one included) * parts.
+//   x_full: optional local [M][K] tensor that also receives the gathered rows (for the weight gradient); null to
+//   leave them in the landing buffer only. comm_ctas must divide 128 * K * 2 / 16; parts in {1, 2, 4, 8}.
+//   phase_mask: 3 in production; 1 = push only and 2 = multiply only let one GPU emulate the ranks in two passes.
+//   Every rank must have passed a barrier after its previous use of the landing buffer before any rank calls this.
+TSB_EXPORT int tsb_gemm_ag(const void* x_local, void* const* peer_land, void* const* peer_flags, void* x_full,
+                           const void* B, void* C, int flag_target, int comm_ctas, int parts, int phase_mask, int M,
+                           int N, int K, long long ldb, long long ldc, int b_mn, int rows_per_rank, int rank, int world,
+                           void* stream) {
   using namespace tsb;
   if (world < 1 || world > kMaxWorld || rows_per_rank % BM || M != rows_per_rank * world || N % 8 || N < 128 || K % 8)
     return -2;
   if (comm_ctas < 1 || (static_cast<long long>(BM) * K * 2) % (16LL * comm_ctas)) return -2;
-  if ((reinterpret_cast<uintptr_t>(x_full) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (ldb % 8) || (ldc % 8)) return -2;
+  if (parts != 1 && parts != 2 && parts != 4 && parts != 8) return -2;
+  if (rank < 0 || rank >= world || (phase_mask & 3) == 0) return -2;
+  if ((reinterpret_cast<uintptr_t>(x_full) & 15) || (reinterpret_cast<uintptr_t>(x_local) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15) || (ldb % 8) || (ldc % 8))
+    return -2;
+  for (int i = 0; i < world; ++i)
+    if (!peer_land[i] || !peer_flags[i] || (reinterpret_cast<uintptr_t>(peer_land[i]) & 15)) return -2;
   CUtensorMap ta, tb;
   const int bn = (N >= 256) ? 256 : 128;
-  if (!tmap2d(&ta, x_full, M, K, static_cast<uint64_t>(K) * 2, BM, BK)) return -3;
+  if (!tmap2d(&ta, peer_land[rank], M, K, static_cast<uint64_t>(K) * 2, BM, BK)) return -3;
   if (!(b_mn ? tmap2d(&tb, B, K, N, ldb * 2, BK, 64) : tmap2d(&tb, B, N, K, ldb * 2, bn, BK))) return -3;
   TpArgs args{};
-  for (int i = 0; i < world; ++i) args.peer_src[i] = static_cast<const __nv_bfloat16*>(peer_src[i]);
+  for (int i = 0; i < world; ++i) {
+    args.peer_land[i] = static_cast<__nv_bfloat16*>(peer_land[i]);
+    args.peer_flags[i] = static_cast<int*>(peer_flags[i]);
+  }
+  args.x_local = static_cast<const __nv_bfloat16*>(x_local);
   args.x_full = static_cast<__nv_bfloat16*>(x_full);
-  args.chunk_flags = flags;
+  args.chunk_flags = args.peer_flags[rank];
   args.flag_target = flag_target;
   args.comm_ctas = comm_ctas;
+  args.parts = parts;
+  args.phase_mask = phase_mask;
   args.rows_per_rank = rows_per_rank;
   args.rank = rank;
   args.world = world;
-  const int grid = sm_count();  // every CTA must be resident: copy CTAs feed the GEMM CTAs of the same launch
+  const int grid = sm_count();  // every CTA must be resident: GEMM CTAs wait for data other CTAs and ranks deliver
   if (comm_ctas >= grid) return -2;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 256)

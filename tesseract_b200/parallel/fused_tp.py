@@ -6,12 +6,16 @@ handles over the process group and maps every peer's buffer into this process (N
 
 * ``gemm_rs``  row-parallel GEMM whose epilogue pushes each tile to the owning rank's staging slot, then one
                cross-rank barrier kernel and a local sum of the ``world`` slots;
-* ``ag_gemm``  copy of the local token shard into the send buffer, one barrier kernel, then ONE kernel in which
-               copy CTAs land the remote shards locally while the other CTAs run the GEMM behind per-block flags.
+* ``ag_gemm``  one barrier kernel ("every rank is done with its landing buffer"), then ONE kernel in which copy
+               CTAs push this rank's token shard into every peer's landing buffer, destination by destination,
+               and bump the receiver's per-block counters, while the other CTAs run the GEMM over the local landing
+               buffer behind those counters.
 
-Send and staging buffers are double-buffered by call parity: a buffer is written again only two calls later, and
+The staging buffer of ``gemm_rs`` is double-buffered by call parity: it is written again only two calls later, and
 every call contains a barrier that a rank can pass only after all its earlier kernels on the stream (its reads of
-the previous buffer generation included) have been issued before it -- so no second barrier per call is needed.
+the previous buffer generation included) have finished -- so no second barrier per call is needed. The landing
+buffer of ``ag_gemm`` is single: the barrier comes first in the call, so when a peer starts to write, this rank has
+finished everything it enqueued before (the GEMM and the weight-gradient GEMM that read the previous contents).
 All device-side waits are bounded and report through the status word (``_native.read_status``).
 """
 from __future__ import annotations
@@ -35,7 +39,7 @@ _native.register_signatures({
     "tsb_symm_barrier": [PP, I, I, I, P],
     "tsb_reduce_slots": [P, P, I, L, P],
     "tsb_gemm_rs": [P, P, PP, I, I, I, L, L, I, I, I, I, P],
-    "tsb_gemm_ag": [PP, P, P, P, P, I, I, I, I, I, L, L, I, I, I, I, P],
+    "tsb_gemm_ag": [P, PP, PP, P, P, P, I, I, I, I, I, I, I, L, L, I, I, I, I, P],
 })
 
 
@@ -93,11 +97,14 @@ class FusedTP:
         self.comm_ctas = comm_ctas
         self.pads = SymmetricMemory(group, rank, world, 256, device)
         self.epoch = 0
-        self._send: SymmetricMemory = None     # 2 x [rows_per_rank, K] bf16
+        self._land: SymmetricMemory = None     # [M, K] bf16 landing buffer of ag_gemm
         self._stage: SymmetricMemory = None    # 2 x [world, rows_per_rank, N] bf16
-        self._send_half = self._stage_half = 0
-        self._send_calls = self._stage_calls = 0
-        self._flags: Dict[int, list] = {}
+        self._land_half = self._stage_half = 0
+        self._stage_calls = 0
+        self._flag_ints = 1 << 16
+        self._flagmem = SymmetricMemory(group, rank, world, 4 * self._flag_ints, device)   # zero-initialised
+        self._flag_next = 0
+        self._flags: Dict[tuple, list] = {}    # (num_m, K) -> [int offset, calls, comm_ctas, parts]
         self.calls = {"gemm_rs": 0, "ag_gemm": 0, "barrier": 0}
 
     # ------------------------------------------------------------------ plumbing
@@ -146,41 +153,48 @@ class FusedTP:
         return out
 
     # ------------------------------------------------------------------ all-gather -> GEMM
-    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False):
-        """(all_gather_rows(x_local [M / world, K]) @ op(w)^T, gathered x [M, K])."""
+    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False, keep: bool = True):
+        """(all_gather_rows(x_local [M / world, K]) @ op(w)^T, gathered x [M, K]).
+
+        With ``keep=False`` the gathered rows are returned as a view of the landing buffer: valid until the next
+        ``ag_gemm`` call on this object (enough for a weight-gradient GEMM issued right after)."""
         rpr, K = x_local.shape
         M = rpr * self.world
         N = w.shape[1] if b_mn else w.shape[0]
-        if rpr % 128 or N % 8 or w.stride(1) != 1:
-            raise ValueError("ag_gemm: rows per rank must be a multiple of 128 and N of 8")
-        send = self._ensure("_send", rpr * K * 2)
-        parity = self._send_calls & 1
-        self._send_calls += 1
-        off = parity * self._send_half
-        send.local[off:off + rpr * K * 2].view(torch.bfloat16).view(rpr, K).copy_(x_local)
-        self.barrier()                                     # every rank's shard is in its send buffer
+        if rpr % 128 or N % 8 or K % 8 or w.stride(1) != 1:
+            raise ValueError("ag_gemm: rows per rank must be a multiple of 128, N and K of 8")
+        x_local = x_local.contiguous()
+        land = self._ensure("_land", (M * K * 2 + 1) // 2)
         num_m = M // 128
-        ent = self._flags.get(num_m)
+        ent = self._flags.get((num_m, K))
         if ent is None:
-            ent = [torch.zeros(num_m, dtype=torch.int32, device=self.device), 0]
-            self._flags[num_m] = ent
+            cc = self.comm_ctas
+            while (128 * K * 2) % (16 * cc):
+                cc //= 2
+            bpr = rpr // 128
+            parts = 1
+            while parts < 8 and self.world * bpr * parts < 2 * cc:
+                parts *= 2
+            if self._flag_next + num_m > self._flag_ints:
+                raise RuntimeError("ag_gemm: out of arrival counters")
+            ent = [self._flag_next, 0, cc, parts]
+            self._flag_next += num_m
+            self._flags[(num_m, K)] = ent
         ent[1] += 1
-        cc = self.comm_ctas
-        while (128 * K * 2) % (16 * cc):
-            cc //= 2
-        # the counters advance by `cc` per call; keep cc fixed per flags buffer
-        if len(ent) == 2:
-            ent.append(cc)
-        cc = ent[2]
-        x_full = torch.empty((M, K), device=x_local.device, dtype=torch.bfloat16)
+        off, calls, cc, parts = ent
+        self.barrier()                                     # every rank is done with its landing buffer
+        x_full = torch.empty((M, K), device=x_local.device, dtype=torch.bfloat16) if keep else None
         y = torch.empty((M, N), device=x_local.device, dtype=torch.bfloat16)
-        check(lib().tsb_gemm_ag(send.offset_ptr_array(off), x_full.data_ptr(), w.data_ptr(), y.data_ptr(),
-                                ent[0].data_ptr(), ent[1] * cc, cc, M, N, K, w.stride(0), y.stride(0), int(b_mn), rpr,
-                                self.rank, self.world, self._stream()), "tsb_gemm_ag")
+        check(lib().tsb_gemm_ag(x_local.data_ptr(), land.ptr_array, self._flagmem.offset_ptr_array(4 * off),
+                                x_full.data_ptr() if keep else None, w.data_ptr(), y.data_ptr(), calls * parts, cc,
+                                parts, 3, M, N, K, w.stride(0), y.stride(0), int(b_mn), rpr, self.rank, self.world,
+                                self._stream()), "tsb_gemm_ag")
         self.calls["ag_gemm"] += 1
+        if not keep:
+            x_full = land.local[:M * K * 2].view(torch.bfloat16).view(M, K)
         return y, x_full
 
     def close(self) -> None:
-        for m in (self.pads, self._send, self._stage):
+        for m in (self.pads, self._land, self._stage, self._flagmem):
             if m is not None:
                 m.close()

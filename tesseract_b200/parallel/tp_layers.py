@@ -71,10 +71,11 @@ def _mm(a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False, out=None, a
     return r
 
 
-def ag_matmul(ctx: TPContext, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False):
-    """(all-gather rows of x_local) @ op(w)^T. Returns (y [T, N], x_full [T, K])."""
+def ag_matmul(ctx: TPContext, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False, keep: bool = True):
+    """(all-gather rows of x_local) @ op(w)^T. Returns (y [T, N], x_full [T, K]). ``keep=False`` allows x_full to
+    be a transient buffer that is only valid until the next gathered matmul."""
     if ctx.impl == "fused" and ctx.fused is not None and x_local.is_cuda:
-        return ctx.fused.ag_gemm(x_local, w, b_mn=b_mn)
+        return ctx.fused.ag_gemm(x_local, w, b_mn=b_mn, keep=keep)
     x_full = ctx.all_gather_rows(x_local)
     return _mm(x_full, w, b_mn=b_mn), x_full
 
@@ -124,7 +125,7 @@ class RowParallelSPFn(torch.autograd.Function):
     def backward(ctx, dy_local):
         x, w = ctx.saved_tensors
         tp = ctx.tp
-        dx, dy_full = ag_matmul(tp, dy_local.contiguous(), w, b_mn=True)  # all_gather(dY) @ W
+        dx, dy_full = ag_matmul(tp, dy_local.contiguous(), w, b_mn=True, keep=False)  # all_gather(dY) @ W
         buf = ctx.wgrad_buf
         dw = None
         if buf is not None:

@@ -1,6 +1,7 @@
 """Fused TP kernels. On one GPU the ranks of a group are emulated by launching each rank's kernel in turn over
-buffers that all live on that GPU (the kernels of different ranks never wait on one another: only the barrier
-kernel does, and it is not used here). With >= 2 GPUs the real peer-memory path runs in child processes."""
+buffers that all live on that GPU, in an order in which no launch waits for a later one (the gather kernel is
+split into its push half and its multiply half for that; the barrier kernel is not used here). With >= 2 GPUs
+the real peer-memory path runs in child processes."""
 import ctypes
 import os
 import socket
@@ -50,37 +51,50 @@ def test_gemm_rs_emulated_ranks(world, rpr, N, K, b_mn):
             assert _rel(staging[r][src], part) < 1e-2
 
 
-@pytest.mark.parametrize("world,rpr,N,K,b_mn", [(1, 256, 512, 256, False), (4, 128, 256, 512, False),
-                                                 (2, 512, 768, 1024, True), (8, 128, 3584, 4096, False)])
-def test_ag_gemm_emulated_ranks(world, rpr, N, K, b_mn):
+@pytest.mark.parametrize("world,rpr,N,K,b_mn,keep", [(1, 256, 512, 256, False, True), (4, 128, 256, 512, False, True),
+                                                      (2, 512, 768, 1024, True, False),
+                                                      (8, 128, 3584, 4096, False, True), (8, 256, 768, 4096, False, False)])
+def test_ag_gemm_emulated_ranks(world, rpr, N, K, b_mn, keep):
+    """Pass 1 runs only the push half of every rank's kernel (shards land in every rank's buffer, counters rise),
+    pass 2 only the multiply half, so no launch ever waits for a later one."""
     from tesseract_b200 import _native
     from tesseract_b200.parallel import fused_tp  # noqa: F401
     lib = _native.lib()
     dev = torch.device("cuda", 0)
     M = rpr * world
     g = torch.Generator(device=dev).manual_seed(world * 7 + K)
-    shards = [torch.randn(rpr, K, device=dev, generator=g).bfloat16() for _ in range(world)]
-    full = torch.cat(shards)
-    pa = _ptr_array(shards)
     stream = torch.cuda.current_stream().cuda_stream
     cc = 16
     while (128 * K * 2) % (16 * cc):
         cc //= 2
-    for r in range(world):
-        w = (torch.randn(N, K, device=dev, generator=g) * 0.1).bfloat16()
-        w_in = w.t().contiguous() if b_mn else w
-        flags = torch.zeros(M // 128, dtype=torch.int32, device=dev)
-        for call in (1, 2):   # the counters keep counting across calls
-            x_full = torch.full((M, K), float("nan"), device=dev, dtype=torch.bfloat16)
-            y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-            _native.check(lib.tsb_gemm_ag(pa, x_full.data_ptr(), w_in.data_ptr(), y.data_ptr(), flags.data_ptr(),
-                                          call * cc, cc, M, N, K, w_in.stride(0), y.stride(0), int(b_mn), rpr, r, world,
-                                          stream), "tsb_gemm_ag")
+    parts = 1
+    while parts < 8 and world * (rpr // 128) * parts < 2 * cc:
+        parts *= 2
+    lands = [torch.full((M, K), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    flags = [torch.zeros(M // 128, dtype=torch.int32, device=dev) for _ in range(world)]
+    pl, pf = _ptr_array(lands), _ptr_array(flags)
+    ws = [(torch.randn(N, K, device=dev, generator=g) * 0.1).bfloat16() for _ in range(world)]
+    w_ins = [w.t().contiguous() if b_mn else w for w in ws]
+    for call in (1, 2):   # the counters keep counting across calls; the data changes
+        shards = [torch.randn(rpr, K, device=dev, generator=g).bfloat16() for _ in range(world)]
+        full = torch.cat(shards)
+        x_fulls = [torch.full((M, K), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(world)]
+        ys = [torch.empty(M, N, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+        for mask in (1, 2):
+            for r in range(world):
+                _native.check(lib.tsb_gemm_ag(shards[r].data_ptr(), pl, pf, x_fulls[r].data_ptr() if keep else None,
+                                              w_ins[r].data_ptr(), ys[r].data_ptr(), call * parts, cc, parts, mask, M, N,
+                                              K, w_ins[r].stride(0), ys[r].stride(0), int(b_mn), rpr, r, world, stream),
+                              "tsb_gemm_ag")
             torch.cuda.synchronize()
             assert _native.read_status(stream) == 0
-            assert torch.equal(x_full, full), "gathered activations differ from the concatenated shards"
-            assert _rel(y, full.float() @ w.float().t()) < 1e-2
-        assert int(flags.min()) == 2 * cc and int(flags.max()) == 2 * cc
+        for r in range(world):
+            assert torch.equal(lands[r], full), "landing buffer differs from the concatenated shards"
+            if keep:
+                assert torch.equal(x_fulls[r], full), "kept activations differ from the concatenated shards"
+            assert _rel(ys[r], full.float() @ ws[r].float().t()) < 1e-2
+    for r in range(world):
+        assert int(flags[r].min()) == 2 * parts and int(flags[r].max()) == 2 * parts
 
 
 def _free_port():
