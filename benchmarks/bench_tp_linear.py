@@ -31,6 +31,9 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--comm-ctas", type=int, default=16)
     ap.add_argument("--peak-tflops", type=float, default=0.0)
+    ap.add_argument("--trace", action="store_true", help="print per-phase timestamps (min, max over CTAs) of one gather call")
+    ap.add_argument("--only", default="", help="gemm_rs or ag_gemm: time only that op")
+    ap.add_argument("--parts", action="store_true", help="also time the halves of the gather kernel separately")
     a = ap.parse_args()
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -84,6 +87,9 @@ def main():
         cases = [("gemm_rs", "o_proj", d // world, d), ("gemm_rs", "down_proj", ff // world, d),
                  ("ag_gemm", "qkv", d, qkv // world), ("ag_gemm", "gate_up", d, 2 * ff // world)]
         for op, name, K, N in cases:
+            if a.only and op != a.only:
+                continue
+            extra = {}
             g = torch.Generator(device=dev).manual_seed(rank + M)
             w = (torch.randn(N, K, device=dev, generator=g) * 0.02).bfloat16()
             if op == "gemm_rs":
@@ -99,6 +105,26 @@ def main():
                 xf = ctx_n.all_gather_rows(x)
                 tg = timed(lambda: _mm(xf, w))
                 err = (ag_matmul(ctx_f, x, w)[0].float() - ag_matmul(ctx_n, x, w)[0].float()).abs().max().item()
+                if a.trace:
+                    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+                    fused.trace = torch.zeros(sms, 8, dtype=torch.int64, device=dev)
+                    dist.barrier()
+                    torch.cuda.synchronize()
+                    fused.ag_gemm(x, w, keep=True)
+                    torch.cuda.synchronize()
+                    tr = fused.trace.cpu().double()
+                    fused.trace = None
+                    t0 = tr[:, 0].min()
+                    names = ["start", "remote_pushed", "all_pushed", "wait_begin", "wait_end", "loads_issued",
+                             "epilogue_done", "kept"]
+                    extra["trace_us"] = {n: [round(float((tr[:, i][tr[:, i] > 0].min() - t0) / 1e3), 1),
+                                             round(float((tr[:, i].max() - t0) / 1e3), 1)]
+                                         for i, n in enumerate(names) if (tr[:, i] > 0).any()}
+                if a.parts:
+                    extra.update({"fused_nokeep_ms": round(timed(lambda: fused.ag_gemm(x, w, keep=False)), 4),
+                             "push_only_ms": round(timed(lambda: fused.ag_gemm(x, w, keep=False, phase_mask=1)), 4),
+                             "mult_only_ms": round(timed(lambda: fused.ag_gemm(x, w, keep=False, phase_mask=2)), 4),
+                             "mult_keep_ms": round(timed(lambda: fused.ag_gemm(x, w, keep=True, phase_mask=2)), 4)})
             flops = 2.0 * M * N * K
             link_bytes = (world - 1) / world * M * d * 2      # bf16 activations crossing NVLink per GPU
             roof_ms = max(flops / (peak * 1e12), link_bytes / (link_gbs * 1e9)) * 1e3
@@ -109,7 +135,7 @@ def main():
                                   "roofline_ms": round(roof_ms, 4), "fused_frac_of_roofline": round(roof_ms / tf, 3),
                                   "nccl_frac_of_roofline": round(roof_ms / tn, 3), "max_abs_diff": err,
                                   "bound": "compute" if flops / (peak * 1e12) > link_bytes / (link_gbs * 1e9) else "link",
-                                  "kernel_status": status}), flush=True)
+                                  "kernel_status": status, **extra}), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -6,14 +6,14 @@
 //                 cores work on the next tile. Tiles owned by other ranks are computed first (rotated by rank,
 //                 so at any moment the ranks write to different peers), the local ones last. A small second
 //                 kernel sums the `world` slots after a cross-rank barrier.
-//   MODE_GATHER   all-gather -> column-parallel GEMM:    a few CTAs of the same persistent kernel PUSH this rank's
-//                 token shard into every rank's landing buffer (local bulk loads into shared memory, 16-byte
+//   MODE_GATHER   all-gather -> column-parallel GEMM:    four extra warps in every CTA of the same persistent kernel
+//                 PUSH this rank's token shard into every rank's landing buffer (16-byte loads from local memory,
 //                 stores to the peer, one destination per time slot so the ranks never write to the same peer)
 //                 and bump a per-128-row counter on the receiver with a system-scope release; the TMA producer of
-//                 every GEMM CTA waits (bounded) for the counter of the row block it is about to load. The local
+//                 every CTA waits (bounded) for the counter of the row block it is about to load. The local
 //                 shard is consumed first, the others in arrival order. Remote data crosses NVLink exactly once,
 //                 as writes, and the GEMM reads only local memory (no TMA multicast, no remote operand reads).
-//                 When the caller keeps the gathered rows, the copy CTAs also move them from the landing buffer
+//                 When the caller keeps the gathered rows, the push warps also move them from the landing buffer
 //                 to the caller's tensor as they arrive.
 //
 // The GEMM pipeline itself is the one of gemm_tcgen05.cu (TMA -> 128B-swizzled smem ring -> tcgen05.mma with
@@ -30,12 +30,12 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kThreads = 192;
+constexpr int kGemmThreads = 192;  // TMA producer, MMA issuer, four epilogue warps
+constexpr int kPushWarps = 4;
+constexpr int kThreads = kGemmThreads + 32 * kPushWarps;  // + warps that move activations between ranks in MODE_GATHER
 constexpr int kMaxWorld = 8;
 constexpr int MODE_SCATTER = 1;
 constexpr int MODE_GATHER = 2;
-constexpr int kPiece = 32768;   // bytes per bulk copy
-constexpr int kCopyBufs = 6;
 
 template <int BN>
 struct Cfg {
@@ -43,7 +43,7 @@ struct Cfg {
   static constexpr int kStageBytesB = BN * BK * 2;
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
   static constexpr int kStages = (BN >= 256) ? 4 : 6;
-  static constexpr int kEpiBytes = 4 * 4096;  // one [32 x 64] bf16 staging tile per epilogue warp
+  static constexpr int kEpiBytes = 4 * 2 * 4096;  // two [32 x 64] bf16 staging tiles per epilogue warp
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024;
   static constexpr int kTmemCols = 2 * BN;
 };
@@ -51,14 +51,14 @@ struct Cfg {
 struct TpArgs {
   __nv_bfloat16* peer_out[kMaxWorld];   // SCATTER: staging base of every rank ([world][rows_per_rank][N])
   __nv_bfloat16* peer_land[kMaxWorld];  // GATHER: landing buffer [M][K] of every rank (peer_land[rank] is local)
-  int* peer_flags[kMaxWorld];           // GATHER: per-128-row-block arrival counters of every rank
+  int* peer_flags[kMaxWorld];           // GATHER: arrival counters [world][nsub] of every rank
   const __nv_bfloat16* x_local;         // GATHER: this rank's token shard [rows_per_rank][K], contiguous, local
   __nv_bfloat16* x_full;                // GATHER: optional local [M][K] copy of the gathered rows (may be null)
   int* chunk_flags;                     // GATHER: == peer_flags[rank]
-  int flag_target;                      // GATHER: counter value meaning "the whole block has landed"
-  int comm_ctas;                        // GATHER: CTAs [0, comm_ctas) copy, the rest multiply
-  int parts;                            // GATHER: slices (= counter increments) per block and call
+  int flag_target;                      // GATHER: counter value meaning "the sub-chunk has landed"
+  int nsub;                             // GATHER: sub-chunks (of whole 128-row blocks) per shard
   int phase_mask;                       // GATHER: bit 0 push the shard, bit 1 multiply (+ keep a copy)
+  long long* trace;                     // GATHER: optional [gridDim.x][8] globaltimer stamps (null = off)
   int rows_per_rank, rank, world;
 };
 
@@ -77,18 +77,6 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n, int
   return {m, r / gm};
 }
 
-__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(smem_dst)),
-               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
-               "r"(bytes)
-               : "memory");
-}
-
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -98,158 +86,129 @@ __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Copy CTA of MODE_GATHER, phase 1 (all threads): PUSH this rank's token shard into the landing buffer of every
-// rank. Time slot s sends the whole shard to rank (rank - s) mod world, so in every slot the ranks write to
-// distinct peers and each receiver gets the shards in the order its GEMM consumes them. A work item is one
-// 1 / parts slice of a 128-row block for one destination; items are dealt round-robin to the copy CTAs. The bytes
-// come through shared memory: one thread prefetches 32 KB pieces of the LOCAL shard with bulk copies (six in
-// flight), all threads store them to the peer with 16-byte stores, and after the last piece of an item one thread
-// issues a system-scope release increment of the receiver's counter for that block.
-__device__ bool gather_push_cta(uint8_t* smem, uint64_t* bars, const TpArgs& a, int K, volatile int* cta_abort,
-                                int* status, int* pieces_done) {
-  const int tid = threadIdx.x;
-  const long long chunk_bytes = static_cast<long long>(BM) * K * 2;
-  const int bpr = a.rows_per_rank / BM;
-  const long long slice = chunk_bytes / a.parts;
-  const int ppi = static_cast<int>((slice + kPiece - 1) / kPiece);
-  const int items_per_slot = bpr * a.parts;
-  const int n_items = a.world * items_per_slot;
-  const int cta = static_cast<int>(blockIdx.x);
-  const int my_items = cta < n_items ? (n_items - cta + a.comm_ctas - 1) / a.comm_ctas : 0;
-  const int n_pieces = my_items * ppi;
-  const uint8_t* shard = reinterpret_cast<const uint8_t*>(a.x_local);
-  const long long shard_off = static_cast<long long>(a.rank) * bpr * chunk_bytes;  // this shard inside [M][K]
+// Push warps of MODE_GATHER. Every CTA of the kernel carries kPushWarps (four) extra warps that take no part in the
+// GEMM: together they PUSH this rank's token shard into the landing buffer of every rank with plain 16-byte loads
+// (local) and stores (peer). Spreading the copy over all SMs matters: one SM sustains only a few tens of GB/s
+// towards a peer, 148 of them saturate the links without taking an SM away from the tensor cores. Time slot s sends
+// the shard to rank (rank - s) mod world, so at any moment the ranks write to distinct peers and each receiver gets
+// the shards in the order its GEMM consumes them (its own shard the GEMM reads in place). A shard is sent as `nsub`
+// sub-chunks of whole 128-row blocks; every push warp of the grid streams one contiguous slice of a sub-chunk,
+// and when the four warps of a CTA have issued their part, ONE thread of the CTA makes it visible with a
+// system-scope fence and increments the receiver's counter for (source rank, sub-chunk). A counter that has risen
+// by gridDim.x means the sub-chunk has landed. Fences are kept this rare on purpose: a system-scope fence stalls
+// the SM's stores for about two microseconds, and one per 16 KB slice halved the push bandwidth.
+constexpr int kPushUnroll = 8;
 
-  auto decode = [&](int i, int& slot, int& blk, long long& off, uint32_t& bytes, bool& last) {
-    const int j = i / ppi, pi = i - j * ppi;
-    const int it = cta + j * a.comm_ctas;
-    slot = it / items_per_slot;
-    const int r = it - slot * items_per_slot;
-    blk = r / a.parts;
-    off = static_cast<long long>(blk) * chunk_bytes + static_cast<long long>(r - blk * a.parts) * slice +
-          static_cast<long long>(pi) * kPiece;
-    bytes = static_cast<uint32_t>(min(static_cast<long long>(kPiece), slice - static_cast<long long>(pi) * kPiece));
-    last = (pi == ppi - 1);
-  };
-  auto issue_load = [&](int i) {
-    int slot, blk;
-    long long off;
-    uint32_t bytes;
-    bool last;
-    decode(i, slot, blk, off, bytes, last);
-    const int s = i % kCopyBufs;
-    mbar_expect_tx(&bars[s], bytes);
-    bulk_g2s(smem + s * kPiece, shard + off, bytes, &bars[s]);
-  };
-
-  if (tid == 0)
-    for (int i = 0; i < n_pieces && i < kCopyBufs; ++i) issue_load(i);
-  bool good = true;
-  for (int i = 0; i < n_pieces; ++i) {
-    const int s = i % kCopyBufs;
-    const bool ok = mbar_wait(&bars[s], (i / kCopyBufs) & 1, cta_abort, status);
-    if (__syncthreads_or(ok ? 0 : 1)) {
-      good = false;
-      break;
-    }
-    int slot, blk;
-    long long off;
-    uint32_t bytes;
-    bool last;
-    decode(i, slot, blk, off, bytes, last);
-    int dst_rank = a.rank - slot;
-    if (dst_rank < 0) dst_rank += a.world;
-    uint8_t* dst = reinterpret_cast<uint8_t*>(a.peer_land[dst_rank]) + shard_off + off;
-    uint8_t* dst2 = (slot == 0 && a.x_full) ? reinterpret_cast<uint8_t*>(a.x_full) + shard_off + off : nullptr;
-    const uint8_t* src = smem + s * kPiece;
-    for (uint32_t o = tid * 16; o < bytes; o += kThreads * 16) {
-      const uint4 v = *reinterpret_cast<const uint4*>(src + o);
-      *reinterpret_cast<uint4*>(dst + o) = v;
-      if (dst2) *reinterpret_cast<uint4*>(dst2 + o) = v;
-    }
-    __syncthreads();  // every thread has read the buffer and issued its stores
-    if (tid == 0) {
-      if (i + kCopyBufs < n_pieces) issue_load(i + kCopyBufs);
-      if (last) {
-        __threadfence_system();
-        red_release_sys_add(a.peer_flags[dst_rank] + a.rank * bpr + blk, 1);
-      }
-    }
-  }
-  *pieces_done = good ? n_pieces : 0;
-  return good;
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// trace slots per CTA: 0 kernel start, 1 remote pushes fenced, 2 all pushes done, 3 first wait for a remote block
+// begins, 4 it ends, 5 last TMA load issued, 6 epilogue of the last tile done, 7 kept copy done
+__device__ __forceinline__ void trace_stamp(const TpArgs& a, int slot) {
+  if (a.trace) a.trace[static_cast<long long>(blockIdx.x) * 8 + slot] = global_ns();
 }
 
-// Copy CTA of MODE_GATHER, phase 2 (one thread): copies the remote shards from the landing buffer into x_full (the
-// tensor the caller keeps for the weight gradient) as they arrive, local memory to local memory through the same
-// ring of shared-memory buffers. `g0` pieces have already gone through the ring in this launch.
-__device__ void gather_keep_cta(uint8_t* smem, uint64_t* bars, const TpArgs& a, int num_m, int K, int g0,
-                                volatile int* cta_abort, int* status) {
-  const long long chunk_bytes = static_cast<long long>(BM) * K * 2;
-  const long long slice = chunk_bytes / a.comm_ctas;  // host guarantees divisibility and 16-byte multiples
-  const int ppc = static_cast<int>((slice + kPiece - 1) / kPiece);
-  const int bpr = a.rows_per_rank / BM;
-  const int n_blocks = num_m - bpr;  // remote blocks, in consumption order
-  const int n_pieces = ppc * n_blocks;
-  const long long cta_off = static_cast<long long>(blockIdx.x) * slice;
+__device__ __forceinline__ void push_warps_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kPushWarps) : "memory"); }
+
+// Copies bytes [0, bytes) from src to dst (and dst2 if not null); warp g of G takes one contiguous slice (a
+// multiple of 512 bytes) and streams it in passes of 4 KB, the loads of the next pass in flight during the stores.
+__device__ __forceinline__ void sliced_copy16(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                              uint8_t* __restrict__ dst2, long long bytes, int g, int G, int lane) {
+  constexpr long long kPass = 512LL * kPushUnroll;
+  const long long slice = ((bytes + G - 1) / G + 511) / 512 * 512;
+  const long long lo = static_cast<long long>(g) * slice;
+  const long long hi = min(bytes, lo + slice);
+  if (lo >= hi) return;
+  uint4 cur[kPushUnroll], nxt[kPushUnroll];
+  auto load = [&](uint4* v, long long o0) {
+#pragma unroll
+    for (int u = 0; u < kPushUnroll; ++u) {
+      const long long o = o0 + (u * 32 + lane) * 16LL;
+      if (o < hi) v[u] = *reinterpret_cast<const uint4*>(src + o);
+    }
+  };
+  load(cur, lo);
+  for (long long o0 = lo; o0 < hi; o0 += kPass) {
+    if (o0 + kPass < hi) load(nxt, o0 + kPass);
+#pragma unroll
+    for (int u = 0; u < kPushUnroll; ++u) {
+      const long long o = o0 + (u * 32 + lane) * 16LL;
+      if (o < hi) {
+        *reinterpret_cast<uint4*>(dst + o) = cur[u];
+        if (dst2) *reinterpret_cast<uint4*>(dst2 + o) = cur[u];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kPushUnroll; ++u) cur[u] = nxt[u];
+  }
+}
+
+__device__ void gather_push_warps(const TpArgs& a, int K, int pw, int lane) {
+  const long long shard_bytes = static_cast<long long>(a.rows_per_rank) * K * 2;
+  const long long sub_bytes = shard_bytes / a.nsub;  // host: nsub divides the blocks of a shard
+  const int G = static_cast<int>(gridDim.x) * kPushWarps;
+  const int g = static_cast<int>(blockIdx.x) * kPushWarps + pw;
+  const uint8_t* shard = reinterpret_cast<const uint8_t*>(a.x_local);
+  const long long shard_off = static_cast<long long>(a.rank) * shard_bytes;  // this shard inside [M][K]
+  // remote destinations first (slots 1 .. world-1); the local copy, which no GEMM warp waits for, goes last
+  for (int s = 1; s <= a.world; ++s) {
+    const int slot = (s == a.world) ? 0 : s;
+    int dst_rank = a.rank - slot;
+    if (dst_rank < 0) dst_rank += a.world;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(a.peer_land[dst_rank]) + shard_off;
+    uint8_t* dst2 = (slot == 0 && a.x_full) ? reinterpret_cast<uint8_t*>(a.x_full) + shard_off : nullptr;
+    for (int j = 0; j < a.nsub; ++j) {
+      const long long base = static_cast<long long>(j) * sub_bytes;
+      sliced_copy16(shard + base, dst + base, dst2 ? dst2 + base : nullptr, sub_bytes, g, G, lane);
+      push_warps_sync();  // the four push warps of this CTA have issued their stores of the sub-chunk
+      if (pw == 0 && lane == 0) {
+        __threadfence_system();
+        red_release_sys_add(a.peer_flags[dst_rank] + a.rank * a.nsub + j, 1);
+        if (j == a.nsub - 1 && (s == a.world - 1 || s == a.world)) trace_stamp(a, s == a.world ? 2 : 1);
+      }
+    }
+  }
+}
+
+// After the push: copy the remote shards from the landing buffer into x_full (the tensor the caller keeps for the
+// weight gradient) as they arrive, in consumption order. Local memory to local memory; waits are bounded.
+__device__ void gather_keep_warps(const TpArgs& a, int K, int pw, int lane, int* status) {
+  const long long shard_bytes = static_cast<long long>(a.rows_per_rank) * K * 2;
+  const long long sub_bytes = shard_bytes / a.nsub;
+  const int G = static_cast<int>(gridDim.x) * kPushWarps;
+  const int g = static_cast<int>(blockIdx.x) * kPushWarps + pw;
   const uint8_t* land = reinterpret_cast<const uint8_t*>(a.peer_land[a.rank]);
   uint8_t* keep = reinterpret_cast<uint8_t*>(a.x_full);
-  int waited_blocks = 0;
-  bool good = true;
-
-  auto piece_off = [&](int i, int& ci, uint32_t& bytes) -> long long {
-    ci = i / ppc;
-    const int pi = i - ci * ppc;
-    int mb = (a.rank + 1) * bpr + ci;
-    if (mb >= num_m) mb -= num_m;
-    bytes = static_cast<uint32_t>(min(static_cast<long long>(kPiece), slice - static_cast<long long>(pi) * kPiece));
-    return static_cast<long long>(mb) * chunk_bytes + cta_off + static_cast<long long>(pi) * kPiece;
-  };
-  auto issue_load = [&](int i) -> bool {
-    int ci;
-    uint32_t bytes;
-    const long long off = piece_off(i, ci, bytes);
-    while (waited_blocks <= ci) {  // the block's pushes must have landed
-      int mb = (a.rank + 1) * bpr + waited_blocks;
-      if (mb >= num_m) mb -= num_m;
+  for (int s = 1; s < a.world; ++s) {
+    int src_rank = a.rank + s;
+    if (src_rank >= a.world) src_rank -= a.world;
+    for (int j = 0; j < a.nsub; ++j) {
       const long long t0 = clock64();
-      while (ld_acquire_sys(&a.chunk_flags[mb]) < a.flag_target) {
-        if (*cta_abort || clock64() - t0 > kWaitCycleLimit) {
-          if (!*cta_abort && status) atomicCAS(status, kStatusOk, kStatusFlagTimeout);
-          *cta_abort = 1;
-          return false;
+      bool ok = true;
+      while (ld_acquire_sys(&a.chunk_flags[src_rank * a.nsub + j]) < a.flag_target) {
+        if (clock64() - t0 > kWaitCycleLimit) {
+          ok = false;
+          break;
         }
-        __nanosleep(200);
+        __nanosleep(500);
       }
-      fence_proxy_async_all();
-      ++waited_blocks;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0 && status) atomicCAS(status, kStatusOk, kStatusFlagTimeout);
+        return;
+      }
+      const long long off = static_cast<long long>(src_rank) * shard_bytes + static_cast<long long>(j) * sub_bytes;
+      sliced_copy16(land + off, keep + off, nullptr, sub_bytes, g, G, lane);
     }
-    const int s = (g0 + i) % kCopyBufs;
-    mbar_expect_tx(&bars[s], bytes);
-    bulk_g2s(smem + s * kPiece, land + off, bytes, &bars[s]);
-    return true;
-  };
-
-  int issued = 0;
-  for (; issued < n_pieces && issued < kCopyBufs && good; ++issued) good = issue_load(issued);
-  for (int i = 0; i < n_pieces && good; ++i) {
-    const int s = (g0 + i) % kCopyBufs;
-    if (!mbar_wait(&bars[s], ((g0 + i) / kCopyBufs) & 1, cta_abort, status)) break;
-    int ci;
-    uint32_t bytes;
-    const long long off = piece_off(i, ci, bytes);
-    bulk_s2g(keep + off, smem + s * kPiece, bytes);
-    tma_store_commit();
-    // the buffer of the previous piece is free once its store has read shared memory
-    tma_store_wait_read<1>();
-    if (i >= 1 && i - 1 + kCopyBufs < n_pieces) good = issue_load(i - 1 + kCopyBufs);
   }
-  tma_store_wait_all<0>();
 }
 
 template <int BN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAL,
+               const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
                __nv_bfloat16* __restrict__ C, int M, int N, int K, long long ldc, TpArgs args, int* status) {
   using C_ = Cfg<BN>;
   constexpr int STAGES = C_::kStages;
@@ -261,7 +220,6 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
   __shared__ __align__(8) uint64_t tmem_full_bar[2];
   __shared__ __align__(8) uint64_t tmem_empty_bar[2];
-  __shared__ __align__(8) uint64_t copy_bar[kCopyBufs];
   __shared__ uint32_t tmem_base_smem;
   __shared__ volatile int cta_abort;
 
@@ -274,10 +232,9 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int bpr = args.rows_per_rank / BM;
   // SCATTER: blocks owned by rank+1 first, own blocks last. GATHER: own blocks first.
   const int m_rot = (MODE == MODE_SCATTER) ? ((args.rank + 1) % args.world) * bpr : args.rank * bpr;
-  const int comm_ctas = (MODE == MODE_GATHER) ? args.comm_ctas : 0;
-  const bool is_copy_cta = (MODE == MODE_GATHER) && static_cast<int>(blockIdx.x) < comm_ctas;
-  const int gemm_cta = static_cast<int>(blockIdx.x) - comm_ctas;
-  const int gemm_ctas = static_cast<int>(gridDim.x) - comm_ctas;
+  const int gemm_cta = static_cast<int>(blockIdx.x);
+  const int gemm_ctas = static_cast<int>(gridDim.x);
+  const bool do_gemm = (MODE != MODE_GATHER) || (args.phase_mask & 2);
 
   if (threadIdx.x == 0) {
     cta_abort = 0;
@@ -289,22 +246,12 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(&tmem_full_bar[a], 1);
       mbar_init(&tmem_empty_bar[a], 4);
     }
-    for (int s = 0; s < kCopyBufs; ++s) mbar_init(&copy_bar[s], 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmAL);
     tma_prefetch_desc(&tmB);
   }
-  if (is_copy_cta) {
-    __syncthreads();
-    int g0 = 0;
-    bool good = true;
-    if (args.phase_mask & 1) good = gather_push_cta(smem, copy_bar, args, K, &cta_abort, status, &g0);
-    if (good && (args.phase_mask & 2) && args.x_full != nullptr && threadIdx.x == 0)
-      gather_keep_cta(smem, copy_bar, args, num_m, K, g0, &cta_abort, status);
-    return;  // copy CTAs hold no TMEM
-  }
-  if (MODE == MODE_GATHER && !(args.phase_mask & 2)) return;  // push-only launch (rank emulation on one GPU)
-  if (warp == 1) {
+  if (warp == 1 && do_gemm) {
     tmem_alloc(&tmem_base_smem, C_::kTmemCols);
     tmem_relinquish();
   }
@@ -313,7 +260,20 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
 
-  if (warp == 0) {
+  if (warp >= kGemmThreads / 32) {
+    // ------------------------------------------------------------ push warps (MODE_GATHER only)
+    if (MODE == MODE_GATHER) {
+      const int pw = warp - kGemmThreads / 32;
+      if (pw == 0 && lane == 0) trace_stamp(args, 0);
+      if (args.phase_mask & 1) gather_push_warps(args, K, pw, lane);
+      if ((args.phase_mask & 2) && args.x_full != nullptr) {
+        gather_keep_warps(args, K, pw, lane, status);
+        if (pw == 0 && lane == 0) trace_stamp(args, 7);
+      }
+    }
+  } else if (!do_gemm) {
+    // push-only launch (rank emulation on one GPU): the GEMM warps have nothing to do
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
@@ -324,10 +284,18 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int m0 = tc.m_blk * BM;
         const int n0 = tc.n_blk * BN;
         bool ok = true;
-        if (MODE == MODE_GATHER && ready_blk != tc.m_blk) {
-          // wait until the copy CTAs have landed this row block in local memory
+        // MODE_GATHER reads the rows of this rank's own shard in place (tmAL), the others from the landing buffer
+        const bool own = (MODE == MODE_GATHER) && tc.m_blk >= m_rot && tc.m_blk < m_rot + bpr;
+        const CUtensorMap* mapA = own ? &tmAL : &tmA;
+        const int m0a = own ? m0 - m_rot * BM : m0;
+        if (MODE == MODE_GATHER && !own && ready_blk != tc.m_blk) {
+          // wait until the owner's push warps have landed the sub-chunk of this row block in local memory
+          const int owner = tc.m_blk / bpr;
+          const int* flag = &args.chunk_flags[owner * args.nsub + (tc.m_blk - owner * bpr) / (bpr / args.nsub)];
           const long long t0 = clock64();
-          while (ld_acquire_sys(&args.chunk_flags[tc.m_blk]) < args.flag_target) {
+          const bool first_wait = (ready_blk < 0);
+          if (first_wait) trace_stamp(args, 3);
+          while (ld_acquire_sys(flag) < args.flag_target) {
             if (cta_abort) { ok = false; break; }
             if (clock64() - t0 > kWaitCycleLimit) {
               cta_abort = 1;
@@ -339,6 +307,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           if (!ok) break;
           fence_proxy_async_all();  // generic-proxy acquire -> async-proxy (TMA) reads
+          if (first_wait) trace_stamp(args, 4);
           ready_blk = tc.m_blk;
         }
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -347,7 +316,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* sA = smem + stage * C_::kStageBytes;
           uint8_t* sB = sA + C_::kStageBytesA;
           mbar_expect_tx(&full_bar[stage], C_::kStageBytes);
-          tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, m0);
+          tma_load_2d(sA, mapA, &full_bar[stage], kb * BK, m0a);
           if (!B_MN) {
             tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n0);
           } else {
@@ -361,6 +330,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (!ok) break;
       }
+      if (MODE == MODE_GATHER) trace_stamp(args, 5);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -403,7 +373,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;
-    uint8_t* st = epi_smem + q * 4096;  // [32 rows][128 B], 16-byte chunks XOR-swizzled by row
+    uint8_t* st_base = epi_smem + q * 8192;  // 2 x [32 rows][128 B], 16-byte chunks XOR-swizzled by row
+    uint32_t st_sel = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = gemm_cta; t < num_tiles; t += gemm_ctas) {
@@ -427,6 +398,12 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
 #pragma unroll 1
       for (int cg = 0; cg < BN / 64; ++cg) {
+        uint8_t* st = st_base + (st_sel & 1u) * 4096;
+        if (MODE == MODE_GATHER) {
+          // the bulk store issued from this buffer two column groups ago must have read it
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+        }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t r[32];
@@ -444,16 +421,29 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) * 16)) = v;
           }
         }
-        __syncwarp();
-        const int col = n0 + cg * 64 + (lane & 7) * 8;
+        if (MODE == MODE_GATHER) {
+          // local output: one bulk tensor store per [32 x 64] tile (the staging layout is the 128-byte swizzle).
+          // It leaves through the TMA unit, not through the load/store queue that the push warps fill with
+          // stores waiting for NVLink, so the epilogue never queues behind them.
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && band0 < M && n0 + cg * 64 < N) {
+            tma_store_2d(&tmC, st, n0 + cg * 64, band0);
+            tma_store_commit();
+          }
+          ++st_sel;
+        } else {
+          __syncwarp();
+          const int col = n0 + cg * 64 + (lane & 7) * 8;
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int rr = it * 4 + (lane >> 3);
-          const uint4 v = *reinterpret_cast<const uint4*>(st + rr * 128 + (((lane & 7) ^ (rr & 7)) * 16));
-          if (band0 + rr < M && col < N)
-            *reinterpret_cast<uint4*>(band_dst + static_cast<long long>(rr) * row_stride + col) = v;
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3);
+            const uint4 v = *reinterpret_cast<const uint4*>(st + rr * 128 + (((lane & 7) ^ (rr & 7)) * 16));
+            if (band0 + rr < M && col < N)
+              *reinterpret_cast<uint4*>(band_dst + static_cast<long long>(rr) * row_stride + col) = v;
+          }
+          __syncwarp();
         }
-        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
@@ -461,11 +451,13 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (MODE == MODE_GATHER && lane == 0) tma_store_wait_all<0>();
+    if (MODE == MODE_GATHER && warp == 2 && lane == 0) trace_stamp(args, 6);
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 1 && do_gemm) {
     if (cta_abort) {
       for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     }
@@ -531,7 +523,7 @@ bool tmap2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, ui
 }
 
 template <int BN, bool B_MN, int MODE>
-int launch_tp(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc,
+int launch_tp(const CUtensorMap& ta, const CUtensorMap& tal, const CUtensorMap& tb, const CUtensorMap& tc, void* C, int M, int N, int K, long long ldc,
               const TpArgs& args, int grid, cudaStream_t s) {
   auto kern = gemm_tp_kernel<BN, B_MN, MODE>;
   static bool attr = false;
@@ -540,7 +532,7 @@ int launch_tp(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int 
     if (e != cudaSuccess) return static_cast<int>(e);
     attr = true;
   }
-  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, s>>>(ta, tb, static_cast<__nv_bfloat16*>(C), M, N, K, ldc, args,
+  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, s>>>(ta, tal, tb, tc, static_cast<__nv_bfloat16*>(C), M, N, K, ldc, args,
                                                    device_status_word());
   return static_cast<int>(cudaGetLastError());
 }
@@ -611,30 +603,30 @@ TSB_EXPORT int tsb_gemm_rs(const void* A, const void* B, void* const* peer_out, 
   if (tiles < grid) grid = tiles;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 256)
-    return b_mn ? launch_tp<256, true, MODE_SCATTER>(ta, tb, nullptr, M, N, K, N, args, grid, s)
-                : launch_tp<256, false, MODE_SCATTER>(ta, tb, nullptr, M, N, K, N, args, grid, s);
-  return b_mn ? launch_tp<128, true, MODE_SCATTER>(ta, tb, nullptr, M, N, K, N, args, grid, s)
-              : launch_tp<128, false, MODE_SCATTER>(ta, tb, nullptr, M, N, K, N, args, grid, s);
+    return b_mn ? launch_tp<256, true, MODE_SCATTER>(ta, ta, tb, ta, nullptr, M, N, K, N, args, grid, s)
+                : launch_tp<256, false, MODE_SCATTER>(ta, ta, tb, ta, nullptr, M, N, K, N, args, grid, s);
+  return b_mn ? launch_tp<128, true, MODE_SCATTER>(ta, ta, tb, ta, nullptr, M, N, K, N, args, grid, s)
+              : launch_tp<128, false, MODE_SCATTER>(ta, ta, tb, ta, nullptr, M, N, K, N, args, grid, s);
 }
 
 // All-gather fused with the column-parallel GEMM: C [M, N] = gather(x_local)[M, K] * op(B).
 //   x_local [rows_per_rank][K] bf16 contiguous: this rank's token shard (any local memory).
 //   peer_land[r]: rank r's landing buffer [M][K] bf16 (peer mapping; peer_land[rank] is local and feeds the GEMM).
-//   peer_flags[r]: rank r's int32 [M / 128] arrival counters (peer mapping), zero at allocation;
-//   flag_target = (#calls so far on these counters, this one included) * parts.
+//   peer_flags[r]: rank r's int32 [world * nsub] arrival counters (peer mapping), zero at allocation;
+//   calls = number of calls so far on these counters, this one included (every call adds the grid size to each).
 //   x_full: optional local [M][K] tensor that also receives the gathered rows (for the weight gradient); null to
-//   leave them in the landing buffer only. comm_ctas must divide 128 * K * 2 / 16; parts in {1, 2, 4, 8}.
+//   leave them in the landing buffer only. nsub: sub-chunks per shard, a divisor of rows_per_rank / 128.
+//   trace: null, or int64 [SM count][8] that receives globaltimer stamps of the phases of every CTA (diagnostics).
 //   phase_mask: 3 in production; 1 = push only and 2 = multiply only let one GPU emulate the ranks in two passes.
 //   Every rank must have passed a barrier after its previous use of the landing buffer before any rank calls this.
 TSB_EXPORT int tsb_gemm_ag(const void* x_local, void* const* peer_land, void* const* peer_flags, void* x_full,
-                           const void* B, void* C, int flag_target, int comm_ctas, int parts, int phase_mask, int M,
+                           const void* B, void* C, int calls, int nsub, int phase_mask, int M,
                            int N, int K, long long ldb, long long ldc, int b_mn, int rows_per_rank, int rank, int world,
-                           void* stream) {
+                           void* trace, void* stream) {
   using namespace tsb;
   if (world < 1 || world > kMaxWorld || rows_per_rank % BM || M != rows_per_rank * world || N % 8 || N < 128 || K % 8)
     return -2;
-  if (comm_ctas < 1 || (static_cast<long long>(BM) * K * 2) % (16LL * comm_ctas)) return -2;
-  if (parts != 1 && parts != 2 && parts != 4 && parts != 8) return -2;
+  if (nsub < 1 || (rows_per_rank / BM) % nsub || calls < 1) return -2;
   if (rank < 0 || rank >= world || (phase_mask & 3) == 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x_full) & 15) || (reinterpret_cast<uintptr_t>(x_local) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15) || (ldb % 8) || (ldc % 8))
@@ -643,7 +635,11 @@ TSB_EXPORT int tsb_gemm_ag(const void* x_local, void* const* peer_land, void* co
     if (!peer_land[i] || !peer_flags[i] || (reinterpret_cast<uintptr_t>(peer_land[i]) & 15)) return -2;
   CUtensorMap ta, tb;
   const int bn = (N >= 256) ? 256 : 128;
+  CUtensorMap tal;
   if (!tmap2d(&ta, peer_land[rank], M, K, static_cast<uint64_t>(K) * 2, BM, BK)) return -3;
+  if (!tmap2d(&tal, x_local, rows_per_rank, K, static_cast<uint64_t>(K) * 2, BM, BK)) return -3;
+  CUtensorMap tcm;  // output, stored in [32 x 64] tiles
+  if ((reinterpret_cast<uintptr_t>(C) & 15) || !tmap2d(&tcm, C, M, N, static_cast<uint64_t>(ldc) * 2, 32, 64)) return -3;
   if (!(b_mn ? tmap2d(&tb, B, K, N, ldb * 2, BK, 64) : tmap2d(&tb, B, N, K, ldb * 2, bn, BK))) return -3;
   TpArgs args{};
   for (int i = 0; i < world; ++i) {
@@ -653,19 +649,18 @@ TSB_EXPORT int tsb_gemm_ag(const void* x_local, void* const* peer_land, void* co
   args.x_local = static_cast<const __nv_bfloat16*>(x_local);
   args.x_full = static_cast<__nv_bfloat16*>(x_full);
   args.chunk_flags = args.peer_flags[rank];
-  args.flag_target = flag_target;
-  args.comm_ctas = comm_ctas;
-  args.parts = parts;
+  args.nsub = nsub;
+  args.trace = static_cast<long long*>(trace);
   args.phase_mask = phase_mask;
   args.rows_per_rank = rows_per_rank;
   args.rank = rank;
   args.world = world;
-  const int grid = sm_count();  // every CTA must be resident: GEMM CTAs wait for data other CTAs and ranks deliver
-  if (comm_ctas >= grid) return -2;
+  const int grid = sm_count();  // one resident CTA per SM: its GEMM warps wait for data that push warps deliver
+  args.flag_target = calls * grid;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 256)
-    return b_mn ? launch_tp<256, true, MODE_GATHER>(ta, tb, C, M, N, K, ldc, args, grid, s)
-                : launch_tp<256, false, MODE_GATHER>(ta, tb, C, M, N, K, ldc, args, grid, s);
-  return b_mn ? launch_tp<128, true, MODE_GATHER>(ta, tb, C, M, N, K, ldc, args, grid, s)
-              : launch_tp<128, false, MODE_GATHER>(ta, tb, C, M, N, K, ldc, args, grid, s);
+    return b_mn ? launch_tp<256, true, MODE_GATHER>(ta, tal, tb, tcm, C, M, N, K, ldc, args, grid, s)
+                : launch_tp<256, false, MODE_GATHER>(ta, tal, tb, tcm, C, M, N, K, ldc, args, grid, s);
+  return b_mn ? launch_tp<128, true, MODE_GATHER>(ta, tal, tb, tcm, C, M, N, K, ldc, args, grid, s)
+              : launch_tp<128, false, MODE_GATHER>(ta, tal, tb, tcm, C, M, N, K, ldc, args, grid, s);
 }

@@ -21,6 +21,7 @@ All device-side waits are bounded and report through the status word (``_native.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List
 
 import torch
@@ -39,7 +40,7 @@ _native.register_signatures({
     "tsb_symm_barrier": [PP, I, I, I, P],
     "tsb_reduce_slots": [P, P, I, L, P],
     "tsb_gemm_rs": [P, P, PP, I, I, I, L, L, I, I, I, I, P],
-    "tsb_gemm_ag": [P, PP, PP, P, P, P, I, I, I, I, I, I, I, L, L, I, I, I, I, P],
+    "tsb_gemm_ag": [P, PP, PP, P, P, P, I, I, I, I, I, I, L, L, I, I, I, I, P, P],
 })
 
 
@@ -94,7 +95,7 @@ class FusedTP:
         if world > 8:
             raise ValueError("FusedTP supports at most 8 ranks (one NVSwitch domain)")
         self.group, self.rank, self.world, self.device = group, rank, world, torch.device(device)
-        self.comm_ctas = comm_ctas
+        self.comm_ctas = comm_ctas          # kept for callers that still pass it; the kernel no longer has copy CTAs
         self.pads = SymmetricMemory(group, rank, world, 256, device)
         self.epoch = 0
         self._land: SymmetricMemory = None     # [M, K] bf16 landing buffer of ag_gemm
@@ -104,7 +105,11 @@ class FusedTP:
         self._flag_ints = 1 << 16
         self._flagmem = SymmetricMemory(group, rank, world, 4 * self._flag_ints, device)   # zero-initialised
         self._flag_next = 0
-        self._flags: Dict[tuple, list] = {}    # (num_m, K) -> [int offset, calls, comm_ctas, parts]
+        self._flags: Dict[tuple, list] = {}    # (rows per rank, K) -> [int offset, calls, nsub]
+        self.keep_mode = os.environ.get("TESSERACT_AG_KEEP", "copy")   # "copy" (copy engine, side stream) | "kernel"
+        self._keep_stream = None
+        self._keep_event = None
+        self.trace = None                   # int64 [SMs, 8] to receive per-CTA phase timestamps of ag_gemm (diagnostics)
         self.calls = {"gemm_rs": 0, "ag_gemm": 0, "barrier": 0}
 
     # ------------------------------------------------------------------ plumbing
@@ -153,11 +158,23 @@ class FusedTP:
         return out
 
     # ------------------------------------------------------------------ all-gather -> GEMM
-    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False, keep: bool = True):
+    def wait_keep(self) -> None:
+        """Make the current stream wait for the last copy of gathered rows out of the landing buffer."""
+        if self._keep_event is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._keep_event)
+            self._keep_event = None
+
+    def ag_gemm(self, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False, keep: bool = True,
+                phase_mask: int = 3):
         """(all_gather_rows(x_local [M / world, K]) @ op(w)^T, gathered x [M, K]).
 
         With ``keep=False`` the gathered rows are returned as a view of the landing buffer: valid until the next
-        ``ag_gemm`` call on this object (enough for a weight-gradient GEMM issued right after)."""
+        ``ag_gemm`` call on this object (enough for a weight-gradient GEMM issued right after). With ``keep=True``
+        they are copied out of the landing buffer by the copy engine on a side stream (``keep_mode="copy"``, the
+        default: the copy overlaps the kernels that follow; consumers call ``wait_keep()``) or by the push warps
+        of the kernel itself (``keep_mode="kernel"``).
+        ``phase_mask`` is for measurements only: 1 runs the push half alone, 2 the multiply half alone over the data
+        the last push delivered."""
         rpr, K = x_local.shape
         M = rpr * self.world
         N = w.shape[1] if b_mn else w.shape[0]
@@ -165,33 +182,46 @@ class FusedTP:
             raise ValueError("ag_gemm: rows per rank must be a multiple of 128, N and K of 8")
         x_local = x_local.contiguous()
         land = self._ensure("_land", (M * K * 2 + 1) // 2)
-        num_m = M // 128
-        ent = self._flags.get((num_m, K))
+        ent = self._flags.get((rpr, K))
         if ent is None:
-            cc = self.comm_ctas
-            while (128 * K * 2) % (16 * cc):
-                cc //= 2
-            bpr = rpr // 128
-            parts = 1
-            while parts < 8 and self.world * bpr * parts < 2 * cc:
-                parts *= 2
-            if self._flag_next + num_m > self._flag_ints:
+            # sub-chunks per shard: finer arrival granularity for small groups; every sub-chunk costs each SM a
+            # pipeline restart and a system-scope fence, so there are few
+            nsub = 1
+            limit = int(os.environ.get("TESSERACT_AG_NSUB", "0")) or (2 if self.world <= 2 else 1)
+            while nsub * 2 <= limit and (rpr // 128) % (nsub * 2) == 0 and rpr * K * 2 // (nsub * 2) >= (8 << 20):
+                nsub *= 2
+            if self._flag_next + self.world * nsub > self._flag_ints:
                 raise RuntimeError("ag_gemm: out of arrival counters")
-            ent = [self._flag_next, 0, cc, parts]
-            self._flag_next += num_m
-            self._flags[(num_m, K)] = ent
-        ent[1] += 1
-        off, calls, cc, parts = ent
+            ent = [self._flag_next, 0, nsub]
+            self._flag_next += self.world * nsub
+            self._flags[(rpr, K)] = ent
+        if phase_mask & 1:
+            ent[1] += 1
+        off, calls, nsub = ent
+        self.wait_keep()                                   # the previous contents have been copied out
         self.barrier()                                     # every rank is done with its landing buffer
-        x_full = torch.empty((M, K), device=x_local.device, dtype=torch.bfloat16) if keep else None
+        in_kernel = keep and (self.keep_mode == "kernel" or phase_mask != 3)
+        x_full = torch.empty((M, K), device=x_local.device, dtype=torch.bfloat16) if in_kernel else None
         y = torch.empty((M, N), device=x_local.device, dtype=torch.bfloat16)
         check(lib().tsb_gemm_ag(x_local.data_ptr(), land.ptr_array, self._flagmem.offset_ptr_array(4 * off),
-                                x_full.data_ptr() if keep else None, w.data_ptr(), y.data_ptr(), calls * parts, cc,
-                                parts, 3, M, N, K, w.stride(0), y.stride(0), int(b_mn), rpr, self.rank, self.world,
-                                self._stream()), "tsb_gemm_ag")
+                                x_full.data_ptr() if in_kernel else None, w.data_ptr(), y.data_ptr(), calls,
+                                nsub, phase_mask, M, N, K, w.stride(0), y.stride(0), int(b_mn), rpr, self.rank, self.world,
+                                self.trace.data_ptr() if self.trace is not None else None, self._stream()),
+              "tsb_gemm_ag")
         self.calls["ag_gemm"] += 1
-        if not keep:
-            x_full = land.local[:M * K * 2].view(torch.bfloat16).view(M, K)
+        if not in_kernel:
+            landed = land.local[:M * K * 2].view(torch.bfloat16).view(M, K)
+            if not keep:
+                return y, landed
+            x_full = torch.empty((M, K), device=x_local.device, dtype=torch.bfloat16)
+            main = torch.cuda.current_stream(self.device)
+            if self._keep_stream is None:
+                self._keep_stream = torch.cuda.Stream(self.device)
+            self._keep_stream.wait_stream(main)
+            with torch.cuda.stream(self._keep_stream):
+                x_full.copy_(landed, non_blocking=True)
+                self._keep_event = torch.cuda.Event()
+                self._keep_event.record(self._keep_stream)
         return y, x_full
 
     def close(self) -> None:

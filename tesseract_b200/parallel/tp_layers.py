@@ -71,11 +71,17 @@ def _mm(a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False, out=None, a
     return r
 
 
-def ag_matmul(ctx: TPContext, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False, keep: bool = True):
+def ag_matmul(ctx: TPContext, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False, keep: bool = True,
+              sync_keep: bool = True):
     """(all-gather rows of x_local) @ op(w)^T. Returns (y [T, N], x_full [T, K]). ``keep=False`` allows x_full to
-    be a transient buffer that is only valid until the next gathered matmul."""
+    be a transient buffer that is only valid until the next gathered matmul. With ``sync_keep=False`` the fused
+    path may still be filling x_full on a side stream when this returns; the caller then calls
+    ``ctx.fused.wait_keep()`` before it reads x_full."""
     if ctx.impl == "fused" and ctx.fused is not None and x_local.is_cuda:
-        return ctx.fused.ag_gemm(x_local, w, b_mn=b_mn, keep=keep)
+        out = ctx.fused.ag_gemm(x_local, w, b_mn=b_mn, keep=keep)
+        if sync_keep:
+            ctx.fused.wait_keep()
+        return out
     x_full = ctx.all_gather_rows(x_local)
     return _mm(x_full, w, b_mn=b_mn), x_full
 
@@ -92,7 +98,7 @@ class ColumnParallelSPFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x_local, w, wgrad_buf, tp: TPContext):
-        y, x_full = ag_matmul(tp, x_local, w)
+        y, x_full = ag_matmul(tp, x_local, w, sync_keep=False)
         ctx.save_for_backward(x_full, w)   # the gathered activations are kept for the weight gradient
         ctx.tp, ctx.wgrad_buf = tp, wgrad_buf
         return y
@@ -103,6 +109,8 @@ class ColumnParallelSPFn(torch.autograd.Function):
         tp = ctx.tp
         dy = dy.contiguous()
         dx_local = matmul_rs(tp, dy, w, b_mn=True)                      # (dY @ W) reduce-scattered to token shards
+        if tp.fused is not None and x_full.is_cuda:
+            tp.fused.wait_keep()                                        # x_full may still be arriving on a side stream
         buf = ctx.wgrad_buf
         dw = None
         if buf is not None:

@@ -64,14 +64,9 @@ def test_ag_gemm_emulated_ranks(world, rpr, N, K, b_mn, keep):
     M = rpr * world
     g = torch.Generator(device=dev).manual_seed(world * 7 + K)
     stream = torch.cuda.current_stream().cuda_stream
-    cc = 16
-    while (128 * K * 2) % (16 * cc):
-        cc //= 2
-    parts = 1
-    while parts < 8 and world * (rpr // 128) * parts < 2 * cc:
-        parts *= 2
+    nsub = 2 if (rpr // 128) % 2 == 0 else 1
     lands = [torch.full((M, K), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(world)]
-    flags = [torch.zeros(M // 128, dtype=torch.int32, device=dev) for _ in range(world)]
+    flags = [torch.zeros(world * nsub, dtype=torch.int32, device=dev) for _ in range(world)]
     pl, pf = _ptr_array(lands), _ptr_array(flags)
     ws = [(torch.randn(N, K, device=dev, generator=g) * 0.1).bfloat16() for _ in range(world)]
     w_ins = [w.t().contiguous() if b_mn else w for w in ws]
@@ -83,9 +78,9 @@ def test_ag_gemm_emulated_ranks(world, rpr, N, K, b_mn, keep):
         for mask in (1, 2):
             for r in range(world):
                 _native.check(lib.tsb_gemm_ag(shards[r].data_ptr(), pl, pf, x_fulls[r].data_ptr() if keep else None,
-                                              w_ins[r].data_ptr(), ys[r].data_ptr(), call * parts, cc, parts, mask, M, N,
-                                              K, w_ins[r].stride(0), ys[r].stride(0), int(b_mn), rpr, r, world, stream),
-                              "tsb_gemm_ag")
+                                              w_ins[r].data_ptr(), ys[r].data_ptr(), call, nsub, mask, M, N,
+                                              K, w_ins[r].stride(0), ys[r].stride(0), int(b_mn), rpr, r, world, None,
+                                              stream), "tsb_gemm_ag")
             torch.cuda.synchronize()
             assert _native.read_status(stream) == 0
         for r in range(world):
@@ -94,7 +89,8 @@ def test_ag_gemm_emulated_ranks(world, rpr, N, K, b_mn, keep):
                 assert torch.equal(x_fulls[r], full), "kept activations differ from the concatenated shards"
             assert _rel(ys[r], full.float() @ ws[r].float().t()) < 1e-2
     for r in range(world):
-        assert int(flags[r].min()) == 2 * parts and int(flags[r].max()) == 2 * parts
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        assert int(flags[r].min()) == 2 * sms and int(flags[r].max()) == 2 * sms
 
 
 def _free_port():
