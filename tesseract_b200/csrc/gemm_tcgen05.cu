@@ -12,6 +12,7 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 namespace tsb {
@@ -45,10 +46,32 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
   return {first_m + r % gm, r / gm};
 }
 
+// Grouped GEMMs (MoE experts) run through the same kernel. `offsets` (device, int32 [groups + 1], every entry a
+// multiple of 128, so no 128-row block and no 64-row reduction step straddles two groups) is read by the kernel,
+// never by the host:
+//   mode 1  rows grouped (expert forward / input gradient): row block m belongs to the group g with
+//           offsets[g] <= 128 m < offsets[g + 1]; the B tensor map stacks the groups' matrices and its row
+//           coordinate advances by b_group_rows per group; row blocks at or beyond offsets[groups] are skipped.
+//   mode 2  reduction grouped (expert weight gradient, A and B both MN-major): work item (g, m_blk, n_blk) reduces
+//           over rows [offsets[g], offsets[g + 1]) and writes C + g * c_group_stride; an empty group adds nothing.
+struct GroupArgs {
+  const int* offsets;
+  int groups;
+  int mode;
+  long long b_group_rows;
+  long long c_group_stride;
+};
+
+__device__ __forceinline__ int group_of_row(const GroupArgs& g, int row) {
+  int e = 0;
+  while (e + 1 < g.groups && __ldg(g.offsets + e + 1) <= row) ++e;
+  return e;
+}
+
 template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* __restrict__ C,
-                 int M, int N, int K, long long ldc, int* status, int split_k) {
+                 int M, int N, int K, long long ldc, int* status, int split_k, GroupArgs grp) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
 
@@ -69,9 +92,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_n = (N + BN - 1) / BN;
   // split_k > 1: work item t covers K slice (t % split_k) of output tile (t / split_k); slices are summed with
   // fp32 atomics by the epilogue (ATOMIC_OUT instantiation, C zero-initialised by the caller)
-  const int num_tiles = num_m * num_n * split_k;
+  const int gmode = grp.offsets ? grp.mode : 0;
+  const int num_tiles = num_m * num_n * (gmode == 2 ? grp.groups : split_k);
   const int total_kb = (K + BK - 1) / BK;
   const int kb_per = (total_kb + split_k - 1) / split_k;
+  const int m_limit = (gmode == 1) ? __ldg(grp.offsets + grp.groups) : M;  // mode 1: rows in use
+  const int tiles_per_group = num_m * num_n;
 
   if (threadIdx.x == 0) {
     cta_abort = 0;
@@ -102,11 +128,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-        const TileCoord tc = tile_coord(t / split_k, num_m, num_n);
+        const TileCoord tc = (gmode == 2) ? tile_coord(t % tiles_per_group, num_m, num_n) : tile_coord(t / split_k, num_m, num_n);
         const int m0 = tc.m_blk * BM;
         const int n0 = tc.n_blk * BN;
-        const int kb0 = (t % split_k) * kb_per;
-        const int kb1 = min(total_kb, kb0 + kb_per);
+        int kb0 = (t % split_k) * kb_per;
+        int kb1 = min(total_kb, kb0 + kb_per);
+        int b_row_off = 0;  // rows of the stacked B tensor map before this tile's group
+        if (gmode == 1) {
+          if (m0 >= m_limit) continue;
+          b_row_off = static_cast<int>(group_of_row(grp, m0) * grp.b_group_rows);
+        } else if (gmode == 2) {
+          const int g = t / tiles_per_group;
+          kb0 = __ldg(grp.offsets + g) / BK;
+          kb1 = __ldg(grp.offsets + g + 1) / BK;
+        }
         bool ok = true;
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &cta_abort, status);
@@ -121,10 +156,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int i = 0; i < BM / 64; ++i) tma_load_2d(sA + i * 8192, &tmA, &full_bar[stage], m0 + i * 64, kb * BK);
           }
           if (!B_MN) {
-            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n0);
+            tma_load_2d(sB, &tmB, &full_bar[stage], kb * BK, n0 + b_row_off);
           } else {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sB + i * 8192, &tmB, &full_bar[stage], n0 + i * 64, kb * BK);
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_2d(sB + i * 8192, &tmB, &full_bar[stage], n0 + i * 64, kb * BK + b_row_off);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -143,12 +179,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int kb0 = (t % split_k) * kb_per;
+        int kb1 = min(total_kb, kb0 + kb_per);
+        if (gmode == 1) {
+          if (tile_coord(t, num_m, num_n).m_blk * BM >= m_limit) continue;
+        } else if (gmode == 2) {
+          const int g = t / tiles_per_group;
+          kb0 = __ldg(grp.offsets + g) / BK;
+          kb1 = __ldg(grp.offsets + g + 1) / BK;
+        }
         bool ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, &cta_abort, status);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        const int kb0 = (t % split_k) * kb_per;
-        const int kb1 = min(total_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, &cta_abort, status);
           if (!ok) break;
@@ -183,19 +226,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const TileCoord tc = tile_coord(t / split_k, num_m, num_n);
+      const TileCoord tc = (gmode == 2) ? tile_coord(t % tiles_per_group, num_m, num_n) : tile_coord(t / split_k, num_m, num_n);
       const int m0 = tc.m_blk * BM;
       const int n0 = tc.n_blk * BN;
-      const bool empty_slice = (t % split_k) * kb_per >= total_kb;
+      bool empty_slice = (t % split_k) * kb_per >= total_kb;
+      OutT* Cg = C;
+      if (gmode == 1) {
+        if (m0 >= m_limit) continue;
+      } else if (gmode == 2) {
+        const int g = t / tiles_per_group;
+        empty_slice = __ldg(grp.offsets + g) >= __ldg(grp.offsets + g + 1);
+        Cg = C + static_cast<long long>(g) * grp.c_group_stride;
+      }
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, &cta_abort, status)) break;
       tc_fence_after();
       const int row = m0 + row_in_tile;
-      OutT* crow = C + static_cast<long long>(row) * ldc;
+      OutT* crow = Cg + static_cast<long long>(row) * ldc;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN + c * 32), r);
         tmem_ld_wait();
+        if (gmode == 2 && empty_slice) {  // a group without rows: nothing was accumulated
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
         const int col0 = n0 + c * 32;
         if (row < M && col0 < N) {
           if (vec_ok && col0 + 32 <= N) {
@@ -321,7 +376,7 @@ bool cached_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
 
 template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
 int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int max_ctas,
-               cudaStream_t stream, int split_k = 1) {
+               cudaStream_t stream, int split_k = 1, GroupArgs grp = GroupArgs{nullptr, 0, 0, 0, 0}) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT, ACCUM>;
   static bool attr_set = false;
@@ -330,12 +385,12 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * split_k;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * ((grp.offsets && grp.mode == 2) ? grp.groups : split_k);
   int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles < grid) grid = tiles;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(C), M, N, K, ldc,
-                                                        device_status_word(), split_k);
+                                                        device_status_word(), split_k, grp);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -408,6 +463,69 @@ TSB_EXPORT int tsb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     case 64: return launch_major<64>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
     default: return launch_major<32>(ta, tb, C, M, N, K, ldc, a_mn, b_mn, out_f32, accumulate, max_ctas, s);
   }
+}
+
+// Grouped GEMM for mixture-of-experts layers; `offsets` (int32 [groups + 1], multiples of 128) stays on the device.
+//   mode 1 (rows grouped):  C[r, :] = A[r, :] * op(B[g(r)])  for the row blocks below offsets[groups].
+//       A [rows_cap, K] bf16 (lda), C [rows_cap, N] bf16 (ldc); rows_cap >= offsets[groups] is the allocated height.
+//       b_mn = 0: B[g] is [N, K];  b_mn = 1: B[g] is [K, N]  (row stride ldb); B[g] starts b_group_stride elements
+//       after B[g - 1] (a multiple of ldb: the groups need not be packed, e.g. expert weights in a flat arena).
+//   mode 2 (reduction grouped, expert weight gradient):  C[g] (+)= A[rows of g, :]^T * B[rows of g, :]
+//       A [rows_cap, M] bf16 (lda), B [rows_cap, N] bf16 (ldb), C[g] [M, N] fp32 or bf16 (ldc), C[g] starting
+//       c_group_stride elements after C[g - 1].
+// Returns 0, a cudaError_t, -2 (bad argument) or -3 (tensor map encoding failed).
+TSB_EXPORT int tsb_gemm_grouped(const void* A, const void* B, void* C, const int* offsets, int groups, int mode,
+                                int rows_cap, int M, int N, int K, long long lda, long long ldb, long long ldc, int b_mn,
+                                long long b_group_stride, long long c_group_stride, int out_f32, int accumulate,
+                                void* stream) {
+  using namespace tsb;
+  if (!offsets || groups < 1 || groups > 1024 || rows_cap <= 0 || rows_cap % BM || N <= 0) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % 8) || (ldb % 8)) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUtensorMap ta, tb;
+  if (mode == 1) {
+    if (K <= 0 || K % 8 || out_f32 || accumulate) return -2;
+    if (b_mn && (K % BK)) return -2;  // the stacked [groups * K, N] map must not read across a group boundary
+    const int bn = (N >= 256) ? 256 : (N >= 128 ? 128 : 64);
+    if (!cached_tmap_2d(&ta, A, rows_cap, K, lda * 2, BM, BK)) return -3;
+    if (b_group_stride <= 0 || b_group_stride % ldb) return -2;
+    const long long grows = b_group_stride / ldb;  // rows of the stacked map per group
+    if (grows < (b_mn ? K : N)) return -2;
+    const uint64_t map_rows = static_cast<uint64_t>(groups - 1) * grows + (b_mn ? K : N);
+    const bool ok = b_mn ? cached_tmap_2d(&tb, B, map_rows, N, ldb * 2, BK, 64)
+                         : cached_tmap_2d(&tb, B, map_rows, K, ldb * 2, bn, BK);
+    if (!ok) return -3;
+    GroupArgs g{offsets, groups, 1, grows, 0};
+    auto go = [&](auto bn_tag, auto bmn_tag) {
+      return launch_cfg<decltype(bn_tag)::value, false, decltype(bmn_tag)::value, __nv_bfloat16, false>(
+          ta, tb, C, rows_cap, N, K, ldc, 0, s, 1, g);
+    };
+    using T = std::true_type;
+    using F = std::false_type;
+    if (bn == 256) return b_mn ? go(std::integral_constant<int, 256>{}, T{}) : go(std::integral_constant<int, 256>{}, F{});
+    if (bn == 128) return b_mn ? go(std::integral_constant<int, 128>{}, T{}) : go(std::integral_constant<int, 128>{}, F{});
+    return b_mn ? go(std::integral_constant<int, 64>{}, T{}) : go(std::integral_constant<int, 64>{}, F{});
+  }
+  if (mode == 2) {
+    if (M <= 0 || M % 8 || N % 8) return -2;
+    const int bn = (N >= 256) ? 256 : (N >= 128 ? 128 : 64);
+    if (!cached_tmap_2d(&ta, A, rows_cap, M, lda * 2, BK, 64)) return -3;
+    if (!cached_tmap_2d(&tb, B, rows_cap, N, ldb * 2, BK, 64)) return -3;
+    if (c_group_stride < static_cast<long long>(M - 1) * ldc + N) return -2;
+    GroupArgs g{offsets, groups, 2, 0, c_group_stride};
+    auto go = [&](auto bn_tag) {
+      constexpr int kBn = decltype(bn_tag)::value;
+      if (out_f32)
+        return accumulate ? launch_cfg<kBn, true, true, float, true>(ta, tb, C, M, N, rows_cap, ldc, 0, s, 1, g)
+                          : launch_cfg<kBn, true, true, float, false>(ta, tb, C, M, N, rows_cap, ldc, 0, s, 1, g);
+      return accumulate ? launch_cfg<kBn, true, true, __nv_bfloat16, true>(ta, tb, C, M, N, rows_cap, ldc, 0, s, 1, g)
+                        : launch_cfg<kBn, true, true, __nv_bfloat16, false>(ta, tb, C, M, N, rows_cap, ldc, 0, s, 1, g);
+    };
+    if (bn == 256) return go(std::integral_constant<int, 256>{});
+    if (bn == 128) return go(std::integral_constant<int, 128>{});
+    return go(std::integral_constant<int, 64>{});
+  }
+  return -2;
 }
 
 // Split-K variant for decode-shaped calls (few rows, the weight matrix is streamed once): the K range is cut into

@@ -123,6 +123,119 @@ moe_scatter_kernel(const int* __restrict__ topk_idx, int* __restrict__ cursor, i
   sorted_token[row] = static_cast<int>(i / k);
 }
 
+// Padded variant: every expert's row block starts at a multiple of `pad` rows (so that a 128-row GEMM tile never
+// holds rows of two experts). offsets[e] are the padded starts, offsets[E] the padded total.
+__global__ void moe_offsets_padded_kernel(const int* __restrict__ counts, int* __restrict__ offsets,
+                                          int* __restrict__ cursor, int E, int pad) {
+  if (threadIdx.x != 0) return;
+  int acc = 0;
+  for (int i = 0; i < E; ++i) {
+    offsets[i] = acc;
+    cursor[i] = acc;
+    acc += (counts[i] + pad - 1) / pad * pad;
+  }
+  offsets[E] = acc;
+}
+
+// sorted_pos[i] = row of assignment i = t * k + r in the padded expert-sorted order; sorted_assign[row] = i.
+__global__ void __launch_bounds__(256)
+moe_scatter_assign_kernel(const int* __restrict__ topk_idx, int* __restrict__ cursor, int* __restrict__ sorted_pos,
+                          int* __restrict__ sorted_assign, long long n_assign) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i >= n_assign) return;
+  const int row = atomicAdd(&cursor[topk_idx[i]], 1);
+  sorted_pos[i] = row;
+  sorted_assign[row] = static_cast<int>(i);
+}
+
+// dst[row, :] = scale(row) * src[assign[row] / k, :] for rows with assign >= 0, zero otherwise (padding rows).
+// scale(row) = row_scale[assign[row]] when row_scale is given. One warp per row, 16-byte accesses (D % 8 == 0).
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ assign,
+                       const float* __restrict__ row_scale, __nv_bfloat16* __restrict__ dst, int rows, int D, int k) {
+  const int row = static_cast<int>((blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int a = assign[row];
+  uint4* out = reinterpret_cast<uint4*>(dst + static_cast<long long>(row) * D);
+  const int nvec = D / 8;
+  if (a < 0) {
+    for (int v = lane; v < nvec; v += 32) out[v] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const uint4* in = reinterpret_cast<const uint4*>(src + static_cast<long long>(a / k) * D);
+  if (!row_scale) {
+    for (int v = lane; v < nvec; v += 32) out[v] = in[v];
+    return;
+  }
+  const float sc = row_scale[a];
+  for (int v = lane; v < nvec; v += 32) {
+    uint4 x = in[v];
+    __nv_bfloat162* e = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __bfloat1622float2(e[j]);
+      e[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+    }
+    out[v] = x;
+  }
+}
+
+// out[t, :] = sum_r w(t, r) * ys[pos[t * k + r], :]; w = gates[t * k + r] or 1 when gates is null. One warp per token.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, const int* __restrict__ pos, const float* __restrict__ gates,
+                   __nv_bfloat16* __restrict__ out, int T, int D, int k) {
+  const int t = static_cast<int>((blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const int nvec = D / 8;
+  for (int v = lane; v < nvec; v += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < k; ++r) {
+      const int row = pos[static_cast<long long>(t) * k + r];
+      const float w = gates ? gates[static_cast<long long>(t) * k + r] : 1.f;
+      const uint4 x = reinterpret_cast<const uint4*>(ys + static_cast<long long>(row) * D)[v];
+      const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(e[j]);
+        acc[2 * j] += w * f.x;
+        acc[2 * j + 1] += w * f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + static_cast<long long>(t) * D)[v] = o;
+  }
+}
+
+// dgate[i] = <dout[i / k, :], ys[pos[i], :]> for every assignment i. One warp per assignment.
+__global__ void __launch_bounds__(256)
+moe_gate_grad_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ ys,
+                     const int* __restrict__ pos, float* __restrict__ dgate, long long n_assign, int D, int k) {
+  const long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (i >= n_assign) return;
+  const uint4* a = reinterpret_cast<const uint4*>(dout + (i / k) * D);
+  const uint4* b = reinterpret_cast<const uint4*>(ys + static_cast<long long>(pos[i]) * D);
+  float acc = 0.f;
+  for (int v = lane; v < D / 8; v += 32) {
+    const uint4 xa = a[v], xb = b[v];
+    const __nv_bfloat162* ea = reinterpret_cast<const __nv_bfloat162*>(&xa);
+    const __nv_bfloat162* eb = reinterpret_cast<const __nv_bfloat162*>(&xb);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 fa = __bfloat1622float2(ea[j]), fb = __bfloat1622float2(eb[j]);
+      acc += fa.x * fb.x + fa.y * fb.y;
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) dgate[i] = acc;
+}
+
 }  // namespace
 }  // namespace tsb
 
@@ -153,5 +266,57 @@ TSB_EXPORT int tsb_moe_sort(const int* topk_idx, const int* counts, int* offsets
   moe_offsets_kernel<<<1, kMaxE, 0, s>>>(counts, offsets, cursor, E);
   const long long n = static_cast<long long>(tokens) * k;
   moe_scatter_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(topk_idx, cursor, sorted_pos, sorted_token, n, k);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Padded expert sort: like tsb_moe_sort, but every expert's row block starts at a multiple of `pad` (128 for the
+// grouped GEMM). sorted_assign: int32 [rows_cap], -1 for padding rows and the unused tail; rows_cap >= the padded
+// total (tokens * k + E * (pad - 1) rounded up to pad always suffices).
+TSB_EXPORT int tsb_moe_sort_padded(const int* topk_idx, const int* counts, int* offsets, int* cursor, int* sorted_pos,
+                                   int* sorted_assign, int tokens, int E, int k, int pad, int rows_cap, void* stream) {
+  using namespace tsb;
+  if (tokens <= 0 || E <= 0 || E > kMaxE || k <= 0 || pad < 1) return -2;
+  const long long n = static_cast<long long>(tokens) * k;
+  if (rows_cap < n + static_cast<long long>(E) * (pad - 1)) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(sorted_assign, 0xFF, static_cast<size_t>(rows_cap) * sizeof(int), s);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  moe_offsets_padded_kernel<<<1, 32, 0, s>>>(counts, offsets, cursor, E, pad);
+  moe_scatter_assign_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(topk_idx, cursor, sorted_pos,
+                                                                                   sorted_assign, n);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dst [rows, D] bf16: row r = (row_scale ? row_scale[assign[r]] : 1) * src[assign[r] / k] or zeros where assign[r] < 0.
+TSB_EXPORT int tsb_moe_gather_rows(const void* src, const int* assign, const float* row_scale, void* dst, int rows,
+                                   int D, int k, void* stream) {
+  using namespace tsb;
+  if (rows <= 0 || D <= 0 || D % 8 || k <= 0) return -2;
+  const unsigned blocks = static_cast<unsigned>((static_cast<long long>(rows) * 32 + 255) / 256);
+  moe_gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), assign, row_scale, static_cast<__nv_bfloat16*>(dst), rows, D, k);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out [T, D] bf16 = sum over the k assignments of a token of (gates ? gates[t, r] : 1) * ys[pos[t, r]].
+TSB_EXPORT int tsb_moe_combine(const void* ys, const int* pos, const float* gates, void* out, int T, int D, int k,
+                               void* stream) {
+  using namespace tsb;
+  if (T <= 0 || D <= 0 || D % 8 || k <= 0) return -2;
+  const unsigned blocks = static_cast<unsigned>((static_cast<long long>(T) * 32 + 255) / 256);
+  moe_combine_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(ys), pos, gates, static_cast<__nv_bfloat16*>(out), T, D, k);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dgate [T * k] fp32 = <dout[t], ys[pos[t, r]]>.
+TSB_EXPORT int tsb_moe_gate_grad(const void* dout, const void* ys, const int* pos, float* dgate, int T, int D, int k,
+                                 void* stream) {
+  using namespace tsb;
+  if (T <= 0 || D <= 0 || D % 8 || k <= 0) return -2;
+  const long long n = static_cast<long long>(T) * k;
+  const unsigned blocks = static_cast<unsigned>((n * 32 + 255) / 256);
+  moe_gate_grad_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(ys), pos, dgate, n, D, k);
   return static_cast<int>(cudaGetLastError());
 }

@@ -153,6 +153,17 @@ class _SwiGLUFn(torch.autograd.Function):
         return dgu.view(ctx.shape)
 
 
+def swiglu_backward(gate_up: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
+    """Gradient of ``swiglu`` with respect to the packed [rows, 2F] input (CUDA kernel; no autograd)."""
+    F = gate_up.shape[-1] // 2
+    gu = gate_up.reshape(-1, 2 * F).contiguous()
+    d2 = dout.reshape(-1, F).contiguous()
+    dgu = torch.empty_like(gu)
+    check(lib().tsb_swiglu_bwd(d2.data_ptr(), gu.data_ptr(), dgu.data_ptr(), gu.shape[0], F, dtype_code(gu.dtype),
+                               stream_ptr(gu.device)), "tsb_swiglu_bwd")
+    return dgu.view(gate_up.shape)
+
+
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     """silu(gate) * up for a packed [..., 2F] tensor (gate = first half of the last dimension)."""
     F = gate_up.shape[-1] // 2

@@ -505,6 +505,76 @@ def test_moe_router_and_sort(dev):
         assert int(rows.min()) >= offsets[e] and int(rows.max()) < offsets[e + 1]
 
 
+@pytest.mark.parametrize("E,N,K,counts", [(4, 256, 192, [130, 0, 257, 1]), (8, 512, 256, [100] * 8),
+                                          (3, 1024, 1024, [1000, 300, 5])])
+def test_grouped_gemm_rows_and_wgrad(dev, E, N, K, counts):
+    """Row-grouped (forward, input gradient) and reduction-grouped (weight gradient) tcgen05 GEMMs against per-group
+    fp32 matmuls; offsets are padded to 128 rows and live on the device."""
+    from tesseract_b200.ops import moe
+    g = torch.Generator(device=dev).manual_seed(E * 31 + N)
+    padded = [(c + 127) // 128 * 128 for c in counts]
+    starts = [sum(padded[:e]) for e in range(E)]
+    rows_cap = sum(padded) + 256                                  # some unused tail blocks
+    offsets = torch.tensor(starts + [sum(padded)], dtype=torch.int32, device=dev)
+    a = torch.zeros(rows_cap, K, device=dev, dtype=torch.bfloat16)
+    for e in range(E):
+        a[starts[e]:starts[e] + counts[e]] = torch.randn(counts[e], K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(E, N, K, device=dev, generator=g) * 0.1).bfloat16()
+    out = moe.grouped_gemm_rows(a, w[0], N * K, offsets, E)
+    dy = torch.zeros(rows_cap, N, device=dev, dtype=torch.bfloat16)
+    for e in range(E):
+        lo, hi = starts[e], starts[e] + counts[e]
+        ref = a[lo:hi].float() @ w[e].float().t()
+        if counts[e]:
+            assert _rel_err(out[lo:hi], ref) < 1e-2
+        dy[lo:hi] = torch.randn(counts[e], N, device=dev, generator=g).bfloat16()
+    dx = moe.grouped_gemm_rows(dy, w[0], N * K, offsets, E, b_mn=True)
+    dw = torch.full((E, N, K), 7.0, device=dev, dtype=torch.float32)
+    moe.grouped_gemm_wgrad(dy, a, offsets, E, dw, N * K, K, accumulate=False)
+    dw_acc = dw.clone()
+    moe.grouped_gemm_wgrad(dy, a, offsets, E, dw_acc, N * K, K, accumulate=True)
+    torch.cuda.synchronize()
+    for e in range(E):
+        lo, hi = starts[e], starts[e] + counts[e]
+        if counts[e]:
+            assert _rel_err(dx[lo:hi], dy[lo:hi].float() @ w[e].float()) < 1e-2
+        ref_w = dy[lo:hi].float().t() @ a[lo:hi].float()
+        if counts[e]:
+            assert _rel_err(dw[e], ref_w) < 1e-2
+            assert _rel_err(dw_acc[e], 2 * ref_w) < 1e-2
+        else:
+            assert float(dw[e].abs().max()) == 0.0
+    from tesseract_b200 import _native
+    assert _native.read_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
+def test_moe_grouped_layer_forward_backward(dev):
+    """The grouped-GEMM expert path against the per-expert reference path of the same module: output, input
+    gradient, router-gate gradient and every expert weight gradient."""
+    from tesseract_b200.nn.moe import MoEFeedForward, route_topk
+    from tesseract_b200.ops import moe as moe_ops
+    torch.manual_seed(1)
+    layer = MoEFeedForward(256, 384, num_experts=4, num_experts_per_tok=2, dtype=torch.bfloat16, device=dev)
+    x = torch.randn(300, 256, device=dev).bfloat16().requires_grad_(True)
+    probs, idx, gates = route_topk(layer.gate(x.detach()), 2)
+    gates = gates.detach().to(torch.bfloat16).requires_grad_(True)
+    dout = torch.randn(300, 256, device=dev).bfloat16()
+
+    out = moe_ops.moe_ffn_grouped(x, idx, gates, layer)
+    out.backward(dout)
+    got = [x.grad.clone(), gates.grad.clone()] + [p.grad.clone() for p in layer.experts.parameters()]
+    x.grad = None
+    gates.grad = None
+    for p in layer.experts.parameters():
+        p.grad = None
+    ref = layer._sparse_reference(x, idx, gates)
+    ref.backward(dout)
+    want = [x.grad, gates.grad] + [p.grad for p in layer.experts.parameters()]
+    assert _rel_err(out, ref) < 2e-2
+    for g_, w_ in zip(got, want):
+        assert _rel_err(g_, w_) < 3e-2
+
+
 def test_moe_layer_gpu_matches_dense_reference(dev):
     from tesseract_b200.nn.moe import MoEFeedForward
     torch.manual_seed(0)
