@@ -181,3 +181,39 @@ def _collectives_worker(rank, world):
 
 def test_rank_local_collectives_over_gloo():
     _run_ranks(_collectives_worker, 3)
+
+
+def _ep_worker(rank, world):
+    import copy
+    from tesseract_b200.nn.moe import MoEFeedForward
+    from tesseract_b200.parallel.expert import ExpertParallel
+    torch.manual_seed(7)
+    full = MoEFeedForward(16, 24, num_experts=4, num_experts_per_tok=2)          # same weights on every rank
+    sharded = copy.deepcopy(full)
+    ep = ExpertParallel(dist.group.WORLD, rank, world)
+    ep.shard_(sharded)
+    assert len(sharded.experts) == 4 // world
+    x = torch.randn(9 + rank, 16, generator=torch.Generator().manual_seed(100 + rank))   # different tokens per rank
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya, yb = full(xa), sharded(xb)
+    assert torch.allclose(ya, yb, atol=1e-5), (ya - yb).abs().max()
+    g = torch.randn_like(ya)
+    ya.backward(g)
+    yb.backward(g)
+    assert torch.allclose(xa.grad, xb.grad, atol=1e-5)
+    assert torch.allclose(full.gate.weight.grad, sharded.gate.weight.grad, atol=1e-5)
+    el = 4 // world
+    for ge in range(4):                                                          # same collective order on every rank
+        for name in ("gate_proj", "up_proj", "down_proj"):
+            w = getattr(full.experts[ge], name).weight
+            want = torch.zeros_like(w) if w.grad is None else w.grad.clone()
+            dist.all_reduce(want)                                                # tokens of every rank reach this expert
+            if ge // el == rank:
+                got = getattr(sharded.experts[ge - rank * el], name).weight.grad
+                assert torch.allclose(got, want, atol=1e-5), name
+    assert ep.stats["rows_sent"] == (9 + rank) * 2
+    return True
+
+
+def test_expert_parallel_matches_single_process_over_gloo_ranks():
+    assert all(_run_ranks(_ep_worker, 2).values())
