@@ -1,0 +1,303 @@
+#!/usr/bin/env python
+"""One hot kernel at a time, on one GPU, at a size that is larger than L2 but small enough to profile.
+
+    python benchmarks/kernel_cases.py --case gemm            # one case
+    python benchmarks/kernel_cases.py --case all             # every case, one JSON line each
+    ncu --set full --clock-control none -k regex:gemm_bf16_kernel -s 3 -c 1 -o prof \
+        python benchmarks/kernel_cases.py --case gemm --iters 1
+
+Every case warms up, then times ``--iters`` launches with CUDA events (an L2 flush between launches) and prints
+the achieved rate next to the measured peak it is bounded by (copy bandwidth / cuBLAS bf16 rate of this machine,
+read from MEASURED_PEAKS.json at the repository root when present). The fused tensor-parallel kernels run here as
+an emulation of two ranks on one GPU: all buffers local, the gather kernel split into its push half and its
+multiply half so that no launch waits for a later one.
+Shapes follow the reference's microbenchmarks where it has one (benchmarks/bench_cuda_matmul.cpp,
+bench_cuda_fused_attention.cpp, bench_cuda_moe.cpp, bench_cuda_mamba_scaling.cpp, bench_cuda_fp8_gemm.cpp).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+
+def peaks():
+    try:
+        d = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+class Bench:
+    def __init__(self, iters: int):
+        self.dev = torch.device("cuda", 0)
+        self.iters = iters
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.dev)
+        self.gen = torch.Generator(device=self.dev).manual_seed(0)
+
+    def randn(self, *shape, scale=1.0):
+        return (torch.randn(*shape, device=self.dev, generator=self.gen) * scale).bfloat16()
+
+    def time(self, fn, warmup=2):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(self.iters):
+            self.flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / self.iters
+
+
+def report(name, ms, flops=None, bytes_=None, **extra):
+    hbm, tf, src = peaks()
+    out = {"case": name, "ms": round(ms, 4)}
+    if flops:
+        out["tflops"] = round(flops / ms / 1e9, 1)
+        out["frac_of_bf16_peak"] = round(flops / ms / 1e9 / tf, 3)
+    if bytes_:
+        out["gbs"] = round(bytes_ / ms / 1e6, 1)
+        out["frac_of_hbm_peak"] = round(bytes_ / ms / 1e6 / hbm, 3)
+    out["peaks"] = src
+    out.update(extra)
+    print(json.dumps(out), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------- cases
+def case_gemm(b: Bench):
+    from tesseract_b200.ops import gemm_bf16
+    M = N = K = 8192
+    a, w = b.randn(M, K), b.randn(N, K, scale=0.02)
+    out = torch.empty(M, N, device=b.dev, dtype=torch.bfloat16)
+    ms = b.time(lambda: gemm_bf16(a, w, out=out))
+    report("gemm", ms, flops=2.0 * M * N * K, shape=[M, N, K])
+
+
+def case_gemm_wgrad(b: Bench):
+    from tesseract_b200.ops import gemm_bf16
+    T, N, K = 16384, 4096, 4096
+    dy, x = b.randn(T, N), b.randn(T, K)
+    dw = torch.zeros(N, K, device=b.dev, dtype=torch.float32)
+    ms = b.time(lambda: gemm_bf16(dy, x, a_mn=True, b_mn=True, out=dw, accumulate=True))
+    report("gemm_wgrad", ms, flops=2.0 * T * N * K, shape=[N, K, T])
+
+
+def case_grouped_gemm(b: Bench):
+    from tesseract_b200.ops import moe
+    E, N, K, per = 8, 4096, 4096, 2048
+    offsets = torch.arange(E + 1, device=b.dev, dtype=torch.int32) * per
+    a, w = b.randn(E * per, K), b.randn(E, N, K, scale=0.02)
+    ms = b.time(lambda: moe.grouped_gemm_rows(a, w[0], N * K, offsets, E))
+    report("grouped_gemm", ms, flops=2.0 * E * per * N * K, shape=[E, per, N, K])
+
+
+def _qkv(b: Bench, B, S, H, Hkv, D):
+    return b.randn(B, S, H + 2 * Hkv, D)
+
+
+def case_flash_fwd(b: Bench):
+    from tesseract_b200.ops import flash_attention_packed
+    B, S, H, Hkv, D = 2, 4096, 32, 8, 128
+    qkv = _qkv(b, B, S, H, Hkv, D)
+    with torch.no_grad():
+        ms = b.time(lambda: flash_attention_packed(qkv, H, Hkv, causal=True))
+    report("flash_fwd", ms, flops=4.0 * B * H * S * S * D / 2, shape=[B, S, H, Hkv, D])
+
+
+def case_flash_bwd(b: Bench):
+    from tesseract_b200.ops import flash_attention_packed
+    B, S, H, Hkv, D = 2, 4096, 32, 8, 128
+    qkv = _qkv(b, B, S, H, Hkv, D).requires_grad_(True)
+    o = flash_attention_packed(qkv, H, Hkv, causal=True)
+    do = torch.randn_like(o)
+
+    def run():
+        qkv.grad = None
+        o.backward(do, retain_graph=True)
+    ms = b.time(run)
+    report("flash_bwd", ms, flops=10.0 * B * H * S * S * D / 2, shape=[B, S, H, Hkv, D])
+
+
+def _paged(b: Bench, A, L, int8):
+    H, Hkv, D, bs = 32, 8, 128, 16
+    mb = (L + bs - 1) // bs
+    nb = A * mb + 1
+    if int8:
+        k = torch.randint(-127, 127, (nb, Hkv, bs, D), device=b.dev, dtype=torch.int8)
+        v = torch.randint(-127, 127, (nb, Hkv, bs, D), device=b.dev, dtype=torch.int8)
+        ks, vs = torch.rand(nb, Hkv, bs, device=b.dev), torch.rand(nb, Hkv, bs, device=b.dev)
+    else:
+        k, v, ks, vs = b.randn(nb, Hkv, bs, D), b.randn(nb, Hkv, bs, D), None, None
+    tables = torch.randperm(nb - 1, device=b.dev)[:A * mb].view(A, mb).int()
+    lens = torch.full((A,), L, device=b.dev, dtype=torch.int32)
+    q = b.randn(A, H, D)
+    return q, k, v, tables, lens, ks, vs, A * L * Hkv * D * 2 * (1 if int8 else 2)
+
+
+def case_decode(b: Bench):
+    from tesseract_b200 import ops
+    q, k, v, tables, lens, ks, vs, nbytes = _paged(b, 256, 1400, False)
+    ms = b.time(lambda: ops.paged_decode_attention(q, k, v, tables, lens, None, ks, vs, max_len_hint=2560))
+    report("decode", ms, bytes_=nbytes, shape=[256, 1400])
+
+
+def case_decode_int8(b: Bench):
+    from tesseract_b200 import ops
+    q, k, v, tables, lens, ks, vs, nbytes = _paged(b, 256, 1400, True)
+    ms = b.time(lambda: ops.paged_decode_attention(q, k, v, tables, lens, None, ks, vs, max_len_hint=2560))
+    report("decode_int8", ms, bytes_=nbytes, shape=[256, 1400])
+
+
+def case_rmsnorm(b: Bench):
+    from tesseract_b200 import ops
+    x, w = b.randn(32768, 4096), torch.ones(4096, device=b.dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        ms = b.time(lambda: ops.rms_norm(x, w, 1e-5))
+    report("rmsnorm", ms, bytes_=2 * x.numel() * 2, shape=list(x.shape))
+
+
+def case_swiglu(b: Bench):
+    from tesseract_b200 import ops
+    x = b.randn(16384, 2 * 14336)
+    with torch.no_grad():
+        ms = b.time(lambda: ops.swiglu(x))
+    report("swiglu", ms, bytes_=x.numel() * 2 * 1.5, shape=list(x.shape))
+
+
+def case_adam(b: Bench):
+    from tesseract_b200 import _native
+    from tesseract_b200.optim import optimizers  # noqa: F401  (registers the signatures of loss_optim.cu)
+    n = 256 << 20
+    p = torch.zeros(n, device=b.dev, dtype=torch.bfloat16)
+    g = torch.zeros(n, device=b.dev, dtype=torch.bfloat16)
+    m = torch.zeros(n, device=b.dev, dtype=torch.float32)
+    v = torch.zeros(n, device=b.dev, dtype=torch.float32)
+    s = torch.cuda.current_stream().cuda_stream
+    lib = _native.lib()
+    ms = b.time(lambda: _native.check(lib.tsb_adam_flat(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), None, n,
+                                                        1e-4, 0.9, 0.999, 1e-8, 0.1, 0.001, 0.0, None, 1, 1, s),
+                                      "tsb_adam_flat"))
+    report("adam", ms, bytes_=n * (2 + 2 + 4 + 4 + 2 + 4 + 4), shape=[n])
+
+
+def case_ce(b: Bench):
+    from tesseract_b200 import ops
+    T, V = 4096, 128256
+    logits = b.randn(T, V)
+    tgt = torch.randint(0, V, (T,), device=b.dev)
+    ms = b.time(lambda: ops.ce_stats(logits, tgt))
+    report("ce_stats", ms, bytes_=T * V * 2, shape=[T, V])
+
+
+def case_scan(b: Bench):
+    from tesseract_b200.ops import ssm
+    B, L, D, N = 4, 4096, 4096, 16
+    u = torch.randn(B, L, D, device=b.dev, generator=b.gen)
+    delta = torch.rand(B, L, D, device=b.dev, generator=b.gen) * 0.1
+    A = -torch.rand(D, N, device=b.dev, generator=b.gen)
+    Bm = torch.randn(B, L, N, device=b.dev, generator=b.gen)
+    C = torch.randn(B, L, N, device=b.dev, generator=b.gen)
+    Dv = torch.ones(D, device=b.dev)
+    with torch.no_grad():
+        ms = b.time(lambda: ssm.selective_scan(u, delta, A, Bm, C, Dv))
+    report("selective_scan", ms, bytes_=3 * B * L * D * 4, shape=[B, L, D, N])
+
+
+def case_gemv(b: Bench):
+    from tesseract_b200 import quant
+    N, K = 14336, 4096
+    w = torch.randn(N, K, device=b.dev, generator=b.gen)
+    q8, s8 = (t.to(b.dev) for t in quant.pack_int8_symmetric(w))     # the packer works on the host
+    x = b.randn(1, K)
+    ms = b.time(lambda: quant.dequantize_matmul_int8(x, q8, s8))
+    report("gemv_w8", ms, bytes_=N * K, shape=[1, N, K])
+
+
+def _ptrs(ts):
+    return (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+
+
+def case_gemm_rs_emul(b: Bench):
+    from tesseract_b200 import _native
+    from tesseract_b200.parallel import fused_tp  # noqa: F401
+    lib = _native.lib()
+    world, rpr, N, K = 2, 4096, 4096, 2048
+    M = world * rpr
+    x, w = b.randn(M, K), b.randn(N, K, scale=0.02)
+    staging = [torch.empty(world, rpr, N, device=b.dev, dtype=torch.bfloat16) for _ in range(world)]
+    pa = _ptrs(staging)
+    s = torch.cuda.current_stream().cuda_stream
+    ms = b.time(lambda: _native.check(lib.tsb_gemm_rs(x.data_ptr(), w.data_ptr(), pa, M, N, K, x.stride(0), w.stride(0),
+                                                      0, rpr, 0, world, s), "tsb_gemm_rs"))
+    report("gemm_rs_emul", ms, flops=2.0 * M * N * K, shape=[M, N, K], note="rank 0 of 2, peers on the same GPU")
+
+
+def case_ag_gemm_emul(b: Bench):
+    from tesseract_b200 import _native
+    from tesseract_b200.parallel import fused_tp  # noqa: F401
+    lib = _native.lib()
+    world, rpr, N, K = 2, 4096, 3072, 4096
+    M = world * rpr
+    shards = [b.randn(rpr, K) for _ in range(world)]
+    w = b.randn(N, K, scale=0.02)
+    lands = [torch.empty(M, K, device=b.dev, dtype=torch.bfloat16) for _ in range(world)]
+    flags = [torch.zeros(world, dtype=torch.int32, device=b.dev) for _ in range(world)]
+    y = torch.empty(M, N, device=b.dev, dtype=torch.bfloat16)
+    pl, pf = _ptrs(lands), _ptrs(flags)
+    s = torch.cuda.current_stream().cuda_stream
+    calls = [0]
+
+    def call(rank, mask):
+        _native.check(lib.tsb_gemm_ag(shards[rank].data_ptr(), pl, pf, None, w.data_ptr(), y.data_ptr(), calls[0], 1,
+                                      mask, M, N, K, w.stride(0), y.stride(0), 0, rpr, rank, world, None, s),
+                      "tsb_gemm_ag")
+
+    def push_all():
+        calls[0] += 1
+        for r in range(world):
+            call(r, 1)
+    push_all()
+    ms_mult = b.time(lambda: call(0, 2))
+    ms_push = b.time(push_all) / world
+    report("ag_gemm_emul", ms_mult, flops=2.0 * M * N * K, shape=[M, N, K], push_ms=round(ms_push, 4),
+           note="multiply half of rank 0 of 2 after both ranks' push halves; push_ms = one rank's push half alone")
+
+
+CASES = {"gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "grouped_gemm": case_grouped_gemm,
+         "flash_fwd": case_flash_fwd, "flash_bwd": case_flash_bwd, "decode": case_decode,
+         "decode_int8": case_decode_int8, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu, "adam": case_adam,
+         "ce_stats": case_ce, "selective_scan": case_scan, "gemv_w8": case_gemv, "gemm_rs_emul": case_gemm_rs_emul,
+         "ag_gemm_emul": case_ag_gemm_emul}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="all", choices=["all"] + sorted(CASES))
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    from tesseract_b200 import _native
+    names = sorted(CASES) if a.case == "all" else [a.case]
+    for n in names:
+        CASES[n](Bench(a.iters))
+        torch.cuda.synchronize()
+    status = _native.read_status(torch.cuda.current_stream().cuda_stream)
+    if status:
+        print(json.dumps({"kernel_status": status}))
+        sys.exit(1)
+
+
+if __name__ == "__main__":
+    main()

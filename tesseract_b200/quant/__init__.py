@@ -82,6 +82,8 @@ def dequantize_matmul_int8(x: torch.Tensor, q_weight: torch.Tensor, weight_scale
     """x [..., in] @ dequant(q_weight [out, in])^T (src/ops/cpu/DequantMatMul.cpp)."""
     x2 = x.reshape(-1, x.shape[-1])
     N, K = q_weight.shape
+    if q_weight.device != x.device or weight_scale.device != x.device:
+        raise ValueError("dequantize_matmul_int8: activations, packed weights and scales must be on one device")
     if _small_m(x2) and K % 16 == 0 and hasattr(lib(), "tsb_gemv_w8"):
         xc = x2.contiguous()
         y = torch.empty((x2.shape[0], N), device=x.device, dtype=x.dtype)
@@ -97,6 +99,8 @@ def dequantize_matmul_int4_group(x: torch.Tensor, q_weight: torch.Tensor, weight
     x2 = x.reshape(-1, x.shape[-1])
     N, K2 = q_weight.shape
     K = K2 * 2
+    if q_weight.device != x.device or weight_scale.device != x.device:
+        raise ValueError("dequantize_matmul_int4_group: activations, packed weights and scales must be on one device")
     if _small_m(x2) and K % 32 == 0 and group_size % 32 == 0 and hasattr(lib(), "tsb_gemv_w4g"):
         xc = x2.contiguous()
         y = torch.empty((x2.shape[0], N), device=x.device, dtype=x.dtype)
