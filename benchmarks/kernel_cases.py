@@ -95,6 +95,15 @@ def case_gemm_wgrad(b: Bench):
     report("gemm_wgrad", ms, flops=2.0 * T * N * K, shape=[N, K, T])
 
 
+def case_gemm_fp8(b: Bench):
+    from tesseract_b200.ops import fp8
+    M = N = K = 8192
+    qa, sa = fp8.quantize_act(b.randn(M, K))
+    qb, sb = fp8.quantize_weight(b.randn(N, K, scale=0.02))
+    ms = b.time(lambda: fp8.fp8_gemm(qa, sa, qb, sb))
+    report("gemm_fp8", ms, flops=2.0 * M * N * K, shape=[M, N, K], note="fractions are of the bf16 peak")
+
+
 def case_grouped_gemm(b: Bench):
     from tesseract_b200.ops import moe
     E, N, K, per = 8, 4096, 4096, 2048
@@ -276,7 +285,7 @@ def case_ag_gemm_emul(b: Bench):
            note="multiply half of rank 0 of 2 after both ranks' push halves; push_ms = one rank's push half alone")
 
 
-CASES = {"gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "grouped_gemm": case_grouped_gemm,
+CASES = {"gemm": case_gemm, "gemm_fp8": case_gemm_fp8, "gemm_wgrad": case_gemm_wgrad, "grouped_gemm": case_grouped_gemm,
          "flash_fwd": case_flash_fwd, "flash_bwd": case_flash_bwd, "decode": case_decode,
          "decode_int8": case_decode_int8, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu, "adam": case_adam,
          "ce_stats": case_ce, "selective_scan": case_scan, "gemv_w8": case_gemv, "gemm_rs_emul": case_gemm_rs_emul,

@@ -222,6 +222,68 @@ def test_adam_matches_reference_formula(dev, use_arena):
         assert torch.allclose(p.detach(), r, atol=1e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("master", [False, True])
+def test_adam_flat_bf16_vector_path_and_tail(dev, master):
+    """bf16 parameters and gradients through the 8-wide kernel plus its scalar tail, against the fp32 formula."""
+    from tesseract_b200 import _native
+    from tesseract_b200.optim import optimizers  # noqa: F401
+    n = 8 * 4099 + 5
+    g0 = torch.Generator(device=dev).manual_seed(4)
+    w32 = torch.randn(n, device=dev, generator=g0)
+    p = w32.bfloat16()
+    mst = w32.clone() if master else None
+    ref = w32.clone() if master else p.float()
+    m = torch.zeros(n, device=dev)
+    v = torch.zeros(n, device=dev)
+    rm, rv = m.clone(), v.clone()
+    lib = _native.lib()
+    s = torch.cuda.current_stream().cuda_stream
+    for t in range(1, 4):
+        g = torch.randn(n, device=dev, generator=g0).bfloat16()
+        bc1, bc2 = 1 - 0.9 ** t, 1 - 0.999 ** t
+        _native.check(lib.tsb_adam_flat(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(),
+                                        mst.data_ptr() if master else None, n, 1e-2, 0.9, 0.999, 1e-8, bc1, bc2, 0.01,
+                                        None, 1, 1, s), "tsb_adam_flat")
+        gf = g.float()
+        rm = 0.9 * rm + 0.1 * gf
+        rv = 0.999 * rv + 0.001 * gf * gf
+        ref = ref - 1e-2 * ((rm / bc1) / ((rv / bc2).sqrt() + 1e-8) + 0.01 * ref)
+        if not master:
+            ref = ref.bfloat16().float()          # without a master copy the weights round to bf16 every step
+    assert torch.allclose(m, rm, atol=1e-6, rtol=1e-5) and torch.allclose(v, rv, atol=1e-7, rtol=1e-5)
+    assert torch.allclose(p.float(), ref.bfloat16().float(), atol=2e-2, rtol=1e-2)
+    if master:
+        assert torch.allclose(mst, ref, atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 264, 512), (1024, 4096, 4096), (64, 6144, 1024)])
+def test_fp8_blockscaled_gemm_and_quantisers(dev, M, N, K):
+    """Quantisers against their torch restatement (same bytes, same scales) and the tcgen05 fp8 GEMM against the
+    fp32 matmul of the dequantised operands."""
+    from tesseract_b200.ops import fp8
+    g = torch.Generator(device=dev).manual_seed(M + N)
+    x = (torch.randn(M, K, device=dev, generator=g) * 3).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    x[0, :128] = 0                                            # an all-zero block takes scale 1
+    qa, sa = fp8.quantize_act(x)
+    qb, sb = fp8.quantize_weight(w)
+    qa_r, sa_r = fp8.quantize_act_ref(x)
+    qb_r, sb_r = fp8.quantize_weight_ref(w)
+    assert torch.allclose(sa, sa_r, rtol=1e-6) and torch.allclose(sb, sb_r, rtol=1e-6)
+    # the device rounds x * (1 / scale), torch rounds x / scale: a few bytes may land on the neighbouring code
+    assert float((qa != qa_r).float().mean()) < 0.02 and float((qb != qb_r).float().mean()) < 0.02
+    da, ra = fp8.dequantize_act(qa, sa), fp8.dequantize_act(qa_r, sa_r)
+    # at most one e4m3 step: 2^-3 relative for normal codes, scale * 2^-9 absolute in the subnormal range
+    assert bool(((da - ra).abs() <= 0.13 * ra.abs() + float(sa.max()) * 2.0 ** -9 * 1.01).all())
+    y = fp8.fp8_gemm(qa, sa, qb, sb)
+    ref = fp8.dequantize_act(qa, sa) @ fp8.dequantize_weight(qb, sb).t()
+    _status_ok()
+    assert _rel_err(y, ref) < 5e-3                            # bf16 output rounding only
+    assert _rel_err(y, x.float() @ w.float().t()) < 6e-2      # end-to-end fp8 quantisation error
+    lin = fp8.Fp8Linear(w)
+    assert _rel_err(lin(x.view(1, M, K)).view(M, N), ref) < 5e-3
+
+
 def test_tiny_llama_train_step_matches_cpu(dev):
     """bf16 GPU step through every native kernel vs the fp32 CPU restatement of the same model."""
     from tesseract_b200.models import LlamaConfig, LlamaModel

@@ -244,3 +244,24 @@ def test_tesseract_python_surface():
     gc = ts.models.MambaGenerateConfig()
     gc.max_new_tokens = 4
     assert len(mm.generate([1, 4, 2], gc)) == 7
+
+
+def test_fp8_block_scaling_restatement_cpu():
+    """1 x 128 / 128 x 128 E4M3 quantisation and the block-scaled matmul (torch restatement used as the oracle of
+    the CUDA kernels): scales, zero blocks, ragged N, round trip error."""
+    from tesseract_b200.ops import fp8
+    torch.manual_seed(0)
+    x = torch.randn(70, 256) * 2
+    w = torch.randn(200, 256) * 0.05
+    x[3, 128:] = 0
+    qa, sa = fp8.quantize_act(x)
+    qb, sb = fp8.quantize_weight(w)
+    assert qa.dtype == torch.uint8 and sa.shape == (2, 70) and sb.shape == (2, 2)
+    assert sa[1, 3] == 1.0
+    assert torch.allclose(sa[0], x[:, :128].abs().amax(1) / 448.0)
+    assert (fp8.dequantize_act(qa, sa) - x).abs().max() <= x.abs().max() / 8          # 3 mantissa bits
+    y = fp8.fp8_gemm(qa, sa, qb, sb).float()
+    ref = x @ w.t()
+    assert ((y - ref).norm() / ref.norm()) < 6e-2
+    lin = fp8.Fp8Linear(w, bias=torch.ones(200))
+    assert torch.allclose(lin(x).float(), y + 1.0, atol=2e-2)
