@@ -365,3 +365,43 @@ class GrammarConstraint:
         self.state = self.automaton.walk(self.state, self.token_bytes[token_id])
         if self.state == K_DEAD:
             raise RuntimeError("GrammarConstraint.accept: token leaves the grammar")
+
+
+def generate_structured(model, prompt_ids, tokenizer, regex: str, cfg=None, token_bytes: Optional[Sequence[bytes]] = None):
+    """``LlamaModel.generate`` with every step's logits masked by the regular expression ``regex``
+    (the reference wires the same constraint into its generate CLI, examples/llama_generate.cpp:133,
+    through ``GrammarConstraint::apply`` / ``accept``). EOS is allowed only in accepting states; generation stops at
+    EOS, at ``max_new_tokens``, or when the grammar allows no further token. Returns prompt + generated ids."""
+    import torch
+
+    from .llama import GenerateConfig
+    from .sampler import Sampler
+    cfg = cfg or GenerateConfig()
+    V = model.config.vocab_size
+    if token_bytes is None:
+        token_bytes = [tokenizer.decode([i]).encode("utf-8") if i < 256 or hasattr(tokenizer, "vocab_size") else b""
+                       for i in range(V)]
+    if len(token_bytes) != V:
+        token_bytes = (list(token_bytes) + [b""] * V)[:V]
+    constraint = GrammarConstraint(RegexAutomaton(regex), token_bytes, cfg.eos_token_id)
+    prompt = [int(t) for t in prompt_ids]
+    total = len(prompt) + cfg.max_new_tokens
+    caches = model.make_quantized_kv_caches(1, total) if cfg.kv_int8 else model.make_kv_caches(1, total)
+    sampler = Sampler(cfg.sampling, cfg.seed) if cfg.do_sample else None
+    out = list(prompt)
+    dev = next(model.parameters()).device
+    logits = model.forward_step(torch.tensor([prompt], dtype=torch.int64, device=dev), caches)
+    for step in range(cfg.max_new_tokens):
+        row = logits[0, -1].float().cpu().numpy().copy()
+        try:
+            constraint.apply(row)
+        except RuntimeError:
+            break                                   # the grammar is exhausted
+        nxt = int(row.argmax()) if sampler is None else sampler.sample(row, out)
+        out.append(nxt)
+        if cfg.eos_token_id >= 0 and nxt == cfg.eos_token_id:
+            break
+        constraint.accept(nxt)
+        if step + 1 < cfg.max_new_tokens:
+            logits = model.forward_step(torch.tensor([[nxt]], dtype=torch.int64, device=dev), caches)
+    return out
