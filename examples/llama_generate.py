@@ -52,7 +52,7 @@ def main() -> int:
         model = LlamaModel.from_pretrained(a.safetensors, cfg, device=dev)
     elif a.model:
         cfg = preset(a.model, dtype, 2048)
-        model = LlamaModel(cfg, device=dev, seed=a.seed)
+        model = LlamaModel(cfg, device=dev, init_std=0.02, seed=a.seed)
     else:
         print("error: pass --model-dir, or --config with --safetensors, or a --model preset. See --help.", file=sys.stderr)
         return 1

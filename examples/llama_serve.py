@@ -36,7 +36,7 @@ def main() -> int:
     dev = pick_device(a.device)
     dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
     cfg = preset(a.model, dtype, 2048)
-    model = LlamaModel(cfg, device=dev, seed=a.seed)
+    model = LlamaModel(cfg, device=dev, init_std=0.02, seed=a.seed)
     model.eval()
     tok = load_tokenizer(a.tokenizer)
     ecfg = EngineConfig(block_size=16, num_blocks=1024, max_seq_len=2048, max_batch_size=a.max_batch, kv_int8=a.kv_int8)
