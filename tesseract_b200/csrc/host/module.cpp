@@ -1,0 +1,69 @@
+// pybind11 bindings of the host runtime (module name: _tsb_host).
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "host_runtime.hpp"
+
+namespace py = pybind11;
+using namespace tsbh;
+
+PYBIND11_MODULE(_tsb_host, m) {
+  m.doc() = "tesseract_b200 host runtime: sampler, BPE merge loop, KV block allocator, parallel file reads";
+
+  py::class_<HostSampler>(m, "HostSampler")
+      .def(py::init([](float temperature, long long top_k, float top_p, float repetition_penalty, uint64_t seed) {
+             SamplingParams p;
+             p.temperature = temperature;
+             p.top_k = top_k;
+             p.top_p = top_p;
+             p.repetition_penalty = repetition_penalty;
+             return new HostSampler(p, seed);
+           }),
+           py::arg("temperature") = 1.f, py::arg("top_k") = 0, py::arg("top_p") = 1.f,
+           py::arg("repetition_penalty") = 1.f, py::arg("seed") = 0)
+      .def("reseed", &HostSampler::reseed)
+      .def("next_u64", &HostSampler::next_u64)
+      .def("uniform_double", &HostSampler::uniform_double)
+      .def("sample",
+           [](HostSampler& s, py::array_t<float, py::array::c_style | py::array::forcecast> logits,
+              py::array_t<int64_t, py::array::c_style | py::array::forcecast> prev) {
+             return s.sample(logits.data(), logits.size(), prev.data(), prev.size());
+           },
+           py::arg("logits"), py::arg("prev_tokens"));
+
+  py::class_<BpeCore>(m, "BpeCore")
+      .def(py::init<const std::unordered_map<std::string, int32_t>&, const std::vector<std::pair<std::string, std::string>>&,
+                    const std::vector<std::string>&>())
+      .def("encode_piece", [](const BpeCore& b, py::bytes piece) { return b.encode_piece(std::string(piece)); });
+
+  py::class_<BlockAllocator>(m, "BlockAllocator")
+      .def(py::init<int64_t>())
+      .def("allocate", &BlockAllocator::allocate)
+      .def("free", &BlockAllocator::free)
+      .def("num_free", &BlockAllocator::num_free)
+      .def("num_blocks", &BlockAllocator::num_blocks)
+      .def("num_used", &BlockAllocator::num_used);
+
+  m.def("read_ranges",
+        [](const std::string& path, const std::vector<int64_t>& offsets, const std::vector<int64_t>& sizes,
+           const std::vector<uintptr_t>& dst, int threads) {
+          py::gil_scoped_release nogil;
+          return read_ranges(path, offsets, sizes, dst, threads);
+        },
+        py::arg("path"), py::arg("offsets"), py::arg("sizes"), py::arg("dst"), py::arg("threads") = 8);
+  m.def("safetensors_header", [](const std::string& path) {
+    auto r = safetensors_header(path);
+    return py::make_tuple(py::bytes(r.first), r.second);
+  });
+  m.def("token_mask",
+        [](py::array_t<int32_t, py::array::c_style | py::array::forcecast> table, int32_t state, py::bytes all_bytes,
+           py::array_t<int64_t, py::array::c_style | py::array::forcecast> offsets) {
+          const std::string bytes(all_bytes);
+          const int64_t n = offsets.size() - 1;
+          py::array_t<uint8_t> out(n);
+          token_mask(table.data(), table.shape(0), state, reinterpret_cast<const uint8_t*>(bytes.data()), offsets.data(), n,
+                     out.mutable_data());
+          return out;
+        });
+}

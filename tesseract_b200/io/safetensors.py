@@ -149,3 +149,32 @@ def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Optional[Di
 def load_file(path: str, device=None) -> Dict[str, torch.Tensor]:
     with SafeTensors.open(path) as st:
         return {k: st.load(k, device) for k in st.keys()}
+
+
+def load_file_parallel(path: str, device=None, threads: int = 8, pin: bool = True) -> Dict[str, torch.Tensor]:
+    """Whole-file load through the native host runtime: the data section is read by ``threads`` pread workers
+    straight into ONE (pinned) host buffer, the tensors are views of it, and a CUDA ``device`` gets them with
+    asynchronous copies from pinned memory. Falls back to ``load_file`` when the runtime is not built."""
+    from .. import _native
+    host = _native.host()
+    if host is None:
+        return load_file(path, device)
+    with SafeTensors.open(path) as st:
+        entries = {k: st._entries[k] for k in st.keys()}
+        data_start = st._data_start
+    total = max((e for _, _, _, e in entries.values()), default=0)
+    buf = torch.empty(max(total, 1), dtype=torch.uint8)
+    if pin and torch.cuda.is_available():
+        buf = buf.pin_memory()
+    if total:
+        got = host.read_ranges(path, [data_start], [total], [buf.data_ptr()], threads)
+        if got != total:
+            raise SafeTensorsError(f"{path}: read {got} of {total} data bytes")
+    out = {}
+    for name, (dt, shape, b, e) in entries.items():
+        tdt = _DTYPES[dt][0]
+        t = buf[b:e].view(tdt).reshape(shape) if e > b else torch.empty(shape, dtype=tdt)
+        out[name] = t.to(device, non_blocking=True) if device is not None else t
+    if device is not None and torch.device(device).type == "cuda":
+        torch.cuda.synchronize(device)
+    return out

@@ -152,6 +152,20 @@ class BpeTokenizer(Tokenizer):
         self.bos_id = next((self.added[t] for t in ("<|begin_of_text|>", "<s>") if t in self.added), -1)
         self.eos_id = next((self.added[t] for t in ("<|end_of_text|>", "</s>", "<|eot_id|>") if t in self.added), -1)
         self._cache: Dict[bytes, List[int]] = {}
+        self._core = None           # native merge loop (csrc/host/bpe_io.cpp), built on first use
+        self._core_tried = False
+
+    def _native_core(self):
+        if not self._core_tried:
+            self._core_tried = True
+            import os
+            if os.environ.get("TESSERACT_HOST", "") != "python":
+                from .. import _native
+                host = _native.host()
+                if host is not None:
+                    merges = sorted(self.ranks.items(), key=lambda kv: kv[1])
+                    self._core = host.BpeCore(self.vocab, [pair for pair, _ in merges], [_B2U[b] for b in range(256)])
+        return self._core
 
     @classmethod
     def from_json(cls, text: str) -> "BpeTokenizer":
@@ -181,6 +195,12 @@ class BpeTokenizer(Tokenizer):
         hit = self._cache.get(piece)
         if hit is not None:
             return hit
+        core = self._native_core()
+        if core is not None:
+            ids = list(core.encode_piece(bytes(piece)))
+            if len(self._cache) < 65536:
+                self._cache[piece] = ids
+            return ids
         syms = [_B2U[b] for b in piece]
         while len(syms) > 1:
             best, best_rank = None, None

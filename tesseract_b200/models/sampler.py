@@ -118,15 +118,40 @@ def sample_from_logits(logits: np.ndarray, params: SamplingParams, prev_tokens: 
     return argmax_lowest_index(work)
 
 
-class Sampler:
-    """Owns the RNG of one request (src/models/Sampler.hpp `Sampler`)."""
+def _host_module():
+    """The native host runtime (csrc/host), or None when it is not built or TESSERACT_HOST=python."""
+    import os
+    if os.environ.get("TESSERACT_HOST", "") == "python":
+        return None
+    from .. import _native
+    return _native.host()
 
-    def __init__(self, params: Optional[SamplingParams] = None, seed: int = 0):
+
+class Sampler:
+    """Owns the RNG of one request (src/models/Sampler.hpp `Sampler`). Runs in the native host runtime
+    (std::mt19937_64 and the same pipeline in C++, csrc/host/sampler.cpp) when that is built; the Python
+    implementation above is its bit-identical twin."""
+
+    def __init__(self, params: Optional[SamplingParams] = None, seed: int = 0, native: Optional[bool] = None):
         self.params = params or SamplingParams()
-        self.rng = MT19937_64(seed)
+        host = _host_module() if native in (None, True) else None
+        if native is True and host is None:
+            raise RuntimeError("Sampler: the native host runtime is not built")
+        self._native = None
+        if host is not None:
+            self._native = host.HostSampler(float(self.params.temperature), int(self.params.top_k),
+                                            float(self.params.top_p), float(self.params.repetition_penalty),
+                                            int(seed) & 0xFFFFFFFFFFFFFFFF)
+        self.rng = MT19937_64(seed) if self._native is None else None
 
     def sample(self, logits, prev_tokens: Sequence[int] = ()) -> int:
-        return sample_from_logits(np.asarray(logits, dtype=np.float32), self.params, prev_tokens, self.rng)
+        lg = np.asarray(logits, dtype=np.float32)
+        if self._native is not None:
+            return int(self._native.sample(lg.reshape(-1), np.asarray(list(prev_tokens), dtype=np.int64)))
+        return sample_from_logits(lg, self.params, prev_tokens, self.rng)
 
     def reseed(self, seed: int) -> None:
-        self.rng.seed(seed)
+        if self._native is not None:
+            self._native.reseed(int(seed) & 0xFFFFFFFFFFFFFFFF)
+        else:
+            self.rng.seed(seed)

@@ -134,8 +134,25 @@ class QuantizedKVCache(KVCacheBase):
         return 2 * (self.k_q.numel() + self.k_scale.numel() * 4)
 
 
+def _native_block_allocator(num_blocks: int):
+    import os
+    if os.environ.get("TESSERACT_HOST", "") == "python":
+        return None
+    from .. import _native
+    host = _native.host()
+    return host.BlockAllocator(num_blocks) if host is not None else None
+
+
 class BlockAllocator:
-    """Free list of block ids; LIFO, seeded so that the first allocation returns block 0."""
+    """Free list of block ids; LIFO, seeded so that the first allocation returns block 0. Backed by the native
+    host runtime (csrc/host/sampler.cpp `BlockAllocator`) when that is built."""
+
+    def __new__(cls, num_blocks: int):
+        if num_blocks > 0 and cls is BlockAllocator:
+            nat = _native_block_allocator(num_blocks)
+            if nat is not None:
+                return nat
+        return super().__new__(cls)
 
     def __init__(self, num_blocks: int):
         if num_blocks <= 0:

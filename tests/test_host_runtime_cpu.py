@@ -1,0 +1,106 @@
+"""The native host runtime (csrc/host, pybind11 module _tsb_host) against its pure-Python twins: identical random
+streams and sampled tokens, identical BPE ids, identical allocator behaviour, parallel file reads."""
+import numpy as np
+import pytest
+import torch
+
+from tesseract_b200 import _native
+
+host = _native.host()
+pytestmark = pytest.mark.skipif(host is None, reason="native host runtime not built")
+
+
+def test_mt19937_64_stream_and_uniform_match_python():
+    from tesseract_b200.models.sampler import MT19937_64
+    for seed in (0, 1, 5489, 2 ** 63 + 12345):
+        py, nat = MT19937_64(seed), host.HostSampler(seed=seed)
+        assert [py.next_u64() for _ in range(700)] == [nat.next_u64() for _ in range(700)]   # crosses a twist
+        assert [py.uniform_double() for _ in range(50)] == [nat.uniform_double() for _ in range(50)]
+    assert host.HostSampler(seed=5489).next_u64() == 14514284786278117030        # std::mt19937_64 default seed, 1st draw
+
+
+@pytest.mark.parametrize("params", [dict(temperature=0.8), dict(temperature=1.3, top_k=7),
+                                    dict(temperature=0.7, top_p=0.9), dict(temperature=1.0, top_k=20, top_p=0.5,
+                                                                           repetition_penalty=1.3),
+                                    dict(temperature=0.0, repetition_penalty=2.0)])
+def test_sampler_tokens_match_python(params):
+    from tesseract_b200.models.sampler import Sampler, SamplingParams
+    rng = np.random.default_rng(3)
+    sp = SamplingParams(**params)
+    a, b = Sampler(sp, seed=11, native=False), Sampler(sp, seed=11, native=True)
+    hist = []
+    for _ in range(60):
+        logits = rng.standard_normal(997).astype(np.float32) * 3
+        logits[rng.integers(0, 997, 5)] = logits.max()            # ties
+        ta, tb = a.sample(logits, hist), b.sample(logits, hist)
+        assert ta == tb
+        hist.append(ta)
+    a.reseed(5)
+    b.reseed(5)
+    assert a.sample(logits, hist) == b.sample(logits, hist)
+
+
+def test_bpe_core_matches_python(monkeypatch):
+    from tesseract_b200.io.tokenizer import _B2U, BpeTokenizer
+    alphabet = [_B2U[b] for b in range(256)]
+    vocab = {ch: i for i, ch in enumerate(alphabet)}
+    merges = []
+    def add(a, b):
+        merges.append((a, b))
+        vocab.setdefault(a + b, len(vocab))
+    sp = _B2U[ord(" ")]
+    add("t", "h"); add("th", "e"); add(sp, "the"); add("i", "n"); add("a", "n"); add(sp, "a"); add("e", "r"); add("in", "g")
+    merges.append(("x", "y"))                                       # merged symbol missing from the vocabulary
+    text = "the other thing in an xy anthem " * 3 + "naïve café 你好"
+    monkeypatch.setenv("TESSERACT_HOST", "python")
+    py_ids = BpeTokenizer(vocab, merges, {"<s>": 900}).encode("<s>" + text)
+    monkeypatch.delenv("TESSERACT_HOST")
+    tok = BpeTokenizer(vocab, merges, {"<s>": 900})
+    nat_ids = tok.encode("<s>" + text)
+    assert tok._core is not None and nat_ids == py_ids
+    assert tok.decode(nat_ids) == text
+
+
+def test_block_allocator_native_behaviour():
+    from tesseract_b200.nn.kv_cache import BlockAllocator
+    al = BlockAllocator(4)
+    assert type(al).__module__ == "_tsb_host"
+    assert [al.allocate() for _ in range(4)] == [0, 1, 2, 3] and al.num_free() == 0 and al.num_used() == 4
+    with pytest.raises(RuntimeError):
+        al.allocate()
+    al.free(2)
+    assert al.allocate() == 2
+    al.free(1)
+    with pytest.raises(RuntimeError):
+        al.free(1)
+    with pytest.raises(RuntimeError):
+        al.free(17)
+    with pytest.raises(ValueError):
+        BlockAllocator(0)
+
+
+def test_parallel_safetensors_load_matches_mmap_reader(tmp_path):
+    from tesseract_b200.io import load_file, load_file_parallel, save_file
+    g = torch.Generator().manual_seed(0)
+    tensors = {"a": torch.randn(1000, 300, generator=g), "b": torch.randint(0, 100, (77,), generator=g),
+               "c.bf16": torch.randn(5000, 64, generator=g).bfloat16(), "empty": torch.zeros(0, 3)}
+    path = str(tmp_path / "m.safetensors")
+    save_file(tensors, path, metadata={"format": "pt"})
+    ref, got = load_file(path), load_file_parallel(path, threads=4, pin=False)
+    assert list(ref) == list(got)
+    for k in ref:
+        assert ref[k].dtype == got[k].dtype and torch.equal(ref[k], got[k])
+    hdr, off = host.safetensors_header(path)
+    assert off % 8 == 0 and b'"__metadata__"' in hdr
+    with pytest.raises(RuntimeError):
+        host.read_ranges(path, [0], [10 ** 9], [0], 2) if False else host.safetensors_header(str(tmp_path / "missing"))
+
+
+def test_token_mask_kernel():
+    # automaton over bytes for [0-9]+ : state 0 --digit--> 1 --digit--> 1
+    table = np.full((2, 256), -1, dtype=np.int32)
+    table[:, ord("0"):ord("9") + 1] = 1
+    toks = [b"12", b"a", b"", b"7", b"3x"]
+    offs = np.cumsum([0] + [len(t) for t in toks]).astype(np.int64)
+    mask = host.token_mask(table, 0, b"".join(toks), offs)
+    assert mask.tolist() == [1, 0, 0, 1, 0]
