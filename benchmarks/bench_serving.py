@@ -8,6 +8,11 @@ JSON line. Timing is wall clock around the engine loop with a device synchronise
 numbers come from the engine's own accounting (each phase ends with the device-to-host read of the new tokens).
 
     python benchmarks/bench_serving.py --requests 256 --kv-int8 0 --top-p 1.0
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29600 \
+        benchmarks/bench_serving.py --requests 256          # tensor parallel over the 8 ranks
+
+With more than one rank every rank runs the same engine on the same requests (tensor-parallel layers, replicated
+sampling); the reported times are the maximum over ranks.
 """
 from __future__ import annotations
 
@@ -22,7 +27,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
 def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, temperature=0.0, max_batch=256,
-                      prompt_range=(128, 2048), out_range=(64, 512), seed=0, cuda_graph=True, device=None, model=None):
+                      prompt_range=(128, 2048), out_range=(64, 512), seed=0, cuda_graph=True, device=None, model=None,
+                      tp_group=None, rank=0, world=1):
     import torch
 
     from tesseract_b200.models import GenerateConfig, LlamaConfig, LlamaModel
@@ -46,7 +52,11 @@ def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, tempera
     num_blocks = total_tokens // block + requests + 64       # every request can be resident at once
     ecfg = EngineConfig(block_size=block, num_blocks=num_blocks, max_seq_len=max_seq, max_batch_size=max_batch,
                         kv_int8=kv_int8)
-    eng = ServingEngine(model, ecfg, use_cuda_graph=cuda_graph, temperature=temperature, top_p=top_p, seed=seed)
+    tp = None
+    if world > 1:
+        from tesseract_b200.serving.engine import TPServe
+        tp = TPServe(tp_group, rank, world, dev, cfg.hidden_size, max_batch=max(512, max_batch))
+    eng = ServingEngine(model, ecfg, use_cuda_graph=cuda_graph, temperature=temperature, top_p=top_p, seed=seed, tp=tp)
     # warm-up: one short request end to end (kernel attributes, allocator pools, first graph bucket)
     eng.add_request(reqs[0][0][:64], GenerateConfig(max_new_tokens=4))
     eng.run()
@@ -60,7 +70,23 @@ def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, tempera
     wall = time.perf_counter() - t0
     m = eng.metrics()
     gen_tokens = sum(o for _, o in reqs)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([eng.stats["prefill_s"], eng.stats["decode_s"], wall], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=tp_group)
+        pre_s, dec_s, wall = t.tolist()
+        m["prefill_tok_s"] = eng.stats["prefill_tokens"] / pre_s if pre_s > 0 else 0.0
+        m["decode_tok_s"] = eng.stats["decode_tokens"] / dec_s if dec_s > 0 else 0.0
+        digest = torch.tensor([sum(sum(r.tokens[r.prompt_len:]) for r in eng.requests.values()) % (1 << 40)],
+                              device=dev, dtype=torch.int64)
+        lo, hi = digest.clone(), digest.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=tp_group)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=tp_group)
+        if int(lo) != int(hi):
+            raise RuntimeError("tensor-parallel ranks generated different tokens")
+    from tesseract_b200 import _native
     return {
+        "tp": world, "kernel_status": _native.read_status(torch.cuda.current_stream(dev).cuda_stream),
         "requests": requests, "kv": "int8" if kv_int8 else "bf16", "sampling": "greedy" if temperature <= 0 else f"top_p={top_p}",
         "prefill_tok_s": m["prefill_tok_s"], "decode_tok_s": m["decode_tok_s"], "ttft_p50_ms": m["ttft_p50_ms"],
         "end_to_end_s": wall, "generated_tokens": gen_tokens, "total_tok_s": (total_tokens) / wall,
@@ -79,9 +105,23 @@ def main():
     ap.add_argument("--max-batch", type=int, default=256)
     ap.add_argument("--no-graph", action="store_true")
     a = ap.parse_args()
+    import torch
+    world, rank = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(dev)
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
     out = run_serving_bench(a.requests, a.layers, bool(a.kv_int8), a.top_p, a.temperature, a.max_batch,
-                            cuda_graph=not a.no_graph)
-    print(json.dumps(out))
+                            cuda_graph=not a.no_graph, device=dev, tp_group=group, rank=rank, world=world)
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -60,27 +60,28 @@ _native.register_signatures({
 })
 
 
-def decode_linear(x: torch.Tensor, w: torch.Tensor, sm_count: int = 148) -> torch.Tensor:
+def decode_linear(x: torch.Tensor, w: torch.Tensor, sm_count: int = 148, out: torch.Tensor | None = None) -> torch.Tensor:
     """x [M, K] @ w [N, K]^T for decode-shaped calls (few rows): when the plain tiling would leave most SMs idle
     the K range is split across CTAs (fp32 atomics into a zeroed buffer, then one cast), so that the whole GPU
-    streams the weight matrix."""
+    streams the weight matrix. ``out`` (bf16 [M, N]) receives the result when given."""
     M, K = x.shape
     N = w.shape[0]
     if not (_use_native(x) and M <= 512 and hasattr(_native.lib(), "tsb_gemm_bf16_splitk")):
-        return matmul_nt(x, w)
+        r = matmul_nt(x, w)
+        return r if out is None else out.copy_(r)
     mt = (M + 127) // 128
     tiles = mt * ((N + 127) // 128)
     if tiles >= sm_count:
-        return gemm_bf16(x, w)
+        return gemm_bf16(x, w, out=out)
     kb = (K + 63) // 64
     split = max(1, min(kb // 4, (2 * sm_count + tiles - 1) // tiles, 16))
     if split == 1:
-        return gemm_bf16(x, w, block_n=128)
+        return gemm_bf16(x, w, block_n=128, out=out)
     out32 = torch.zeros((M, N), device=x.device, dtype=torch.float32)
     rc = _native.lib().tsb_gemm_bf16_splitk(x.data_ptr(), w.data_ptr(), out32.data_ptr(), M, N, K, x.stride(0),
                                             w.stride(0), N, 0, split, 128, _native.stream_ptr(x.device))
     _native.check(rc, "tsb_gemm_bf16_splitk")
-    return out32.to(torch.bfloat16)
+    return out32.to(torch.bfloat16) if out is None else out.copy_(out32)
 
 
 def matmul_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
@@ -134,7 +135,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     computes it even when ``weight`` itself is not an autograd leaf (a fused view over several
     parameters that share one arena).
     """
-    if _use_native(x) and weight.dtype == torch.bfloat16 and weight.stride(-1) == 1:
+    # the tcgen05 path needs 16-byte aligned rows in all three GEMMs (forward, dX, dW): out and in multiples of 8
+    aligned = weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0 and weight.stride(0) % 8 == 0
+    if _use_native(x) and weight.dtype == torch.bfloat16 and weight.stride(-1) == 1 and aligned:
         y = _LinearFn.apply(x, weight, wgrad_buf, bool(force_wgrad and wgrad_buf is not None))
         if bias is not None:
             y = y + bias

@@ -39,6 +39,7 @@ _native.register_signatures({
     "tsb_ipc_close": [P],
     "tsb_symm_barrier": [PP, I, I, I, P],
     "tsb_reduce_slots": [P, P, I, L, P],
+    "tsb_allreduce_oneshot": [PP, PP, P, P, L, I, I, P],
     "tsb_gemm_rs": [P, P, PP, I, I, I, L, L, I, I, I, I, P],
     "tsb_gemm_ag": [P, PP, PP, P, P, P, I, I, I, I, I, I, L, L, I, I, I, I, P, P],
 })
@@ -228,3 +229,43 @@ class FusedTP:
         for m in (self.pads, self._land, self._stage, self._flagmem):
             if m is not None:
                 m.close()
+
+
+class SymmAllReduce:
+    """Latency-optimised all-reduce of small bf16 tensors over peer memory (``csrc/allreduce_oneshot.cu``), for
+    tensor-parallel decode. Usage per call: write the partial into ``input_view(rows, cols)`` (it alternates
+    between two symmetric buffers), then ``reduce(rows, cols)`` returns the sum in a regular local tensor. All
+    pointers and the epoch counter live on the device, so the pair can be captured in a CUDA graph."""
+
+    def __init__(self, group, rank: int, world: int, device, max_elems: int):
+        if world > 8:
+            raise ValueError("SymmAllReduce supports at most 8 ranks (one NVSwitch domain)")
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.max_elems = (max_elems + 7) // 8 * 8
+        self.half_bytes = self.max_elems * 2
+        self.buf = SymmetricMemory(group, rank, world, 2 * self.half_bytes, device)
+        self.flags = SymmetricMemory(group, rank, world, 256, device)
+        self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self._ptrs = [self.buf.offset_ptr_array(0), self.buf.offset_ptr_array(self.half_bytes)]
+        self.parity = 0
+        self.calls = 0
+
+    def input_view(self, rows: int, cols: int) -> torch.Tensor:
+        n = rows * cols
+        if n > self.max_elems or n % 8:
+            raise ValueError("SymmAllReduce: message larger than the buffer or not a multiple of 8 elements")
+        off = self.parity * self.half_bytes
+        return self.buf.local[off:off + n * 2].view(torch.bfloat16).view(rows, cols)
+
+    def reduce(self, rows: int, cols: int) -> torch.Tensor:
+        out = torch.empty((rows, cols), dtype=torch.bfloat16, device=self.device)
+        check(lib().tsb_allreduce_oneshot(self._ptrs[self.parity], self.flags.ptr_array, self.state.data_ptr(),
+                                          out.data_ptr(), rows * cols, self.rank, self.world,
+                                          torch.cuda.current_stream(self.device).cuda_stream), "tsb_allreduce_oneshot")
+        self.parity ^= 1
+        self.calls += 1
+        return out
+
+    def close(self) -> None:
+        self.buf.close()
+        self.flags.close()

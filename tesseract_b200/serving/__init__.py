@@ -1,3 +1,3 @@
-from .engine import ServingEngine, argmax_rows, sample_top_p_rows
+from .engine import ServingEngine, TPServe, argmax_rows, sample_top_p_rows
 
-__all__ = ["ServingEngine", "argmax_rows", "sample_top_p_rows"]
+__all__ = ["ServingEngine", "TPServe", "argmax_rows", "sample_top_p_rows"]

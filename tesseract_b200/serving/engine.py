@@ -13,6 +13,12 @@ the device:
 * the decode step is captured into CUDA graphs per batch-size bucket, so a step costs one graph launch;
 * prompts admitted in the same step are prefilled together (projections and FFN batched over all their tokens,
   FlashAttention per prompt), instead of one un-batched prefill per request (src/models/Scheduler.cpp:115-124).
+
+Tensor parallelism (``tp=TPServe(...)``, one process per GPU, every rank runs the same engine on the same requests):
+attention heads and FFN columns are split over the ranks (q/k/v and gate/up column-parallel, o_proj and down_proj
+row-parallel), each rank keeps the KV pool of its own KV heads, and the two partial sums per layer are combined
+with the one-shot peer-memory all-reduce kernel on the decode path (inside the CUDA graph) and with NCCL on the
+prefill path. Embedding, norms and lm_head are replicated, so every rank picks the same token without talking.
 """
 from __future__ import annotations
 
@@ -69,18 +75,40 @@ def sample_top_p_rows(logits: torch.Tensor, temperature: float, top_p: float, se
     return out
 
 
+class TPServe:
+    """Tensor-parallel context of a serving engine: process group, this rank, and the peer-memory all-reduce."""
+
+    def __init__(self, group, rank: int, world: int, device, hidden_size: int, max_batch: int = 512):
+        from ..parallel.fused_tp import SymmAllReduce
+        self.group, self.rank, self.world = group, rank, world
+        self.max_rows = max_batch
+        self.ar = SymmAllReduce(group, rank, world, device, max_batch * hidden_size)
+        self.nccl_calls = 0
+
+    def all_reduce_big(self, x: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+        dist.all_reduce(x, group=self.group)
+        self.nccl_calls += 1
+        return x
+
+
 class ServingEngine:
     BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
 
     def __init__(self, model: LlamaModel, cfg: Optional[EngineConfig] = None, use_cuda_graph: bool = True,
-                 temperature: float = 0.0, top_p: float = 1.0, seed: int = 0):
+                 temperature: float = 0.0, top_p: float = 1.0, seed: int = 0, tp: Optional[TPServe] = None):
         self.model, self.cfg = model, cfg or EngineConfig()
+        self.tp = tp
         c, mc = self.cfg, model.config
         self.device = model._device()
         if self.device.type != "cuda" or mc.dtype not in (torch.bfloat16, torch.float16):
             raise ValueError("ServingEngine needs a bf16 / fp16 model on a CUDA device "
                              "(use ContinuousBatchingScheduler for CPU or fp32 models)")
         self.H, self.Hkv, self.D = mc.num_attention_heads, mc.kv_heads(), mc.head_dim
+        if tp is not None:
+            if self.H % tp.world or self.Hkv % tp.world or mc.intermediate_size % tp.world:
+                raise ValueError("ServingEngine: heads, KV heads and FFN width must divide over the TP ranks")
+            self.H, self.Hkv = self.H // tp.world, self.Hkv // tp.world
         self.L = len(model.layers)
         self.temperature, self.top_p, self.seed = temperature, top_p, seed
         self.greedy = temperature <= 1e-6
@@ -107,19 +135,48 @@ class ServingEngine:
 
     # ------------------------------------------------------------------ weights
     def _fuse_weights(self) -> None:
-        """q/k/v and gate/up become views of one concatenated tensor per layer (one GEMM each)."""
-        self.wqkv, self.wgu = [], []
+        """q/k/v and gate/up become one concatenated tensor per layer (one GEMM each). Under tensor parallelism
+        every tensor is this rank's shard (rows of q/k/v/gate/up, columns of o_proj/down_proj) and the full
+        projection weights of the model are released."""
+        self.wqkv, self.wgu, self.wo, self.wdown = [], [], [], []
+        tp = self.tp
         with torch.no_grad():
             for blk in self.model.layers:
                 a, f = blk.attn, blk.ffn
-                w = torch.cat([a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], dim=0).contiguous()
-                n0, n1 = a.q_proj.weight.shape[0], a.k_proj.weight.shape[0]
-                a.q_proj.weight.data, a.k_proj.weight.data, a.v_proj.weight.data = w[:n0], w[n0:n0 + n1], w[n0 + n1:]
-                self.wqkv.append(w)
-                g = torch.cat([f.gate_proj.weight, f.up_proj.weight], dim=0).contiguous()
-                nf = f.gate_proj.weight.shape[0]
-                f.gate_proj.weight.data, f.up_proj.weight.data = g[:nf], g[nf:]
-                self.wgu.append(g)
+                if tp is None:
+                    w = torch.cat([a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], dim=0).contiguous()
+                    n0, n1 = a.q_proj.weight.shape[0], a.k_proj.weight.shape[0]
+                    a.q_proj.weight.data, a.k_proj.weight.data, a.v_proj.weight.data = w[:n0], w[n0:n0 + n1], w[n0 + n1:]
+                    g = torch.cat([f.gate_proj.weight, f.up_proj.weight], dim=0).contiguous()
+                    nf = f.gate_proj.weight.shape[0]
+                    f.gate_proj.weight.data, f.up_proj.weight.data = g[:nf], g[nf:]
+                    self.wqkv.append(w)
+                    self.wgu.append(g)
+                    self.wo.append(a.o_proj.weight)
+                    self.wdown.append(f.down_proj.weight)
+                    continue
+                r, D = tp.rank, self.D
+                q0, k0 = r * self.H * D, r * self.Hkv * D
+                self.wqkv.append(torch.cat([a.q_proj.weight[q0:q0 + self.H * D], a.k_proj.weight[k0:k0 + self.Hkv * D],
+                                            a.v_proj.weight[k0:k0 + self.Hkv * D]], dim=0).contiguous())
+                self.wo.append(a.o_proj.weight[:, q0:q0 + self.H * D].contiguous())
+                fl = f.gate_proj.weight.shape[0] // tp.world
+                self.wgu.append(torch.cat([f.gate_proj.weight[r * fl:(r + 1) * fl], f.up_proj.weight[r * fl:(r + 1) * fl]],
+                                          dim=0).contiguous())
+                self.wdown.append(f.down_proj.weight[:, r * fl:(r + 1) * fl].contiguous())
+                for lin in (a.q_proj, a.k_proj, a.v_proj, a.o_proj, f.gate_proj, f.up_proj, f.down_proj):
+                    lin.weight.data = torch.empty(0, dtype=lin.weight.dtype, device=lin.weight.device)
+
+    def _mm_reduce(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """x @ w^T summed over the tensor-parallel ranks (row-parallel projection)."""
+        tp = self.tp
+        if tp is None:
+            return self._mm(x, w)
+        T, N = x.shape[0], w.shape[0]
+        if T <= tp.max_rows and x.dtype == torch.bfloat16:
+            ops.decode_linear(x, w, out=tp.ar.input_view(T, N))
+            return tp.ar.reduce(T, N)
+        return tp.all_reduce_big(self._mm(x, w))
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids, gen: Optional[GenerateConfig] = None) -> int:
@@ -217,10 +274,10 @@ class ServingEngine:
             for (a, b) in prefill_bounds:
                 outs.append(ops.flash_attention_packed(q4[a:b].unsqueeze(0), H, Hkv, causal=True).view(b - a, H * D))
             o = torch.cat(outs, dim=0) if len(outs) > 1 else outs[0]
-        a_out = self._mm(o, blk.attn.o_proj.weight)
+        a_out = self._mm_reduce(o, self.wo[li])
         h2, res = ops.rms_norm(a_out, blk.norm_2.weight, blk.norm_2.eps, residual=res)
         gu = self._mm(h2, self.wgu[li])
-        f = self._mm(ops.swiglu(gu), blk.ffn.down_proj.weight)
+        f = self._mm_reduce(ops.swiglu(gu), self.wdown[li])
         return f, res
 
     @staticmethod
@@ -232,6 +289,8 @@ class ServingEngine:
 
     def _forward(self, tokens, positions, slots, tables, lens, prefill_bounds=None, last_rows=None):
         m = self.model
+        if self.tp is not None:
+            self.tp.ar.parity = 0     # every pass makes an even number of all-reduces: the two buffers strictly alternate
         x = ops.embedding(tokens, m.embed_tokens.weight)
         res = None
         for li in range(self.L):

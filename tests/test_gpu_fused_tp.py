@@ -158,6 +158,43 @@ def _worker(rank, world, port, q):
         ep_errs = [((ya.float() - yb.float()).norm() / ya.float().norm()).item(),
                    ((xa.grad.float() - xb.grad.float()).norm() / xa.grad.float().norm()).item()]
         errs += ep_errs
+        # tensor-parallel serving: sharded engine (one-shot all-reduce kernel inside the decode CUDA graph) against
+        # the single-GPU engine on the same seeded model and requests
+        from tesseract_b200.models import GenerateConfig, LlamaModel
+        from tesseract_b200.models.scheduler import EngineConfig
+        from tesseract_b200.serving import ServingEngine, TPServe
+        from tesseract_b200.parallel.fused_tp import SymmAllReduce
+        ar = SymmAllReduce(dist.group.WORLD, rank, world, dev, 64 * 512)
+        for it in range(4):                                            # both buffers, several epochs
+            part = torch.randn(64, 512, device=dev, generator=g).bfloat16()
+            ar.input_view(64, 512).copy_(part)
+            got = ar.reduce(64, 512)
+            want = part.float().clone()
+            dist.all_reduce(want)
+            errs.append(((got.float() - want).norm() / want.norm()).item())
+        scfg = LlamaConfig(vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=4 * world,
+                           num_key_value_heads=world, intermediate_size=1024, max_position_embeddings=256,
+                           dtype=torch.bfloat16)
+        ecfg = EngineConfig(block_size=16, num_blocks=256, max_seq_len=256, max_batch_size=8)
+        prompts = [[(7 * i + j) % 2048 for j in range(20 + 9 * i)] for i in range(5)]
+        outs = {}
+        for mode in ("single", "tp"):
+            m = LlamaModel(scfg, device=dev, init_std=0.05, seed=9)
+            tp = TPServe(dist.group.WORLD, rank, world, dev, scfg.hidden_size) if mode == "tp" else None
+            eng = ServingEngine(m, ecfg, tp=tp)
+            ids = [eng.add_request(p, GenerateConfig(max_new_tokens=12)) for p in prompts]
+            eng.run()
+            outs[mode] = [eng.result(i)[len(p):] for i, p in zip(ids, prompts)]
+        flat = torch.tensor([t for o in outs["tp"] for t in o], device=dev)
+        lo, hi = flat.clone(), flat.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        assert torch.equal(lo, hi), "tensor-parallel ranks picked different tokens"
+        same = sum(a == b for x, y in zip(outs["single"], outs["tp"]) for a, b in zip(x, y))
+        agree = same / sum(len(x) for x in outs["single"])
+        assert all(x[0] == y[0] for x, y in zip(outs["single"], outs["tp"])), "first tokens differ from the single-GPU engine"
+        assert agree > 0.6, agree
+        status |= _native.read_status(torch.cuda.current_stream().cuda_stream)
         dist.barrier()
         q.put((rank, None, (errs, status, losses)))
     except Exception:  # pragma: no cover

@@ -284,6 +284,18 @@ def test_fp8_blockscaled_gemm_and_quantisers(dev, M, N, K):
     assert _rel_err(lin(x.view(1, M, K)).view(M, N), ref) < 5e-3
 
 
+def test_linear_with_unaligned_width_falls_back(dev):
+    """A 4-wide projection (an MoE router with four experts) cannot use 16-byte aligned rows: forward and backward
+    run through the library path instead of refusing."""
+    from tesseract_b200.ops import linear
+    x = torch.randn(33, 256, device=dev).bfloat16().requires_grad_(True)
+    w = (torch.randn(4, 256, device=dev) * 0.1).bfloat16().requires_grad_(True)
+    y = linear(x, w)
+    y.float().sum().backward()
+    assert _rel_err(y, x.float() @ w.float().t()) < 1e-2
+    assert x.grad is not None and w.grad is not None and w.grad.shape == w.shape
+
+
 def test_tiny_llama_train_step_matches_cpu(dev):
     """bf16 GPU step through every native kernel vs the fp32 CPU restatement of the same model."""
     from tesseract_b200.models import LlamaConfig, LlamaModel
