@@ -88,7 +88,8 @@ def parse_args():
     ap.add_argument("--global-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--micro-batch", type=int, default=0, help="sequences per forward/backward pass (0 = choose)")
-    ap.add_argument("--serve", type=int, default=-1, help="also run the serving benchmark (1 GPU only; -1 = auto)")
+    ap.add_argument("--serve", type=int, default=-1,
+                    help="also run the serving benchmark, tensor-parallel over all ranks (-1 = when all 32 layers run)")
     ap.add_argument("--serve-requests", type=int, default=256)
     ap.add_argument("--layers", type=int, default=32, help="(debug only) fewer layers; invalidates the metric")
     ap.add_argument("--master-weights", action="store_true")
@@ -190,8 +191,8 @@ def main():
                "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4 * world}
 
     serve = None
-    want_serve = args.serve == 1 or (args.serve == -1 and world == 1 and args.layers == 32)
-    if want_serve and world == 1:
+    want_serve = args.serve == 1 or (args.serve == -1 and args.layers == 32)
+    if want_serve:
         # free the training state first: the serving model and its KV pool need the memory
         del trainer, dev_batches
         import gc
@@ -200,7 +201,8 @@ def main():
         try:
             sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "benchmarks"))
             from bench_serving import run_serving_bench
-            serve = run_serving_bench(requests=args.serve_requests, layers=args.layers, device=device)
+            serve = run_serving_bench(requests=args.serve_requests, layers=args.layers, device=device,
+                                      tp_group=dist.group.WORLD if world > 1 else None, rank=rank, world=world)
         except Exception as e:  # the training number stands on its own
             serve = {"error": f"{type(e).__name__}: {e}"[:300]}
 
