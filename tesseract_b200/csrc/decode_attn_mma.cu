@@ -139,21 +139,29 @@ paged_decode_mma_kernel(MmaDecParams p) {
 
   // tiles of this warp: warp, warp + 4, ... ; `issue(j)` starts the copies of this warp's j-th tile
   const int my_tiles = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
+  // Pool row of token t for this KV head (block-table lookup, clamped): computed once per tile by lanes 0..15,
+  // one row each, and handed to the copying lanes with shuffles -- the copy loop itself is then two cp.async and
+  // one shuffle per 16-byte piece, no divisions and no table reads.
+  auto row_of = [&](int t, bool valid) -> long long {
+    int blk = valid ? table[t / p.bs] : 0;
+    blk = (blk < 0 || blk >= p.nb) ? 0 : blk;
+    return (static_cast<long long>(blk) * p.Hkv + hk) * p.bs + (valid ? t % p.bs : 0);
+  };
   auto issue = [&](int j) {
     const int tile = warp + j * kWarps;
     const int tok0 = t_begin + tile * kTile;
     const uint32_t dstK = wsmem_u32 + (j % kStagesD) * kStageBytes;
     const uint32_t dstV = dstK + (INT8 ? kRawTile : kTileBytes);
+    const int my_t = tok0 + (lane & 15);
+    const bool my_valid = my_t < t_end;
+    const long long my_row = row_of(my_t, my_valid);           // lanes 16..31 duplicate lanes 0..15
+    constexpr int kRowsPerIter = 32 / kChunks;
+    const int piece = lane % kChunks;
 #pragma unroll
-    for (int i = 0; i < (kTile * kChunks + 31) / 32; ++i) {
-      const int c = lane + 32 * i;
-      if (c >= kTile * kChunks) break;
-      const int r = c / kChunks, piece = c % kChunks;
-      const int t = tok0 + r;
-      const bool valid = t < t_end;
-      int blk = valid ? table[t / p.bs] : 0;
-      blk = (blk < 0 || blk >= p.nb) ? 0 : blk;
-      const long long row = (static_cast<long long>(blk) * p.Hkv + hk) * p.bs + (valid ? t % p.bs : 0);
+    for (int i = 0; i < kTile / kRowsPerIter; ++i) {
+      const int r = i * kRowsPerIter + lane / kChunks;
+      const long long row = __shfl_sync(0xffffffffu, my_row, r);
+      const int valid = __shfl_sync(0xffffffffu, static_cast<int>(my_valid), r);
       const size_t off = static_cast<size_t>(row) * kRawRow + piece * 16;
       const uint32_t d = r * (INT8 ? kRawRow : kRowBytes) + piece * 16;
       cp_async16(dstK + d, static_cast<const char*>(p.k_pool) + off, valid ? 16 : 0);
@@ -161,15 +169,9 @@ paged_decode_mma_kernel(MmaDecParams p) {
     }
     if constexpr (INT8) {
       // scales: 16 K + 16 V floats per tile, 4 bytes each -> one 4-byte async copy per lane
-      const int r = lane & 15;
-      const int t = tok0 + r;
-      const bool valid = t < t_end;
-      int blk = valid ? table[t / p.bs] : 0;
-      blk = (blk < 0 || blk >= p.nb) ? 0 : blk;
-      const long long row = (static_cast<long long>(blk) * p.Hkv + hk) * p.bs + (valid ? t % p.bs : 0);
-      const float* src = (lane < 16 ? p.k_scale : p.v_scale) + row;
+      const float* src = (lane < 16 ? p.k_scale : p.v_scale) + my_row;
       const uint32_t dst = dstK + 2 * kRawTile + lane * 4;
-      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid ? 4 : 0) : "memory");
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(my_valid ? 4 : 0) : "memory");
     }
   };
 #pragma unroll
