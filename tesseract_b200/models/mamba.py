@@ -1,6 +1,7 @@
 """Mamba language model: embed -> N x (RMSNorm -> Mamba -> residual) -> norm -> lm_head
-(src/models/MambaModel.cpp:60-173). ``generate`` prefills with one full-sequence scan that also yields the
-recurrent state (the reference steps the prompt token by token) and then decodes with O(1) state."""
+(src/models/MambaModel.cpp:60-173). ``generate`` feeds the prompt through the recurrent step token by token, as the
+reference does, and then decodes with O(1) state; ``forward`` (training, scoring) uses the chunked full-sequence
+scan kernel."""
 from __future__ import annotations
 
 from dataclasses import dataclass
