@@ -28,7 +28,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, temperature=0.0, max_batch=256,
                       prompt_range=(128, 2048), out_range=(64, 512), seed=0, cuda_graph=True, device=None, model=None,
-                      tp_group=None, rank=0, world=1):
+                      tp_group=None, rank=0, world=1, max_prefill_tokens=16384):
     import torch
 
     from tesseract_b200.models import GenerateConfig, LlamaConfig, LlamaModel
@@ -56,7 +56,8 @@ def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, tempera
     if world > 1:
         from tesseract_b200.serving.engine import TPServe
         tp = TPServe(tp_group, rank, world, dev, cfg.hidden_size, max_batch=max(512, max_batch))
-    eng = ServingEngine(model, ecfg, use_cuda_graph=cuda_graph, temperature=temperature, top_p=top_p, seed=seed, tp=tp)
+    eng = ServingEngine(model, ecfg, use_cuda_graph=cuda_graph, temperature=temperature, top_p=top_p, seed=seed, tp=tp,
+                        max_prefill_tokens=max_prefill_tokens)
     # warm-up: one short request end to end (kernel attributes, allocator pools, first graph bucket)
     eng.add_request(reqs[0][0][:64], GenerateConfig(max_new_tokens=4))
     eng.run()
@@ -91,7 +92,7 @@ def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, tempera
         "prefill_tok_s": m["prefill_tok_s"], "decode_tok_s": m["decode_tok_s"], "ttft_p50_ms": m["ttft_p50_ms"],
         "end_to_end_s": wall, "generated_tokens": gen_tokens, "total_tok_s": (total_tokens) / wall,
         "steps": m["steps"], "max_batch": max_batch, "block_size": block, "cuda_graph": cuda_graph,
-        "weights": "bf16", "layers": len(model.layers),
+        "weights": "bf16", "layers": len(model.layers), "max_prefill_tokens": max_prefill_tokens,
     }
 
 
@@ -104,6 +105,7 @@ def main():
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--max-batch", type=int, default=256)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--max-prefill-tokens", type=int, default=16384, help="prompt tokens admitted per engine step (0 = all)")
     a = ap.parse_args()
     import torch
     world, rank = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0))
@@ -115,7 +117,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     out = run_serving_bench(a.requests, a.layers, bool(a.kv_int8), a.top_p, a.temperature, a.max_batch,
-                            cuda_graph=not a.no_graph, device=dev, tp_group=group, rank=rank, world=world)
+                            cuda_graph=not a.no_graph, device=dev, tp_group=group, rank=rank, world=world,
+                            max_prefill_tokens=a.max_prefill_tokens)
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

@@ -96,9 +96,13 @@ class ServingEngine:
     BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
 
     def __init__(self, model: LlamaModel, cfg: Optional[EngineConfig] = None, use_cuda_graph: bool = True,
-                 temperature: float = 0.0, top_p: float = 1.0, seed: int = 0, tp: Optional[TPServe] = None):
+                 temperature: float = 0.0, top_p: float = 1.0, seed: int = 0, tp: Optional[TPServe] = None,
+                 max_prefill_tokens: int = 0):
         self.model, self.cfg = model, cfg or EngineConfig()
         self.tp = tp
+        # prompt tokens admitted per step (0 = no limit): bounds the time to first token of the requests at the
+        # head of the queue and the size of the prefill activations; at least one request is always admitted
+        self.max_prefill_tokens = max_prefill_tokens
         c, mc = self.cfg, model.config
         self.device = model._device()
         if self.device.type != "cuda" or mc.dtype not in (torch.bfloat16, torch.float16):
@@ -307,9 +311,12 @@ class ServingEngine:
 
     # ------------------------------------------------------------------ scheduling
     def _admit(self) -> List[_Req]:
-        admitted, reserved = [], 0
+        admitted, reserved, ptoks = [], 0, 0
         while self.waiting and len(self.running) + len(admitted) < self.cfg.max_batch_size:
             head = self.waiting[0]
+            if admitted and self.max_prefill_tokens > 0 and ptoks + head.prompt_len > self.max_prefill_tokens:
+                break
+            ptoks += head.prompt_len
             need = self._blocks_for(head.prompt_len + 1)
             if self.free_blocks() - reserved < need:
                 if not self.running and not admitted:

@@ -493,6 +493,16 @@ def test_serving_engine_graph_vs_eager_and_generate(dev, kv_int8):
         m = eng.metrics()
         assert m["requests"] == len(prompts) and m["decode_tok_s"] > 0
     assert outs[True] == outs[False]
+    # admitting at most 40 prompt tokens per step changes the schedule, not a request's tokens (bf16 KV: batch
+    # composition does not enter a request's arithmetic)
+    eng = ServingEngine(model, EngineConfig(block_size=16, num_blocks=64, max_seq_len=256, max_batch_size=4,
+                                            kv_int8=kv_int8), use_cuda_graph=False, max_prefill_tokens=40)
+    ids = [eng.add_request(p, GenerateConfig(max_new_tokens=12)) for p in prompts]
+    eng.run()
+    chunked = [eng.result(i) for i in ids]
+    assert eng.steps > m["steps"] and all(len(a) == len(b) for a, b in zip(chunked, outs[False]))
+    same = sum(int(a == b) for x, y in zip(chunked, outs[False]) for a, b in zip(x, y))
+    assert same >= 0.9 * sum(len(x) for x in chunked)
     _status_ok()
     if not kv_int8:
         agree = 0
