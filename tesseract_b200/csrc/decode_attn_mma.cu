@@ -17,6 +17,8 @@
 // reference's one-CTA-per-(request, head) CUDA-core kernel).
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace tsb {
 namespace {
 
@@ -87,6 +89,9 @@ struct MmaDecParams {
 template <typename T, int D, bool INT8>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_mma_kernel(MmaDecParams p) {
+  // INT8 pools run their products in fp16 whatever the model type: int8 -> fp16 is one byte-permute and half a
+  // subtract per element (1024 + u is exact in fp16), and |k|, |v| <= 128 with fp32 accumulation loses nothing.
+  using MT = typename std::conditional<INT8, __half, T>::type;
   constexpr int kRowBytes = D * 2 + 16;           // padded row: consecutive rows fall into different 16-byte bank groups
   constexpr int kTileBytes = kTile * kRowBytes;   // one K (or V) tile as the tensor core reads it
   constexpr int kRawRow = INT8 ? D : D * 2;       // bytes per pool row
@@ -125,8 +130,14 @@ paged_decode_mma_kernel(MmaDecParams p) {
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       if (g < p.gh) {
-        qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
-        qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8);
+        if constexpr (std::is_same<MT, T>::value) {
+          qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
+          qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8);
+        } else {
+          const T* q0 = qrow + ks * 16 + 2 * t4;
+          qa[ks][0] = MmaT<MT>::pack(to_f32<T>(q0[0]), to_f32<T>(q0[1]));
+          qa[ks][1] = MmaT<MT>::pack(to_f32<T>(q0[8]), to_f32<T>(q0[9]));
+        }
       } else {
         qa[ks][0] = qa[ks][1] = 0u;
       }
@@ -201,10 +212,20 @@ paged_decode_mma_kernel(MmaDecParams p) {
         const int cc = c - which * kTile * kChunks;
         const int r = cc / kChunks, piece = cc % kChunks;
         const uint4 v = *reinterpret_cast<const uint4*>(raw + which * kRawTile + r * kRawRow + piece * 16);
-        const int8_t* e = reinterpret_cast<const int8_t*>(&v);
+        const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
         uint32_t w[8];
 #pragma unroll
-        for (int q2 = 0; q2 < 8; ++q2) w[q2] = MmaT<T>::pack(static_cast<float>(e[2 * q2]), static_cast<float>(e[2 * q2 + 1]));
+        for (int q4 = 0; q4 < 4; ++q4) {
+          // bytes x (int8) -> u = x + 128 -> fp16 bit patterns 0x6400 | u = 1024 + u -> minus 1152 = x, exactly
+          const uint32_t u = vw[q4] ^ 0x80808080u;
+          const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140);  // (1024 + u0, 1024 + u1)
+          const uint32_t hi = __byte_perm(u, 0x64646464u, 0x4342);  // (1024 + u2, 1024 + u3)
+          const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+          const __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias);
+          const __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
+          w[2 * q4] = *reinterpret_cast<const uint32_t*>(&a);
+          w[2 * q4 + 1] = *reinterpret_cast<const uint32_t*>(&b);
+        }
         uint8_t* dst = conv + which * kTileBytes + r * kRowBytes + piece * 32;
         *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
         *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
@@ -227,8 +248,8 @@ paged_decode_mma_kernel(MmaDecParams p) {
       const int r = (mat >> 1) * 8 + (lane & 7);
       ldsm_x4(kb, sK + r * kRowBytes + ks * 32 + (mat & 1) * 16);
       const uint32_t afrag[4] = {qa[ks][0], 0u, qa[ks][1], 0u};
-      MmaT<T>::mma(s[0], afrag, kb[0], kb[1]);
-      MmaT<T>::mma(s[1], afrag, kb[2], kb[3]);
+      MmaT<MT>::mma(s[0], afrag, kb[0], kb[1]);
+      MmaT<MT>::mma(s[1], afrag, kb[2], kb[3]);
     }
     // ---- online softmax for head row g (rows g + 8 are padding); this lane holds tokens b*8 + 2t, +1
     float mx = -INFINITY;
@@ -260,9 +281,9 @@ paged_decode_mma_kernel(MmaDecParams p) {
         w10 *= sc[16 + 8 + 2 * t4];
         w11 *= sc[16 + 8 + 2 * t4 + 1];
       }
-      pa[0] = MmaT<T>::pack(w00, w01);  // (head g, tokens 2t, 2t+1)
+      pa[0] = MmaT<MT>::pack(w00, w01);  // (head g, tokens 2t, 2t+1)
       pa[1] = 0u;                       // heads g + 8: padding
-      pa[2] = MmaT<T>::pack(w10, w11);  // (head g, tokens 8 + 2t, +1)
+      pa[2] = MmaT<MT>::pack(w10, w11);  // (head g, tokens 8 + 2t, +1)
       pa[3] = 0u;
     }
     m_run = m_new;
@@ -276,8 +297,8 @@ paged_decode_mma_kernel(MmaDecParams p) {
       ldsm_x4_trans(vb, sV + r * kRowBytes + nb2 * 32 + (mat >> 1) * 16);
       float c0[4] = {o[2 * nb2][0] * corr, o[2 * nb2][1] * corr, 0.f, 0.f};
       float c1[4] = {o[2 * nb2 + 1][0] * corr, o[2 * nb2 + 1][1] * corr, 0.f, 0.f};
-      MmaT<T>::mma(c0, pa, vb[0], vb[1]);
-      MmaT<T>::mma(c1, pa, vb[2], vb[3]);
+      MmaT<MT>::mma(c0, pa, vb[0], vb[1]);
+      MmaT<MT>::mma(c1, pa, vb[2], vb[3]);
       o[2 * nb2][0] = c0[0];
       o[2 * nb2][1] = c0[1];
       o[2 * nb2 + 1][0] = c1[0];

@@ -16,6 +16,9 @@
 // Also writes the per-row log-sum-exp needed by the backward kernel.
 #include "common.cuh"
 
+#include <cstdlib>
+#include <cstring>
+
 namespace tsb {
 namespace {
 
@@ -56,7 +59,11 @@ __device__ __forceinline__ uint64_t mnmajor_desc(uint32_t base, int ks, uint32_t
   return umma_smem_desc_sw128(base + ks * 2048, half_stride, 1024);
 }
 
-template <int D>
+// LAZY = true: the output accumulates in TMEM over all key tiles (the P V product adds to it) and is rescaled only
+// when a row's maximum has grown by more than 2^8 since the reference maximum of its exponents was set; the score
+// row is read from TMEM once per tile and kept in registers for both the maximum and the exponentials.
+// LAZY = false: the output is folded into fp32 registers after every tile (two reads of the score row per tile).
+template <int D, bool LAZY>
 __global__ void __launch_bounds__(kFaThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, FaParams p) {
@@ -173,7 +180,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t d = tmem_base + Cfg::kColO;
 #pragma unroll
         for (int ks = 0; ks < BKV / 16; ++ks)
-          umma_f16(d, kmajor_desc<128>(p_base, ks), mnmajor_desc(v_base, ks, 16384), idesc_o, ks != 0);
+          umma_f16(d, kmajor_desc<128>(p_base, ks), mnmajor_desc(v_base, ks, 16384), idesc_o,
+                   LAZY ? ((j | ks) != 0) : (ks != 0));
         umma_commit(&o_full);
         umma_commit(&v_empty[st]);
       }
@@ -183,6 +191,152 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int row = warp * 32 + lane;        // row within the tile == TMEM lane
     const int qi = q0 + row;                 // query index
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int row_limit = qi + offset;  // last visible key under causal masking
+    if constexpr (LAZY) {
+      float m_ref = -INFINITY, l_run = 0.f;  // m_ref: the maximum the exponents of this row currently refer to
+      bool ok = true;
+      const float kGrow = 8.f;                // rescale when the maximum has grown by more than 2^8
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        // a failed (timed-out) wait leaves the loop warp-uniformly: the TMEM accesses below are warp-collective
+        if (!__all_sync(0xffffffffu, mbar_wait(&s_full[st], (j >> 1) & 1, &cta_abort, p.status) ? 1 : 0)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t s_addr = tmem_base + lane_addr + (st ? Cfg::kColS1 : Cfg::kColS0);
+        uint32_t sr[BKV];
+#pragma unroll
+        for (int c = 0; c < BKV / 32; ++c) tmem_ld_32x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[c * 32]));
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&s_free[st]);              // the scores live in registers now: the MMA warp may refill the buffer
+        const int c0 = j * BKV;
+        const bool need_mask = (p.causal && c0 + BKV - 1 > q0 + offset) || (c0 + BKV > p.Sk);
+        int vis = BKV;
+        if (need_mask) {
+          int lim = p.Sk - c0;
+          if (p.causal) lim = min(lim, row_limit - c0 + 1);
+          vis = max(0, min(BKV, lim));
+        }
+        float m_tile = -INFINITY;
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < BKV; ++i)
+            if (i < vis) m_tile = fmaxf(m_tile, __uint_as_float(sr[i]));
+        } else {
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < BKV; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(sr[i]));
+            m1 = fmaxf(m1, __uint_as_float(sr[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(sr[i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(sr[i + 3]));
+          }
+          m_tile = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        }
+        // the previous P V product must be finished: it reads sP, and a rescale below rewrites its result
+        if (j > 0) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&o_full, (j - 1) & 1, &cta_abort, p.status) ? 1 : 0)) { ok = false; break; }
+          tc_fence_after();
+        }
+        float factor = 1.f;
+        bool grow = false;
+        if (m_tile != -INFINITY) {
+          if (m_ref == -INFINITY) {
+            m_ref = m_tile;                    // first visible scores of this row: nothing accumulated yet
+            grow = (j > 0);                    // (earlier tiles were fully masked for this row: O and l are zero)
+            factor = 1.f;
+          } else if ((m_tile - m_ref) * p.scale_log2 > kGrow) {
+            factor = exp2f((m_ref - m_tile) * p.scale_log2);
+            m_ref = m_tile;
+            grow = true;
+          }
+        }
+        if (j > 0 && __any_sync(0xffffffffu, grow && factor != 1.f)) {
+          // warp-collective: every lane rescales its own TMEM lane (factor 1 where nothing changed)
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + lane_addr + Cfg::kColO + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+            tmem_st_32x32(tmem_base + lane_addr + Cfg::kColO + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+        l_run *= factor;
+        const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+        const float mneg = -m_use * p.scale_log2;
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = exp2f(fmaf(__uint_as_float(sr[c * 32 + i]), p.scale_log2, mneg));
+            float p1 = exp2f(fmaf(__uint_as_float(sr[c * 32 + i + 1]), p.scale_log2, mneg));
+            if (need_mask) {
+              if (c * 32 + i >= vis) p0 = 0.f;
+              if (c * 32 + i + 1 >= vis) p1 = 0.f;
+            }
+            // the denominator sums what the tensor core will actually multiply (bf16-rounded P)
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            const float2 pf = __bfloat1622float2(pb);
+            l0 += pf.x;
+            l1 += pf.y;
+            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+          }
+          const int half = c >> 1;
+          uint8_t* prow = sP + half * 16384 + row * 128;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int chunk = (c & 1) * 4 + q4;
+            const int sw = chunk ^ (row & 7);
+            *reinterpret_cast<uint4*>(prow + sw * 16) =
+                make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+          }
+        }
+        l_run += l0 + l1;
+        tc_fence_before();
+        fence_proxy_async_smem();
+        mbar_arrive(&p_full);
+      }
+      // every lane of the warp takes part in the TMEM reads; only the global stores depend on the row
+      const bool warp_ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+      bool have_o = false;
+      if (warp_ok && n_tiles > 0) have_o = mbar_wait(&o_full, (n_tiles - 1) & 1, &cta_abort, p.status);
+      have_o = __all_sync(0xffffffffu, have_o ? 1 : 0) != 0;
+      if (have_o) tc_fence_after();
+      if (warp_ok && (have_o || n_tiles == 0)) {
+        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* orow = p.o + b * p.o_sb + static_cast<long long>(qi < p.Sq ? qi : 0) * p.o_ss + h * p.o_sh;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          if (have_o) {
+            tmem_ld_32x32(tmem_base + lane_addr + Cfg::kColO + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          if (qi < p.Sq) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[e]) * inv_l, __uint_as_float(r[e + 1]) * inv_l);
+              v.y = pack_bf16x2(__uint_as_float(r[e + 2]) * inv_l, __uint_as_float(r[e + 3]) * inv_l);
+              v.z = pack_bf16x2(__uint_as_float(r[e + 4]) * inv_l, __uint_as_float(r[e + 5]) * inv_l);
+              v.w = pack_bf16x2(__uint_as_float(r[e + 6]) * inv_l, __uint_as_float(r[e + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + c * 32 + e) = v;
+            }
+          }
+        }
+        if (qi < p.Sq && p.lse) {
+          const float lse = l_run > 0.f ? (m_ref * p.scale + __logf(l_run)) : -INFINITY;
+          p.lse[(static_cast<long long>(b) * p.H + h) * p.Sq + qi] = lse;
+        }
+      }
+    } else {
     float o_acc[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
@@ -333,6 +487,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         p.lse[(static_cast<long long>(b) * p.H + h) * p.Sq + qi] = lse;
       }
     }
+    }  // eager variant
   }
 
   tc_fence_before();
@@ -392,24 +547,22 @@ TSB_EXPORT int tsb_flash_fwd(const void* q, const void* k, const void* v, void* 
   p.status = device_status_word();
   dim3 grid((Sq + BQ - 1) / BQ, H, B);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (D == 128) {
-    static bool attr = false;
-    if (!attr) {
-      cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           FaCfg<128>::kSmemBytes);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      attr = true;
-    }
-    flash_fwd_kernel<128><<<grid, kFaThreads, FaCfg<128>::kSmemBytes, s>>>(tq, tk, tv, p);
-  } else {
-    static bool attr = false;
-    if (!attr) {
-      cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           FaCfg<64>::kSmemBytes);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      attr = true;
-    }
-    flash_fwd_kernel<64><<<grid, kFaThreads, FaCfg<64>::kSmemBytes, s>>>(tq, tk, tv, p);
-  }
+  // TESSERACT_FLASH_FWD=eager selects the variant that folds the output into registers after every key tile
+  static const bool lazy = [] {
+    const char* e = getenv("TESSERACT_FLASH_FWD");
+    return !(e && strcmp(e, "eager") == 0);
+  }();
+  auto launch = [&](auto kern, int smem_bytes) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    kern<<<grid, kFaThreads, smem_bytes, s>>>(tq, tk, tv, p);
+    return 0;
+  };
+  int rc;
+  if (D == 128)
+    rc = lazy ? launch(flash_fwd_kernel<128, true>, FaCfg<128>::kSmemBytes) : launch(flash_fwd_kernel<128, false>, FaCfg<128>::kSmemBytes);
+  else
+    rc = lazy ? launch(flash_fwd_kernel<64, true>, FaCfg<64>::kSmemBytes) : launch(flash_fwd_kernel<64, false>, FaCfg<64>::kSmemBytes);
+  if (rc) return rc;
   return static_cast<int>(cudaGetLastError());
 }

@@ -21,9 +21,40 @@ argmax_rows_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, l
   const T* x = logits + blockIdx.x * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) {
+  int j0 = 0;
+  if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // 16-byte loads, four of them in flight per thread; a thread visits its elements in increasing order, so the
+    // strict comparison keeps the lowest index among equal values
+    const int nvec = V / 8;
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    for (int c0 = threadIdx.x; c0 < nvec; c0 += 4 * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * blockDim.x;
+        if (c < nvec) v[u] = xv[c];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * blockDim.x;
+        if (c < nvec) {
+          const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float f = to_f32<T>(e[k]);
+            if (f > best) {
+              best = f;
+              bi = c * 8 + k;
+            }
+          }
+        }
+      }
+    }
+    j0 = nvec * 8;
+  }
+  for (int j = j0 + threadIdx.x; j < V; j += blockDim.x) {
     const float f = to_f32<T>(x[j]);
-    if (f > best) {
+    if (f > best || (f == best && j < bi)) {
       best = f;
       bi = j;
     }

@@ -296,6 +296,27 @@ def test_linear_with_unaligned_width_falls_back(dev):
     assert x.grad is not None and w.grad is not None and w.grad.shape == w.shape
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_flash_forward_with_growing_row_maxima(dev, causal):
+    """Scores that keep growing along the key axis (and rows whose first visible key comes late) force the
+    forward kernel to rescale the output it accumulates in tensor memory several times per row."""
+    from tesseract_b200.ops import attention_ref, flash_attention
+    B, S, H, Hkv, D = 2, 700, 4, 2, 128
+    g = torch.Generator(device=dev).manual_seed(12)
+    q = torch.randn(B, S, H, D, device=dev, generator=g).bfloat16()
+    k = torch.randn(B, S, Hkv, D, device=dev, generator=g)
+    v = torch.randn(B, S, Hkv, D, device=dev, generator=g).bfloat16()
+    ramp = torch.linspace(0.2, 6.0, S, device=dev).view(1, S, 1, 1)          # later keys score up to 30x higher
+    k = (k * ramp).bfloat16()
+    with torch.no_grad():
+        got = flash_attention(q, k, v, causal=causal)
+        ref = attention_ref(q.transpose(1, 2).float(), k.transpose(1, 2).float(), v.transpose(1, 2).float(),
+                            causal=causal).transpose(1, 2)
+    _status_ok()
+    assert torch.isfinite(got.float()).all()
+    assert _rel_err(got, ref) < 2e-2
+
+
 def test_tiny_llama_train_step_matches_cpu(dev):
     """bf16 GPU step through every native kernel vs the fp32 CPU restatement of the same model."""
     from tesseract_b200.models import LlamaConfig, LlamaModel
@@ -462,6 +483,14 @@ def test_device_sampling_kernels(dev):
     ref = logits.float().argmax(-1)
     assert int(got[3]) == 100
     assert torch.equal(got.long(), ref) or (got.long() != ref).sum() <= 1
+    for V in (5003, 128256, 7):                    # scalar tail / unaligned rows, the Llama-3 vocabulary, tiny
+        lg = torch.randn(9, V, device=dev).bfloat16()
+        lg[2, V - 1] = 60.0                         # the maximum sits in the tail
+        lg[4, 0] = lg[4, V // 2] = 55.0             # ties resolve to the lowest index
+        got2 = argmax_rows(lg)
+        assert int(got2[2]) == V - 1 and int(got2[4]) == 0
+        vals = lg.float().gather(1, got2.long().view(-1, 1)).view(-1)
+        assert torch.equal(vals, lg.float().max(-1).values)
     peaked = torch.full((8, 1000), -10.0, device=dev).bfloat16()
     peaked[:, 7] = 5.0
     peaked[:, 9] = 4.5
