@@ -104,6 +104,20 @@ def case_gemm_fp8(b: Bench):
     report("gemm_fp8", ms, flops=2.0 * M * N * K, shape=[M, N, K], note="fractions are of the bf16 peak")
 
 
+def case_decode_gemm(b: Bench):
+    """Weight-streaming GEMMs of one decode step (Llama-8B layer shapes) at 64 and 256 rows."""
+    from tesseract_b200 import ops
+    for M in (64, 256):
+        tot_ms, tot_bytes = 0.0, 0
+        for name, N, K in (("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)):
+            x, w = b.randn(M, K), b.randn(N, K, scale=0.02)
+            ms = b.time(lambda: ops.decode_linear(x, w))
+            tot_ms += ms
+            tot_bytes += N * K * 2
+            report(f"decode_gemm_{name}_M{M}", ms, bytes_=N * K * 2, shape=[M, N, K])
+        report(f"decode_gemm_layer_M{M}", tot_ms, bytes_=tot_bytes)
+
+
 def case_grouped_gemm(b: Bench):
     from tesseract_b200.ops import moe
     E, N, K, per = 8, 4096, 4096, 2048
@@ -285,7 +299,7 @@ def case_ag_gemm_emul(b: Bench):
            note="multiply half of rank 0 of 2 after both ranks' push halves; push_ms = one rank's push half alone")
 
 
-CASES = {"gemm": case_gemm, "gemm_fp8": case_gemm_fp8, "gemm_wgrad": case_gemm_wgrad, "grouped_gemm": case_grouped_gemm,
+CASES = {"gemm": case_gemm, "gemm_fp8": case_gemm_fp8, "decode_gemm": case_decode_gemm, "gemm_wgrad": case_gemm_wgrad, "grouped_gemm": case_grouped_gemm,
          "flash_fwd": case_flash_fwd, "flash_bwd": case_flash_bwd, "decode": case_decode,
          "decode_int8": case_decode_int8, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu, "adam": case_adam,
          "ce_stats": case_ce, "selective_scan": case_scan, "gemv_w8": case_gemv, "gemm_rs_emul": case_gemm_rs_emul,

@@ -70,16 +70,35 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, sm_count: int = 148, out: to
         r = matmul_nt(x, w)
         return r if out is None else out.copy_(r)
     mt = (M + 127) // 128
-    tiles = mt * ((N + 127) // 128)
-    if tiles >= sm_count:
-        return gemm_bf16(x, w, out=out)
     kb = (K + 63) // 64
-    split = max(1, min(kb // 4, (2 * sm_count + tiles - 1) // tiles, 16))
+    if os.environ.get("TESSERACT_DECODE_GEMM", "") == "simple":
+        tiles = mt * ((N + 127) // 128)
+        if tiles >= sm_count:
+            return gemm_bf16(x, w, out=out)
+        bn, split = 128, max(1, min(kb // 4, (2 * sm_count + tiles - 1) // tiles, 16))
+    else:
+        # pick the tile width and the K split whose work items fill whole waves of the persistent grid: the weight
+        # matrix is streamed once, so an SM that idles in the last wave is lost bandwidth. Every extra K slice
+        # costs fp32 atomics on the [M, N] output, which is why the penalty grows with M.
+        best = None
+        for bn_c in (256, 128, 64):
+            if bn_c > 64 and N < bn_c:
+                continue
+            tiles = mt * ((N + bn_c - 1) // bn_c)
+            for split_c in range(1, 17):
+                if split_c > 1 and (kb // split_c < 4 or bn_c == 256):
+                    break
+                items = tiles * split_c
+                waves = (items + sm_count - 1) // sm_count
+                cost = waves * sm_count / items + 0.015 * (split_c - 1) * max(1.0, M / 64) + (0.03 if bn_c == 64 else 0.0)
+                if best is None or cost < best[0] - 1e-9:
+                    best = (cost, bn_c, split_c)
+        _, bn, split = best
     if split == 1:
-        return gemm_bf16(x, w, block_n=128, out=out)
+        return gemm_bf16(x, w, block_n=bn, out=out)
     out32 = torch.zeros((M, N), device=x.device, dtype=torch.float32)
     rc = _native.lib().tsb_gemm_bf16_splitk(x.data_ptr(), w.data_ptr(), out32.data_ptr(), M, N, K, x.stride(0),
-                                            w.stride(0), N, 0, split, 128, _native.stream_ptr(x.device))
+                                            w.stride(0), N, 0, split, bn, _native.stream_ptr(x.device))
     _native.check(rc, "tsb_gemm_bf16_splitk")
     return out32.to(torch.bfloat16) if out is None else out.copy_(out32)
 
