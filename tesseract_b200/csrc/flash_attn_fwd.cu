@@ -547,10 +547,11 @@ TSB_EXPORT int tsb_flash_fwd(const void* q, const void* k, const void* v, void* 
   p.status = device_status_word();
   dim3 grid((Sq + BQ - 1) / BQ, H, B);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // TESSERACT_FLASH_FWD=eager selects the variant that folds the output into registers after every key tile
+  // TESSERACT_FLASH_FWD=lazy selects the variant that keeps the output in TMEM and rescales it only when a row
+  // maximum has grown by more than 2^8; measured at 417 TFLOP/s against 436 for the default on the S = 4096 case
   static const bool lazy = [] {
     const char* e = getenv("TESSERACT_FLASH_FWD");
-    return !(e && strcmp(e, "eager") == 0);
+    return e && strcmp(e, "lazy") == 0;
   }();
   auto launch = [&](auto kern, int smem_bytes) -> int {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);

@@ -71,15 +71,15 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, sm_count: int = 148, out: to
         return r if out is None else out.copy_(r)
     mt = (M + 127) // 128
     kb = (K + 63) // 64
-    if os.environ.get("TESSERACT_DECODE_GEMM", "") == "simple":
+    if os.environ.get("TESSERACT_DECODE_GEMM", "") != "waves":
         tiles = mt * ((N + 127) // 128)
         if tiles >= sm_count:
             return gemm_bf16(x, w, out=out)
         bn, split = 128, max(1, min(kb // 4, (2 * sm_count + tiles - 1) // tiles, 16))
     else:
-        # pick the tile width and the K split whose work items fill whole waves of the persistent grid: the weight
-        # matrix is streamed once, so an SM that idles in the last wave is lost bandwidth. Every extra K slice
-        # costs fp32 atomics on the [M, N] output, which is why the penalty grows with M.
+        # experimental (TESSERACT_DECODE_GEMM=waves): pick the tile width and the K split whose work items fill
+        # whole waves of the persistent grid. Measured equal to the simple rule at 64 rows and 40 % slower at 256
+        # rows (more and smaller atomics), so it is not the default.
         best = None
         for bn_c in (256, 128, 64):
             if bn_c > 64 and N < bn_c:
