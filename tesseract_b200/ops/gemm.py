@@ -55,6 +55,8 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: boo
 
 
 _native.register_signatures({
+    "tsb_gemm_cluster_splitk": [_native.P, _native.P, _native.P, _native.I, _native.I, _native.I, _native.L, _native.L,
+                                _native.L, _native.I, _native.P],
     "tsb_gemm_bf16_splitk": [_native.P, _native.P, _native.P, _native.I, _native.I, _native.I, _native.L, _native.L,
                              _native.L, _native.I, _native.I, _native.I, _native.P],
 })
@@ -71,7 +73,23 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, sm_count: int = 148, out: to
         return r if out is None else out.copy_(r)
     mt = (M + 127) // 128
     kb = (K + 63) // 64
-    if os.environ.get("TESSERACT_DECODE_GEMM", "") != "waves":
+    mode = os.environ.get("TESSERACT_DECODE_GEMM", "cluster")
+    tiles128 = mt * ((N + 127) // 128)
+    if mode == "cluster" and hasattr(_native.lib(), "tsb_gemm_cluster_splitk") and x.stride(0) % 8 == 0 \
+            and w.stride(0) % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and 2 * tiles128 <= sm_count:
+        # K slices of one output tile form a thread-block cluster and are summed through distributed shared
+        # memory: no zero fill, no atomics, no cast. Only for problems whose CTAs fit in ONE wave: every CTA of
+        # this non-persistent kernel pays a fixed start-up cost, and clusters of a second wave have to wait for
+        # a whole group of SMs to drain (measured 2-4x slower than the persistent kernel there).
+        sp = 1
+        while sp < 8 and tiles128 * sp * 2 <= sm_count and kb // (sp * 2) >= 8:
+            sp *= 2
+        res = out if out is not None else torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
+        rc = _native.lib().tsb_gemm_cluster_splitk(x.data_ptr(), w.data_ptr(), res.data_ptr(), M, N, K, x.stride(0),
+                                                   w.stride(0), res.stride(0), sp, _native.stream_ptr(x.device))
+        _native.check(rc, "tsb_gemm_cluster_splitk")
+        return res
+    if mode != "waves":
         tiles = mt * ((N + 127) // 128)
         if tiles >= sm_count:
             return gemm_bf16(x, w, out=out)

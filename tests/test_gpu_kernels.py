@@ -317,6 +317,25 @@ def test_flash_forward_with_growing_row_maxima(dev, causal):
     assert _rel_err(got, ref) < 2e-2
 
 
+@pytest.mark.parametrize("M,N,K,split", [(64, 512, 512, 1), (64, 512, 512, 2), (256, 6144, 4096, 4), (37, 264, 1032, 8),
+                                          (130, 4096, 14336, 8), (1, 128, 128, 2)])
+def test_cluster_splitk_gemm(dev, M, N, K, split):
+    """K slices reduced through the shared memory of a thread-block cluster, against the fp32 product."""
+    from tesseract_b200 import _native
+    from tesseract_b200.ops import gemm  # noqa: F401
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    out = torch.full((M, N), float("nan"), device=dev, dtype=torch.bfloat16)
+    _native.check(_native.lib().tsb_gemm_cluster_splitk(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, x.stride(0),
+                                                        w.stride(0), out.stride(0), split,
+                                                        torch.cuda.current_stream().cuda_stream), "tsb_gemm_cluster_splitk")
+    torch.cuda.synchronize()
+    _status_ok()
+    assert torch.isfinite(out.float()).all()
+    assert _rel_err(out, x.float() @ w.float().t()) < 1e-2
+
+
 def test_tiny_llama_train_step_matches_cpu(dev):
     """bf16 GPU step through every native kernel vs the fp32 CPU restatement of the same model."""
     from tesseract_b200.models import LlamaConfig, LlamaModel
