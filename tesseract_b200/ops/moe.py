@@ -27,6 +27,13 @@ _native.register_signatures({
     "tsb_moe_combine": [P, P, P, P, I, I, I, P],
     "tsb_moe_gate_grad": [P, P, P, P, I, I, I, P],
     "tsb_gemm_grouped": [P, P, P, P, I, I, I, I, I, I, L, L, L, I, L, L, I, I, P],
+    "tsb_ep_publish_counts": [_native.ctypes.POINTER(_native.ctypes.c_void_p), P, I, I, I, P],
+    "tsb_ep_plan": [P, P, P, P, I, I, I, I, P],
+    "tsb_ep_fill_i32": [P, L, I, P],
+    "tsb_ep_dispatch": [P, P, P, _native.ctypes.POINTER(_native.ctypes.c_void_p), _native.ctypes.POINTER(_native.ctypes.c_void_p),
+                        P, P, P, L, I, I, I, I, I, I, L, P],
+    "tsb_ep_return": [P, P, _native.ctypes.POINTER(_native.ctypes.c_void_p), L, P, I, L, I, P],
+    "tsb_ep_clean_copy": [P, P, P, L, P, I, P],
 })
 
 
@@ -165,6 +172,63 @@ def grouped_path_ok(x2: torch.Tensor, moe) -> bool:
     return moe.d_model % 64 == 0 and moe.d_ff % 64 == 0
 
 
+def grouped_experts_backward(xs, h, a, dys, offsets, E, stride, w_gu0, w_dn0):
+    """Backward of gate_up -> SwiGLU -> down over expert-grouped rows: returns (d xs [rows, D], dW fp32 flat
+    [E * stride] in the layout of the weights: [gate | up | down] per expert). All experts per launch."""
+    from .fused import swiglu_backward
+    dev = dys.device
+    D = xs.shape[1]
+    F2 = h.shape[1]
+    F = F2 // 2
+    dw = torch.empty(E * stride, dtype=torch.float32, device=dev)
+    grouped_gemm_wgrad(dys, a, offsets, E, dw[F2 * D:], stride, F, accumulate=False)    # d W_down [D, F]
+    da = grouped_gemm_rows(dys, w_dn0, stride, offsets, E, b_mn=True)                     # [rows, F]
+    dh = swiglu_backward(h, da)
+    grouped_gemm_wgrad(dh, xs, offsets, E, dw, stride, D, accumulate=False)              # d W_gate_up [2F, D]
+    dxs = grouped_gemm_rows(dh, w_gu0, stride, offsets, E, b_mn=True)                     # [rows, D]
+    return dxs, dw
+
+
+def split_expert_grads(dw, E, stride, F, D):
+    """Views of a flat [E * stride] gradient as the per-expert (gate, up, down) weight gradients, in bf16."""
+    dwe = dw.view(E, stride)
+    grads = []
+    for e in range(E):
+        grads += [dwe[e, :F * D].view(F, D), dwe[e, F * D:2 * F * D].view(F, D), dwe[e, 2 * F * D:].view(D, F)]
+    return [g.to(torch.bfloat16) for g in grads]
+
+
+def expert_weight_stack(moe):
+    """(weights list [gate, up, down per expert], per-expert stride, [2F, D] view of expert 0's gate|up, expert 0's
+    down): re-homes the expert weights in one flat buffer first if they are not laid out that way yet."""
+    E = moe.num_experts if len(moe.experts) == moe.num_experts else len(moe.experts)
+    F, D = moe.d_ff, moe.d_model
+    per = 3 * F * D
+
+    def collect():
+        out = []
+        for ex in moe.experts:
+            out += [ex.gate_proj.weight, ex.up_proj.weight, ex.down_proj.weight]
+        return out
+
+    ws = collect()
+
+    def laid_out():
+        if E > 1 and _strided_stack(ws[0::3]) != per:
+            return False
+        for e in range(E):
+            base, es = ws[3 * e].data_ptr(), ws[3 * e].element_size()
+            if ws[3 * e + 1].data_ptr() != base + F * D * es or ws[3 * e + 2].data_ptr() != base + 2 * F * D * es:
+                return False
+        return all(w.is_contiguous() for w in ws)
+
+    if not laid_out():
+        fuse_expert_storage_(moe)
+        ws = collect()
+    w_gu0 = torch.as_strided(ws[0].detach(), (2 * F, D), (D, 1))      # gate and up of expert 0 as one [2F, D] matrix
+    return ws, per, w_gu0, ws[2].detach()
+
+
 class _GroupedExpertsFn(torch.autograd.Function):
     """All experts of one MoE layer as grouped tcgen05 GEMMs over expert-sorted, 128-row-padded activations:
     gather -> gate_up (grouped) -> SwiGLU -> down (grouped) -> weighted combine. Nothing is read back to the host."""
@@ -194,15 +258,9 @@ class _GroupedExpertsFn(torch.autograd.Function):
         check(lib().tsb_moe_gate_grad(dout.data_ptr(), ys.data_ptr(), pos.data_ptr(), dgate.data_ptr(), T, D, k,
                                       stream_ptr(dev)), "tsb_moe_gate_grad")
         dys = gather_rows(dout, assign, k, row_scale=gates32.view(-1))          # gate-weighted dOut per sorted row
+        dxs, dw = grouped_experts_backward(xs, h, a, dys, offsets, E, stride, w_gu0, w_dn0)
         F2 = h.shape[1]
         F = F2 // 2
-        # weight gradients, all experts per launch, in the layout of the weights: [gate | up | down] per expert
-        dw = torch.empty(E * stride, dtype=torch.float32, device=dev)
-        grouped_gemm_wgrad(dys, a, offsets, E, dw[F2 * D:], stride, F, accumulate=False)    # d W_down [D, F]
-        da = grouped_gemm_rows(dys, w_dn0, stride, offsets, E, b_mn=True)                     # [rows, F]
-        dh = swiglu_backward(h, da)
-        grouped_gemm_wgrad(dh, xs, offsets, E, dw, stride, D, accumulate=False)              # d W_gate_up [2F, D]
-        dxs = grouped_gemm_rows(dh, w_gu0, stride, offsets, E, b_mn=True)                     # [rows, D]
         dx = combine_rows(dxs, pos, T, k)
         dwe = dw.view(E, stride)
         grads = []

@@ -158,6 +158,29 @@ def _worker(rank, world, port, q):
         ep_errs = [((ya.float() - yb.float()).norm() / ya.float().norm()).item(),
                    ((xa.grad.float() - xb.grad.float()).norm() / xa.grad.float().norm()).item()]
         errs += ep_errs
+        # the same layer with the device-side exchange over peer memory (no NCCL, no host read of the counts)
+        from tesseract_b200.parallel.expert import FusedExpertParallel
+        fused_l = copy.deepcopy(full)
+        fep = FusedExpertParallel(dist.group.WORLD, rank, world, dev, 256, 2 * world, 2, max_tokens=512)
+        fep.shard_(fused_l)
+        for it in range(2):                                          # twice: buffers and tags are reused
+            xc = xe.clone().requires_grad_(True)
+            yc = fused_l(xc)
+            yc.backward(ge)
+            errs += [((ya.float() - yc.float()).norm() / ya.float().norm()).item(),
+                     ((xa.grad.float() - xc.grad.float()).norm() / xa.grad.float().norm()).item()]
+        for ge_i in range(2 * world):                                # expert weight gradients: same order everywhere
+            for name in ("gate_proj", "up_proj", "down_proj"):
+                wfull = getattr(full.experts[ge_i], name).weight
+                want = torch.zeros_like(wfull, dtype=torch.float32) if wfull.grad is None else wfull.grad.float().clone()
+                dist.all_reduce(want)
+                el_ = 2
+                if ge_i // el_ == rank:
+                    got = getattr(fused_l.experts[ge_i - rank * el_], name).weight.grad.float()
+                    # two backward passes accumulated into .grad
+                    errs.append(((got / 2 - want).norm() / want.norm().clamp_min(1e-6)).item())
+        assert fep.calls == 2
+        status |= _native.read_status(torch.cuda.current_stream().cuda_stream)
         # tensor-parallel serving: sharded engine (one-shot all-reduce kernel inside the decode CUDA graph) against
         # the single-GPU engine on the same seeded model and requests
         from tesseract_b200.models import GenerateConfig, LlamaModel
