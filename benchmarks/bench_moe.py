@@ -32,6 +32,8 @@ def main():
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--top-k", type=int, default=2)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="expert-parallel token exchange: device-side pushes over peer memory, or NCCL all-to-all")
     a = ap.parse_args()
     world, rank = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
@@ -53,7 +55,12 @@ def main():
         layer.num_experts, layer.top_k = a.experts, a.top_k
         for p in layer.gate.parameters():
             dist.broadcast(p.data, src=0)
-        ExpertParallel(dist.group.WORLD, rank, world).shard_(layer)
+        if a.exchange == "fused":
+            from tesseract_b200.parallel.expert import FusedExpertParallel
+            FusedExpertParallel(dist.group.WORLD, rank, world, dev, a.d_model, a.experts, a.top_k,
+                                max_tokens=a.tokens).shard_(layer)
+        else:
+            ExpertParallel(dist.group.WORLD, rank, world).shard_(layer)
     for p in layer.parameters():
         p.data.mul_(0.5)
     x = torch.randn(a.tokens, a.d_model, device=dev).bfloat16().requires_grad_(True)
@@ -95,7 +102,7 @@ def main():
     status = _native.read_status(torch.cuda.current_stream().cuda_stream)
     if rank == 0:
         print(json.dumps({"bench": "moe_layer", "ep": world, "tokens_per_rank": a.tokens, "experts": a.experts,
-                          "top_k": a.top_k, "d_model": a.d_model, "d_ff": a.d_ff, "fwd_ms": round(ms_f, 3),
+                          "top_k": a.top_k, "exchange": a.exchange if world > 1 else "local", "d_model": a.d_model, "d_ff": a.d_ff, "fwd_ms": round(ms_f, 3),
                           "fwd_bwd_ms": round(ms_fb, 3), "fwd_tflops_per_gpu": round(flops_f / ms_f / 1e9, 1),
                           "fwd_bwd_tflops_per_gpu": round(3 * flops_f / ms_fb / 1e9, 1), "kernel_status": status}))
     if world > 1:

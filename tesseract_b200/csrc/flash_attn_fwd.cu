@@ -422,16 +422,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
           }
         } else {
+          // interior tiles: the denominator sums the fp32 probabilities (the bf16 rounding of P is unbiased, so
+          // the two agree to well below the output precision) -- two instructions fewer per pair
           float l0 = 0.f, l1 = 0.f;
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const float p0 = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, mneg));
             const float p1 = exp2f(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, mneg));
-            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-            const float2 pf = __bfloat1622float2(pb);
-            l0 += pf.x;
-            l1 += pf.y;
-            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+            l0 += p0;
+            l1 += p1;
+            packed[i >> 1] = pack_bf16x2(p0, p1);
           }
           l_tile += l0 + l1;
         }

@@ -214,6 +214,10 @@ def expert_weight_stack(moe):
     ws = collect()
 
     def laid_out():
+        # one storage (adjacent but separate allocations cannot be viewed as one matrix), constant expert stride
+        base_storage = ws[0].untyped_storage().data_ptr()
+        if any(w.untyped_storage().data_ptr() != base_storage for w in ws):
+            return False
         if E > 1 and _strided_stack(ws[0::3]) != per:
             return False
         for e in range(E):
@@ -272,32 +276,9 @@ class _GroupedExpertsFn(torch.autograd.Function):
 
 def moe_ffn_grouped(x2: torch.Tensor, idx: torch.Tensor, gates: torch.Tensor, moe, counts: torch.Tensor = None):
     """x2 [T, D] bf16, idx [T, k] expert ids, gates [T, k] -> [T, D] through the grouped tcgen05 GEMM path."""
-    E, k = moe.num_experts, idx.shape[1]
-    ws = []
-    for ex in moe.experts:
-        ws += [ex.gate_proj.weight, ex.up_proj.weight, ex.down_proj.weight]
-    F, D = moe.d_ff, moe.d_model
-    per = 3 * F * D
-
-    def laid_out():
-        gus = ws[0::3]
-        if _strided_stack(gus) != per and E > 1:
-            return False
-        for e in range(E):
-            base = ws[3 * e].data_ptr()
-            es = ws[3 * e].element_size()
-            if ws[3 * e + 1].data_ptr() != base + F * D * es or ws[3 * e + 2].data_ptr() != base + 2 * F * D * es:
-                return False
-        return all(w.is_contiguous() for w in ws)
-
-    if not laid_out():
-        fuse_expert_storage_(moe)
-        ws = []
-        for ex in moe.experts:
-            ws += [ex.gate_proj.weight, ex.up_proj.weight, ex.down_proj.weight]
+    E, k = len(moe.experts), idx.shape[1]
+    ws, per, w_gu0, w_dn0 = expert_weight_stack(moe)
     idx32 = idx.to(torch.int32).contiguous()
     if counts is None:
         counts = torch.bincount(idx32.view(-1), minlength=E).to(torch.int32)
-    w_gu0 = torch.as_strided(ws[0].detach(), (2 * F, D), (D, 1))      # gate and up of expert 0 as one [2F, D] matrix
-    w_dn0 = ws[2].detach()
     return _GroupedExpertsFn.apply(x2.contiguous(), gates, idx32, counts, per, E, k, w_gu0, w_dn0, *ws)

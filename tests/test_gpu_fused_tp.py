@@ -148,6 +148,7 @@ def _worker(rank, world, port, q):
         torch.manual_seed(21)
         full = MoEFeedForward(256, 384, num_experts=2 * world, num_experts_per_tok=2, dtype=torch.bfloat16, device=dev)
         sharded = copy.deepcopy(full)
+        fused_l = copy.deepcopy(full)
         ExpertParallel(dist.group.WORLD, rank, world).shard_(sharded)
         xe = torch.randn(200 + 8 * rank, 256, device=dev, generator=g).bfloat16()
         xa, xb = xe.clone().requires_grad_(True), xe.clone().requires_grad_(True)
@@ -160,7 +161,6 @@ def _worker(rank, world, port, q):
         errs += ep_errs
         # the same layer with the device-side exchange over peer memory (no NCCL, no host read of the counts)
         from tesseract_b200.parallel.expert import FusedExpertParallel
-        fused_l = copy.deepcopy(full)
         fep = FusedExpertParallel(dist.group.WORLD, rank, world, dev, 256, 2 * world, 2, max_tokens=512)
         fep.shard_(fused_l)
         for it in range(2):                                          # twice: buffers and tags are reused
