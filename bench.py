@@ -27,7 +27,7 @@ import sys
 import time
 
 REFERENCE_UNAVAILABLE = ("reference is a CMake/C++ project without setup.py or pyproject.toml: "
-                         "`pip install --no-index ... /root/reference` fails with 'Directory is not installable'")
+                         "an offline `pip install` of its source tree fails with 'Directory is not installable'")
 
 _SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
                "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"

@@ -6,7 +6,7 @@ block's backward has finished (everything that contributes to the block's weight
 the all-reduce of that block's bucket on a side stream while the earlier blocks are still being differentiated.
 Only the last micro-batch of a step communicates; ``finish_step`` reduces whatever is left and joins the streams.
 
-The reference has no data parallelism (SURVEY: only a comment in src/ops/cpu/Arithmetic.cpp:270).
+The reference has no data parallelism (it is mentioned only in a comment, src/ops/cpu/Arithmetic.cpp:270).
 """
 from __future__ import annotations
 
