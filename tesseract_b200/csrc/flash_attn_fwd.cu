@@ -16,6 +16,8 @@
 // Also writes the per-row log-sum-exp needed by the backward kernel.
 #include "common.cuh"
 
+#include <algorithm>
+
 #include <cstdlib>
 #include <cstring>
 
@@ -41,6 +43,7 @@ struct FaParams {
   float* lse;
   int B, Sq, Sk, H, Hkv;
   long long o_sb, o_ss, o_sh;
+  const int* cu_seqlens;  // varlen: int32 [B + 1] row offsets of the sequences in the packed token axis, else null
   float scale_log2;  // softmax scale * log2(e)
   float scale;
   int causal;
@@ -66,8 +69,20 @@ __device__ __forceinline__ uint64_t mnmajor_desc(uint32_t base, int ks, uint32_t
 template <int D, bool LAZY>
 __global__ void __launch_bounds__(kFaThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, FaParams p) {
+                 const __grid_constant__ CUtensorMap tmV, FaParams p_in) {
   using Cfg = FaCfg<D>;
+  // Variable-length batches: the sequences sit one after another on ONE token axis (tensor maps with batch 1);
+  // block z handles sequence z, whose rows start at cu_seqlens[z]. Tiles that reach past its end read rows of the
+  // next sequence (or the zero fill) and the length mask below discards them.
+  FaParams p = p_in;
+  int row0 = 0;
+  int bb = blockIdx.z;
+  if (p_in.cu_seqlens) {
+    row0 = p_in.cu_seqlens[blockIdx.z];
+    p.Sq = p.Sk = p_in.cu_seqlens[blockIdx.z + 1] - row0;
+    bb = 0;
+    if (static_cast<int>(gridDim.x - 1 - blockIdx.x) * BQ >= p.Sq) return;  // no query rows: the whole CTA leaves
+  }
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -128,7 +143,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0 && n_tiles > 0) {
       mbar_expect_tx(&q_full, Cfg::kTileBytes);
 #pragma unroll
-      for (int hf = 0; hf < Cfg::kHalves; ++hf) tma_load_4d(sQ + hf * 16384, &tmQ, &q_full, hf * 64, q0, h, b);
+      for (int hf = 0; hf < Cfg::kHalves; ++hf) tma_load_4d(sQ + hf * 16384, &tmQ, &q_full, hf * 64, q0 + row0, h, bb);
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1u;
@@ -136,12 +151,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_expect_tx(&k_full[st], Cfg::kTileBytes);
 #pragma unroll
         for (int hf = 0; hf < Cfg::kHalves; ++hf)
-          tma_load_4d(sK + st * Cfg::kTileBytes + hf * 16384, &tmK, &k_full[st], hf * 64, j * BKV, hk, b);
+          tma_load_4d(sK + st * Cfg::kTileBytes + hf * 16384, &tmK, &k_full[st], hf * 64, j * BKV + row0, hk, bb);
         if (!mbar_wait(&v_empty[st], par, &cta_abort, p.status)) break;
         mbar_expect_tx(&v_full[st], Cfg::kTileBytes);
 #pragma unroll
         for (int hf = 0; hf < Cfg::kHalves; ++hf)
-          tma_load_4d(sV + st * Cfg::kTileBytes + hf * 16384, &tmV, &v_full[st], hf * 64, j * BKV, hk, b);
+          tma_load_4d(sV + st * Cfg::kTileBytes + hf * 16384, &tmV, &v_full[st], hf * 64, j * BKV + row0, hk, bb);
       }
     }
   } else if (warp == 5) {
@@ -308,7 +323,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (have_o) tc_fence_after();
       if (warp_ok && (have_o || n_tiles == 0)) {
         const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* orow = p.o + b * p.o_sb + static_cast<long long>(qi < p.Sq ? qi : 0) * p.o_ss + h * p.o_sh;
+        __nv_bfloat16* orow = p.o + bb * p.o_sb + static_cast<long long>(row0 + (qi < p.Sq ? qi : 0)) * p.o_ss + h * p.o_sh;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
@@ -472,7 +487,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     if (ok && qi < p.Sq) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* orow = p.o + b * p.o_sb + static_cast<long long>(qi) * p.o_ss + h * p.o_sh;
+      __nv_bfloat16* orow = p.o + bb * p.o_sb + static_cast<long long>(row0 + qi) * p.o_ss + h * p.o_sh;
 #pragma unroll
       for (int c = 0; c < D / 8; ++c) {
         uint4 v;
@@ -539,6 +554,7 @@ TSB_EXPORT int tsb_flash_fwd(const void* q, const void* k, const void* v, void* 
   FaParams p;
   p.o = static_cast<__nv_bfloat16*>(o);
   p.lse = lse;
+  p.cu_seqlens = nullptr;
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.H = H; p.Hkv = Hkv;
   p.o_sb = o_sb; p.o_ss = o_ss; p.o_sh = o_sh;
   p.scale = scale;
@@ -564,6 +580,52 @@ TSB_EXPORT int tsb_flash_fwd(const void* q, const void* k, const void* v, void* 
     rc = lazy ? launch(flash_fwd_kernel<128, true>, FaCfg<128>::kSmemBytes) : launch(flash_fwd_kernel<128, false>, FaCfg<128>::kSmemBytes);
   else
     rc = lazy ? launch(flash_fwd_kernel<64, true>, FaCfg<64>::kSmemBytes) : launch(flash_fwd_kernel<64, false>, FaCfg<64>::kSmemBytes);
+  if (rc) return rc;
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Variable-length causal self-attention over sequences packed on one token axis (batched prefill of prompts of
+// different lengths in ONE launch): q [T, H, D], k / v [T, Hkv, D], o [T, H, D] bf16 with token / head strides in
+// elements (unit stride in D, multiples of 8, 16-byte aligned bases); cu_seqlens int32 [n_seqs + 1] on the device,
+// cu_seqlens[0] = 0, cu_seqlens[n_seqs] = T; max_len >= the longest sequence. D is 64 or 128.
+TSB_EXPORT int tsb_flash_fwd_varlen(const void* q, const void* k, const void* v, void* o, const int* cu_seqlens,
+                                    int n_seqs, int max_len, int T, int H, int Hkv, int D, long long q_ss, long long q_sh,
+                                    long long k_ss, long long k_sh, long long v_ss, long long v_sh, long long o_ss,
+                                    long long o_sh, float scale, void* stream) {
+  using namespace tsb;
+  if (n_seqs <= 0 || max_len <= 0 || T <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || (D != 64 && D != 128) || !cu_seqlens)
+    return -2;
+  const long long strides[] = {q_ss, q_sh, k_ss, k_sh, v_ss, v_sh, o_ss, o_sh};
+  for (long long st : strides)
+    if (st % 8) return -2;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(o)) & 15)
+    return -2;
+  CUtensorMap tq, tk, tv;
+  const long long big = static_cast<long long>(T) * std::max({q_ss, k_ss, v_ss});  // batch stride of the single batch
+  if (!make_bshd_tmap(&tq, q, 1, T, H, D, big, q_ss, q_sh, 128)) return -3;
+  if (!make_bshd_tmap(&tk, k, 1, T, Hkv, D, big, k_ss, k_sh, 128)) return -3;
+  if (!make_bshd_tmap(&tv, v, 1, T, Hkv, D, big, v_ss, v_sh, 128)) return -3;
+  FaParams p;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.lse = nullptr;
+  p.cu_seqlens = cu_seqlens;
+  p.B = n_seqs; p.Sq = max_len; p.Sk = max_len; p.H = H; p.Hkv = Hkv;
+  p.o_sb = 0; p.o_ss = o_ss; p.o_sh = o_sh;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = 1;
+  p.status = device_status_word();
+  dim3 grid((max_len + BQ - 1) / BQ, H, n_seqs);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto launch = [&](auto kern, int smem_bytes) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    kern<<<grid, kFaThreads, smem_bytes, s>>>(tq, tk, tv, p);
+    return 0;
+  };
+  const int rc = (D == 128) ? launch(flash_fwd_kernel<128, false>, FaCfg<128>::kSmemBytes)
+                            : launch(flash_fwd_kernel<64, false>, FaCfg<64>::kSmemBytes);
   if (rc) return rc;
   return static_cast<int>(cudaGetLastError());
 }

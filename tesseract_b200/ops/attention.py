@@ -17,6 +17,7 @@ from .._native import check, lib, stream_ptr
 
 _native.register_signatures({
     "tsb_flash_fwd": [_native.P] * 5 + [_native.I] * 6 + [_native.L] * 12 + [_native.F, _native.I, _native.P],
+    "tsb_flash_fwd_varlen": [_native.P] * 5 + [_native.I] * 6 + [_native.L] * 8 + [_native.F, _native.P],
     "tsb_flash_bwd": [_native.P] * 10 + [_native.I] * 6 + [_native.L] * 12 + [_native.F, _native.I, _native.P],
     "tsb_flash_bwd_scratch_bytes": [_native.I] * 4,
 })
@@ -176,3 +177,29 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: b
                            "(rebuild with `python -m tesseract_b200.build`)")
     o = attention_ref(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), causal=causal, scale=scale)
     return o.transpose(1, 2).contiguous()
+
+
+def flash_attention_varlen_packed(qkv: torch.Tensor, cu_seqlens: torch.Tensor, max_len: int, num_heads: int,
+                                  num_kv_heads: int, scale: float | None = None) -> torch.Tensor:
+    """Causal self-attention over sequences of different lengths packed on one token axis (inference, no autograd):
+    qkv [T, H + 2 Hkv, D] (queries, keys, values along the head axis), cu_seqlens int32 [n + 1] -> [T, H, D].
+    One kernel launch for the whole batch on CUDA bf16; per-sequence calls otherwise."""
+    T, _, D = qkv.shape
+    H, Hkv = num_heads, num_kv_heads
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    n = cu_seqlens.shape[0] - 1
+    if (qkv.is_cuda and qkv.dtype == torch.bfloat16 and D in (64, 128) and qkv.is_contiguous()
+            and _native_flash_available() and hasattr(lib(), "tsb_flash_fwd_varlen")):
+        q, k, v = qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:]
+        o = torch.empty((T, H, D), device=qkv.device, dtype=qkv.dtype)
+        cu = cu_seqlens.to(device=qkv.device, dtype=torch.int32).contiguous()
+        check(lib().tsb_flash_fwd_varlen(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), cu.data_ptr(), n,
+                                         int(max_len), T, H, Hkv, D, q.stride(0), q.stride(1), k.stride(0), k.stride(1),
+                                         v.stride(0), v.stride(1), o.stride(0), o.stride(1), float(scale),
+                                         stream_ptr(qkv.device)), "tsb_flash_fwd_varlen")
+        return o
+    bounds = cu_seqlens.tolist()
+    outs = [flash_attention_packed(qkv[a:b].unsqueeze(0), H, Hkv, causal=True, scale=scale)[0]
+            for a, b in zip(bounds[:-1], bounds[1:])]
+    return torch.cat(outs, dim=0)

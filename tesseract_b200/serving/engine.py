@@ -273,11 +273,9 @@ class ServingEngine:
                                             ks.data_ptr() if ks is not None else None,
                                             vs.data_ptr() if vs is not None else None, None, T, H, Hkv, D,
                                             self.cfg.block_size, dt, 0, stream_ptr(qkv.device)), "tsb_kv_append_paged")
-            outs = []
-            q4 = qkv.view(T, H + 2 * Hkv, D)
-            for (a, b) in prefill_bounds:
-                outs.append(ops.flash_attention_packed(q4[a:b].unsqueeze(0), H, Hkv, causal=True).view(b - a, H * D))
-            o = torch.cat(outs, dim=0) if len(outs) > 1 else outs[0]
+            # every prompt of the step in ONE variable-length attention launch
+            cu, max_len = prefill_bounds
+            o = ops.flash_attention_varlen_packed(qkv.view(T, H + 2 * Hkv, D), cu, max_len, H, Hkv).view(T, H * D)
         a_out = self._mm_reduce(o, self.wo[li])
         h2, res = ops.rms_norm(a_out, blk.norm_2.weight, blk.norm_2.eps, residual=res)
         gu = self._mm(h2, self.wgu[li])
@@ -341,6 +339,8 @@ class ServingEngine:
             off += r.prompt_len
             last.append(off - 1)
         dev = self.device
+        cu = torch.tensor([0] + [b for _, b in bounds], dtype=torch.int32).to(dev, non_blocking=True)
+        bounds = (cu, max(b - a for a, b in bounds))
         tokens = torch.tensor(toks, dtype=torch.int64).to(dev, non_blocking=True)
         meta = torch.tensor([pos, slots], dtype=torch.int32).to(dev, non_blocking=True)
         last_rows = torch.tensor(last, dtype=torch.int64).to(dev, non_blocking=True)
