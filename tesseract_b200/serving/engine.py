@@ -103,6 +103,8 @@ class ServingEngine:
         # prompt tokens admitted per step (0 = no limit): bounds the time to first token of the requests at the
         # head of the queue and the size of the prefill activations; at least one request is always admitted
         self.max_prefill_tokens = max_prefill_tokens
+        import os
+        self.varlen_prefill = os.environ.get("TESSERACT_PREFILL_VARLEN", "0") == "1"
         c, mc = self.cfg, model.config
         self.device = model._device()
         if self.device.type != "cuda" or mc.dtype not in (torch.bfloat16, torch.float16):
@@ -273,9 +275,15 @@ class ServingEngine:
                                             ks.data_ptr() if ks is not None else None,
                                             vs.data_ptr() if vs is not None else None, None, T, H, Hkv, D,
                                             self.cfg.block_size, dt, 0, stream_ptr(qkv.device)), "tsb_kv_append_paged")
-            # every prompt of the step in ONE variable-length attention launch
-            cu, max_len = prefill_bounds
-            o = ops.flash_attention_varlen_packed(qkv.view(T, H + 2 * Hkv, D), cu, max_len, H, Hkv).view(T, H * D)
+            cu, max_len, spans = prefill_bounds
+            q4 = qkv.view(T, H + 2 * Hkv, D)
+            if self.varlen_prefill:
+                # every prompt of the step in ONE variable-length attention launch
+                o = ops.flash_attention_varlen_packed(q4, cu, max_len, H, Hkv).view(T, H * D)
+            else:
+                outs = [ops.flash_attention_packed(q4[a:b].unsqueeze(0), H, Hkv, causal=True).view(b - a, H * D)
+                        for (a, b) in spans]
+                o = torch.cat(outs, dim=0) if len(outs) > 1 else outs[0]
         a_out = self._mm_reduce(o, self.wo[li])
         h2, res = ops.rms_norm(a_out, blk.norm_2.weight, blk.norm_2.eps, residual=res)
         gu = self._mm(h2, self.wgu[li])
@@ -340,7 +348,7 @@ class ServingEngine:
             last.append(off - 1)
         dev = self.device
         cu = torch.tensor([0] + [b for _, b in bounds], dtype=torch.int32).to(dev, non_blocking=True)
-        bounds = (cu, max(b - a for a, b in bounds))
+        bounds = (cu, max(b - a for a, b in bounds), list(bounds))
         tokens = torch.tensor(toks, dtype=torch.int64).to(dev, non_blocking=True)
         meta = torch.tensor([pos, slots], dtype=torch.int32).to(dev, non_blocking=True)
         last_rows = torch.tensor(last, dtype=torch.int64).to(dev, non_blocking=True)
