@@ -62,61 +62,54 @@ _native.register_signatures({
 })
 
 
+def plan_decode_gemm(M: int, N: int, K: int, sm_count: int = 148, mode: str = "cluster"):
+    """How a decode-shaped product x [M, K] @ w [N, K]^T is run: ``("cluster", S)`` -- S K-slices per output tile,
+    reduced through the shared memory of a thread-block cluster; ``("plain", 0)`` -- the persistent GEMM;
+    ``("atomic", S)`` -- S K-slices added into a zeroed fp32 buffer with atomics, then one cast."""
+    mt = (M + 127) // 128
+    kb = (K + 63) // 64
+    tiles = mt * ((N + 127) // 128)
+    if mode == "cluster" and 2 * tiles <= sm_count:
+        # only for problems whose CTAs fit in ONE wave: every CTA of the non-persistent cluster kernel pays a fixed
+        # start-up cost, and clusters of a second wave have to wait for a whole group of SMs to drain (measured
+        # 2-4x slower than the persistent kernel there)
+        sp = 1
+        while sp < 8 and tiles * sp * 2 <= sm_count and kb // (sp * 2) >= 8:
+            sp *= 2
+        return "cluster", sp
+    if tiles >= sm_count:
+        return "plain", 0
+    split = max(1, min(kb // 4, (2 * sm_count + tiles - 1) // tiles, 16))
+    return ("atomic", split) if split > 1 else ("plain", 128)
+
+
 def decode_linear(x: torch.Tensor, w: torch.Tensor, sm_count: int = 148, out: torch.Tensor | None = None) -> torch.Tensor:
-    """x [M, K] @ w [N, K]^T for decode-shaped calls (few rows): when the plain tiling would leave most SMs idle
-    the K range is split across CTAs (fp32 atomics into a zeroed buffer, then one cast), so that the whole GPU
-    streams the weight matrix. ``out`` (bf16 [M, N]) receives the result when given."""
+    """x [M, K] @ w [N, K]^T for decode-shaped calls (few rows against a weight matrix that is streamed once): when
+    the plain tiling would leave most SMs idle the K range is split across CTAs -- a thread-block cluster per output
+    tile that sums its slices through distributed shared memory (``csrc/gemm_cluster_splitk.cu``), or, with
+    ``TESSERACT_DECODE_GEMM=simple``, fp32 atomics into a zeroed buffer and one cast. ``out`` (bf16 [M, N])
+    receives the result when given."""
     M, K = x.shape
     N = w.shape[0]
     if not (_use_native(x) and M <= 512 and hasattr(_native.lib(), "tsb_gemm_bf16_splitk")):
         r = matmul_nt(x, w)
         return r if out is None else out.copy_(r)
-    mt = (M + 127) // 128
-    kb = (K + 63) // 64
     mode = os.environ.get("TESSERACT_DECODE_GEMM", "cluster")
-    tiles128 = mt * ((N + 127) // 128)
-    if mode == "cluster" and hasattr(_native.lib(), "tsb_gemm_cluster_splitk") and x.stride(0) % 8 == 0 \
-            and w.stride(0) % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and 2 * tiles128 <= sm_count:
-        # K slices of one output tile form a thread-block cluster and are summed through distributed shared
-        # memory: no zero fill, no atomics, no cast. Only for problems whose CTAs fit in ONE wave: every CTA of
-        # this non-persistent kernel pays a fixed start-up cost, and clusters of a second wave have to wait for
-        # a whole group of SMs to drain (measured 2-4x slower than the persistent kernel there).
-        sp = 1
-        while sp < 8 and tiles128 * sp * 2 <= sm_count and kb // (sp * 2) >= 8:
-            sp *= 2
+    if not (hasattr(_native.lib(), "tsb_gemm_cluster_splitk") and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1):
+        mode = "simple"
+    kind, arg = plan_decode_gemm(M, N, K, sm_count, mode)
+    if kind == "cluster":
         res = out if out is not None else torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
         rc = _native.lib().tsb_gemm_cluster_splitk(x.data_ptr(), w.data_ptr(), res.data_ptr(), M, N, K, x.stride(0),
-                                                   w.stride(0), res.stride(0), sp, _native.stream_ptr(x.device))
+                                                   w.stride(0), res.stride(0), arg, _native.stream_ptr(x.device))
         _native.check(rc, "tsb_gemm_cluster_splitk")
         return res
-    if mode != "waves":
-        tiles = mt * ((N + 127) // 128)
-        if tiles >= sm_count:
-            return gemm_bf16(x, w, out=out)
-        bn, split = 128, max(1, min(kb // 4, (2 * sm_count + tiles - 1) // tiles, 16))
-    else:
-        # experimental (TESSERACT_DECODE_GEMM=waves): pick the tile width and the K split whose work items fill
-        # whole waves of the persistent grid. Measured equal to the simple rule at 64 rows and 40 % slower at 256
-        # rows (more and smaller atomics), so it is not the default.
-        best = None
-        for bn_c in (256, 128, 64):
-            if bn_c > 64 and N < bn_c:
-                continue
-            tiles = mt * ((N + bn_c - 1) // bn_c)
-            for split_c in range(1, 17):
-                if split_c > 1 and (kb // split_c < 4 or bn_c == 256):
-                    break
-                items = tiles * split_c
-                waves = (items + sm_count - 1) // sm_count
-                cost = waves * sm_count / items + 0.015 * (split_c - 1) * max(1.0, M / 64) + (0.03 if bn_c == 64 else 0.0)
-                if best is None or cost < best[0] - 1e-9:
-                    best = (cost, bn_c, split_c)
-        _, bn, split = best
-    if split == 1:
-        return gemm_bf16(x, w, block_n=bn, out=out)
+    if kind == "plain":
+        return gemm_bf16(x, w, block_n=arg, out=out)
     out32 = torch.zeros((M, N), device=x.device, dtype=torch.float32)
     rc = _native.lib().tsb_gemm_bf16_splitk(x.data_ptr(), w.data_ptr(), out32.data_ptr(), M, N, K, x.stride(0),
-                                            w.stride(0), N, 0, split, bn, _native.stream_ptr(x.device))
+                                            w.stride(0), N, 0, arg, 128, _native.stream_ptr(x.device))
     _native.check(rc, "tsb_gemm_bf16_splitk")
     return out32.to(torch.bfloat16) if out is None else out.copy_(out32)
 

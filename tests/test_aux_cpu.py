@@ -91,3 +91,20 @@ def test_graph_capture_run_and_backward():
     xr = x.clone().requires_grad_()
     m(xr).sum().backward()
     assert torch.allclose(gx, xr.grad)
+
+
+def test_decode_gemm_plan():
+    """The decode GEMM planner: one wave of cluster CTAs for small outputs, the persistent GEMM once the tiles
+    fill the GPU, atomics only on request."""
+    from tesseract_b200.ops.gemm import plan_decode_gemm
+    for M in (1, 64, 256):
+        kind, s = plan_decode_gemm(M, 4096, 4096)                  # o_proj: 32 or 64 tiles
+        assert kind == "cluster" and s in (1, 2, 4, 8)
+        tiles = ((M + 127) // 128) * 32
+        assert tiles * s <= 148 and (s == 8 or tiles * s * 2 > 148 or 64 // (s * 2) < 8)
+    assert plan_decode_gemm(64, 28672, 4096) == ("plain", 0)       # gate_up: 224 tiles already fill the GPU
+    assert plan_decode_gemm(256, 128256, 4096) == ("plain", 0)     # lm_head
+    assert plan_decode_gemm(64, 4096, 512)[0] == "cluster" and plan_decode_gemm(64, 4096, 512)[1] == 1   # 8 k-blocks
+    kind, s = plan_decode_gemm(64, 6144, 4096, mode="simple")
+    assert kind == "atomic" and 2 <= s <= 16
+    assert plan_decode_gemm(64, 28672, 4096, mode="simple") == ("plain", 0)
