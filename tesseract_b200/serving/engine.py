@@ -104,7 +104,7 @@ class ServingEngine:
         # head of the queue and the size of the prefill activations; at least one request is always admitted
         self.max_prefill_tokens = max_prefill_tokens
         import os
-        self.varlen_prefill = os.environ.get("TESSERACT_PREFILL_VARLEN", "0") == "1"
+        self.varlen_prefill = os.environ.get("TESSERACT_PREFILL_VARLEN", "1") == "1"   # 0: one launch per prompt
         c, mc = self.cfg, model.config
         self.device = model._device()
         if self.device.type != "cuda" or mc.dtype not in (torch.bfloat16, torch.float16):
