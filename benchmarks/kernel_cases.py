@@ -104,6 +104,21 @@ def case_gemm_fp8(b: Bench):
     report("gemm_fp8", ms, flops=2.0 * M * N * K, shape=[M, N, K], note="fractions are of the bf16 peak")
 
 
+def case_gemm_fp8_pertensor(b: Bench):
+    """The reference's FP8 benchmark shape family (square, one scale per operand); its bar is FP8 >= 1.3 x FP16
+    (benchmarks/bench_cuda_fp8_gemm.cpp:156-159): the 16-bit product of the same shape is timed next to it."""
+    from tesseract_b200.ops import fp8, gemm_bf16
+    for n in (4096, 8192):
+        x, w = b.randn(n, n), b.randn(n, n, scale=0.02)
+        qa, sa = fp8.quantize_tensor(x)
+        qb, sb = fp8.quantize_tensor(w)
+        ms8 = b.time(lambda: fp8.fp8_gemm_pertensor(qa, sa, qb, sb))
+        out = torch.empty(n, n, device=b.dev, dtype=torch.bfloat16)
+        ms16 = b.time(lambda: gemm_bf16(x, w, out=out))
+        report(f"gemm_fp8_pertensor_{n}", ms8, flops=2.0 * n ** 3, shape=[n, n, n], bf16_ms=round(ms16, 4),
+               fp8_over_bf16=round(ms16 / ms8, 3), note="fractions are of the bf16 peak")
+
+
 def case_decode_gemm(b: Bench):
     """Weight-streaming GEMMs of one decode step (Llama-8B layer shapes) at 64 and 256 rows."""
     from tesseract_b200 import ops
@@ -299,7 +314,7 @@ def case_ag_gemm_emul(b: Bench):
            note="multiply half of rank 0 of 2 after both ranks' push halves; push_ms = one rank's push half alone")
 
 
-CASES = {"gemm": case_gemm, "gemm_fp8": case_gemm_fp8, "decode_gemm": case_decode_gemm, "gemm_wgrad": case_gemm_wgrad, "grouped_gemm": case_grouped_gemm,
+CASES = {"gemm": case_gemm, "gemm_fp8": case_gemm_fp8, "gemm_fp8_pertensor": case_gemm_fp8_pertensor, "decode_gemm": case_decode_gemm, "gemm_wgrad": case_gemm_wgrad, "grouped_gemm": case_grouped_gemm,
          "flash_fwd": case_flash_fwd, "flash_bwd": case_flash_bwd, "decode": case_decode,
          "decode_int8": case_decode_int8, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu, "adam": case_adam,
          "ce_stats": case_ce, "selective_scan": case_scan, "gemv_w8": case_gemv, "gemm_rs_emul": case_gemm_rs_emul,

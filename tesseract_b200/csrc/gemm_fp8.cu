@@ -224,8 +224,203 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Per-tensor-scaled variant: C = (sa * sb) * A8 * B8^T with ONE scale per operand (the reference's FP8 contract,
+// src/cuda/Fp8MatMul.cu:93-157). The whole K range accumulates in TMEM, so the kernel has the shape of the bf16
+// GEMM -- 128 x 256 tiles, accumulator double-buffered across tiles, epilogue once per tile -- with 128 K bytes per
+// stage and kind::f8f6f4 instructions: half the operand bytes per FLOP of the bf16 kernel.
+constexpr int PBN = 256;
+constexpr int kPStages = 4;
+constexpr int kPStageBytes = (BM + PBN) * BKB;  // 48 KB
+constexpr int kPSmemBytes = kPStages * kPStageBytes + 1024;
+constexpr int kPThreads = 192;
+
+__global__ void __launch_bounds__(kPThreads, 1)
+gemm_fp8_pt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   __nv_bfloat16* __restrict__ C, const float* __restrict__ scale_a, const float* __restrict__ scale_b,
+                   int M, int N, int K, long long ldc, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t full_bar[kPStages];
+  __shared__ __align__(8) uint64_t empty_bar[kPStages];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ volatile int cta_abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (M + BM - 1) / BM;
+  const int num_n = (N + PBN - 1) / PBN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = K / BKB;
+
+  if (threadIdx.x == 0) {
+    cta_abort = 0;
+    for (int s = 0; s < kPStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_smem, 2 * PBN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+
+  auto tile_mn = [&](int t, int& m0, int& n0) {
+    constexpr int GM = 16;
+    const int group_size = GM * num_n;
+    const int gid = t / group_size;
+    const int first_m = gid * GM;
+    const int gm = min(num_m - first_m, GM);
+    const int r = t - gid * group_size;
+    m0 = (first_m + r % gm) * BM;
+    n0 = (r / gm) * PBN;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int m0, n0;
+        tile_mn(t, m0, n0);
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &cta_abort, status);
+          if (!ok) break;
+          uint8_t* sA = smem + stage * kPStageBytes;
+          uint8_t* sB = sA + BM * BKB;
+          mbar_expect_tx(&full_bar[stage], kPStageBytes);
+          tma_load_2d(sA, &tmA, &full_bar[stage], kb * BKB, m0);
+          tma_load_2d(sB, &tmB, &full_bar[stage], kb * BKB, n0);
+          if (++stage == kPStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BM, PBN, 0, 0, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        bool ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u, &cta_abort, status);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * PBN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, &cta_abort, status);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + stage * kPStageBytes);
+          const uint32_t b_base = a_base + BM * BKB;
+#pragma unroll
+          for (int k = 0; k < BKB / 32; ++k)
+            umma_f8(d_tmem, umma_smem_desc_sw128(a_base + k * 32, 16, 1024), umma_smem_desc_sw128(b_base + k * 32, 16, 1024),
+                    idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kPStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    const float scale = __ldg(scale_a) * __ldg(scale_b);
+    const bool vec = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int m0, n0;
+      tile_mn(t, m0, n0);
+      const bool ok = mbar_wait(&tmem_full_bar[acc], acc_phase, &cta_abort, status);
+      if (!__all_sync(0xffffffffu, ok ? 1 : 0)) break;
+      tc_fence_after();
+      const int row = m0 + row_in_tile;
+      __nv_bfloat16* crow = C + static_cast<long long>(row) * ldc;
+#pragma unroll 1
+      for (int c = 0; c < PBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * PBN + c * 32), r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (vec && col0 + v * 8 + 8 <= N) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]) * scale, __uint_as_float(r[v * 8 + 1]) * scale);
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]) * scale, __uint_as_float(r[v * 8 + 3]) * scale);
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]) * scale, __uint_as_float(r[v * 8 + 5]) * scale);
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]) * scale, __uint_as_float(r[v * 8 + 7]) * scale);
+              *reinterpret_cast<uint4*>(crow + col0 + v * 8) = o;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (col0 + v * 8 + j < N) crow[col0 + v * 8 + j] = __float2bfloat16(__uint_as_float(r[v * 8 + j]) * scale);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (cta_abort) {
+      for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * PBN);
+  }
+}
+
+// One CTA per 1024 elements: q = e4m3(x / scale) with a given per-tensor scale.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_tensor_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, const float* __restrict__ scale, long long n);
+
 __device__ __forceinline__ uint8_t to_e4m3(float x) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_tensor_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, const float* __restrict__ scale, long long n) {
+  const float inv = 1.f / __ldg(scale);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    q[i] = to_e4m3(to_f32<T>(x[i]) * inv);
 }
 
 // One warp per (row, 128-wide K block): absmax -> scale = absmax / 448 (1 if the block is zero) -> e4m3 bytes.
@@ -340,6 +535,48 @@ TSB_EXPORT int tsb_quant_weight_128x128(const void* w, void* q, float* scales, i
     case 0: quant_weight_128x128_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(w), qo, scales, N, K, ldw); break;
     case 1: quant_weight_128x128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(w), qo, scales, N, K, ldw); break;
     case 2: quant_weight_128x128_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(w), qo, scales, N, K, ldw); break;
+    default: return -2;
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// C [M, N] bf16 = (scale_a * scale_b) * A8 [M, K] * B8 [N, K]^T with one fp32 scale per operand (device scalars).
+// K % 128 == 0; operands contiguous rows of K bytes, 16-byte aligned.
+TSB_EXPORT int tsb_gemm_fp8_pertensor(const void* A8, const void* B8, void* C, const float* scale_a, const float* scale_b,
+                                      int M, int N, int K, long long ldc, void* stream) {
+  using namespace tsb;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 128 || !scale_a || !scale_b) return -2;
+  if ((reinterpret_cast<uintptr_t>(A8) & 15) || (reinterpret_cast<uintptr_t>(B8) & 15)) return -2;
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, A8, 1, M, K, static_cast<uint64_t>(K), BM, BKB, true)) return -3;
+  if (!make_tmap_2d(&tb, B8, 1, N, K, static_cast<uint64_t>(K), PBN, BKB, true)) return -3;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_pt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + PBN - 1) / PBN);
+  int grid = sm_count();
+  if (tiles < grid) grid = tiles;
+  gemm_fp8_pt_kernel<<<grid, kPThreads, kPSmemBytes, static_cast<cudaStream_t>(stream)>>>(
+      ta, tb, static_cast<__nv_bfloat16*>(C), scale_a, scale_b, M, N, K, ldc, device_status_word());
+  return static_cast<int>(cudaGetLastError());
+}
+
+// q [n] e4m3 = x [n] / *scale (device scalar), saturating. dtype: 0 fp32, 1 bf16, 2 fp16.
+TSB_EXPORT int tsb_quant_tensor_e4m3(const void* x, void* q, const float* scale, long long n, int dtype, void* stream) {
+  using namespace tsb;
+  if (n <= 0 || !scale) return -2;
+  long long blocks = (n + 1023) / 1024;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* qo = static_cast<uint8_t*>(q);
+  switch (dtype) {
+    case 0: quant_tensor_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const float*>(x), qo, scale, n); break;
+    case 1: quant_tensor_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), qo, scale, n); break;
+    case 2: quant_tensor_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const __half*>(x), qo, scale, n); break;
     default: return -2;
   }
   return static_cast<int>(cudaGetLastError());

@@ -19,6 +19,8 @@ _native.register_signatures({
     "tsb_gemm_fp8_blockscaled": [P, P, P, P, P, I, I, I, L, P],
     "tsb_quant_act_1x128": [P, P, P, I, I, L, I, P],
     "tsb_quant_weight_128x128": [P, P, P, I, I, L, I, P],
+    "tsb_gemm_fp8_pertensor": [P, P, P, P, P, I, I, I, L, P],
+    "tsb_quant_tensor_e4m3": [P, P, P, L, I, P],
 })
 
 E4M3_MAX = 448.0
@@ -130,3 +132,36 @@ class Fp8Linear(torch.nn.Module):
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
         return y.view(*x.shape[:-1], self.out_features)
+
+
+# ----------------------------------------------------------------------------------------- per-tensor scaling
+def quantize_tensor(x: torch.Tensor):
+    """x -> (e4m3 bytes uint8 of the same shape, fp32 scale [1] on x's device): scale = absmax / 448 (1 for an all-zero
+    tensor). The reference's FP8 contract (one device scale per operand, src/cuda/Fp8MatMul.cu:34-41,93-157)."""
+    amax = x.detach().abs().amax().float().reshape(1)
+    scale = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+    xc = x.contiguous()
+    if not _native_ok(xc):
+        q = (xc.float() / scale).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8)
+        return q, scale
+    q = torch.empty(xc.shape, dtype=torch.uint8, device=xc.device)
+    check(lib().tsb_quant_tensor_e4m3(xc.data_ptr(), q.data_ptr(), scale.data_ptr(), xc.numel(),
+                                      _native.dtype_code(xc.dtype), stream_ptr(xc.device)), "tsb_quant_tensor_e4m3")
+    return q, scale
+
+
+def fp8_gemm_pertensor(qa: torch.Tensor, sa: torch.Tensor, qb: torch.Tensor, sb: torch.Tensor) -> torch.Tensor:
+    """bf16 [M, N] = (sa * sb) * qa [M, K] @ qb [N, K]^T with one scale per operand; the whole K range accumulates
+    in tensor memory (tcgen05 kind::f8f6f4, 128 x 256 tiles)."""
+    M, K = qa.shape
+    N = qb.shape[0]
+    if not _native_ok(qa):
+        a = qa.view(torch.float8_e4m3fn).float() * sa.float()
+        b = qb.view(torch.float8_e4m3fn).float() * sb.float()
+        return (a @ b.t()).to(torch.bfloat16)
+    if K % 128 or not (qa.is_contiguous() and qb.is_contiguous()):
+        raise ValueError("fp8_gemm_pertensor: K must be a multiple of 128 and the operands contiguous")
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=qa.device)
+    check(lib().tsb_gemm_fp8_pertensor(qa.data_ptr(), qb.data_ptr(), out.data_ptr(), sa.data_ptr(), sb.data_ptr(), M, N, K,
+                                       out.stride(0), stream_ptr(qa.device)), "tsb_gemm_fp8_pertensor")
+    return out

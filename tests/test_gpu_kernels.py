@@ -358,6 +358,24 @@ def test_flash_varlen_matches_per_sequence(dev, D):
         off += n
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 264, 512), (2048, 4096, 4096)])
+def test_fp8_pertensor_gemm(dev, M, N, K):
+    """Per-tensor-scaled E4M3 GEMM (whole K accumulated in tensor memory) against the fp32 product of the
+    dequantised operands, and against the unquantised product within fp8 error."""
+    from tesseract_b200.ops import fp8
+    g = torch.Generator(device=dev).manual_seed(M + K)
+    x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    qa, sa = fp8.quantize_tensor(x)
+    qb, sb = fp8.quantize_tensor(w)
+    assert abs(float(sa) - float(x.float().abs().max()) / 448.0) < 1e-6
+    y = fp8.fp8_gemm_pertensor(qa, sa, qb, sb)
+    _status_ok()
+    ref = (qa.view(torch.float8_e4m3fn).float() * sa) @ (qb.view(torch.float8_e4m3fn).float() * sb).t()
+    assert _rel_err(y, ref) < 5e-3
+    assert _rel_err(y, x.float() @ w.float().t()) < 8e-2
+
+
 def test_tiny_llama_train_step_matches_cpu(dev):
     """bf16 GPU step through every native kernel vs the fp32 CPU restatement of the same model."""
     from tesseract_b200.models import LlamaConfig, LlamaModel
