@@ -82,15 +82,21 @@ def test_graph_capture_run_and_backward():
             return self.b(torch.relu(self.a(x))) + 1.0
 
     m = MLP()
-    with GraphScope() as scope:
-        g = scope.trace(m)
-    assert g.op_kinds() == ["matmul", "relu", "matmul", "add"] and g.inputs == ["x"]
     x = torch.randn(3, 4)
-    assert torch.equal(run(g, x), m(x))
-    (gx,) = build_backward(g)(x)
-    xr = x.clone().requires_grad_()
+    with GraphScope() as scope:
+        g = scope.trace(m, x, names=["x"])
+    assert [k for k in g.op_kinds() if k in ("matmul", "relu")] == ["matmul", "relu", "matmul"] and g.op_kinds()[-1] == "add"
+    assert [g.value(i).name for i in g.inputs] == ["x"] and len(g.params) == 4
+    x2 = torch.randn(3, 4)
+    env = {g.inputs[0]: x2}
+    env.update({vid: p.detach() for vid, p in zip(g.params, m.parameters())})
+    assert torch.allclose(run(g, env)[0], m(x2))
+    res = build_backward(g, wrt=[g.inputs[0]])
+    env[res.cotangents[0]] = torch.ones(3, 2)
+    gx = run(g, env)[-1]
+    xr = x2.clone().requires_grad_()
     m(xr).sum().backward()
-    assert torch.allclose(gx, xr.grad)
+    assert torch.allclose(gx, xr.grad, atol=1e-6)
 
 
 def test_decode_gemm_plan():

@@ -756,3 +756,29 @@ def test_moe_layer_gpu_matches_dense_reference(dev):
         out = moe_l(x)
         ref = moe_l.forward_dense_reference(x)
     assert _rel_err(out, ref) < 3e-2
+
+
+def test_graph_train_step_replays_as_one_cuda_graph(dev):
+    """Graph-mode training on the GPU: forward + backward recorded once and replayed as a CUDA graph gives the
+    eager tape's loss and gradients on fresh batches."""
+    import torch.nn.functional as F
+    from tesseract_b200.graph import GraphTrainStep
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(64, 48), torch.nn.ReLU(), torch.nn.Linear(48, 10)).to(dev)
+    x, y = torch.randn(32, 1, 8, 8, device=dev), torch.randint(0, 10, (32,), device=dev)
+    step = GraphTrainStep(model, F.cross_entropy, x, y)
+    assert step.executor.cuda_graph
+    for _ in range(3):
+        x, y = torch.randn(32, 1, 8, 8, device=dev), torch.randint(0, 10, (32,), device=dev)
+        loss = step(x, y).clone()
+        got = [p.grad.clone() for p in model.parameters()]
+        for p in model.parameters():
+            p.grad = None
+        ref = F.cross_entropy(model(x), y)
+        ref.backward()
+        assert abs(float(loss) - float(ref)) < 1e-4
+        for g_, p in zip(got, model.parameters()):
+            assert _rel_err(g_, p.grad) < 1e-3
+        with torch.no_grad():
+            for p in model.parameters():
+                p.sub_(0.1 * p.grad)            # in-place update: the next replay must see it
