@@ -91,4 +91,15 @@ std::pair<std::string, int64_t> safetensors_header(const std::string& path);
 void token_mask(const int32_t* table, int64_t num_states, int32_t state, const uint8_t* bytes, const int64_t* offsets,
                 int64_t n_tokens, uint8_t* allowed);
 
+// ---- CPU decode GEMV, INT8 weights x INT8 activations (gemv_int8.cpp)
+bool gemv_vnni_supported();
+// Per-vector symmetric quantisation: scale = absmax / 127 (1 for a zero vector); returns the scale.
+float quantize_row_int8(const float* x, int64_t K, int8_t* xq);
+void compute_row_sums(const int8_t* W, int64_t N, int64_t K, int32_t* rowsum);
+// y[n] = xscale * wscale[n] * sum_k xq[k] * W[n,k] for rows [n_begin, n_end); rowsum may be null (scalar path).
+void gemv_w8a8_range(const int8_t* W, const float* wscale, const int32_t* rowsum, const int8_t* xq, float xscale, float* y,
+                     int64_t n_begin, int64_t n_end, int64_t K);
+void gemv_w8a8(const int8_t* W, const float* wscale, const int32_t* rowsum, const int8_t* xq, float xscale, float* y,
+               int64_t N, int64_t K, int threads);
+
 }  // namespace tsbh

@@ -3,6 +3,9 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <algorithm>
+#include <stdexcept>
+
 #include "host_runtime.hpp"
 
 namespace py = pybind11;
@@ -66,4 +69,48 @@ PYBIND11_MODULE(_tsb_host, m) {
                      out.mutable_data());
           return out;
         });
+
+  m.def("gemv_vnni_supported", &gemv_vnni_supported);
+  m.def("quantize_row_int8", [](py::array_t<float, py::array::c_style | py::array::forcecast> x) {
+    py::array_t<int8_t> q(x.size());
+    const float scale = quantize_row_int8(x.data(), x.size(), q.mutable_data());
+    return py::make_tuple(q, scale);
+  });
+  m.def("compute_row_sums", [](py::array_t<int8_t, py::array::c_style | py::array::forcecast> W) {
+    if (W.ndim() != 2) throw std::invalid_argument("compute_row_sums: W must be [N, K]");
+    py::array_t<int32_t> out(W.shape(0));
+    compute_row_sums(W.data(), W.shape(0), W.shape(1), out.mutable_data());
+    return out;
+  });
+  m.def("gemv_w8a8",
+        [](py::array_t<int8_t, py::array::c_style | py::array::forcecast> W,
+           py::array_t<float, py::array::c_style | py::array::forcecast> wscale, py::object rowsum,
+           py::array_t<int8_t, py::array::c_style | py::array::forcecast> xq, float xscale, int64_t n_begin, int64_t n_end,
+           int threads) {
+          if (W.ndim() != 2) throw std::invalid_argument("gemv_w8a8: W must be [N, K]");
+          const int64_t N = W.shape(0), K = W.shape(1);
+          if (wscale.size() != N || xq.size() != K) throw std::invalid_argument("gemv_w8a8: wscale [N] and xq [K] expected");
+          if (n_end < 0) n_end = N;
+          if (n_begin < 0 || n_end > N || n_begin > n_end) throw std::invalid_argument("gemv_w8a8: bad row range");
+          py::array_t<int32_t, py::array::c_style | py::array::forcecast> rs;
+          const int32_t* rsp = nullptr;
+          if (!rowsum.is_none()) {
+            rs = rowsum.cast<py::array_t<int32_t, py::array::c_style | py::array::forcecast>>();
+            if (rs.size() != N) throw std::invalid_argument("gemv_w8a8: rowsum [N] expected");
+            rsp = rs.data();
+          }
+          py::array_t<float> y(N);
+          float* yp = y.mutable_data();
+          std::fill(yp, yp + N, 0.f);
+          {
+            py::gil_scoped_release nogil;
+            if (n_begin == 0 && n_end == N)
+              gemv_w8a8(W.data(), wscale.data(), rsp, xq.data(), xscale, yp, N, K, threads);
+            else
+              gemv_w8a8_range(W.data(), wscale.data(), rsp, xq.data(), xscale, yp, n_begin, n_end, K);
+          }
+          return y;
+        },
+        py::arg("W"), py::arg("wscale"), py::arg("rowsum"), py::arg("xq"), py::arg("xscale"), py::arg("n_begin") = 0,
+        py::arg("n_end") = -1, py::arg("threads") = 0);
 }
