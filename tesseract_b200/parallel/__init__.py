@@ -4,6 +4,7 @@ from .comm import CommBackend, NcclCommBackend, SimCommBackend
 from .data_parallel import GradReducer
 from .factory import build_parallel_trainer
 from .tensor_parallel import ColumnParallelLinear, RowParallelLinear
+from .zero import ShardedAdam, shard_ranges
 
-__all__ = ["CommBackend", "NcclCommBackend", "SimCommBackend", "GradReducer", "build_parallel_trainer",
+__all__ = ["ShardedAdam", "shard_ranges", "CommBackend", "NcclCommBackend", "SimCommBackend", "GradReducer", "build_parallel_trainer",
            "ColumnParallelLinear", "RowParallelLinear"]

@@ -24,6 +24,13 @@ def _attach_reducer(model, trainer, group):
     model.grad_reducer = red
     trainer.grad_reducer = red
     trainer.dp_group = None
+    if getattr(trainer.cfg, "zero_stage", 0) == 1:
+        from .zero import ShardedAdam
+        c = trainer.cfg
+        trainer.opt = ShardedAdam(trainer.arena, group, lr=c.lr, beta1=c.beta1, beta2=c.beta2, eps=c.eps,
+                                  weight_decay=c.weight_decay, max_grad_norm=c.max_grad_norm)
+    elif getattr(trainer.cfg, "zero_stage", 0) not in (0, 1):
+        raise ValueError("zero_stage: 0 (replicated optimizer state) or 1 (sharded Adam moments)")
     return red
 
 

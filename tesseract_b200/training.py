@@ -32,6 +32,7 @@ class TrainConfig:
     grad_dtype: torch.dtype = torch.bfloat16
     master_weights: bool = False    # fp32 master copy of bf16 parameters
     ce_chunk_rows: int = 4096
+    zero_stage: int = 0             # 1: Adam moments sharded over the data-parallel ranks (parallel/zero.py)
 
 
 class Trainer:

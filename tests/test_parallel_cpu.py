@@ -217,3 +217,41 @@ def _ep_worker(rank, world):
 
 def test_expert_parallel_matches_single_process_over_gloo_ranks():
     assert all(_run_ranks(_ep_worker, 2).values())
+
+
+def _zero_worker(rank, world):
+    from tesseract_b200.models import LlamaConfig
+    from tesseract_b200.parallel import ShardedAdam, build_parallel_trainer
+    from tesseract_b200.training import TrainConfig
+    cfg = LlamaConfig(vocab_size=64, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                      intermediate_size=128, max_position_embeddings=32)
+    flats, losses = {}, {}
+    for stage in (0, 1):
+        tc = TrainConfig(lr=1e-3, micro_batch=1, max_grad_norm=1.0, weight_decay=0.01, zero_stage=stage)
+        trainer, plan = build_parallel_trainer(cfg, tc, world, rank, "cpu", "dp", seed=5)
+        g = torch.Generator().manual_seed(100 + plan["dp_rank"])
+        batch = torch.randint(0, 64, (2, 17), generator=g)
+        losses[stage] = [trainer.train_step(batch) for _ in range(3)]
+        flats[stage] = trainer.arena.flat.clone()
+        if stage == 1:
+            assert isinstance(trainer.opt, ShardedAdam)
+            full = 2 * 4 * trainer.arena.numel
+            assert trainer.opt.state_bytes() <= full // world + 2 * 4 * 64
+            sd = trainer.opt.state_dict()
+            assert sd["flat_m"].numel() == trainer.opt.end - trainer.opt.begin
+            trainer.opt.load_state_dict(sd)
+            gathered = [torch.empty_like(flats[1]) for _ in range(world)]
+            dist.all_gather(gathered, flats[1])
+            assert all(torch.equal(gathered[0], t) for t in gathered), "replicas diverged"
+    assert torch.equal(flats[0], flats[1]), float((flats[0] - flats[1]).abs().max())
+    assert losses[0] == losses[1]
+    return True
+
+
+def test_zero1_sharded_adam_matches_replicated_adam_over_gloo_ranks():
+    from tesseract_b200.parallel import shard_ranges
+    for numel, world in ((1000, 3), (64, 4), (130, 2), (5, 8)):
+        r = shard_ranges(numel, world)
+        assert r[0][0] == 0 and r[-1][1] == numel and all(a[1] == b[0] for a, b in zip(r, r[1:]))
+        assert all(a % 64 == 0 for a, _ in r if a < numel)
+    _run_ranks(_zero_worker, 3)
