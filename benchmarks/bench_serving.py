@@ -28,7 +28,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, temperature=0.0, max_batch=256,
                       prompt_range=(128, 2048), out_range=(64, 512), seed=0, cuda_graph=True, device=None, model=None,
-                      tp_group=None, rank=0, world=1, max_prefill_tokens=16384):
+                      tp_group=None, rank=0, world=1, max_prefill_tokens=16384, fp8_prefill=False):
     import torch
 
     from tesseract_b200.models import GenerateConfig, LlamaConfig, LlamaModel
@@ -57,7 +57,7 @@ def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, tempera
         from tesseract_b200.serving.engine import TPServe
         tp = TPServe(tp_group, rank, world, dev, cfg.hidden_size, max_batch=max(512, max_batch))
     eng = ServingEngine(model, ecfg, use_cuda_graph=cuda_graph, temperature=temperature, top_p=top_p, seed=seed, tp=tp,
-                        max_prefill_tokens=max_prefill_tokens)
+                        max_prefill_tokens=max_prefill_tokens, fp8_prefill=fp8_prefill)
     # warm-up: one short request end to end (kernel attributes, allocator pools, first graph bucket)
     eng.add_request(reqs[0][0][:64], GenerateConfig(max_new_tokens=4))
     eng.run()
@@ -88,7 +88,7 @@ def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, tempera
     from tesseract_b200 import _native
     return {
         "tp": world, "kernel_status": _native.read_status(torch.cuda.current_stream(dev).cuda_stream),
-        "requests": requests, "kv": "int8" if kv_int8 else "bf16", "sampling": "greedy" if temperature <= 0 else f"top_p={top_p}",
+        "requests": requests, "kv": "int8" if kv_int8 else "bf16", "fp8_prefill": bool(fp8_prefill), "sampling": "greedy" if temperature <= 0 else f"top_p={top_p}",
         "prefill_tok_s": m["prefill_tok_s"], "decode_tok_s": m["decode_tok_s"], "ttft_p50_ms": m["ttft_p50_ms"],
         "end_to_end_s": wall, "generated_tokens": gen_tokens, "total_tok_s": (total_tokens) / wall,
         "steps": m["steps"], "max_batch": max_batch, "block_size": block, "cuda_graph": cuda_graph,
@@ -105,6 +105,7 @@ def main():
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--max-batch", type=int, default=256)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--fp8-prefill", type=int, default=0, help="1: prefill GEMMs on per-tensor-scaled E4M3 weight copies")
     ap.add_argument("--max-prefill-tokens", type=int, default=16384, help="prompt tokens admitted per engine step (0 = all)")
     a = ap.parse_args()
     import torch
@@ -118,7 +119,7 @@ def main():
         group = dist.group.WORLD
     out = run_serving_bench(a.requests, a.layers, bool(a.kv_int8), a.top_p, a.temperature, a.max_batch,
                             cuda_graph=not a.no_graph, device=dev, tp_group=group, rank=rank, world=world,
-                            max_prefill_tokens=a.max_prefill_tokens)
+                            max_prefill_tokens=a.max_prefill_tokens, fp8_prefill=bool(a.fp8_prefill))
     if rank == 0:
         print(json.dumps(out))
     if world > 1:

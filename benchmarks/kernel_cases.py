@@ -215,6 +215,14 @@ def case_swiglu(b: Bench):
     report("swiglu", ms, bytes_=x.numel() * 2 * 1.5, shape=list(x.shape))
 
 
+def case_swiglu_bwd(b: Bench):
+    from tesseract_b200.ops import fused
+    x = b.randn(16384, 2 * 14336)
+    d = b.randn(16384, 14336)
+    ms = b.time(lambda: fused.swiglu_backward(x, d))
+    report("swiglu_bwd", ms, bytes_=d.numel() * 2 * 5, shape=list(x.shape))
+
+
 def case_adam(b: Bench):
     from tesseract_b200 import _native
     from tesseract_b200.optim import optimizers  # noqa: F401  (registers the signatures of loss_optim.cu)
@@ -316,7 +324,7 @@ def case_ag_gemm_emul(b: Bench):
 
 CASES = {"gemm": case_gemm, "gemm_fp8": case_gemm_fp8, "gemm_fp8_pertensor": case_gemm_fp8_pertensor, "decode_gemm": case_decode_gemm, "gemm_wgrad": case_gemm_wgrad, "grouped_gemm": case_grouped_gemm,
          "flash_fwd": case_flash_fwd, "flash_bwd": case_flash_bwd, "decode": case_decode,
-         "decode_int8": case_decode_int8, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu, "adam": case_adam,
+         "decode_int8": case_decode_int8, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu, "swiglu_bwd": case_swiglu_bwd, "adam": case_adam,
          "ce_stats": case_ce, "selective_scan": case_scan, "gemv_w8": case_gemv, "gemm_rs_emul": case_gemm_rs_emul,
          "ag_gemm_emul": case_ag_gemm_emul}
 

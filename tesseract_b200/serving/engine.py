@@ -97,9 +97,14 @@ class ServingEngine:
 
     def __init__(self, model: LlamaModel, cfg: Optional[EngineConfig] = None, use_cuda_graph: bool = True,
                  temperature: float = 0.0, top_p: float = 1.0, seed: int = 0, tp: Optional[TPServe] = None,
-                 max_prefill_tokens: int = 0):
+                 max_prefill_tokens: int = 0, fp8_prefill: bool = False):
         self.model, self.cfg = model, cfg or EngineConfig()
         self.tp = tp
+        # fp8_prefill: the layer GEMMs of prefill-sized batches (more than 512 rows) run on E4M3 copies of the weights
+        # with one scale per tensor and a per-call activation scale (about 2 x the bf16 GEMM rate); decode-sized
+        # batches and the LM head stay bf16. Off by default: it changes the numerics of the prompt pass.
+        self.fp8_prefill = bool(fp8_prefill)
+        self._w8: Dict[int, tuple] = {}
         # prompt tokens admitted per step (0 = no limit): bounds the time to first token of the requests at the
         # head of the queue and the size of the prefill activations; at least one request is always admitted
         self.max_prefill_tokens = max_prefill_tokens
@@ -129,6 +134,12 @@ class ServingEngine:
         self.allocator = BlockAllocator(c.num_blocks)
         self.max_blocks = (c.max_seq_len + c.block_size - 1) // c.block_size
         self._fuse_weights()
+        if self.fp8_prefill:
+            from ..ops import fp8
+            for ws in (self.wqkv, self.wo, self.wgu, self.wdown):
+                for w in ws:
+                    if w.dtype == torch.bfloat16 and w.shape[1] % 128 == 0:
+                        self._w8[id(w)] = fp8.quantize_tensor(w)
         self.waiting: Deque[_Req] = deque()
         self.running: List[_Req] = []
         self.requests: Dict[int, _Req] = {}
@@ -290,12 +301,19 @@ class ServingEngine:
         f = self._mm_reduce(ops.swiglu(gu), self.wdown[li])
         return f, res
 
-    @staticmethod
-    def _mm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        """x @ w^T: split-K streaming GEMM for decode-sized batches, the regular tcgen05 GEMM otherwise."""
+    def _mm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """x @ w^T: split-K streaming GEMM for decode-sized batches, the regular tcgen05 GEMM otherwise (the
+        per-tensor-scaled fp8 GEMM when ``fp8_prefill`` holds an E4M3 copy of ``w``)."""
         if x.dtype != torch.bfloat16:
             return x @ w.t()
-        return ops.decode_linear(x, w) if x.shape[0] <= 512 else ops.gemm_bf16(x, w)
+        if x.shape[0] <= 512:
+            return ops.decode_linear(x, w)
+        w8 = self._w8.get(id(w))
+        if w8 is not None:
+            from ..ops import fp8
+            qa, sa = fp8.quantize_tensor(x)
+            return fp8.fp8_gemm_pertensor(qa, sa, w8[0], w8[1])
+        return ops.gemm_bf16(x, w)
 
     def _forward(self, tokens, positions, slots, tables, lens, prefill_bounds=None, last_rows=None):
         m = self.model

@@ -601,6 +601,34 @@ def test_serving_engine_graph_vs_eager_and_generate(dev, kv_int8):
         assert agree >= 0.7 * 12 * len(prompts), agree
 
 
+def test_serving_engine_fp8_prefill_weights(dev):
+    """Opt-in E4M3 weight copies for prefill-sized GEMMs: the projection agrees with bf16 within fp8 error, decode
+    sized batches keep the bf16 path, and a run over prompts longer than 512 tokens finishes every request."""
+    from tesseract_b200.models import GenerateConfig, LlamaConfig, LlamaModel
+    from tesseract_b200.models.scheduler import EngineConfig
+    from tesseract_b200.serving import ServingEngine
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, intermediate_size=1024, max_position_embeddings=1024, dtype=torch.bfloat16)
+    model = LlamaModel(cfg, device=dev, init_std=0.05, seed=2)
+    ecfg = EngineConfig(block_size=16, num_blocks=256, max_seq_len=1024, max_batch_size=4)
+    eng = ServingEngine(model, ecfg, use_cuda_graph=False, fp8_prefill=True)
+    assert len(eng._w8) == 4 * cfg.num_hidden_layers
+    x = (torch.randn(1024, 512, device=dev, generator=torch.Generator(device=dev).manual_seed(0))).bfloat16()
+    for w in (eng.wqkv[0], eng.wgu[1]):
+        got, ref = eng._mm(x, w).float(), x.float() @ w.float().t()
+        assert _rel_err(got, ref) < 0.06
+        small = eng._mm(x[:64], w).float()                       # decode-sized: bf16 path, tight agreement
+        assert _rel_err(small, ref[:64]) < 1e-2
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 512, (n,), generator=g).tolist() for n in (700, 40, 300)]
+    ids = [eng.add_request(p, GenerateConfig(max_new_tokens=8)) for p in prompts]
+    eng.run()
+    outs = [eng.result(i) for i in ids]
+    assert [len(o) for o in outs] == [len(p) + 8 for p in prompts] and eng.free_blocks() == 256
+    assert all(0 <= t < 512 for o in outs for t in o)
+    _status_ok()
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (64, 6144, 4096), (256, 4096, 14336), (37, 1000, 520)])
 def test_decode_linear_split_k(dev, M, N, K):
     from tesseract_b200 import ops
