@@ -229,12 +229,17 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // src/cuda/Fp8MatMul.cu:93-157). The whole K range accumulates in TMEM, so the kernel has the shape of the bf16
 // GEMM -- 128 x 256 tiles, accumulator double-buffered across tiles, epilogue once per tile -- with 128 K bytes per
 // stage and kind::f8f6f4 instructions: half the operand bytes per FLOP of the bf16 kernel.
-constexpr int PBN = 256;
+// The tile width PBN is 256 for problems that fill the GPU and 128 / 64 for small ones (a 1024^3 product has only 32
+// tiles of 128 x 256 for 148 SMs).
 constexpr int kPStages = 4;
-constexpr int kPStageBytes = (BM + PBN) * BKB;  // 48 KB
-constexpr int kPSmemBytes = kPStages * kPStageBytes + 1024;
 constexpr int kPThreads = 192;
+template <int PBN>
+struct PtCfg {
+  static constexpr int kStageBytes = (BM + PBN) * BKB;  // 48 KB at PBN = 256
+  static constexpr int kSmemBytes = kPStages * kStageBytes + 1024;
+};
 
+template <int PBN>
 __global__ void __launch_bounds__(kPThreads, 1)
 gemm_fp8_pt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    __nv_bfloat16* __restrict__ C, const float* __restrict__ scale_a, const float* __restrict__ scale_b,
@@ -300,9 +305,9 @@ gemm_fp8_pt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, &cta_abort, status);
           if (!ok) break;
-          uint8_t* sA = smem + stage * kPStageBytes;
+          uint8_t* sA = smem + stage * PtCfg<PBN>::kStageBytes;
           uint8_t* sB = sA + BM * BKB;
-          mbar_expect_tx(&full_bar[stage], kPStageBytes);
+          mbar_expect_tx(&full_bar[stage], PtCfg<PBN>::kStageBytes);
           tma_load_2d(sA, &tmA, &full_bar[stage], kb * BKB, m0);
           tma_load_2d(sB, &tmB, &full_bar[stage], kb * BKB, n0);
           if (++stage == kPStages) {
@@ -329,7 +334,7 @@ gemm_fp8_pt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           ok = mbar_wait(&full_bar[stage], phase, &cta_abort, status);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_base = smem_u32(smem + stage * kPStageBytes);
+          const uint32_t a_base = smem_u32(smem + stage * PtCfg<PBN>::kStageBytes);
           const uint32_t b_base = a_base + BM * BKB;
 #pragma unroll
           for (int k = 0; k < BKB / 32; ++k)
@@ -549,19 +554,27 @@ TSB_EXPORT int tsb_gemm_fp8_pertensor(const void* A8, const void* B8, void* C, c
   if ((reinterpret_cast<uintptr_t>(A8) & 15) || (reinterpret_cast<uintptr_t>(B8) & 15)) return -2;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, A8, 1, M, K, static_cast<uint64_t>(K), BM, BKB, true)) return -3;
-  if (!make_tmap_2d(&tb, B8, 1, N, K, static_cast<uint64_t>(K), PBN, BKB, true)) return -3;
-  static bool attr = false;
-  if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_pt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr = true;
-  }
-  const int tiles = ((M + BM - 1) / BM) * ((N + PBN - 1) / PBN);
-  int grid = sm_count();
-  if (tiles < grid) grid = tiles;
-  gemm_fp8_pt_kernel<<<grid, kPThreads, kPSmemBytes, static_cast<cudaStream_t>(stream)>>>(
-      ta, tb, static_cast<__nv_bfloat16*>(C), scale_a, scale_b, M, N, K, ldc, device_status_word());
-  return static_cast<int>(cudaGetLastError());
+  const int num_m = (M + BM - 1) / BM;
+  auto tiles_at = [&](int bn) { return num_m * ((N + bn - 1) / bn); };
+  const int sms = sm_count();
+  // the widest tile that still gives at least half the SMs a tile each
+  const int bn = 2 * tiles_at(256) >= sms ? 256 : (2 * tiles_at(128) >= sms ? 128 : 64);
+  if (!make_tmap_2d(&tb, B8, 1, N, K, static_cast<uint64_t>(K), bn, BKB, true)) return -3;
+  auto launch = [&](auto kernel, int smem_bytes, bool& attr) -> int {
+    if (!attr) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      attr = true;
+    }
+    int grid = tiles_at(bn) < sms ? tiles_at(bn) : sms;
+    kernel<<<grid, kPThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
+        ta, tb, static_cast<__nv_bfloat16*>(C), scale_a, scale_b, M, N, K, ldc, device_status_word());
+    return static_cast<int>(cudaGetLastError());
+  };
+  static bool attr256 = false, attr128 = false, attr64 = false;
+  if (bn == 256) return launch(gemm_fp8_pt_kernel<256>, PtCfg<256>::kSmemBytes, attr256);
+  if (bn == 128) return launch(gemm_fp8_pt_kernel<128>, PtCfg<128>::kSmemBytes, attr128);
+  return launch(gemm_fp8_pt_kernel<64>, PtCfg<64>::kSmemBytes, attr64);
 }
 
 // q [n] e4m3 = x [n] / *scale (device scalar), saturating. dtype: 0 fp32, 1 bf16, 2 fp16.

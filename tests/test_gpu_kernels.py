@@ -358,7 +358,8 @@ def test_flash_varlen_matches_per_sequence(dev, D):
         off += n
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 264, 512), (2048, 4096, 4096)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 264, 512), (1024, 2048, 512), (1024, 1024, 1024),
+                                   (2048, 4096, 4096)])     # tile widths 64, 64, 128, 64, 256
 def test_fp8_pertensor_gemm(dev, M, N, K):
     """Per-tensor-scaled E4M3 GEMM (whole K accumulated in tensor memory) against the fp32 product of the
     dequantised operands, and against the unquantised product within fp8 error."""
