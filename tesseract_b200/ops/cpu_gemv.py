@@ -22,6 +22,14 @@ def _host():
     return h if h is not None and hasattr(h, "gemv_w8a8") else None
 
 
+def _threads(threads: int) -> int:
+    """0 lets the native code pick (up to 16 hardware threads) unless TESSERACT_GEMM_MAX_THREADS caps it."""
+    cap = int(os.environ.get("TESSERACT_GEMM_MAX_THREADS", "0") or 0)
+    if cap > 0:
+        return min(threads, cap) if threads > 0 else cap
+    return threads
+
+
 def gemv_vnni_supported() -> bool:
     h = _host()
     return bool(h.gemv_vnni_supported()) if h is not None else False
@@ -66,7 +74,7 @@ def gemv_w8a8_range(W: torch.Tensor, wscale: torch.Tensor, rowsum: Optional[torc
     if h is not None:
         rs = None if rowsum is None else rowsum.to(torch.int32).contiguous().numpy()
         y = h.gemv_w8a8(W.contiguous().numpy(), wscale.float().contiguous().numpy(), rs, xq.contiguous().numpy(),
-                        float(xscale), int(n_begin), int(n_end), int(threads))
+                        float(xscale), int(n_begin), int(n_end), _threads(int(threads)))
         return torch.from_numpy(np.asarray(y))
     y = torch.zeros(N, dtype=torch.float32)
     acc = (W[n_begin:n_end].to(torch.int32) * xq.to(torch.int32)[None, :]).sum(dim=1, dtype=torch.int32)

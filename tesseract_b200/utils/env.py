@@ -24,6 +24,15 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_DEBUG", "", "non-empty: native code prints diagnostics (e.g. failed TMA descriptor encodings)"),
     EnvVar("TESSERACT_GEMM_MAX_THREADS", "0", "cap on CPU GEMV / GEMM worker threads of the host runtime (0 = all)"),
     EnvVar("TESSERACT_WATCHDOG_TIMEOUT_S", "60", "seconds without a heartbeat before a rank is declared lost"),
+    EnvVar("TESSERACT_HOST", "native", "host runtime: native (C++ module) | python (the bit-identical Python twins)"),
+    EnvVar("TESSERACT_DECODE_GEMM", "cluster", "decode-sized GEMMs: cluster (split-K reduced through DSMEM) | simple (fp32 atomics)"),
+    EnvVar("TESSERACT_FLASH_FWD", "eager", "FlashAttention forward rescaling: eager | lazy (output kept in tensor memory; slower)"),
+    EnvVar("TESSERACT_PREFILL_VARLEN", "1", "serving prefill attention: 1 (one variable-length launch) | 0 (one launch per prompt)"),
+    EnvVar("TESSERACT_AG_KEEP", "copy", "all-gather -> GEMM: how the gathered activations are kept for backward: copy (copy engine) | kernel"),
+    EnvVar("TESSERACT_AG_NSUB", "0", "all-gather -> GEMM: sub-chunks signalled per rank (0 = chosen by size; at most 2)"),
+    EnvVar("TESSERACT_RMS_PREFETCH", "1", "RMSNorm forward: 1 (next row prefetched across the reduction) | 0 (plain kernel, for A/B runs)"),
+    EnvVar("TESSERACT_RMS_THREADS", "0", "RMSNorm forward threads per row: 0 (256) | 128 | 256, for A/B runs"),
+    EnvVar("TESSERACT_SWIGLU", "2", "SwiGLU kernels: 2 (row-wise, two vector pairs per thread) | 0 (flat kernel, for A/B runs)"),
 ]}
 
 

@@ -114,3 +114,21 @@ def test_decode_gemm_plan():
     kind, s = plan_decode_gemm(64, 6144, 4096, mode="simple")
     assert kind == "atomic" and 2 <= s <= 16
     assert plan_decode_gemm(64, 28672, 4096, mode="simple") == ("plain", 0)
+
+
+def test_every_environment_variable_read_by_the_code_is_registered():
+    import os
+    import re
+    from tesseract_b200.utils import env
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    used = set()
+    for base in ("tesseract_b200", "benchmarks", "examples"):
+        for d, _, files in os.walk(os.path.join(root, base)):
+            for f in files:
+                if f.endswith((".py", ".cu", ".cuh", ".cpp", ".hpp")):
+                    text = open(os.path.join(d, f), errors="replace").read()
+                    used |= set(re.findall(r'(?:getenv\(|environ\.get\(|environ\[)\s*"(TESSERACT_[A-Z0-9_]+)"', text))
+    used |= set(re.findall(r'environ\.get\(\s*"(TESSERACT_[A-Z0-9_]+)"', open(os.path.join(root, "bench.py")).read()))
+    missing = sorted(used - set(env.REGISTRY))
+    assert not missing, f"not in utils/env.py: {missing}"
+    assert "TESSERACT_SWIGLU" in used and len(used) >= 12
