@@ -14,7 +14,14 @@ synchronise, timed with CUDA events, max over ranks:
   * ``value``: steps fed from a device-resident batch;
   * ``e2e``:   ``Trainer.train_step`` -- the public call -- fed from pinned host memory each step
                (host-to-device copy of the tokens and device-to-host read of the loss included).
-Rank 0 prints ONE JSON line. ``--impl reference`` reports why the reference cannot be run here.
+Rank 0 prints ONE JSON line.
+
+``--impl reference`` runs the UNMODIFIED reference instead (built offline by ``baseline/build_reference.py`` into
+``baseline/_ref``): the same metric and shape through the reference's own public C++ API (``LlamaModel``,
+``ops::cross_entropy_with_logits``, ``Engine::backward``, ``optim::Adam`` -- the loop of its examples/llama_train.cpp --
+and its ``ContinuousBatchingScheduler`` for the serving half), driven by the two harness executables of
+``baseline/harness``; nothing of this repository's models, kernels or engine is on that path. Where the reference
+cannot run a case the line is ``{"impl": "reference", "unavailable": "<the actual error>"}``.
 """
 from __future__ import annotations
 
@@ -26,8 +33,10 @@ import subprocess
 import sys
 import time
 
-REFERENCE_UNAVAILABLE = ("reference is a CMake/C++ project without setup.py or pyproject.toml: "
-                         "an offline `pip install` of its source tree fails with 'Directory is not installable'")
+REPO_ROOT = os.path.dirname(os.path.abspath(__file__))
+REF_BIN = os.path.join(REPO_ROOT, "baseline", "_ref", "bin")
+METRIC = "Llama-3-8B-shape training tokens/s (fwd+bwd+Adam, max over ranks)"
+DATA = "synthetic uniform random token ids; random-init N(0,0.02) weights"
 
 _SMI_FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
                "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -95,14 +104,135 @@ def parse_args():
     ap.add_argument("--master-weights", action="store_true")
     ap.add_argument("--parallelism", default="auto", help="auto | dp | tp  (auto: tensor+sequence parallel over all ranks)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ref-time-budget", type=float, default=float(os.environ.get("TESSERACT_REF_TIME_BUDGET", 780)),
+                    help="(--impl reference) seconds the whole reference arm may take; the timed step count shrinks to fit")
     return ap.parse_args()
+
+
+def _run_harness(cmd, timeout):
+    """Runs one harness process; returns (parsed JSON line or None, error text)."""
+    try:
+        p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=timeout)
+    except subprocess.TimeoutExpired:
+        return None, f"timed out after {timeout:.0f} s"
+    except OSError as e:
+        return None, f"{type(e).__name__}: {e}"
+    for line in reversed(p.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            try:
+                out = json.loads(line)
+            except ValueError:
+                continue
+            if out.get("ok"):
+                return out, ""
+            return None, str(out.get("error", "unknown error"))[:400]
+    tail = (p.stderr.strip() or p.stdout.strip())[-400:].replace("\n", " | ")
+    return None, f"exit code {p.returncode}: {tail}"
+
+
+def run_reference(args):
+    """The reference arm: the unmodified reference, through its own API, on the same metric and shape."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    train_bin, serve_bin = os.path.join(REF_BIN, "ref_train_bench"), os.path.join(REF_BIN, "ref_serve_bench")
+
+    def unavailable(why, **extra):
+        print(json.dumps({"impl": "reference", "unavailable": why, **extra}))
+        return 0
+
+    if not os.path.exists(train_bin):
+        return unavailable("baseline/_ref is not built (python baseline/build_reference.py builds the reference offline "
+                           "with CMake; a pip install of its source tree fails: no setup.py / pyproject.toml)")
+    t_start = time.time()
+    if max(world, args.gpus) > 1:
+        # The reference trains on one device only: examples/llama_train.cpp and LlamaModel have no parallel form, its
+        # Column/RowParallelLinear hold every rank's shard in one process, and NcclCommBackend has no autograd.
+        # Its one multi-GPU program, the tensor-parallel MLP forward + ncclAllReduce microbenchmark, runs as context.
+        n = max(world, args.gpus)
+        ctx, tp_bin = {}, os.path.join(REF_BIN, "bench_cuda_nccl_tp")
+        if os.path.exists(tp_bin):
+            try:
+                p = subprocess.run([tp_bin, "--world", str(n), "--d", "4096", "--dff", "14336", "--M", "4096"],
+                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=240)
+                ctx = {"bench_cuda_nccl_tp": {"world": n, "rc": p.returncode,
+                                              "lines": [l for l in p.stdout.splitlines() if "ms" in l or "PASS" in l
+                                                        or "FAIL" in l or "skip" in l][-6:]}}
+            except Exception as e:  # context only
+                ctx = {"bench_cuda_nccl_tp": {"error": f"{type(e).__name__}: {e}"[:200]}}
+        return unavailable(f"the reference has no multi-GPU training or serving entry point (examples/llama_train.cpp and "
+                           f"LlamaModel run on one device; NcclCommBackend has no autograd): nothing to run at {n} GPUs",
+                           n_gpus=n, context=ctx)
+
+    shape = ["--vocab", "128256", "--hidden", "4096", "--heads", "32", "--kv-heads", "8", "--ffn", "14336",
+             "--layers", str(args.layers)]
+    budget = args.ref_time_budget
+    train_budget = budget * 0.55
+    sampler = ClockSampler(0)
+    sampler.start()
+    attempts, result = [], None
+    # bf16 first (the metric's dtype; parameters, gradients and Adam state in bf16 as the reference keeps them in the
+    # parameter dtype), then the reference's default fp32. One sequence per pass: its training attention keeps the
+    # [B, H, S, S] scores and probabilities for backward. Each attempt is its own process, because the reference's
+    # caching allocator keeps what it took after an out-of-memory error.
+    for dtype in ("bf16", "f32"):
+        left = train_budget - (time.time() - t_start)
+        if left < 60:
+            attempts.append({"dtype": dtype, "error": "no time left in the reference arm's budget"})
+            break
+        cmd = [train_bin, "--steps", str(args.steps), "--warmup", str(args.warmup), "--batch", str(args.global_batch),
+               "--seq", str(args.seq_len), "--micro", "1", "--dtype", dtype, "--e2e", "0" if args.no_e2e else "1",
+               "--time-limit", f"{left * 0.8:.0f}"] + shape
+        out, err = _run_harness(cmd, timeout=left)
+        if out is not None:
+            result = out
+            break
+        attempts.append({"dtype": dtype, "error": err})
+    clocks = sampler.stop()
+    if result is None:
+        return unavailable("the reference's own training step failed at this shape: " +
+                           "; ".join(f"[{a['dtype']}] {a['error']}" for a in attempts), attempts=attempts)
+
+    serve = None
+    want_serve = args.serve == 1 or (args.serve == -1 and args.layers == 32)
+    left = budget - (time.time() - t_start)
+    if want_serve and os.path.exists(serve_bin) and left > 90:
+        out, err = _run_harness([serve_bin, "--requests", str(args.serve_requests), "--dtype", "bf16",
+                                 "--time-limit", f"{left * 0.6:.0f}"] + shape, timeout=left)
+        serve = out if out is not None else {"error": err}
+        if out is not None:
+            serve.update({"tp": 1, "weights": "bf16", "cuda_graph": False,
+                          "prefill_tok_s": None, "note": "prefill and decode share the reference's step(); "
+                          "decode_tok_s is taken over the steps that admitted no request"})
+    B, S, steps = args.global_batch, args.seq_len, int(result["steps"])
+    ms = float(result["ms_per_step"])
+    e2e = None
+    if result.get("e2e_ms_per_step", -1) > 0:
+        e2e = {"value": B * S / (result["e2e_ms_per_step"] / 1e3), "unit": "tokens/s",
+               "ms_per_step": result["e2e_ms_per_step"], "h2d_bytes_per_step": result["h2d_bytes_per_step"],
+               "d2h_bytes_per_step": result["d2h_bytes_per_step"]}
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": B * S / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "warmup": int(result["warmup"]), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": {"bf16": "bf16", "f32": "fp32"}[result["dtype"]], "data":
+        "synthetic uniform random token ids; the reference's own initialiser (U(+-1/sqrt(in)) linears, N(0,1) embedding)",
+        "config": {"model": "llama-3-8b-shape" + ("" if args.layers == 32 else f"-DEBUG-{args.layers}-layers"),
+                   "global_batch": B, "seq_len": S, "parallelism": "single", "micro_batch": int(result["micro_batch"]),
+                   "optimizer": "reference optim::Adam (state in the parameter dtype)",
+                   "l2_hygiene": "inputs_larger_than_l2 (weights streamed per pass)",
+                   "api": "LlamaModel::forward / ops::cross_entropy_with_logits / Engine::backward / optim::Adam::step",
+                   "steps_requested": args.steps, "failed_attempts": attempts},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": None, "final_loss": result.get("loss"),
+        "device_mem_used_gb": result.get("device_mem_used_gb"), "serve": serve,
+        "wall_s": round(time.time() - t_start, 1)}))
+    return 0
 
 
 def main():
     args = parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
+        return run_reference(args)
 
     import torch
     import torch.distributed as dist
@@ -214,10 +344,10 @@ def main():
         tok_s = B * S * args.steps / (ms_dev / 1e3)
         loss_val = float(last_loss[0]) if not isinstance(last_loss[0], float) else last_loss[0]
         out = {
-            "metric": "Llama-3-8B-shape training tokens/s (fwd+bwd+Adam, max over ranks)",
+            "metric": METRIC,
             "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform random token ids; random-init N(0,0.02) weights",
+            "vs_baseline": None, "dtype": "bf16", "data": DATA,
             "config": {"model": "llama-3-8b-shape" + ("" if args.layers == 32 else f"-DEBUG-{args.layers}-layers"),
                        "global_batch": B, "seq_len": S, "parallelism": plan["name"], "micro_batch": args.micro_batch,
                        "optimizer": "Adam fp32 m/v" + (" + fp32 master" if args.master_weights else ""),
