@@ -289,4 +289,26 @@ bool make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t r
 bool make_tmap_nd(CUtensorMap* out, const void* base, int elem_bytes, int rank, const uint64_t* dims,
                   const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
 int sm_count();
+
+// "Done once" remembered per device: cudaFuncSetAttribute (and the like) applies to the current device only, so a
+// process that drives several GPUs has to repeat it on each. Racing threads may both run the guarded call; it is
+// idempotent.
+class PerDeviceFlag {
+ public:
+  bool unset() const {
+    const int d = current();
+    return d < 0 || !done_[d];
+  }
+  void set() {
+    const int d = current();
+    if (d >= 0) done_[d] = true;
+  }
+
+ private:
+  static int current() {
+    int d = 0;
+    return (cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < 64) ? d : -1;
+  }
+  bool done_[64] = {};
+};
 }  // namespace tsb

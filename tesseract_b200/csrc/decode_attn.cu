@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "tsb_no_alloc.h"
 
+#include <atomic>
 #include <mutex>
 
 namespace tsb {
@@ -535,23 +536,23 @@ TSB_EXPORT int tsb_paged_decode_static(const void* q, const void* k_pool, const 
                                        int H, int Hkv, int D, int bs, int nb, int max_logical, float scale,
                                        int max_len, int dtype, void* stream) {
   using namespace tsb;
-  static float* scratch_of_device[64] = {nullptr};
+  static std::atomic<float*> scratch_of_device[64];   // zero-initialised; read without the lock on the fast path
   static std::mutex mu;
   if (A <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || (D != 64 && D != 128) || bs <= 0) return -2;
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= 64) return -2;
-  float* scratch = scratch_of_device[dev];
+  float* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
   if (!scratch) {
     std::lock_guard<std::mutex> lk(mu);
-    scratch = scratch_of_device[dev];
+    scratch = scratch_of_device[dev].load(std::memory_order_relaxed);
     if (!scratch) {
       void* p = nullptr;
       e = cudaGetSymbolAddress(&p, g_static_decode_scratch);
       if (e != cudaSuccess) return static_cast<int>(e);
       scratch = static_cast<float*>(p);
-      scratch_of_device[dev] = scratch;
+      scratch_of_device[dev].store(scratch, std::memory_order_release);
     }
   }
   int gh = 1, splits = 1;
@@ -564,3 +565,13 @@ TSB_EXPORT int tsb_paged_decode_static(const void* q, const void* k_pool, const 
 }
 
 TSB_EXPORT long long tsb_paged_decode_static_capacity_floats() { return TSB_STATIC_DECODE_SCRATCH_FLOATS; }
+
+// Host-only: the fp32 elements of split-K scratch the plan for this problem asks for on the current device (0 when
+// one key split suffices). tsb_paged_decode_static refuses exactly when this exceeds the capacity above.
+TSB_EXPORT long long tsb_paged_decode_static_need_floats(int A, int H, int Hkv, int D, int max_len, int kv_int8) {
+  using namespace tsb;
+  if (A <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || D <= 0) return -2;
+  int gh = 1, splits = 1;
+  decode_plan(A, H, Hkv, max_len, kv_int8 != 0, &gh, &splits);
+  return splits > 1 ? static_cast<long long>(A) * H * splits * (D + 2) : 0;
+}

@@ -365,11 +365,11 @@ int launch_mma(const MmaDecParams& p, cudaStream_t s) {
   constexpr int merge = (kWarps * 8 * D + 2 * kWarps * 8) * 4;
   constexpr int smem = (ring > merge ? ring : merge) + 128;
   auto kern = paged_decode_mma_kernel<T, D, INT8>;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceFlag attr;
+  if (attr.unset()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr = true;
+    attr.set();
   }
   const int G = p.H / p.Hkv;
   dim3 grid(p.splits, p.Hkv * (G / p.gh), p.A);

@@ -461,21 +461,21 @@ TSB_EXPORT int tsb_flash_bwd(const void* dO, const void* q, const void* k, const
   p.status = device_status_word();
   dim3 grid((Sk + BT - 1) / BT, Hkv, B);
   if (D == 128) {
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceFlag attr;
+    if (attr.unset()) {
       e = cudaFuncSetAttribute(flash_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                BwdCfg<128>::kSmemBytes);
       if (e != cudaSuccess) return static_cast<int>(e);
-      attr = true;
+      attr.set();
     }
     flash_bwd_kernel<128><<<grid, kBwdThreads, BwdCfg<128>::kSmemBytes, s>>>(tq, tk, tv, tdo, p);
   } else {
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceFlag attr;
+    if (attr.unset()) {
       e = cudaFuncSetAttribute(flash_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                BwdCfg<64>::kSmemBytes);
       if (e != cudaSuccess) return static_cast<int>(e);
-      attr = true;
+      attr.set();
     }
     flash_bwd_kernel<64><<<grid, kBwdThreads, BwdCfg<64>::kSmemBytes, s>>>(tq, tk, tv, tdo, p);
   }

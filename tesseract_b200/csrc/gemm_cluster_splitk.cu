@@ -222,11 +222,11 @@ gemm_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
 template <int S>
 int launch_ck(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, cudaStream_t s) {
   auto kern = gemm_cluster_splitk_kernel<S>;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceFlag attr;
+  if (attr.unset()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr = true;
+    attr.set();
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   cudaLaunchConfig_t cfg{};

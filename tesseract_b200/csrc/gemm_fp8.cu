@@ -496,11 +496,11 @@ TSB_EXPORT int tsb_gemm_fp8_blockscaled(const void* A8, const void* B8, void* C,
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, A8, 1, M, K, static_cast<uint64_t>(K), BM, BKB, true)) return -3;
   if (!make_tmap_2d(&tb, B8, 1, N, K, static_cast<uint64_t>(K), BN, BKB, true)) return -3;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceFlag attr;
+  if (attr.unset()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr = true;
+    attr.set();
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = sm_count();
@@ -560,18 +560,18 @@ TSB_EXPORT int tsb_gemm_fp8_pertensor(const void* A8, const void* B8, void* C, c
   // the widest tile that still gives at least half the SMs a tile each
   const int bn = 2 * tiles_at(256) >= sms ? 256 : (2 * tiles_at(128) >= sms ? 128 : 64);
   if (!make_tmap_2d(&tb, B8, 1, N, K, static_cast<uint64_t>(K), bn, BKB, true)) return -3;
-  auto launch = [&](auto kernel, int smem_bytes, bool& attr) -> int {
-    if (!attr) {
+  auto launch = [&](auto kernel, int smem_bytes, PerDeviceFlag& attr) -> int {
+    if (attr.unset()) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
       if (e != cudaSuccess) return static_cast<int>(e);
-      attr = true;
+      attr.set();
     }
     int grid = tiles_at(bn) < sms ? tiles_at(bn) : sms;
     kernel<<<grid, kPThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(
         ta, tb, static_cast<__nv_bfloat16*>(C), scale_a, scale_b, M, N, K, ldc, device_status_word());
     return static_cast<int>(cudaGetLastError());
   };
-  static bool attr256 = false, attr128 = false, attr64 = false;
+  static PerDeviceFlag attr256, attr128, attr64;
   if (bn == 256) return launch(gemm_fp8_pt_kernel<256>, PtCfg<256>::kSmemBytes, attr256);
   if (bn == 128) return launch(gemm_fp8_pt_kernel<128>, PtCfg<128>::kSmemBytes, attr128);
   return launch(gemm_fp8_pt_kernel<64>, PtCfg<64>::kSmemBytes, attr64);

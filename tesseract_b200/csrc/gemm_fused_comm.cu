@@ -82,6 +82,11 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// Arrival counters and barrier epochs only ever grow, modulo 2^32: "has the counter reached the target" is decided
+// on the wrapped difference, which stays correct across the wrap as long as the two are less than 2^31 apart.
+__device__ __forceinline__ bool counter_behind(int value, int target) {
+  return static_cast<int>(static_cast<unsigned>(value) - static_cast<unsigned>(target)) < 0;
+}
 __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -187,7 +192,7 @@ __device__ void gather_keep_warps(const TpArgs& a, int K, int pw, int lane, int*
     for (int j = 0; j < a.nsub; ++j) {
       const long long t0 = clock64();
       bool ok = true;
-      while (ld_acquire_sys(&a.chunk_flags[src_rank * a.nsub + j]) < a.flag_target) {
+      while (counter_behind(ld_acquire_sys(&a.chunk_flags[src_rank * a.nsub + j]), a.flag_target)) {
         if (clock64() - t0 > kWaitCycleLimit) {
           ok = false;
           break;
@@ -295,7 +300,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const long long t0 = clock64();
           const bool first_wait = (ready_blk < 0);
           if (first_wait) trace_stamp(args, 3);
-          while (ld_acquire_sys(flag) < args.flag_target) {
+          while (counter_behind(ld_acquire_sys(flag), args.flag_target)) {
             if (cta_abort) { ok = false; break; }
             if (clock64() - t0 > kWaitCycleLimit) {
               cta_abort = 1;
@@ -498,7 +503,8 @@ reduce_slots_kernel(const __nv_bfloat16* __restrict__ staging, __nv_bfloat16* __
 struct BarrierArgs {
   int* pads[kMaxWorld];
 };
-__global__ void symm_barrier_kernel(BarrierArgs pads, int rank, int world, int epoch, int* status) {
+__global__ void symm_barrier_kernel(BarrierArgs pads, int rank, int world, int epoch, long long limit_cycles,
+                                    int* status) {
   const int r = threadIdx.x;
   if (r >= world) return;
   __threadfence_system();
@@ -508,8 +514,8 @@ __global__ void symm_barrier_kernel(BarrierArgs pads, int rank, int world, int e
   while (true) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-    if (v >= epoch) break;
-    if (clock64() - t0 > kWaitCycleLimit) {
+    if (!counter_behind(v, epoch)) break;
+    if (clock64() - t0 > limit_cycles) {
       if (status) atomicCAS(status, kStatusOk, kStatusFlagTimeout);
       break;
     }
@@ -526,11 +532,11 @@ template <int BN, bool B_MN, int MODE>
 int launch_tp(const CUtensorMap& ta, const CUtensorMap& tal, const CUtensorMap& tb, const CUtensorMap& tc, void* C, int M, int N, int K, long long ldc,
               const TpArgs& args, int grid, cudaStream_t s) {
   auto kern = gemm_tp_kernel<BN, B_MN, MODE>;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceFlag attr;
+  if (attr.unset()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr = true;
+    attr.set();
   }
   kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, s>>>(ta, tal, tb, tc, static_cast<__nv_bfloat16*>(C), M, N, K, ldc, args,
                                                    device_status_word());
@@ -559,13 +565,20 @@ TSB_EXPORT int tsb_ipc_open(const void* handle64, void** out) {
 TSB_EXPORT int tsb_ipc_close(void* p) { return static_cast<int>(cudaIpcCloseMemHandle(p)); }
 
 // pads[r] = address (in this process) of rank r's flag pad (world int32 slots each).
-TSB_EXPORT int tsb_symm_barrier(void* const* pads, int rank, int world, int epoch, void* stream) {
+// limit_cycles: how long (SM clock cycles) a rank waits for its peers before it gives up, records
+// kStatusFlagTimeout in the status word and returns; <= 0 selects the library default of about one second.
+TSB_EXPORT int tsb_symm_barrier_limit(void* const* pads, int rank, int world, int epoch, long long limit_cycles,
+                                      void* stream) {
   using namespace tsb;
   if (world < 1 || world > kMaxWorld) return -2;
   BarrierArgs a;
   for (int i = 0; i < kMaxWorld; ++i) a.pads[i] = i < world ? static_cast<int*>(pads[i]) : nullptr;
-  symm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a, rank, world, epoch, device_status_word());
+  symm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, rank, world, epoch, limit_cycles > 0 ? limit_cycles : kWaitCycleLimit, device_status_word());
   return static_cast<int>(cudaGetLastError());
+}
+TSB_EXPORT int tsb_symm_barrier(void* const* pads, int rank, int world, int epoch, void* stream) {
+  return tsb_symm_barrier_limit(pads, rank, world, epoch, 0, stream);
 }
 
 TSB_EXPORT int tsb_reduce_slots(const void* staging, void* out, int slots, long long n, void* stream) {
@@ -613,7 +626,8 @@ TSB_EXPORT int tsb_gemm_rs(const void* A, const void* B, void* const* peer_out, 
 //   x_local [rows_per_rank][K] bf16 contiguous: this rank's token shard (any local memory).
 //   peer_land[r]: rank r's landing buffer [M][K] bf16 (peer mapping; peer_land[rank] is local and feeds the GEMM).
 //   peer_flags[r]: rank r's int32 [world * nsub] arrival counters (peer mapping), zero at allocation;
-//   calls = number of calls so far on these counters, this one included (every call adds the grid size to each).
+//   calls = number of calls so far on these counters, this one included, modulo 2^32 (every call adds the grid
+//   size to each counter; counters and target wrap together).
 //   x_full: optional local [M][K] tensor that also receives the gathered rows (for the weight gradient); null to
 //   leave them in the landing buffer only. nsub: sub-chunks per shard, a divisor of rows_per_rank / 128.
 //   trace: null, or int64 [SM count][8] that receives globaltimer stamps of the phases of every CTA (diagnostics).
@@ -626,7 +640,7 @@ TSB_EXPORT int tsb_gemm_ag(const void* x_local, void* const* peer_land, void* co
   using namespace tsb;
   if (world < 1 || world > kMaxWorld || rows_per_rank % BM || M != rows_per_rank * world || N % 8 || N < 128 || K % 8)
     return -2;
-  if (nsub < 1 || (rows_per_rank / BM) % nsub || calls < 1) return -2;
+  if (nsub < 1 || (rows_per_rank / BM) % nsub) return -2;
   if (rank < 0 || rank >= world || (phase_mask & 3) == 0) return -2;
   if ((reinterpret_cast<uintptr_t>(x_full) & 15) || (reinterpret_cast<uintptr_t>(x_local) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15) || (ldb % 8) || (ldc % 8))
@@ -656,7 +670,7 @@ TSB_EXPORT int tsb_gemm_ag(const void* x_local, void* const* peer_land, void* co
   args.rank = rank;
   args.world = world;
   const int grid = sm_count();  // one resident CTA per SM: its GEMM warps wait for data that push warps deliver
-  args.flag_target = calls * grid;
+  args.flag_target = static_cast<int>(static_cast<unsigned>(calls) * static_cast<unsigned>(grid));  // modulo 2^32
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn == 256)
     return b_mn ? launch_tp<256, true, MODE_GATHER>(ta, tal, tb, tcm, C, M, N, K, ldc, args, grid, s)

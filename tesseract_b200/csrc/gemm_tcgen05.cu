@@ -379,11 +379,11 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int
                cudaStream_t stream, int split_k = 1, GroupArgs grp = GroupArgs{nullptr, 0, 0, 0, 0}) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT, ACCUM>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceFlag attr_set;
+  if (attr_set.unset()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    attr_set.set();
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * ((grp.offsets && grp.mode == 2) ? grp.groups : split_k);
   int grid = sm_count();

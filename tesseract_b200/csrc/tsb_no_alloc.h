@@ -45,6 +45,13 @@ int tsb_paged_decode_static(const void* q, const void* k_pool, const void* v_poo
 /* Capacity of the built-in array in fp32 elements. */
 long long tsb_paged_decode_static_capacity_floats(void);
 
+/* Host-only helper: fp32 elements of scratch that the split plan of this problem needs on the current device
+ * (0 when a single key split is used). The call above refuses exactly when this exceeds the capacity. With the
+ * present split plan (at most 8 CTAs' worth of splits per SM) the need stays below the capacity on a 148-SM GPU
+ * for every problem, so the refusal is a guard for other devices and future plans rather than a path callers
+ * meet today. */
+long long tsb_paged_decode_static_need_floats(int A, int H, int Hkv, int D, int max_len, int kv_int8);
+
 #ifdef __cplusplus
 }
 #endif

@@ -38,11 +38,18 @@ _native.register_signatures({
     "tsb_ipc_open": [P, PP],
     "tsb_ipc_close": [P],
     "tsb_symm_barrier": [PP, I, I, I, P],
+    "tsb_symm_barrier_limit": [PP, I, I, I, L, P],
     "tsb_reduce_slots": [P, P, I, L, P],
     "tsb_allreduce_oneshot": [PP, PP, P, P, L, I, I, P],
     "tsb_gemm_rs": [P, P, PP, I, I, I, L, L, I, I, I, I, P],
     "tsb_gemm_ag": [P, PP, PP, P, P, P, I, I, I, I, I, I, L, L, I, I, I, I, P, P],
 })
+
+
+def _wrap_i32(v: int) -> int:
+    """A monotonically growing counter as the int32 the kernels compare modulo 2^32."""
+    v &= 0xFFFFFFFF
+    return v - (1 << 32) if v >= (1 << 31) else v
 
 
 class _RawCuda:
@@ -119,8 +126,8 @@ class FusedTP:
 
     def barrier(self) -> None:
         self.epoch += 1
-        check(lib().tsb_symm_barrier(self.pads.ptr_array, self.rank, self.world, self.epoch, self._stream()),
-              "tsb_symm_barrier")
+        check(lib().tsb_symm_barrier(self.pads.ptr_array, self.rank, self.world, _wrap_i32(self.epoch),
+                                     self._stream()), "tsb_symm_barrier")
         self.calls["barrier"] += 1
 
     def _ensure(self, which: str, half_bytes: int) -> SymmetricMemory:
@@ -205,7 +212,7 @@ class FusedTP:
         x_full = torch.empty((M, K), device=x_local.device, dtype=torch.bfloat16) if in_kernel else None
         y = torch.empty((M, N), device=x_local.device, dtype=torch.bfloat16)
         check(lib().tsb_gemm_ag(x_local.data_ptr(), land.ptr_array, self._flagmem.offset_ptr_array(4 * off),
-                                x_full.data_ptr() if in_kernel else None, w.data_ptr(), y.data_ptr(), calls,
+                                x_full.data_ptr() if in_kernel else None, w.data_ptr(), y.data_ptr(), _wrap_i32(calls),
                                 nsub, phase_mask, M, N, K, w.stride(0), y.stride(0), int(b_mn), rpr, self.rank, self.world,
                                 self.trace.data_ptr() if self.trace is not None else None, self._stream()),
               "tsb_gemm_ag")
@@ -214,15 +221,18 @@ class FusedTP:
             landed = land.local[:M * K * 2].view(torch.bfloat16).view(M, K)
             if not keep:
                 return y, landed
-            x_full = torch.empty((M, K), device=x_local.device, dtype=torch.bfloat16)
             main = torch.cuda.current_stream(self.device)
             if self._keep_stream is None:
                 self._keep_stream = torch.cuda.Stream(self.device)
             self._keep_stream.wait_stream(main)
             with torch.cuda.stream(self._keep_stream):
+                # allocated on the stream that writes it: if the caller drops the tensor early (a forward pass
+                # under no_grad), the caching allocator reuses the block only after this copy in stream order ...
+                x_full = torch.empty((M, K), device=x_local.device, dtype=torch.bfloat16)
                 x_full.copy_(landed, non_blocking=True)
                 self._keep_event = torch.cuda.Event()
                 self._keep_event.record(self._keep_stream)
+            x_full.record_stream(main)      # ... and its readers on the main stream are known to the allocator too
         return y, x_full
 
     def close(self) -> None:

@@ -98,7 +98,11 @@ class ColumnParallelSPFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x_local, w, wgrad_buf, tp: TPContext):
-        y, x_full = ag_matmul(tp, x_local, w, sync_keep=False)
+        need_bwd = any(ctx.needs_input_grad[:2])
+        # without a backward pass (evaluation under no_grad) the gathered rows are not copied out at all
+        y, x_full = ag_matmul(tp, x_local, w, keep=need_bwd, sync_keep=False)
+        if not need_bwd:
+            return y
         ctx.save_for_backward(x_full, w)   # the gathered activations are kept for the weight gradient
         ctx.tp, ctx.wgrad_buf = tp, wgrad_buf
         return y

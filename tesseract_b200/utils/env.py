@@ -32,6 +32,8 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_AG_NSUB", "0", "all-gather -> GEMM: sub-chunks signalled per rank (0 = chosen by size; at most 2)"),
     EnvVar("TESSERACT_RMS_PREFETCH", "1", "RMSNorm forward: 1 (next row prefetched across the reduction) | 0 (plain kernel, for A/B runs)"),
     EnvVar("TESSERACT_RMS_THREADS", "0", "RMSNorm forward threads per row: 0 (256) | 128 | 256, for A/B runs"),
+    EnvVar("TESSERACT_REF_TIME_BUDGET", "780", "bench.py --impl reference: seconds the reference arm may take in total"),
+    EnvVar("TESSERACT_REFERENCE_DIR", "/root/reference", "baseline/build_reference.py: source tree of the reference to build"),
     EnvVar("TESSERACT_SWIGLU", "2", "SwiGLU kernels: 2 (row-wise, two vector pairs per thread) | 0 (flat kernel, for A/B runs)"),
 ]}
 

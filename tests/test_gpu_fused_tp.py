@@ -236,11 +236,19 @@ def test_fused_tp_matches_nccl_on_real_peers():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = [q.get(timeout=300) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=60)
+    try:
+        for p in procs:
+            p.start()
+        results = [q.get(timeout=300) for _ in range(world)]
+        for p in procs:
+            p.join(timeout=60)
+    finally:
+        # a rank that raised leaves its peers inside a collective: never leave children holding GPUs behind
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=30)
     bad = [r for r in results if r[1] is not None]
     assert not bad, bad[0][1]
     for _, _, (errs, status, losses) in results:
@@ -249,3 +257,39 @@ def test_fused_tp_matches_nccl_on_real_peers():
         assert losses["fused"][2] is True and losses["nccl"][2] is False
         assert abs(losses["fused"][0] - losses["nccl"][0]) < 2e-2
         assert losses["fused"][1] < losses["fused"][0]
+
+
+def test_barrier_wait_runs_out_and_reports_through_the_status_word():
+    """A rank whose peer never signals: the barrier kernel gives up after its (here: short) limit, records the
+    flag-timeout code, returns, and the context stays usable -- nothing traps or hangs. The "peer" is a second
+    flag pad on the same GPU that nothing ever writes."""
+    import ctypes
+
+    from tesseract_b200 import _native
+    from tesseract_b200.parallel import fused_tp  # noqa: F401  (registers the signatures)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    _native.read_status(stream)                                 # clear
+    pads = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(2)]
+    arr = (ctypes.c_void_p * 2)(*[p.data_ptr() for p in pads])
+    limit = 100_000_000                                         # about 50 ms of SM clock
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    _native.check(_native.lib().tsb_symm_barrier_limit(arr, 0, 2, 1, limit, stream), "tsb_symm_barrier_limit")
+    t1.record()
+    torch.cuda.synchronize()
+    assert t0.elapsed_time(t1) < 2000.0
+    assert int(pads[0][0]) == 1 and int(pads[1][0]) == 1        # this rank did announce itself to both pads
+    assert _native.read_status(stream) == 2                     # kStatusFlagTimeout
+    assert _native.read_status(stream) == 0                     # reading clears it
+    # the next launches work: the same barrier with the peer's slot already signalled passes at once
+    pads[0][1] = 2
+    _native.check(_native.lib().tsb_symm_barrier_limit(arr, 0, 2, 2, limit, stream), "tsb_symm_barrier_limit")
+    x = torch.randn(256, 256, device=dev, dtype=torch.bfloat16)
+    from tesseract_b200.ops.gemm import gemm_bf16
+    y = gemm_bf16(x, x)
+    torch.cuda.synchronize()
+    assert _native.read_status(stream) == 0
+    assert torch.isfinite(y.float()).all()

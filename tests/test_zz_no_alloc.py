@@ -58,12 +58,17 @@ def test_static_scratch_decode_matches_regular_entry_point_twice():
         out = torch.full_like(q, float("nan"))
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated(dev)
+        # the driver's view as well (torch's counter would miss a raw cudaMalloc inside the library); the first
+        # call may still page in the kernels, so the strict comparison starts with the second one
+        free_before = torch.cuda.mem_get_info(dev)[0]
         rc = fn(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), None, None, tables.data_ptr(), lens_t.data_ptr(),
                 out.data_ptr(), A, H, Hkv, D, bs, k_pool.shape[0], tables.shape[1], 1.0 / D ** 0.5,
                 tables.shape[1] * bs, 1, stream)
         assert rc == 0, rc
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated(dev) == before
+        if call > 0:
+            assert torch.cuda.mem_get_info(dev)[0] >= free_before
         assert torch.isfinite(out.float()).all()
         # same kernels, same split count, same inputs: the two entry points agree to the last bit
         assert torch.equal(out, ref)
@@ -93,3 +98,27 @@ def test_static_scratch_decode_large_batch_fits_or_is_refused_cleanly():
     else:
         ref = ops.paged_decode_attention(q, k_pool, v_pool, tables, lens_t, max_len_hint=tables.shape[1] * bs)
         assert torch.equal(out, ref)
+
+
+def test_static_scratch_need_is_below_capacity_and_refusal_rule_is_the_documented_one():
+    """The host-only planning hook: what a problem needs, against what the built-in array holds. On a B200 the
+    split plan never asks for more than the array has (so the refusal is a guard, not a path callers meet); a
+    single key split needs nothing."""
+    from tesseract_b200 import _native
+    torch.cuda.set_device(0)
+    lib = ctypes.CDLL(str(_native.cuda_lib_path()))
+    need = lib.tsb_paged_decode_static_need_floats
+    need.argtypes, need.restype = [ctypes.c_int] * 6, ctypes.c_longlong
+    cap = lib.tsb_paged_decode_static_capacity_floats
+    cap.restype = ctypes.c_longlong
+    assert need(0, 32, 8, 128, 1024, 0) == -2
+    worst = 0
+    for A in (1, 4, 32, 96, 256, 1024):
+        for H, Hkv in ((32, 8), (8, 2), (64, 8)):
+            for max_len in (16, 512, 4096, 131072):
+                for i8 in (0, 1):
+                    n = need(A, H, Hkv, 128, max_len, i8)
+                    assert n >= 0
+                    worst = max(worst, n)
+    assert need(1024, 32, 8, 128, 16, 0) == 0                  # short contexts: one split, no scratch
+    assert 0 < worst <= cap()
