@@ -31,7 +31,11 @@ bool gemv_vnni_supported() {
 float quantize_row_int8(const float* x, int64_t K, int8_t* xq) {
   float amax = 0.f;
   for (int64_t k = 0; k < K; ++k) amax = std::max(amax, std::fabs(x[k]));
-  const float scale = amax > 0.f ? amax / 127.f : 1.f;
+  if (amax <= 0.f) {   // all-zero vector: zeros with scale 0 (src/ops/cpu/GemvVnni.cpp:126-133), so y = 0 exactly
+    for (int64_t k = 0; k < K; ++k) xq[k] = 0;
+    return 0.f;
+  }
+  const float scale = amax / 127.f;
   const float inv = 1.f / scale;
   for (int64_t k = 0; k < K; ++k) {
     const float r = std::nearbyint(x[k] * inv);

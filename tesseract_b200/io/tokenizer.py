@@ -30,6 +30,17 @@ class Tokenizer:
 
     bos_id: int = -1
     eos_id: int = -1
+    unk_id: int = -1
+
+    # accessor spelling of the reference's Python module (python/_core.cpp:334-336)
+    def bos_token_id(self) -> int:
+        return self.bos_id
+
+    def eos_token_id(self) -> int:
+        return self.eos_id
+
+    def unk_token_id(self) -> int:
+        return self.unk_id
 
 
 @dataclass
@@ -151,6 +162,7 @@ class BpeTokenizer(Tokenizer):
         self._added_ids = set(self.added.values())
         self.bos_id = next((self.added[t] for t in ("<|begin_of_text|>", "<s>") if t in self.added), -1)
         self.eos_id = next((self.added[t] for t in ("<|end_of_text|>", "</s>", "<|eot_id|>") if t in self.added), -1)
+        self.unk_id = next((self.added[t] for t in ("<unk>", "<|unk|>") if t in self.added), -1)
         self._cache: Dict[bytes, List[int]] = {}
         self._core = None           # native merge loop (csrc/host/bpe_io.cpp), built on first use
         self._core_tried = False
@@ -257,6 +269,8 @@ class BpeTokenizer(Tokenizer):
             start = i
         if start < n:
             ids.extend(self._encode_plain(text[start:]))
+        if add_special_tokens and self.eos_id >= 0:      # BOS ... EOS, as src/io/BpeTokenizer.cpp:472,513
+            ids.append(self.eos_id)
         return ids
 
     def decode(self, ids, skip_special_tokens: bool = True) -> str:

@@ -36,14 +36,16 @@ def gemv_vnni_supported() -> bool:
 
 
 def quantize_row_int8(x: torch.Tensor) -> Tuple[torch.Tensor, float]:
-    """x [K] fp32 -> (int8 [K], scale): scale = absmax / 127 (1 for a zero vector), round to nearest even, clip +-127."""
+    """x [K] fp32 -> (int8 [K], scale): scale = absmax / 127 (0 for a zero vector), round to nearest even, clip +-127."""
     x = x.detach().reshape(-1).float().cpu()
     h = _host()
     if h is not None:
         q, scale = h.quantize_row_int8(x.numpy())
         return torch.from_numpy(np.asarray(q)), float(scale)
     amax = float(x.abs().max()) if x.numel() else 0.0
-    scale = float(np.float32(amax) / np.float32(127.0)) if amax > 0 else 1.0
+    if amax <= 0:
+        return torch.zeros_like(x, dtype=torch.int8), 0.0
+    scale = float(np.float32(amax) / np.float32(127.0))
     inv = np.float32(1.0) / np.float32(scale)
     q = torch.clamp(torch.round(x * float(inv)), -127, 127).to(torch.int8)
     return q, scale

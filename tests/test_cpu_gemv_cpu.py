@@ -61,6 +61,14 @@ def test_w8a8_approximates_the_fp32_product_and_zero_vector():
     ref = Wf.double() @ x.double()
     assert float(((y.double() - ref) ** 2).sum().sqrt() / (ref ** 2).sum().sqrt()) < 0.03
     zq, zs = cpu_gemv.quantize_row_int8(torch.zeros(64))
-    assert zs == 1.0 and int(zq.abs().sum()) == 0
+    assert zs == 0.0 and int(zq.abs().sum()) == 0
     with pytest.raises(ValueError):
         cpu_gemv.gemv_w8a8(W, wscale[:5], None, xq, xscale)
+
+
+def test_zero_vector_quantises_to_zeros_with_scale_zero(monkeypatch):
+    """The reference returns scale 0 for an all-zero activation (src/ops/cpu/GemvVnni.cpp:126-133)."""
+    for host in ("native", "python"):
+        monkeypatch.setenv("TESSERACT_HOST", host)
+        q, scale = cpu_gemv.quantize_row_int8(torch.zeros(96))
+        assert scale == 0.0 and int(q.abs().max()) == 0 and q.dtype == torch.int8
