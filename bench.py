@@ -189,10 +189,27 @@ def run_reference(args):
             result = out
             break
         attempts.append({"dtype": dtype, "error": err})
+    reduced = None
+    if result is None and args.layers == 32:
+        # Context only (never the headline): the same step at the largest depth the reference can hold in its one
+        # trainable dtype, so that its per-layer cost on this GPU is on record next to the failure.
+        left = train_budget - (time.time() - t_start)
+        for layers in (8, 4):
+            if left < 45:
+                break
+            cmd = [train_bin, "--steps", str(min(args.steps, 5)), "--warmup", "2", "--batch", str(args.global_batch),
+                   "--seq", str(args.seq_len), "--micro", "1", "--dtype", "f32", "--e2e", "0",
+                   "--time-limit", f"{left * 0.8:.0f}"] + shape[:-1] + [str(layers)]
+            out, err = _run_harness(cmd, timeout=left)
+            if out is not None:
+                reduced = {"layers": layers, "dtype": "fp32", "ms_per_step": out["ms_per_step"], "steps": out["steps"],
+                           "tokens_per_s": args.global_batch * args.seq_len / (out["ms_per_step"] / 1e3),
+                           "device_mem_used_gb": out.get("device_mem_used_gb"),
+                           "note": "NOT the named model: fewer layers, same layer shape, batch and sequence length"}
+                break
+            reduced = {"layers": layers, "error": err}
+            left = train_budget - (time.time() - t_start)
     clocks = sampler.stop()
-    if result is None:
-        return unavailable("the reference's own training step failed at this shape: " +
-                           "; ".join(f"[{a['dtype']}] {a['error']}" for a in attempts), attempts=attempts)
 
     serve = None
     want_serve = args.serve == 1 or (args.serve == -1 and args.layers == 32)
@@ -205,6 +222,11 @@ def run_reference(args):
             serve.update({"tp": 1, "weights": "bf16", "cuda_graph": False,
                           "prefill_tok_s": None, "note": "prefill and decode share the reference's step(); "
                           "decode_tok_s is taken over the steps that admitted no request"})
+    if result is None:
+        return unavailable("the reference's own training step failed at this shape: " +
+                           "; ".join(f"[{a['dtype']}] {a['error']}" for a in attempts), attempts=attempts,
+                           context={"train_reduced_depth": reduced, "serve": serve, "clocks": clocks,
+                                    "wall_s": round(time.time() - t_start, 1)})
     B, S, steps = args.global_batch, args.seq_len, int(result["steps"])
     ms = float(result["ms_per_step"])
     e2e = None
@@ -324,12 +346,33 @@ def main():
         e2e = {"value": tok_e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4 * world}
 
+    import gc
+    reduced = None
+    if world == 1 and args.layers == 32 and not args.no_e2e:
+        # Context for the reference arm (never the headline): the reference cannot hold the 32-layer model in its one
+        # trainable dtype on one GPU, so both arms also time the same step on an 8-layer model of the same layer
+        # shape, batch and sequence length.
+        del trainer
+        gc.collect()
+        torch.cuda.empty_cache()
+        cfg8 = LlamaConfig.llama_3_8b(dtype=torch.bfloat16, max_position_embeddings=args.seq_len)
+        cfg8.num_hidden_layers = 8
+        trainer8, _ = build_parallel_trainer(cfg8, tcfg, world, rank, device, args.parallelism, seed=1234)
+        for i in range(2):
+            trainer8.step_on_device(dev_batches[i % 2])
+        n8 = min(args.steps, 5)
+        ms8 = timed(lambda i: trainer8.step_on_device(dev_batches[i % 2]), n8)
+        reduced = {"layers": 8, "dtype": "bf16", "ms_per_step": ms8 / n8, "steps": n8,
+                   "tokens_per_s": B * S * n8 / (ms8 / 1e3),
+                   "note": "NOT the named model: fewer layers, same layer shape, batch and sequence length"}
+        del trainer8
+        trainer = None
+
     serve = None
     want_serve = args.serve == 1 or (args.serve == -1 and args.layers == 32)
     if want_serve:
         # free the training state first: the serving model and its KV pool need the memory
         del trainer, dev_batches
-        import gc
         gc.collect()
         torch.cuda.empty_cache()
         try:
@@ -356,6 +399,7 @@ def main():
                        "attention": os.environ.get("TESSERACT_ATTN", "tcgen05"),
                        "fused_comm": plan.get("fused_comm", False)},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val, "serve": serve,
+            "train_reduced_depth": reduced,
             "kernel_status": status,
         }
         print(json.dumps(out))
