@@ -102,7 +102,9 @@ def parse_args():
     ap.add_argument("--serve-requests", type=int, default=256)
     ap.add_argument("--layers", type=int, default=32, help="(debug only) fewer layers; invalidates the metric")
     ap.add_argument("--master-weights", action="store_true")
-    ap.add_argument("--parallelism", default="auto", help="auto | dp | tp  (auto: tensor+sequence parallel over all ranks)")
+    ap.add_argument("--parallelism", default="auto",
+                    help="auto | dp | tp | tpK (tensor parallel over K ranks, data parallel over the rest) | a comma list: "
+                         "every mesh listed is measured and `value` is the fastest")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ref-time-budget", type=float, default=float(os.environ.get("TESSERACT_REF_TIME_BUDGET", 780)),
                     help="(--impl reference) seconds the whole reference arm may take; the timed step count shrinks to fit")
@@ -194,7 +196,8 @@ def run_reference(args):
         # Context only (never the headline): the same step at the largest depth the reference can hold in its one
         # trainable dtype, so that its per-layer cost on this GPU is on record next to the failure.
         left = train_budget - (time.time() - t_start)
-        for layers in (8, 4):
+        tried = []
+        for layers in (8, 4, 2, 1):
             if left < 45:
                 break
             cmd = [train_bin, "--steps", str(min(args.steps, 5)), "--warmup", "2", "--batch", str(args.global_batch),
@@ -205,9 +208,11 @@ def run_reference(args):
                 reduced = {"layers": layers, "dtype": "fp32", "ms_per_step": out["ms_per_step"], "steps": out["steps"],
                            "tokens_per_s": args.global_batch * args.seq_len / (out["ms_per_step"] / 1e3),
                            "device_mem_used_gb": out.get("device_mem_used_gb"),
+                           "failed_deeper": tried,
                            "note": "NOT the named model: fewer layers, same layer shape, batch and sequence length"}
                 break
-            reduced = {"layers": layers, "error": err}
+            tried.append({"layers": layers, "error": err})
+            reduced = {"failed": tried}
             left = train_budget - (time.time() - t_start)
     clocks = sampler.stop()
 
@@ -251,17 +256,43 @@ def run_reference(args):
     return 0
 
 
+def _mesh_list(spec: str, world: int):
+    """--parallelism -> [(mode, tp_size, label)]. ``auto`` measures the named mesh (tensor + sequence parallel over all
+    ranks) and, from 4 GPUs on, the hybrid with tensor-parallel pairs and data parallelism over the rest."""
+    if world == 1:
+        return [("auto", 0, "single")]
+    if spec == "auto":
+        spec = {2: "tp2", 4: "tp4,tp2", 8: "tp8,tp2"}.get(world, f"tp{world}")
+    out = []
+    for item in spec.split(","):
+        item = item.strip().lower()
+        if item == "dp":
+            out.append(("dp", 0, f"dp{world}"))
+        elif item == "tp":
+            out.append(("tp", world, f"tp{world}"))
+        elif item.startswith("tp") and item[2:].split("x")[0].isdigit():
+            k = int(item[2:].split("x")[0])
+            if k < 1 or world % k:
+                raise SystemExit(f"--parallelism {item}: {k} does not divide {world} ranks")
+            out.append(("tp" if k > 1 else "dp", k, item))
+        else:
+            raise SystemExit(f"--parallelism: cannot read {item!r} (auto | dp | tp | tpK | a comma list of those)")
+    return out
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
 
+    import gc
+
     import torch
     import torch.distributed as dist
 
     from tesseract_b200 import _native
-    from tesseract_b200.models import LlamaConfig, LlamaModel
-    from tesseract_b200.training import TrainConfig, Trainer
+    from tesseract_b200.models import LlamaConfig
+    from tesseract_b200.training import TrainConfig
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -277,29 +308,7 @@ def main():
 
     from tesseract_b200.parallel import build_parallel_trainer  # noqa: WPS433 (after process group init)
 
-    cfg = LlamaConfig.llama_3_8b(dtype=torch.bfloat16, max_position_embeddings=args.seq_len)
-    cfg.num_hidden_layers = args.layers
-    if args.micro_batch <= 0:
-        # two sequences per pass on a single GPU (42 GB of activations next to 96 GB of model state; measured 5.6 %
-        # faster than one); with the model sharded over >= 2 ranks there is room for larger passes, which means
-        # larger GEMMs and fewer launches
-        tp_like = world > 1 and args.parallelism in ("auto", "tp")
-        if tp_like:
-            args.micro_batch = min(args.global_batch, 4 if world < 8 else 8)
-        else:
-            args.micro_batch = 2 if (world == 1 and args.global_batch % 2 == 0) else 1
-    tcfg = TrainConfig(lr=1e-4, micro_batch=args.micro_batch, grad_dtype=torch.bfloat16,
-                       master_weights=args.master_weights)
-    trainer, plan = build_parallel_trainer(cfg, tcfg, world, rank, device, args.parallelism, seed=1234)
-
     B, S = args.global_batch, args.seq_len
-    if B % plan["dp"]:
-        raise SystemExit(f"global batch {B} is not divisible by the data-parallel degree {plan['dp']}")
-    local_b = B // plan["dp"]
-    gen = torch.Generator().manual_seed(1000 + plan["dp_rank"])
-    host_batches = [torch.randint(0, cfg.vocab_size, (local_b, S + 1), generator=gen, dtype=torch.int64).pin_memory()
-                    for _ in range(2)]
-    dev_batches = [b.to(device) for b in host_batches]
 
     def barrier():
         if world > 1:
@@ -319,64 +328,108 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    last_loss = [0.0]
+    def teardown(trainer, plan):
+        """Frees a trainer and the peer-mapped memory behind it (collective)."""
+        barrier()
+        res = list(plan.get("resources", []))
+        plan["resources"] = []
+        if getattr(trainer, "grad_reducer", None) is not None:
+            trainer.grad_reducer.symm = None
+        for r in res:
+            r.close()
+        gc.collect()
+        torch.cuda.empty_cache()
+        barrier()
 
-    def dev_step(i):
-        last_loss[0] = trainer.step_on_device(dev_batches[i % 2])
+    def measure(mode, tp_size, layers, steps, warmup, want_e2e):
+        """Builds the trainer of one mesh, times ``steps`` steps from a device-resident batch (and, if asked, through
+        ``Trainer.train_step`` from pinned host memory), tears it down. Returns a dict."""
+        cfg = LlamaConfig.llama_3_8b(dtype=torch.bfloat16, max_position_embeddings=S)
+        cfg.num_hidden_layers = layers
+        dp = 1 if world == 1 else (world if mode == "dp" else world // max(tp_size, 1))
+        if B % dp:
+            raise SystemExit(f"global batch {B} is not divisible by the data-parallel degree {dp}")
+        local_b = B // dp
+        mb = args.micro_batch
+        if mb <= 0:
+            # two sequences per pass on a single GPU (42 GB of activations next to 96 GB of model state; measured
+            # 5.6 % faster than one); with the model sharded over >= 2 ranks there is room for larger passes, which
+            # means larger GEMMs and fewer launches
+            if world > 1 and mode != "dp":
+                mb = min(local_b, 4 if tp_size < 8 else 8)
+            else:
+                mb = 2 if (world == 1 and local_b % 2 == 0) else 1
+        mb = min(mb, local_b)
+        tcfg = TrainConfig(lr=1e-4, micro_batch=mb, grad_dtype=torch.bfloat16, master_weights=args.master_weights)
+        trainer, plan = build_parallel_trainer(cfg, tcfg, world, rank, device, mode, seed=1234, tp_size=tp_size)
+        gen = torch.Generator().manual_seed(1000 + plan["dp_rank"])
+        host_batches = [torch.randint(0, cfg.vocab_size, (local_b, S + 1), generator=gen, dtype=torch.int64).pin_memory()
+                        for _ in range(2)]
+        dev_batches = [b.to(device) for b in host_batches]
+        last = [0.0]
 
-    def e2e_step(i):
-        last_loss[0] = trainer.train_step(host_batches[i % 2])
+        def dev_step(i):
+            last[0] = trainer.step_on_device(dev_batches[i % 2])
 
-    for i in range(args.warmup):
-        dev_step(i)
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    launches0 = _native.launch_count()
-    ms_dev = timed(dev_step, args.steps)
-    launches = _native.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
-    status = _native.read_status(torch.cuda.current_stream().cuda_stream)
+        def e2e_step(i):
+            last[0] = trainer.train_step(host_batches[i % 2])
 
-    e2e = None
-    if not args.no_e2e:
-        e2e_step(0)
-        ms_e2e = timed(e2e_step, args.steps)
-        tok_e2e = B * S * args.steps / (ms_e2e / 1e3)
-        e2e = {"value": tok_e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-               "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4 * world}
+        for i in range(warmup):
+            dev_step(i)
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        launches0 = _native.launch_count()
+        ms_dev = timed(dev_step, steps)
+        launches = _native.launch_count() - launches0
+        clocks = sampler.stop() if rank == 0 else None
+        out = {"name": plan["name"], "ms_per_step": ms_dev / steps, "tokens_per_s": B * S * steps / (ms_dev / 1e3),
+               "micro_batch": mb, "fused_comm": plan.get("fused_comm", False), "dp_comm": plan.get("dp_comm"),
+               "gpu_launches": launches, "clocks": clocks, "e2e": None,
+               "status": _native.read_status(torch.cuda.current_stream().cuda_stream)}
+        red = getattr(trainer, "grad_reducer", None)
+        if red is not None:
+            out["dp_overlapped_bytes_per_step"] = int(red.overlapped_bytes)
+        if want_e2e:
+            e2e_step(0)
+            ms_e2e = timed(e2e_step, steps)
+            out["e2e"] = {"value": B * S * steps / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / steps,
+                          "h2d_bytes_per_step": B * (S + 1) * 8, "d2h_bytes_per_step": 4 * world}
+        out["final_loss"] = float(last[0])
+        teardown(trainer, plan)
+        del trainer, dev_batches
+        gc.collect()
+        torch.cuda.empty_cache()
+        return out
 
-    import gc
+    meshes = _mesh_list(args.parallelism, world)
+    results = []
+    for k, (mode, tp_size, _label) in enumerate(meshes):
+        # the end-to-end region runs with the first mesh measured and again with the winner if that is another one
+        results.append(measure(mode, tp_size, args.layers, args.steps, args.warmup,
+                               want_e2e=(not args.no_e2e and len(meshes) == 1)))
+    best = min(range(len(results)), key=lambda k: results[k]["ms_per_step"])
+    if len(meshes) > 1 and not args.no_e2e:
+        mode, tp_size, _ = meshes[best]
+        again = measure(mode, tp_size, args.layers, args.steps, args.warmup, want_e2e=True)
+        results[best]["e2e"] = again["e2e"]
+        results[best]["repeat_ms_per_step"] = again["ms_per_step"]
+    win = results[best]
+
     reduced = None
     if world == 1 and args.layers == 32 and not args.no_e2e:
         # Context for the reference arm (never the headline): the reference cannot hold the 32-layer model in its one
         # trainable dtype on one GPU, so both arms also time the same step on an 8-layer model of the same layer
         # shape, batch and sequence length.
-        del trainer
-        gc.collect()
-        torch.cuda.empty_cache()
-        cfg8 = LlamaConfig.llama_3_8b(dtype=torch.bfloat16, max_position_embeddings=args.seq_len)
-        cfg8.num_hidden_layers = 8
-        trainer8, _ = build_parallel_trainer(cfg8, tcfg, world, rank, device, args.parallelism, seed=1234)
-        for i in range(2):
-            trainer8.step_on_device(dev_batches[i % 2])
-        n8 = min(args.steps, 5)
-        ms8 = timed(lambda i: trainer8.step_on_device(dev_batches[i % 2]), n8)
-        reduced = {"layers": 8, "dtype": "bf16", "ms_per_step": ms8 / n8, "steps": n8,
-                   "tokens_per_s": B * S * n8 / (ms8 / 1e3),
+        r8 = measure("auto", 0, 8, min(args.steps, 5), 2, want_e2e=False)
+        reduced = {"layers": 8, "dtype": "bf16", "ms_per_step": r8["ms_per_step"], "tokens_per_s": r8["tokens_per_s"],
                    "note": "NOT the named model: fewer layers, same layer shape, batch and sequence length"}
-        del trainer8
-        trainer = None
 
     serve = None
     want_serve = args.serve == 1 or (args.serve == -1 and args.layers == 32)
     if want_serve:
-        # free the training state first: the serving model and its KV pool need the memory
-        del trainer, dev_batches
-        gc.collect()
-        torch.cuda.empty_cache()
         try:
-            sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "benchmarks"))
+            sys.path.insert(0, os.path.join(REPO_ROOT, "benchmarks"))
             from bench_serving import run_serving_bench
             serve = run_serving_bench(requests=args.serve_requests, layers=args.layers, device=device,
                                       tp_group=dist.group.WORLD if world > 1 else None, rank=rank, world=world)
@@ -384,23 +437,26 @@ def main():
             serve = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     if rank == 0:
-        tok_s = B * S * args.steps / (ms_dev / 1e3)
-        loss_val = float(last_loss[0]) if not isinstance(last_loss[0], float) else last_loss[0]
         out = {
             "metric": METRIC,
-            "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "strong",
+            "value": win["tokens_per_s"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": win["ms_per_step"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": DATA,
             "config": {"model": "llama-3-8b-shape" + ("" if args.layers == 32 else f"-DEBUG-{args.layers}-layers"),
-                       "global_batch": B, "seq_len": S, "parallelism": plan["name"], "micro_batch": args.micro_batch,
+                       "global_batch": B, "seq_len": S, "parallelism": win["name"], "micro_batch": win["micro_batch"],
                        "optimizer": "Adam fp32 m/v" + (" + fp32 master" if args.master_weights else ""),
                        "grad_dtype": "bf16", "l2_hygiene": "inputs_larger_than_l2 (16 GB of weights streamed per pass)",
                        "gemm": os.environ.get("TESSERACT_GEMM", "tcgen05"),
                        "attention": os.environ.get("TESSERACT_ATTN", "tcgen05"),
-                       "fused_comm": plan.get("fused_comm", False)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val, "serve": serve,
-            "train_reduced_depth": reduced,
-            "kernel_status": status,
+                       "fused_comm": win["fused_comm"], "dp_comm": win["dp_comm"]},
+            "clocks": win["clocks"], "e2e": win["e2e"], "gpu_launches": win["gpu_launches"],
+            "final_loss": win["final_loss"], "serve": serve, "train_reduced_depth": reduced,
+            "kernel_status": max(r["status"] for r in results),
+            # every mesh measured in this run with the same K and W; `value` is the fastest of them
+            "meshes": {r["name"]: {k: r[k] for k in ("ms_per_step", "tokens_per_s", "micro_batch", "fused_comm", "dp_comm",
+                                                     "final_loss") if k in r} |
+                       ({"dp_overlapped_bytes_per_step": r["dp_overlapped_bytes_per_step"]}
+                        if "dp_overlapped_bytes_per_step" in r else {}) for r in results},
         }
         print(json.dumps(out))
     if world > 1:

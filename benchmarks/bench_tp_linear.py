@@ -49,8 +49,7 @@ def main():
     peak = a.peak_tflops
     if peak <= 0:
         try:
-            peak = json.load(open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
-                                               "MEASURED_PEAKS.json")))["bf16_tflops"]
+            peak = json.load(open(os.environ["TESSERACT_PEAKS_FILE"]))["bf16_tflops"]
         except Exception:
             peak = 1590.0
     link_gbs = 770.0

@@ -8,7 +8,7 @@
 
 Every case warms up, then times ``--iters`` launches with CUDA events (an L2 flush between launches) and prints
 the achieved rate next to the measured peak it is bounded by (copy bandwidth / cuBLAS bf16 rate of this machine,
-read from MEASURED_PEAKS.json at the repository root when present). The fused tensor-parallel kernels run here as
+given with --hbm-gbs / --bf16-tflops or a JSON file named by --peaks-file / $TESSERACT_PEAKS_FILE). The fused tensor-parallel kernels run here as
 an emulation of two ranks on one GPU: all buffers local, the gather kernel split into its push half and its
 multiply half so that no launch waits for a later one.
 Shapes follow the reference's microbenchmarks where it has one (benchmarks/bench_cuda_matmul.cpp,
@@ -28,12 +28,24 @@ sys.path.insert(0, ROOT)
 import torch  # noqa: E402
 
 
+_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "default"}
+
+
+def set_peaks(hbm_gbs=None, bf16_tflops=None, peaks_file=None):
+    """The denominators of the reported fractions: --hbm-gbs / --bf16-tflops, or a JSON file with the keys
+    ``hbm_gbs`` and ``bf16_tflops`` (--peaks-file or $TESSERACT_PEAKS_FILE), else 6650 GB/s and 1590 TFLOP/s."""
+    path = peaks_file or os.environ.get("TESSERACT_PEAKS_FILE", "")
+    if path:
+        d = json.load(open(path))
+        _PEAKS.update(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), src="measured")
+    if hbm_gbs:
+        _PEAKS.update(hbm_gbs=float(hbm_gbs), src="given")
+    if bf16_tflops:
+        _PEAKS.update(bf16_tflops=float(bf16_tflops), src="given")
+
+
 def peaks():
-    try:
-        d = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
-    except Exception:
-        return 6650.0, 1590.0, "fallback"
+    return _PEAKS["hbm_gbs"], _PEAKS["bf16_tflops"], _PEAKS["src"]
 
 
 class Bench:
@@ -131,6 +143,28 @@ def case_decode_gemm(b: Bench):
             tot_bytes += N * K * 2
             report(f"decode_gemm_{name}_M{M}", ms, bytes_=N * K * 2, shape=[M, N, K])
         report(f"decode_gemm_layer_M{M}", tot_ms, bytes_=tot_bytes)
+
+
+def case_stream_linear(b: Bench):
+    """The weight-streaming decode GEMM (bf16 and block-scaled fp8 weights) on the layer shapes of one decode step,
+    next to the cluster split-K kernel it replaces; bytes = the weight matrix once."""
+    from tesseract_b200 import ops
+    from tesseract_b200.ops import fp8
+    for M in (16, 64, 141, 256):
+        tot = {"bf16": [0.0, 0], "fp8": [0.0, 0], "old": [0.0, 0]}
+        for name, N, K in (("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)):
+            x, w = b.randn(M, K), b.randn(N, K, scale=0.02)
+            q, sc = fp8.quantize_weight(w)
+            ms_old = b.time(lambda: ops.decode_linear(x, w))
+            ms_bf = b.time(lambda: ops.stream_linear(x, w))
+            ms_f8 = b.time(lambda: ops.stream_linear(x, q, sc))
+            for key, ms, nbytes in (("old", ms_old, N * K * 2), ("bf16", ms_bf, N * K * 2), ("fp8", ms_f8, N * K)):
+                tot[key][0] += ms
+                tot[key][1] += nbytes
+            report(f"stream_linear_bf16_{name}_M{M}", ms_bf, bytes_=N * K * 2, shape=[M, N, K], cluster_splitk_ms=round(ms_old, 4))
+            report(f"stream_linear_fp8_{name}_M{M}", ms_f8, bytes_=N * K, shape=[M, N, K])
+        for key in ("old", "bf16", "fp8"):
+            report(f"stream_linear_layer_{key}_M{M}", tot[key][0], bytes_=tot[key][1])
 
 
 def case_grouped_gemm(b: Bench):
@@ -326,14 +360,18 @@ CASES = {"gemm": case_gemm, "gemm_fp8": case_gemm_fp8, "gemm_fp8_pertensor": cas
          "flash_fwd": case_flash_fwd, "flash_bwd": case_flash_bwd, "decode": case_decode,
          "decode_int8": case_decode_int8, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu, "swiglu_bwd": case_swiglu_bwd, "adam": case_adam,
          "ce_stats": case_ce, "selective_scan": case_scan, "gemv_w8": case_gemv, "gemm_rs_emul": case_gemm_rs_emul,
-         "ag_gemm_emul": case_ag_gemm_emul}
+         "ag_gemm_emul": case_ag_gemm_emul, "stream_linear": case_stream_linear}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="all", choices=["all"] + sorted(CASES))
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--hbm-gbs", type=float, default=0.0, help="measured copy bandwidth of this GPU (GB/s)")
+    ap.add_argument("--bf16-tflops", type=float, default=0.0, help="measured library bf16 GEMM rate of this GPU")
+    ap.add_argument("--peaks-file", default="", help="JSON file with hbm_gbs and bf16_tflops")
     a = ap.parse_args()
+    set_peaks(a.hbm_gbs, a.bf16_tflops, a.peaks_file)
     from tesseract_b200 import _native
     names = sorted(CASES) if a.case == "all" else [a.case]
     for n in names:

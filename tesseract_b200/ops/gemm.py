@@ -114,6 +114,46 @@ def decode_linear(x: torch.Tensor, w: torch.Tensor, sm_count: int = 148, out: to
     return out32.to(torch.bfloat16) if out is None else out.copy_(out32)
 
 
+_native.register_signatures({
+    "tsb_gemm_decode_wq": [_native.P, _native.P, _native.P, _native.P, _native.I, _native.I, _native.I, _native.L,
+                           _native.L, _native.L, _native.I, _native.I, _native.I, _native.I, _native.P],
+})
+
+
+def stream_linear(x: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None, pdl: bool = False, bn: int = 0, split: int = 0) -> torch.Tensor:
+    """x [M, K] (bf16) @ W^T for decode-sized M with the weight-streaming kernel (``csrc/gemm_decode_wq.cu``).
+
+    ``w`` is bf16 [N, K], or -- with ``w_scale`` (fp32 [ceil(N/128), ceil(K/128)]) -- the E4M3 payload (uint8 /
+    float8_e4m3fn [N, K]) of a 128 x 128 block-scaled weight as ``ops.fp8.quantize_weight`` produces it. Activations
+    are not quantised. ``pdl=True`` launches with programmatic stream serialisation: the kernel may begin (and
+    prefetch weights) while the previous kernel of the stream is still running. CPU tensors / other dtypes run the
+    torch restatement."""
+    M, K = x.shape
+    N = w.shape[0]
+    fp8 = w_scale is not None
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and _native.available()):
+        wf = w.float() if not fp8 else _dequant_block128(w, w_scale)
+        r = (x.float() @ wf.t()).to(x.dtype)
+        return r if out is None else out.copy_(r)
+    if x.stride(1) != 1 or w.stride(1) != 1:
+        raise ValueError("stream_linear: rows must be contiguous")
+    res = out if out is not None else torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
+    rc = _native.lib().tsb_gemm_decode_wq(x.data_ptr(), w.data_ptr(), w_scale.data_ptr() if fp8 else None,
+                                          res.data_ptr(), M, N, K, x.stride(0), w.stride(0), res.stride(0), int(fp8),
+                                          bn, split, int(pdl), _native.stream_ptr(x.device))
+    _native.check(rc, "tsb_gemm_decode_wq")
+    return res
+
+
+def _dequant_block128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """fp32 [N, K] from an E4M3 payload and its [ceil(N/128), ceil(K/128)] block scales."""
+    N, K = q.shape
+    w = q.view(torch.float8_e4m3fn).float()
+    s = scale.float().repeat_interleave(128, dim=0)[:N].repeat_interleave(128, dim=1)[:, :K]
+    return w * s
+
+
 def matmul_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """a [M,K] @ b[N,K]^T without autograd."""
     if _use_native(a):

@@ -19,7 +19,9 @@ _ALIGN_ELEMS = 128  # every parameter starts on a 256-byte (bf16) / 512-byte (fp
 
 class ParamArena:
     def __init__(self, params: Iterable[nn.Parameter], grad_dtype: torch.dtype | None = None,
-                 master_weights: bool = False):
+                 master_weights: bool = False, grad_alloc=None):
+        """``grad_alloc(numel, dtype, device) -> flat tensor`` lets the caller place the gradient buffer (e.g. in
+        peer-mapped memory, so that a data-parallel all-reduce kernel can work on it in place)."""
         self.params = [p for p in params]
         if not self.params:
             raise ValueError("ParamArena: no parameters")
@@ -36,7 +38,13 @@ class ParamArena:
             off += (n + _ALIGN_ELEMS - 1) // _ALIGN_ELEMS * _ALIGN_ELEMS
         self.numel = off
         self.flat = torch.zeros(off, dtype=self.dtype, device=self.device)
-        self.grad = torch.zeros(off, dtype=self.grad_dtype, device=self.device)
+        if grad_alloc is not None:
+            self.grad = grad_alloc(off, self.grad_dtype, self.device)
+            if self.grad.numel() != off or self.grad.dtype != self.grad_dtype or not self.grad.is_contiguous():
+                raise ValueError("ParamArena: grad_alloc returned a buffer of the wrong size, dtype or layout")
+            self.grad.zero_()
+        else:
+            self.grad = torch.zeros(off, dtype=self.grad_dtype, device=self.device)
         with torch.no_grad():
             for p, o in zip(self.params, self.offsets):
                 view = self.flat[o:o + p.numel()].view(p.shape)

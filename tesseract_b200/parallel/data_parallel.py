@@ -6,6 +6,10 @@ block's backward has finished (everything that contributes to the block's weight
 the all-reduce of that block's bucket on a side stream while the earlier blocks are still being differentiated.
 Only the last micro-batch of a step communicates; ``finish_step`` reduces whatever is left and joins the streams.
 
+The all-reduce itself is this repository's two-shot peer-memory kernel (``csrc/allreduce_twoshot.cu``) whenever the
+gradient arena lives in symmetric memory (``symm`` given: the factory places it there on CUDA ranks of one node);
+NCCL / gloo ``all_reduce`` otherwise (CPU ranks, or ``TESSERACT_DP_COMM=nccl`` for A/B runs).
+
 The reference has no data parallelism (it is mentioned only in a comment, src/ops/cpu/Arithmetic.cpp:270).
 """
 from __future__ import annotations
@@ -28,10 +32,12 @@ class _BucketMarker(torch.autograd.Function):
 
 
 class GradReducer:
-    def __init__(self, arena, group, buckets: List[Tuple[int, int]], average: bool = True):
-        """``buckets``: [begin, end) element ranges of ``arena.grad`` in forward order."""
+    def __init__(self, arena, group, buckets: List[Tuple[int, int]], average: bool = True, symm=None):
+        """``buckets``: [begin, end) element ranges of ``arena.grad`` in forward order. ``symm``: a
+        ``fused_tp.SymmGradAllReduce`` over the symmetric buffer that ``arena.grad`` is a view of (offset 0)."""
         import torch.distributed as dist
         self.arena, self.group, self.buckets, self.average = arena, group, buckets, average
+        self.symm = symm
         self.world = dist.get_world_size(group)
         self._dist = dist
         self._last = False
@@ -85,7 +91,12 @@ class GradReducer:
     def _reduce(self, bid: int, overlapped: bool) -> None:
         a, b = self.buckets[bid]
         g = self.arena.grad[a:b]
-        if self.stream is not None:
+        if self.symm is not None:
+            self.stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.stream):
+                self.symm.all_reduce_(a * g.element_size(), b - a, g.dtype,
+                                      scale=(1.0 / self.world) if self.average else 1.0)
+        elif self.stream is not None:
             self.stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.stream):
                 if self.average:

@@ -16,9 +16,48 @@ from ..training import TrainConfig, Trainer
 from .data_parallel import GradReducer
 
 
-def _attach_reducer(model, trainer, group):
+def _symm_grad_alloc(group, device):
+    """Returns ``(grad_alloc, holder)`` for ``Trainer``: the gradient arena goes into peer-mapped memory of the
+    data-parallel group so that the all-reduce kernel can work on it in place; ``holder["symm"]`` is the
+    ``SymmetricMemory`` afterwards. ``(None, None)`` when the NCCL path is selected or the ranks are not CUDA."""
+    if torch.device(device).type != "cuda" or os.environ.get("TESSERACT_DP_COMM", "symm") != "symm":
+        return None, None
+    import torch.distributed as dist
+    from .fused_tp import SymmetricMemory
+    if dist.get_world_size(group) > 8:
+        return None, None
+    holder = {}
+
+    def alloc(numel, dtype, dev):
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        sm = SymmetricMemory(group, dist.get_rank(group), dist.get_world_size(group), (nbytes + 255) // 256 * 256, dev)
+        holder["symm"] = sm
+        return sm.local[:nbytes].view(dtype)
+
+    return alloc, holder
+
+
+def _resources(trainer, fused, holder):
+    """Objects that own peer-mapped device memory and must be ``close()``d (collectively, after a device synchronise
+    and a barrier) when a trainer is torn down before the process ends."""
+    out = []
+    red = getattr(trainer, "grad_reducer", None)
+    if red is not None and getattr(red, "symm", None) is not None:
+        out.append(red.symm)
+    if holder and "symm" in holder:
+        out.append(holder["symm"])
+    if fused is not None:
+        out.append(fused)
+    return out
+
+
+def _attach_reducer(model, trainer, group, holder=None):
     buckets = GradReducer.layer_buckets(model, trainer.arena)
-    red = GradReducer(trainer.arena, group, buckets)
+    symm = None
+    if holder and "symm" in holder:
+        from .fused_tp import SymmGradAllReduce
+        symm = SymmGradAllReduce(holder["symm"])
+    red = GradReducer(trainer.arena, group, buckets, symm=symm)
     # bucket index of block 0: buckets are sorted by arena offset = registration order; the embedding comes first
     red.block_bucket0 = 1 if len(buckets) > len(model.layers) else 0
     model.grad_reducer = red
@@ -37,18 +76,20 @@ def _attach_reducer(model, trainer, group):
 def build_parallel_trainer(cfg: LlamaConfig, tcfg: TrainConfig, world: int, rank: int, device, mode: str = "auto",
                            seed: int = 0, tp_size: int = 0):
     """Returns ``(trainer, plan)``; ``plan`` has ``name`` (e.g. "tp8+sp", "dp4"), ``dp``, ``dp_rank``, ``tp``,
-    ``tp_rank`` and ``fused_comm``."""
+    ``tp_rank``, ``fused_comm``, ``dp_comm`` and ``resources`` (see ``_resources``)."""
     if world == 1:
         model = LlamaModel(cfg, device=device, init_std=0.02, seed=seed)
         return Trainer(model, tcfg), {"name": "single", "dp": 1, "dp_rank": 0, "tp": 1, "tp_rank": 0,
-                                      "fused_comm": False}
+                                      "fused_comm": False, "dp_comm": None, "resources": []}
     import torch.distributed as dist
     if mode == "dp":
         model = LlamaModel(cfg, device=device, init_std=0.02, seed=seed)
-        trainer = Trainer(model, tcfg)
-        _attach_reducer(model, trainer, dist.group.WORLD)
+        grad_alloc, holder = _symm_grad_alloc(dist.group.WORLD, device)
+        trainer = Trainer(model, tcfg, grad_alloc=grad_alloc)
+        _attach_reducer(model, trainer, dist.group.WORLD, holder)
         return trainer, {"name": f"dp{world}", "dp": world, "dp_rank": rank, "tp": 1, "tp_rank": 0,
-                         "fused_comm": False}
+                         "fused_comm": False, "dp_comm": "symm-twoshot" if holder else "nccl",
+                         "resources": _resources(trainer, None, holder)}
     if mode in ("auto", "tp"):
         from .tp_layers import TPContext
         from .tp_model import TPLlamaModel
@@ -79,10 +120,12 @@ def build_parallel_trainer(cfg: LlamaConfig, tcfg: TrainConfig, world: int, rank
                 if rank == 0:
                     print(f"[tesseract_b200] fused TP kernels unavailable ({e}); using NCCL collectives", flush=True)
         model = TPLlamaModel(cfg, ctx, device=device, init_std=0.02, seed=seed)
-        trainer = Trainer(model, tcfg)
+        grad_alloc, holder = _symm_grad_alloc(dp_group, device) if dp > 1 else (None, None)
+        trainer = Trainer(model, tcfg, grad_alloc=grad_alloc)
         if dp > 1:
-            _attach_reducer(model, trainer, dp_group)
+            _attach_reducer(model, trainer, dp_group, holder)
         name = f"tp{tp}+sp" + (f" x dp{dp}" if dp > 1 else "")
         return trainer, {"name": name, "dp": dp, "dp_rank": dp_rank, "tp": tp, "tp_rank": tp_rank,
-                         "fused_comm": fused_ok}
+                         "fused_comm": fused_ok, "dp_comm": ("symm-twoshot" if holder else "nccl") if dp > 1 else None,
+                         "resources": _resources(trainer, ctx.fused, holder)}
     raise ValueError(f"unknown parallelism mode {mode!r}")

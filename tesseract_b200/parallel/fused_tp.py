@@ -41,6 +41,7 @@ _native.register_signatures({
     "tsb_symm_barrier_limit": [PP, I, I, I, L, P],
     "tsb_reduce_slots": [P, P, I, L, P],
     "tsb_allreduce_oneshot": [PP, PP, P, P, L, I, I, P],
+    "tsb_allreduce_twoshot": [PP, PP, P, L, I, I, I, I, F, I, I, L, P],
     "tsb_gemm_rs": [P, P, PP, I, I, I, L, L, I, I, I, I, P],
     "tsb_gemm_ag": [P, PP, PP, P, P, P, I, I, I, I, I, I, L, L, I, I, I, I, P, P],
 })
@@ -278,4 +279,43 @@ class SymmAllReduce:
 
     def close(self) -> None:
         self.buf.close()
+        self.flags.close()
+
+
+class SymmGradAllReduce:
+    """In-place all-reduce of ranges of ONE large symmetric buffer (the gradient arena of data-parallel ranks) with the
+    two-shot peer-memory kernel of ``csrc/allreduce_twoshot.cu``: no NCCL, one launch per range, bounded waits.
+
+    ``buffer`` is the ``SymmetricMemory`` that holds the data; ``all_reduce_(byte_offset, n_elems, dtype, scale)``
+    reduces that range on every rank (every rank must issue the same calls in the same order, on any stream)."""
+
+    def __init__(self, buffer: SymmetricMemory, ctas: int = 0):
+        self.buf = buffer
+        self.rank, self.world = buffer.rank, buffer.world
+        self.device = buffer.local.device
+        self.flags = SymmetricMemory(buffer.group, buffer.rank, buffer.world, 256, self.device)
+        self.state = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.epoch = 0
+        self.ctas = ctas or int(os.environ.get("TESSERACT_DP_CTAS", "0"))
+        self.calls = 0
+        self.bytes = 0
+
+    def all_reduce_(self, byte_offset: int, n_elems: int, dtype: torch.dtype, scale: float = 1.0,
+                    phase_mask: int = 7, limit_cycles: int = 0) -> None:
+        code = {torch.bfloat16: 1, torch.float32: 0}.get(dtype)
+        if code is None:
+            raise ValueError("SymmGradAllReduce: bf16 or fp32 data only")
+        if byte_offset % 16 or n_elems % (8 if code else 4):
+            raise ValueError("SymmGradAllReduce: ranges start on 16 bytes and hold whole 16-byte vectors")
+        if phase_mask & 1:
+            self.epoch += 1
+        check(lib().tsb_allreduce_twoshot(self.buf.offset_ptr_array(byte_offset), self.flags.ptr_array,
+                                          self.state.data_ptr(), n_elems, code, self.rank, self.world,
+                                          _wrap_i32(self.epoch), float(scale), self.ctas, phase_mask, limit_cycles,
+                                          torch.cuda.current_stream(self.device).cuda_stream),
+              "tsb_allreduce_twoshot")
+        self.calls += 1
+        self.bytes += n_elems * (2 if code else 4)
+
+    def close(self) -> None:
         self.flags.close()

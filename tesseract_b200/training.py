@@ -36,11 +36,12 @@ class TrainConfig:
 
 
 class Trainer:
-    def __init__(self, model, cfg: TrainConfig, dp_group=None, grad_reducer=None):
+    def __init__(self, model, cfg: TrainConfig, dp_group=None, grad_reducer=None, grad_alloc=None):
         self.model, self.cfg = model, cfg
         p0 = next(model.parameters())
         gd = cfg.grad_dtype if p0.dtype != torch.float32 else torch.float32
-        self.arena = ParamArena.from_module(model, grad_dtype=gd, master_weights=cfg.master_weights)
+        self.arena = ParamArena.from_module(model, grad_dtype=gd, master_weights=cfg.master_weights,
+                                            grad_alloc=grad_alloc)
         self.opt = Adam(self.arena, cfg.lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.max_grad_norm)
         self.dp_group = dp_group
         self.grad_reducer = grad_reducer
@@ -74,6 +75,11 @@ class Trainer:
             total += loss.detach()
         if hasattr(self.model, "sync_replicated_grads"):
             self.arena.fold_autograd_grads()
+            red_stream = getattr(self.grad_reducer, "stream", None)
+            if red_stream is not None:
+                # hybrid mesh: bucket all-reduces of this step may still be running on the reducer's stream over the
+                # very gradients that the tensor-parallel sum below updates in place
+                torch.cuda.current_stream().wait_stream(red_stream)
             self.model.sync_replicated_grads()
         if self.grad_reducer is not None:
             self.grad_reducer.finish_step()

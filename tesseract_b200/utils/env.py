@@ -34,6 +34,9 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_RMS_THREADS", "0", "RMSNorm forward threads per row: 0 (256) | 128 | 256, for A/B runs"),
     EnvVar("TESSERACT_REF_TIME_BUDGET", "780", "bench.py --impl reference: seconds the reference arm may take in total"),
     EnvVar("TESSERACT_REFERENCE_DIR", "/root/reference", "baseline/build_reference.py: source tree of the reference to build"),
+    EnvVar("TESSERACT_DP_COMM", "symm", "data-parallel gradient all-reduce: symm (two-shot peer-memory kernel) | nccl"),
+    EnvVar("TESSERACT_DP_CTAS", "0", "CTAs of the gradient all-reduce kernel (0 = 48)"),
+    EnvVar("TESSERACT_PEAKS_FILE", "", "benchmarks: JSON file with the measured hbm_gbs / bf16_tflops of this GPU (roofline denominators)"),
     EnvVar("TESSERACT_SWIGLU", "2", "SwiGLU kernels: 2 (row-wise, two vector pairs per thread) | 0 (flat kernel, for A/B runs)"),
 ]}
 

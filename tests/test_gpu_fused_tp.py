@@ -218,6 +218,42 @@ def _worker(rank, world, port, q):
         assert all(x[0] == y[0] for x, y in zip(outs["single"], outs["tp"])), "first tokens differ from the single-GPU engine"
         assert agree > 0.6, agree
         status |= _native.read_status(torch.cuda.current_stream().cuda_stream)
+        # data-parallel gradient all-reduce: the two-shot peer-memory kernel against NCCL on the same buffers, then two
+        # optimizer steps of a small replicated model with either collective
+        from tesseract_b200.parallel.fused_tp import SymmGradAllReduce, SymmetricMemory
+        n = 3 * 1024 * 1024 + 128
+        sm = SymmetricMemory(dist.group.WORLD, rank, world, n * 2, dev)
+        gar = SymmGradAllReduce(sm)
+        view = sm.local[:n * 2].view(torch.bfloat16)
+        for it in range(3):
+            data = torch.randn(n, device=dev, generator=g).bfloat16()
+            view.copy_(data)
+            lo_e, hi_e = 1024 * it, n - 128 * it                     # different ranges of the same buffer
+            want = data[lo_e:hi_e].float().clone()
+            dist.all_reduce(want)
+            torch.cuda.synchronize()
+            dist.barrier()
+            gar.all_reduce_(lo_e * 2, hi_e - lo_e, torch.bfloat16, scale=1.0 / world)
+            got = view[lo_e:hi_e].float() * world
+            errs.append(((got - want).norm() / want.norm()).item())
+            same_bits = view[lo_e:hi_e].view(torch.int16).to(torch.int64).sum()
+            a1, a2 = same_bits.clone(), same_bits.clone()
+            dist.all_reduce(a1, op=dist.ReduceOp.MIN)
+            dist.all_reduce(a2, op=dist.ReduceOp.MAX)
+            assert int(a1) == int(a2), "ranks hold different reduced gradients"
+            if lo_e > 0:
+                assert torch.equal(view[:lo_e], data[:lo_e])        # outside the range: untouched
+        dp_losses = {}
+        for comm in ("symm", "nccl"):
+            os.environ["TESSERACT_DP_COMM"] = comm
+            trainer, plan = build_parallel_trainer(cfg, TrainConfig(lr=1e-3, micro_batch=1), world, rank, dev, "dp", seed=3)
+            assert plan["dp_comm"] == ("symm-twoshot" if comm == "symm" else "nccl")
+            batch = torch.randint(0, 1024, (2, 257), generator=torch.Generator().manual_seed(50 + rank)).pin_memory()
+            dp_losses[comm] = (trainer.train_step(batch), trainer.train_step(batch))
+            if comm == "symm":
+                assert trainer.grad_reducer.symm.calls > 0 and trainer.grad_reducer.overlapped_bytes > 0
+        losses["dp"] = dp_losses
+        status |= _native.read_status(torch.cuda.current_stream().cuda_stream)
         dist.barrier()
         q.put((rank, None, (errs, status, losses)))
     except Exception:  # pragma: no cover
@@ -257,6 +293,9 @@ def test_fused_tp_matches_nccl_on_real_peers():
         assert losses["fused"][2] is True and losses["nccl"][2] is False
         assert abs(losses["fused"][0] - losses["nccl"][0]) < 2e-2
         assert losses["fused"][1] < losses["fused"][0]
+        dp = losses["dp"]
+        assert abs(dp["symm"][0] - dp["nccl"][0]) < 1e-3 and abs(dp["symm"][1] - dp["nccl"][1]) < 2e-2
+        assert dp["symm"][1] < dp["symm"][0]
 
 
 def test_barrier_wait_runs_out_and_reports_through_the_status_word():
@@ -293,3 +332,51 @@ def test_barrier_wait_runs_out_and_reports_through_the_status_word():
     torch.cuda.synchronize()
     assert _native.read_status(stream) == 0
     assert torch.isfinite(y.float()).all()
+
+
+def test_twoshot_allreduce_emulated_ranks_on_one_gpu():
+    """The gradient all-reduce kernel with every rank's buffer on ONE GPU: the ranks run one after the other, phase by
+    phase (start barrier with the peers' flags already written, reduce + broadcast, end barrier), which gives what
+    concurrent ranks give because a vector is read and rewritten by its owning rank only."""
+    import ctypes
+
+    from tesseract_b200 import _native
+    from tesseract_b200.parallel import fused_tp  # noqa: F401
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    _native.read_status(stream)
+    for world, n, dtype in ((4, 8 * 1000 + 8 * 3, torch.bfloat16), (8, 4 * 515, torch.float32), (2, 8 * 4096, torch.bfloat16)):
+        g = torch.Generator(device=dev).manual_seed(world)
+        bufs = [torch.randn(n, device=dev, generator=g).to(dtype) for _ in range(world)]
+        want = torch.stack([b.float() for b in bufs]).sum(0) / world
+        flags = [torch.zeros(32, dtype=torch.int32, device=dev) for _ in range(world)]
+        states = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(world)]
+        parr = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+        farr = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+        code = 1 if dtype == torch.bfloat16 else 0
+        for phase in (1, 2, 4):
+            for r in range(world):
+                if phase == 4:                       # the peers' "done" flags, as concurrent ranks would have set them
+                    flags[r][16:16 + world] = 1
+                _native.check(_native.lib().tsb_allreduce_twoshot(parr, farr, states[r].data_ptr(), n, code, r, world, 1,
+                                                                  1.0 / world, 7, phase, 200_000_000, stream),
+                              "tsb_allreduce_twoshot")
+        torch.cuda.synchronize()
+        assert _native.read_status(stream) == 0
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-6
+        for b in bufs:
+            assert torch.equal(b, bufs[0])           # every rank ends with the same bits
+            assert (b.float() - want).abs().max() <= tol * want.abs().max()
+        assert all(int(f[:world].min()) == 1 for f in flags)
+    # a start barrier whose peer never arrives runs out and reports
+    flags = [torch.zeros(32, dtype=torch.int32, device=dev) for _ in range(2)]
+    state = torch.zeros(2, dtype=torch.int32, device=dev)
+    bufs = [torch.ones(64, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    parr = (ctypes.c_void_p * 2)(*[b.data_ptr() for b in bufs])
+    farr = (ctypes.c_void_p * 2)(*[f.data_ptr() for f in flags])
+    _native.check(_native.lib().tsb_allreduce_twoshot(parr, farr, state.data_ptr(), 64, 1, 0, 2, 1, 1.0, 4, 7, 50_000_000,
+                                                      stream), "tsb_allreduce_twoshot")
+    torch.cuda.synchronize()
+    assert _native.read_status(stream) == 2
+    assert torch.equal(bufs[0], torch.ones_like(bufs[0]))       # nothing was reduced

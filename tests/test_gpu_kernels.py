@@ -641,6 +641,47 @@ def test_decode_linear_split_k(dev, M, N, K):
     assert _rel_err(got, x.float() @ w.float().t()) < 8e-3
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("M,N,K,bn,split", [(1, 4096, 4096, 0, 0), (64, 6144, 4096, 0, 0), (128, 4096, 14336, 0, 0),
+                                            (141, 1536, 4096, 0, 0), (37, 1000, 576, 48, 2), (256, 768, 4096, 0, 0),
+                                            (16, 300, 128, 112, 1), (96, 28672, 4096, 0, 0), (8, 520, 1024, 256, 8)])
+def test_stream_linear_bf16_and_fp8_block_scaled(dev, M, N, K, bn, split, fp8):
+    """The weight-streaming decode GEMM against an fp32 product of the same (dequantised) operands; ragged N, M
+    beyond one row block, every cluster split, and the programmatic-launch flag."""
+    from tesseract_b200 import ops
+    from tesseract_b200.ops import fp8 as f8
+    from tesseract_b200.ops.gemm import _dequant_block128, stream_linear
+    g = torch.Generator(device=dev).manual_seed(M * 7 + N)
+    x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    if fp8:
+        if K % 128:
+            pytest.skip("block scales need K % 128 == 0")
+        q, sc = f8.quantize_weight(w)
+        want = x.float() @ _dequant_block128(q, sc).t()
+        got = stream_linear(x, q, sc, bn=bn, split=split)
+        got_pdl = stream_linear(x, q, sc, bn=bn, split=split, pdl=True)
+        # and the quantisation itself is the usual E4M3 error against the bf16 weights
+        full = x.float() @ w.float().t()
+        assert ((want - full).norm() / full.norm()).item() < 0.05
+    else:
+        want = x.float() @ w.float().t()
+        got = stream_linear(x, w, bn=bn, split=split)
+        got_pdl = stream_linear(x, w, bn=bn, split=split, pdl=True)
+    torch.cuda.synchronize()
+    assert got.shape == (M, N)
+    err = ((got.float() - want).norm() / want.norm()).item()
+    assert err < (1.2e-2 if fp8 else 6e-3), err
+    assert (got.float() - want).abs().max().item() < 0.05 * want.abs().max().item() + 0.05
+    assert torch.equal(got, got_pdl)
+    # the result lands in a caller's (strided) buffer as well
+    buf = torch.zeros(M, N + 8, device=dev, dtype=torch.bfloat16)
+    stream_linear(x, q if fp8 else w, sc if fp8 else None, out=buf[:, :N], bn=bn, split=split)
+    assert torch.equal(buf[:, :N], got) and float(buf[:, N:].abs().max()) == 0.0
+    from tesseract_b200 import _native
+    assert _native.read_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("B,L,d,N", [(2, 1, 64, 16), (1, 50, 96, 8), (2, 300, 128, 16), (1, 1000, 64, 32)])
 def test_selective_scan_and_conv1d(dev, dtype, B, L, d, N):
