@@ -116,18 +116,76 @@ __device__ __forceinline__ float uniform_from(unsigned long long seed, unsigned 
   return static_cast<float>(z >> 40) * (1.0f / 16777216.0f);
 }
 
+// Order-preserving map of a float onto an unsigned integer (for bisection on exact element values).
+__device__ __forceinline__ unsigned int float_key(float f) {
+  const unsigned int u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(unsigned int k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// In place: logits[row, t] is divided (if positive) or multiplied (otherwise) by `penalty` once per OCCURRENCE of t
+// among the row's first hist_len[row] history tokens (the host sampler's rule, src/models/Sampler.cpp:29-50). The
+// thread that holds the first occurrence of a token counts the later ones and applies the power in one go.
+template <typename T>
+__global__ void __launch_bounds__(256)
+repetition_penalty_kernel(T* __restrict__ logits, long long ld, int V, const int* __restrict__ history, long long hist_ld,
+                          const int* __restrict__ hist_len, float penalty) {
+  const int row = blockIdx.x;
+  const int n = hist_len[row];
+  const int* h = history + row * hist_ld;
+  T* x = logits + row * ld;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int t = h[i];
+    if (t < 0 || t >= V) continue;
+    bool first = true;
+    for (int j = 0; j < i; ++j)
+      if (h[j] == t) {
+        first = false;
+        break;
+      }
+    if (!first) continue;
+    int cnt = 1;
+    for (int j = i + 1; j < n; ++j) cnt += (h[j] == t) ? 1 : 0;
+    float v = to_f32<T>(x[t]);
+    for (int c = 0; c < cnt; ++c) v = v > 0.f ? v / penalty : v * penalty;
+    x[t] = from_f32<T>(v);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kSampThreads)
 sample_top_p_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, long long ld, float inv_temp,
-                    float top_p, unsigned long long seed, unsigned long long step) {
+                    float top_p, int top_k, unsigned long long seed, unsigned long long step,
+                    const unsigned long long* __restrict__ step_ptr) {
   __shared__ float red[32];
   __shared__ float s_scan[kSampThreads];
   const T* x = logits + blockIdx.x * ld;
+  if (step_ptr) step = *step_ptr;       // a device-resident counter: the launch can sit in a CUDA graph
   float m = -INFINITY;
   for (int j = threadIdx.x; j < V; j += blockDim.x) m = fmaxf(m, to_f32<T>(x[j]) * inv_temp);
   m = block_reduce_max(m, red);
+  // top-k: the k-th largest scaled logit by bisection on the ordered integer image of the values (exact; ties at the
+  // k-th value all survive, as in the host sampler). kth = -inf keeps everything.
+  float kth = -INFINITY;
+  if (top_k > 0 && top_k < V) {
+    unsigned int lo_k = float_key(-INFINITY), hi_k = float_key(m);   // count(x >= key_float(lo_k)) >= k throughout
+    while (lo_k < hi_k) {
+      const unsigned int mid = lo_k + ((hi_k - lo_k + 1u) >> 1);
+      const float t = key_float(mid);
+      float cnt = 0.f;
+      for (int j = threadIdx.x; j < V; j += blockDim.x) cnt += (to_f32<T>(x[j]) * inv_temp >= t) ? 1.f : 0.f;
+      cnt = block_reduce_sum(cnt, red);
+      if (cnt >= static_cast<float>(top_k)) lo_k = mid; else hi_k = mid - 1u;
+    }
+    kth = key_float(lo_k);
+  }
   float s = 0.f;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) s += __expf(to_f32<T>(x[j]) * inv_temp - m);
+  for (int j = threadIdx.x; j < V; j += blockDim.x) {
+    const float z = to_f32<T>(x[j]) * inv_temp;
+    if (z >= kth) s += __expf(z - m);
+  }
   const float denom = block_reduce_sum(s, red);
   // bisection on the probability threshold t: mass(p >= t) is non-increasing in t; find the largest t whose
   // mass still reaches top_p (the smallest nucleus). p is in (0, 1]; the top token has p_max = 1 / denom.
@@ -137,8 +195,9 @@ sample_top_p_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, 
       const float mid = 0.5f * (lo + hi);
       float mass = 0.f;
       for (int j = threadIdx.x; j < V; j += blockDim.x) {
-        const float p = __expf(to_f32<T>(x[j]) * inv_temp - m) / denom;
-        if (p >= mid) mass += p;
+        const float z = to_f32<T>(x[j]) * inv_temp;
+        const float p = z >= kth ? __expf(z - m) / denom : 0.f;
+        if (p >= mid && p > 0.f) mass += p;
       }
       mass = block_reduce_sum(mass, red);
       if (mass >= top_p) lo = mid; else hi = mid;
@@ -148,8 +207,9 @@ sample_top_p_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, 
   // mass of the survivors, then an inverse-CDF walk in index order
   float keep = 0.f;
   for (int j = threadIdx.x; j < V; j += blockDim.x) {
-    const float p = __expf(to_f32<T>(x[j]) * inv_temp - m) / denom;
-    if (p >= thr) keep += p;
+    const float z = to_f32<T>(x[j]) * inv_temp;
+    const float p = z >= kth ? __expf(z - m) / denom : 0.f;
+    if (p >= thr && p > 0.f) keep += p;
   }
   const float total = block_reduce_sum(keep, red);
   const float target = uniform_from(seed, blockIdx.x, step) * total;
@@ -158,8 +218,9 @@ sample_top_p_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, 
   const int j0 = threadIdx.x * per, j1 = min(V, j0 + per);
   float mine = 0.f;
   for (int j = j0; j < j1; ++j) {
-    const float p = __expf(to_f32<T>(x[j]) * inv_temp - m) / denom;
-    if (p >= thr) mine += p;
+    const float z = to_f32<T>(x[j]) * inv_temp;
+    const float p = z >= kth ? __expf(z - m) / denom : 0.f;
+    if (p >= thr && p > 0.f) mine += p;
   }
   s_scan[threadIdx.x] = mine;
   __syncthreads();
@@ -177,8 +238,9 @@ sample_top_p_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, 
     const int a0 = owner * per, a1 = min(V, a0 + per);
     int pick = -1, last = -1;
     for (int j = a0; j < a1; ++j) {
-      const float p = __expf(to_f32<T>(x[j]) * inv_temp - m) / denom;
-      if (p >= thr) {
+      const float z = to_f32<T>(x[j]) * inv_temp;
+      const float p = z >= kth ? __expf(z - m) / denom : 0.f;
+      if (p >= thr && p > 0.f) {
         last = j;
         acc += p;
         if (acc >= target) {
@@ -220,6 +282,33 @@ TSB_EXPORT int tsb_sample_top_p_rows(const void* logits, int* out, int rows, int
   if (rows <= 0 || V <= 0 || temperature <= 0.f || top_p <= 0.f) return -2;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   TSB_DISPATCH_FLOAT(dtype, (tsb::sample_top_p_kernel<T><<<rows, tsb::kSampThreads, 0, s>>>(
-                                static_cast<const T*>(logits), out, V, ld, 1.f / temperature, top_p, seed, step)));
+                                static_cast<const T*>(logits), out, V, ld, 1.f / temperature, top_p, 0, seed, step,
+                                nullptr)));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The full device sampler, in the host sampler's stage order (src/models/Sampler.cpp:29-116): temperature, top-k
+// (0 = off; ties at the k-th value survive), top-p over the renormalised survivors, one uniform draw per row. The
+// draw for (row, step) is a pure function of (seed, row, step); with step_ptr != null the step is read from that
+// device counter at run time, so the launch can be captured in a CUDA graph and replayed.
+TSB_EXPORT int tsb_sample_rows(const void* logits, int* out, int rows, int V, long long ld, float temperature, int top_k,
+                               float top_p, unsigned long long seed, unsigned long long step,
+                               const unsigned long long* step_ptr, int dtype, void* stream) {
+  if (rows <= 0 || V <= 0 || temperature <= 0.f || top_p <= 0.f || top_k < 0) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TSB_DISPATCH_FLOAT(dtype, (tsb::sample_top_p_kernel<T><<<rows, tsb::kSampThreads, 0, s>>>(
+                                static_cast<const T*>(logits), out, V, ld, 1.f / temperature, top_p, top_k, seed, step,
+                                step_ptr)));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// logits [rows, V] in place: repetition penalty over history [rows, hist_ld] int32 (hist_len[row] valid entries each).
+TSB_EXPORT int tsb_repetition_penalty_rows(void* logits, int rows, int V, long long ld, const int* history,
+                                           long long hist_ld, const int* hist_len, float penalty, int dtype,
+                                           void* stream) {
+  if (rows <= 0 || V <= 0 || penalty <= 0.f || !history || !hist_len) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TSB_DISPATCH_FLOAT(dtype, (tsb::repetition_penalty_kernel<T><<<rows, 256, 0, s>>>(
+                                static_cast<T*>(logits), ld, V, history, hist_ld, hist_len, penalty)));
   return static_cast<int>(cudaGetLastError());
 }

@@ -41,7 +41,24 @@ P, I, L, F = _native.P, _native.I, _native.L, _native.F
 _native.register_signatures({
     "tsb_argmax_rows": [P, P, I, I, L, I, P],
     "tsb_sample_top_p_rows": [P, P, I, I, L, F, F, _native.ctypes.c_ulonglong, _native.ctypes.c_ulonglong, I, P],
+    "tsb_sample_rows": [P, P, I, I, L, F, I, F, _native.ctypes.c_ulonglong, _native.ctypes.c_ulonglong, P, I, P],
+    "tsb_repetition_penalty_rows": [P, I, I, L, P, L, P, F, I, P],
 })
+
+
+class _Weight:
+    """A projection weight as the engine holds it: bf16 [N, K] (``w``), or the E4M3 payload ``q`` [N, K] with its
+    fp32 128 x 128 block scales ``s`` [ceil(N / 128), K / 128]."""
+    __slots__ = ("w", "q", "s", "shape")
+
+    def __init__(self, w=None, q=None, s=None):
+        self.w, self.q, self.s = w, q, s
+        self.shape = tuple((w if w is not None else q).shape)
+
+    def nbytes(self) -> int:
+        if self.w is not None:
+            return self.w.numel() * self.w.element_size()
+        return self.q.numel() + self.s.numel() * 4
 
 
 @dataclass
@@ -64,6 +81,28 @@ def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     check(lib().tsb_argmax_rows(logits.data_ptr(), out.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0),
                                 _native.dtype_code(logits.dtype), stream_ptr(logits.device)), "tsb_argmax_rows")
     return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, step: int = 0,
+                step_counter: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Temperature -> top-k (0 = off) -> top-p -> one draw per row, on the device. With ``step_counter`` (an int64
+    device tensor of one element) the step is read from it when the kernel runs, so the launch can be captured in a
+    CUDA graph; the caller advances the counter."""
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    check(lib().tsb_sample_rows(logits.data_ptr(), out.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0),
+                                float(temperature), int(top_k), float(top_p), seed, step,
+                                step_counter.data_ptr() if step_counter is not None else None,
+                                _native.dtype_code(logits.dtype), stream_ptr(logits.device)), "tsb_sample_rows")
+    return out
+
+
+def repetition_penalty_rows_(logits: torch.Tensor, history: torch.Tensor, hist_len: torch.Tensor, penalty: float) -> None:
+    """In place: every occurrence of a token in ``history[row, :hist_len[row]]`` (int32) divides its positive logit
+    by ``penalty`` or multiplies its non-positive logit by it (src/models/Sampler.cpp:29-50)."""
+    check(lib().tsb_repetition_penalty_rows(logits.data_ptr(), logits.shape[0], logits.shape[1], logits.stride(0),
+                                            history.data_ptr(), history.stride(0), hist_len.data_ptr(), float(penalty),
+                                            _native.dtype_code(logits.dtype), stream_ptr(logits.device)),
+          "tsb_repetition_penalty_rows")
 
 
 def sample_top_p_rows(logits: torch.Tensor, temperature: float, top_p: float, seed: int, step: int) -> torch.Tensor:
@@ -97,9 +136,18 @@ class ServingEngine:
 
     def __init__(self, model: LlamaModel, cfg: Optional[EngineConfig] = None, use_cuda_graph: bool = True,
                  temperature: float = 0.0, top_p: float = 1.0, seed: int = 0, tp: Optional[TPServe] = None,
-                 max_prefill_tokens: int = 0, fp8_prefill: bool = False):
+                 max_prefill_tokens: int = 0, fp8_prefill: bool = False, weights: str = "bf16", top_k: int = 0,
+                 repetition_penalty: float = 1.0):
         self.model, self.cfg = model, cfg or EngineConfig()
         self.tp = tp
+        # weights="fp8": every layer projection and the LM head are held as E4M3 with 128 x 128 block scales (half the
+        # bytes a decode step streams). Decode-sized batches multiply bf16 activations with them in the
+        # weight-streaming kernel (the weights are widened on the fly, activations are not quantised); prompt-sized
+        # batches quantise the activations 1 x 128 and run the block-scaled fp8 GEMM.
+        if weights not in ("bf16", "fp8"):
+            raise ValueError("ServingEngine: weights must be 'bf16' or 'fp8'")
+        self.weights = weights
+        self.top_k, self.repetition_penalty = int(top_k), float(repetition_penalty)
         # fp8_prefill: the layer GEMMs of prefill-sized batches (more than 512 rows) run on E4M3 copies of the weights
         # with one scale per tensor and a per-call activation scale (about 2 x the bf16 GEMM rate); decode-sized
         # batches and the LM head stay bf16. Off by default: it changes the numerics of the prompt pass.
@@ -110,6 +158,10 @@ class ServingEngine:
         self.max_prefill_tokens = max_prefill_tokens
         import os
         self.varlen_prefill = os.environ.get("TESSERACT_PREFILL_VARLEN", "1") == "1"   # 0: one launch per prompt
+        # programmatic dependent launch of the decode GEMMs: they start (and prefetch weights) under the tail of the
+        # kernel before them
+        self.pdl = os.environ.get("TESSERACT_PDL", "1") == "1"
+        self.stream_rows = 256       # batches up to this many rows go through the weight-streaming GEMM
         c, mc = self.cfg, model.config
         self.device = model._device()
         if self.device.type != "cuda" or mc.dtype not in (torch.bfloat16, torch.float16):
@@ -134,12 +186,13 @@ class ServingEngine:
         self.allocator = BlockAllocator(c.num_blocks)
         self.max_blocks = (c.max_seq_len + c.block_size - 1) // c.block_size
         self._fuse_weights()
-        if self.fp8_prefill:
+        if self.fp8_prefill and self.weights == "bf16":
             from ..ops import fp8
             for ws in (self.wqkv, self.wo, self.wgu, self.wdown):
-                for w in ws:
-                    if w.dtype == torch.bfloat16 and w.shape[1] % 128 == 0:
-                        self._w8[id(w)] = fp8.quantize_tensor(w)
+                for W in ws:
+                    if W.w is not None and W.w.dtype == torch.bfloat16 and W.shape[1] % 128 == 0:
+                        self._w8[id(W)] = fp8.quantize_tensor(W.w)
+        self._step_dev = torch.zeros(1, dtype=torch.int64, device=self.device)   # sampling step counter (graph-safe)
         self.waiting: Deque[_Req] = deque()
         self.running: List[_Req] = []
         self.requests: Dict[int, _Req] = {}
@@ -157,6 +210,15 @@ class ServingEngine:
         projection weights of the model are released."""
         self.wqkv, self.wgu, self.wo, self.wdown = [], [], [], []
         tp = self.tp
+        fp8_mode = self.weights == "fp8"
+
+        def pack(w: torch.Tensor) -> _Weight:
+            if fp8_mode and w.dtype == torch.bfloat16 and w.shape[1] % 128 == 0:
+                from ..ops import fp8
+                q, sc = fp8.quantize_weight(w.contiguous())
+                return _Weight(q=q, s=sc)
+            return _Weight(w=w)
+
         with torch.no_grad():
             for blk in self.model.layers:
                 a, f = blk.attn, blk.ffn
@@ -167,33 +229,45 @@ class ServingEngine:
                     g = torch.cat([f.gate_proj.weight, f.up_proj.weight], dim=0).contiguous()
                     nf = f.gate_proj.weight.shape[0]
                     f.gate_proj.weight.data, f.up_proj.weight.data = g[:nf], g[nf:]
-                    self.wqkv.append(w)
-                    self.wgu.append(g)
-                    self.wo.append(a.o_proj.weight)
-                    self.wdown.append(f.down_proj.weight)
+                    self.wqkv.append(pack(w))
+                    self.wgu.append(pack(g))
+                    self.wo.append(pack(a.o_proj.weight))
+                    self.wdown.append(pack(f.down_proj.weight))
+                    if fp8_mode:   # the bf16 originals are not needed any more
+                        for lin in (a.q_proj, a.k_proj, a.v_proj, a.o_proj, f.gate_proj, f.up_proj, f.down_proj):
+                            lin.weight.data = torch.empty(0, dtype=lin.weight.dtype, device=lin.weight.device)
                     continue
                 r, D = tp.rank, self.D
                 q0, k0 = r * self.H * D, r * self.Hkv * D
-                self.wqkv.append(torch.cat([a.q_proj.weight[q0:q0 + self.H * D], a.k_proj.weight[k0:k0 + self.Hkv * D],
-                                            a.v_proj.weight[k0:k0 + self.Hkv * D]], dim=0).contiguous())
-                self.wo.append(a.o_proj.weight[:, q0:q0 + self.H * D].contiguous())
+                self.wqkv.append(pack(torch.cat([a.q_proj.weight[q0:q0 + self.H * D], a.k_proj.weight[k0:k0 + self.Hkv * D],
+                                                 a.v_proj.weight[k0:k0 + self.Hkv * D]], dim=0).contiguous()))
+                self.wo.append(pack(a.o_proj.weight[:, q0:q0 + self.H * D].contiguous()))
                 fl = f.gate_proj.weight.shape[0] // tp.world
-                self.wgu.append(torch.cat([f.gate_proj.weight[r * fl:(r + 1) * fl], f.up_proj.weight[r * fl:(r + 1) * fl]],
-                                          dim=0).contiguous())
-                self.wdown.append(f.down_proj.weight[:, r * fl:(r + 1) * fl].contiguous())
+                self.wgu.append(pack(torch.cat([f.gate_proj.weight[r * fl:(r + 1) * fl],
+                                                f.up_proj.weight[r * fl:(r + 1) * fl]], dim=0).contiguous()))
+                self.wdown.append(pack(f.down_proj.weight[:, r * fl:(r + 1) * fl].contiguous()))
                 for lin in (a.q_proj, a.k_proj, a.v_proj, a.o_proj, f.gate_proj, f.up_proj, f.down_proj):
                     lin.weight.data = torch.empty(0, dtype=lin.weight.dtype, device=lin.weight.device)
+            self.w_head = pack(self.model.lm_head.weight)
+            tied = self.model.lm_head.weight.data_ptr() == self.model.embed_tokens.weight.data_ptr()
+            if fp8_mode and self.w_head.q is not None and not tied:
+                self.model.lm_head.weight.data = torch.empty(0, dtype=self.model.lm_head.weight.dtype,
+                                                             device=self.model.lm_head.weight.device)
 
-    def _mm_reduce(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        """x @ w^T summed over the tensor-parallel ranks (row-parallel projection)."""
+    def weight_bytes(self) -> int:
+        """Bytes of projection and LM-head weights this rank streams per decode step."""
+        return sum(W.nbytes() for ws in (self.wqkv, self.wo, self.wgu, self.wdown) for W in ws) + self.w_head.nbytes()
+
+    def _mm_reduce(self, x: torch.Tensor, W: _Weight) -> torch.Tensor:
+        """x @ W^T summed over the tensor-parallel ranks (row-parallel projection)."""
         tp = self.tp
         if tp is None:
-            return self._mm(x, w)
-        T, N = x.shape[0], w.shape[0]
+            return self._mm(x, W)
+        T, N = x.shape[0], W.shape[0]
         if T <= tp.max_rows and x.dtype == torch.bfloat16:
-            ops.decode_linear(x, w, out=tp.ar.input_view(T, N))
+            self._mm(x, W, out=tp.ar.input_view(T, N))
             return tp.ar.reduce(T, N)
-        return tp.all_reduce_big(self._mm(x, w))
+        return tp.all_reduce_big(self._mm(x, W))
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids, gen: Optional[GenerateConfig] = None) -> int:
@@ -301,19 +375,29 @@ class ServingEngine:
         f = self._mm_reduce(ops.swiglu(gu), self.wdown[li])
         return f, res
 
-    def _mm(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        """x @ w^T: split-K streaming GEMM for decode-sized batches, the regular tcgen05 GEMM otherwise (the
-        per-tensor-scaled fp8 GEMM when ``fp8_prefill`` holds an E4M3 copy of ``w``)."""
+    def _mm(self, x: torch.Tensor, W: _Weight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x @ W^T. Decode-sized batches: the weight-streaming GEMM (bf16 or block-scaled fp8 weights, bf16
+        activations). Larger batches: the tcgen05 bf16 GEMM, or for fp8 weights the block-scaled fp8 GEMM with the
+        activations quantised 1 x 128 (the per-tensor-scaled fp8 GEMM when ``fp8_prefill`` holds such a copy)."""
         if x.dtype != torch.bfloat16:
-            return x @ w.t()
-        if x.shape[0] <= 512:
-            return ops.decode_linear(x, w)
-        w8 = self._w8.get(id(w))
+            r = x @ W.w.t()
+            return r if out is None else out.copy_(r)
+        if x.shape[0] <= self.stream_rows:
+            if W.q is not None:
+                return ops.stream_linear(x, W.q, W.s, out=out, pdl=self.pdl)
+            return ops.stream_linear(x, W.w, out=out, pdl=self.pdl)
+        if W.q is not None:
+            from ..ops import fp8
+            qa, sa = fp8.quantize_act(x.contiguous())
+            r = fp8.fp8_gemm(qa, sa, W.q, W.s)
+            return r if out is None else out.copy_(r)
+        w8 = self._w8.get(id(W))
         if w8 is not None:
             from ..ops import fp8
             qa, sa = fp8.quantize_tensor(x)
-            return fp8.fp8_gemm_pertensor(qa, sa, w8[0], w8[1])
-        return ops.gemm_bf16(x, w)
+            r = fp8.fp8_gemm_pertensor(qa, sa, w8[0], w8[1])
+            return r if out is None else out.copy_(r)
+        return ops.gemm_bf16(x, W.w, out=out)
 
     def _forward(self, tokens, positions, slots, tables, lens, prefill_bounds=None, last_rows=None):
         m = self.model
@@ -326,12 +410,25 @@ class ServingEngine:
         h, _ = ops.rms_norm(x, m.norm.weight, m.norm.eps, residual=res)
         if last_rows is not None:
             h = h.index_select(0, last_rows)
-        return self._mm(h.contiguous(), m.lm_head.weight)
+        return self._mm(h.contiguous(), self.w_head)
 
-    def _pick(self, logits: torch.Tensor) -> torch.Tensor:
+    def _pick(self, logits: torch.Tensor, reqs: Optional[List[_Req]] = None) -> torch.Tensor:
+        """Next token per row, on the device. Greedy: arg-max. Otherwise the device sampler; its step comes from a
+        device counter that is advanced right after, so the pair can sit in a captured graph."""
+        if self.repetition_penalty != 1.0 and reqs is not None:
+            n = len(reqs)
+            width = max(len(r.tokens) for r in reqs)
+            hist = torch.zeros((logits.shape[0], width), dtype=torch.int32)
+            lens = torch.zeros(logits.shape[0], dtype=torch.int32)
+            for i, r in enumerate(reqs):
+                hist[i, :len(r.tokens)] = torch.tensor(r.tokens, dtype=torch.int32)
+                lens[i] = len(r.tokens)
+            repetition_penalty_rows_(logits, hist.to(logits.device), lens.to(logits.device), self.repetition_penalty)
         if self.greedy:
             return argmax_rows(logits)
-        return sample_top_p_rows(logits, self.temperature, self.top_p, self.seed, self.steps)
+        out = sample_rows(logits, self.temperature, self.top_k, self.top_p, self.seed, step_counter=self._step_dev)
+        self._step_dev.add_(1)
+        return out
 
     # ------------------------------------------------------------------ scheduling
     def _admit(self) -> List[_Req]:
@@ -371,7 +468,7 @@ class ServingEngine:
         meta = torch.tensor([pos, slots], dtype=torch.int32).to(dev, non_blocking=True)
         last_rows = torch.tensor(last, dtype=torch.int64).to(dev, non_blocking=True)
         logits = self._forward(tokens, meta[0], meta[1], None, None, prefill_bounds=bounds, last_rows=last_rows)
-        nxt = self._pick(logits).cpu().tolist()
+        nxt = self._pick(logits, reqs).cpu().tolist()
         now = time.perf_counter()
         for r, t in zip(reqs, nxt):
             r.t_first = now
@@ -429,7 +526,7 @@ class ServingEngine:
         n = len(reqs)
         A = self._bucket(n) if self.use_cuda_graph else n
         host = self._decode_inputs(reqs, A)
-        if self.use_cuda_graph and self.greedy:
+        if self.use_cuda_graph and self.repetition_penalty == 1.0:
             g = self._graphs.get(A)
             if g is None:
                 g = self._capture(A, host)
@@ -438,7 +535,7 @@ class ServingEngine:
             nxt = g["next"][:n].cpu().tolist()
         else:
             logits = self._run_packed(host.to(self.device, non_blocking=True))
-            nxt = self._pick(logits)[:n].cpu().tolist()
+            nxt = self._pick(logits, reqs)[:n].cpu().tolist()
         for r, t in zip(reqs, nxt):
             self._emit(r, int(t))
         self.stats["decode_tokens"] += n
@@ -452,14 +549,14 @@ class ServingEngine:
         with torch.cuda.stream(stream):
             for _ in range(2):                                # warm-up: lazy allocations, attribute settings
                 logits = self._run_packed(g["inp"])
-                g["next"] = argmax_rows(logits)
+                g["next"] = self._pick(logits)
         torch.cuda.current_stream(dev).wait_stream(stream)
         torch.cuda.synchronize(dev)
         # the warm-up runs appended to the cache at the fed positions; the captured replay overwrites the same slots
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             logits = self._run_packed(g["inp"])
-            g["next"] = argmax_rows(logits)
+            g["next"] = self._pick(logits)
         g["graph"] = graph
         self._graphs[A] = g
         return g
