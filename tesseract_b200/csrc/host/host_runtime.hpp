@@ -91,6 +91,12 @@ std::pair<std::string, int64_t> safetensors_header(const std::string& path);
 void token_mask(const int32_t* table, int64_t num_states, int32_t state, const uint8_t* bytes, const int64_t* offsets,
                 int64_t n_tokens, uint8_t* allowed);
 
+// ---- CPU FP32 GEMM (gemm_f32.cpp): C[M, N] = A[M, K] * op(B); b_nk = B stored [N, K] (a Linear weight)
+bool gemm_avx2_supported();
+int gemm_num_threads(int64_t M, int64_t N, int64_t K, int requested);
+void gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, bool b_nk, float* C, int64_t ldc, int64_t M,
+              int64_t N, int64_t K, int threads);
+
 // ---- CPU decode GEMV, INT8 weights x INT8 activations (gemv_int8.cpp)
 bool gemv_vnni_supported();
 // Per-vector symmetric quantisation: scale = absmax / 127 (1 for a zero vector); returns the scale.

@@ -70,6 +70,23 @@ PYBIND11_MODULE(_tsb_host, m) {
           return out;
         });
 
+  m.def("gemm_avx2_supported", &gemm_avx2_supported);
+  m.def("gemm_num_threads", &gemm_num_threads, py::arg("M"), py::arg("N"), py::arg("K"), py::arg("requested") = 0);
+  m.def("gemm_f32",
+        [](py::array_t<float, py::array::c_style | py::array::forcecast> A,
+           py::array_t<float, py::array::c_style | py::array::forcecast> B, bool b_nk, int threads) {
+          if (A.ndim() != 2 || B.ndim() != 2) throw std::invalid_argument("gemm_f32: A and B must be matrices");
+          const int64_t M = A.shape(0), K = A.shape(1);
+          const int64_t N = b_nk ? B.shape(0) : B.shape(1);
+          if ((b_nk ? B.shape(1) : B.shape(0)) != K) throw std::invalid_argument("gemm_f32: inner dimensions differ");
+          py::array_t<float> C({M, N});
+          {
+            py::gil_scoped_release nogil;
+            gemm_f32(A.data(), K, B.data(), B.shape(1), b_nk, C.mutable_data(), N, M, N, K, threads);
+          }
+          return C;
+        },
+        py::arg("A"), py::arg("B"), py::arg("b_nk") = false, py::arg("threads") = 0);
   m.def("gemv_vnni_supported", &gemv_vnni_supported);
   m.def("quantize_row_int8", [](py::array_t<float, py::array::c_style | py::array::forcecast> x) {
     py::array_t<int8_t> q(x.size());

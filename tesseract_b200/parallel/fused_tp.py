@@ -42,6 +42,7 @@ _native.register_signatures({
     "tsb_reduce_slots": [P, P, I, L, P],
     "tsb_allreduce_oneshot": [PP, PP, P, P, L, I, I, P],
     "tsb_allreduce_twoshot": [PP, PP, P, L, I, I, I, I, F, I, I, L, P],
+    "tsb_allreduce_norm_oneshot": [PP, PP, P, P, P, P, P, I, I, F, I, I, P],
     "tsb_gemm_rs": [P, P, PP, I, I, I, L, L, I, I, I, I, P],
     "tsb_gemm_ag": [P, PP, PP, P, P, P, I, I, I, I, I, I, L, L, I, I, I, I, P, P],
 })
@@ -276,6 +277,21 @@ class SymmAllReduce:
         self.parity ^= 1
         self.calls += 1
         return out
+
+    def reduce_norm(self, rows: int, cols: int, residual, weight: torch.Tensor, eps: float):
+        """The all-reduce fused with the residual add and RMSNorm that follow it in a transformer block: returns
+        ``(rmsnorm(h) * weight, h)`` with ``h = sum over ranks + residual`` (``residual`` may be None)."""
+        y = torch.empty((rows, cols), dtype=torch.bfloat16, device=self.device)
+        h = torch.empty((rows, cols), dtype=torch.bfloat16, device=self.device)
+        check(lib().tsb_allreduce_norm_oneshot(self._ptrs[self.parity], self.flags.ptr_array, self.state.data_ptr(),
+                                               residual.data_ptr() if residual is not None else None,
+                                               weight.data_ptr(), y.data_ptr(), h.data_ptr(), rows, cols, float(eps),
+                                               self.rank, self.world,
+                                               torch.cuda.current_stream(self.device).cuda_stream),
+              "tsb_allreduce_norm_oneshot")
+        self.parity ^= 1
+        self.calls += 1
+        return y, h
 
     def close(self) -> None:
         self.buf.close()

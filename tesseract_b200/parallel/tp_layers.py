@@ -13,6 +13,7 @@ and vice versa, so the same two fused primitives serve both directions.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -71,13 +72,25 @@ def _mm(a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False, out=None, a
     return r
 
 
+# Token counts (whole step, all ranks) from which the fused kernels are used; below them the collective + GEMM pair
+# wins (measured at TP = 8: the gather kernel loses to NCCL + GEMM at 4096 tokens, the scatter kernel wins from the
+# smallest size it can run). Both need whole 128-row tiles per rank.
+_FUSED_MIN_TOKENS = {"ag": int(os.environ.get("TESSERACT_TP_FUSED_MIN_AG", "8192")),
+                     "rs": int(os.environ.get("TESSERACT_TP_FUSED_MIN_RS", "1024"))}
+
+
+def _fused_applies(ctx: TPContext, x: torch.Tensor, tokens: int, rows_per_rank: int, kind: str) -> bool:
+    return (ctx.impl == "fused" and ctx.fused is not None and x.is_cuda and x.dtype == torch.bfloat16
+            and rows_per_rank % 128 == 0 and tokens >= _FUSED_MIN_TOKENS[kind])
+
+
 def ag_matmul(ctx: TPContext, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool = False, keep: bool = True,
               sync_keep: bool = True):
     """(all-gather rows of x_local) @ op(w)^T. Returns (y [T, N], x_full [T, K]). ``keep=False`` allows x_full to
     be a transient buffer that is only valid until the next gathered matmul. With ``sync_keep=False`` the fused
     path may still be filling x_full on a side stream when this returns; the caller then calls
     ``ctx.fused.wait_keep()`` before it reads x_full."""
-    if ctx.impl == "fused" and ctx.fused is not None and x_local.is_cuda:
+    if _fused_applies(ctx, x_local, x_local.shape[0] * ctx.size, x_local.shape[0], "ag"):
         out = ctx.fused.ag_gemm(x_local, w, b_mn=b_mn, keep=keep)
         if sync_keep:
             ctx.fused.wait_keep()
@@ -88,7 +101,7 @@ def ag_matmul(ctx: TPContext, x_local: torch.Tensor, w: torch.Tensor, b_mn: bool
 
 def matmul_rs(ctx: TPContext, x: torch.Tensor, w: torch.Tensor, b_mn: bool = False) -> torch.Tensor:
     """reduce-scatter over ranks of x @ op(w)^T along rows. Returns y_local [T / tp, N]."""
-    if ctx.impl == "fused" and ctx.fused is not None and x.is_cuda:
+    if _fused_applies(ctx, x, x.shape[0], x.shape[0] // ctx.size, "rs"):
         return ctx.fused.gemm_rs(x, w, b_mn=b_mn)
     return ctx.reduce_scatter_rows(_mm(x, w, b_mn=b_mn))
 

@@ -258,16 +258,26 @@ class ServingEngine:
         """Bytes of projection and LM-head weights this rank streams per decode step."""
         return sum(W.nbytes() for ws in (self.wqkv, self.wo, self.wgu, self.wdown) for W in ws) + self.w_head.nbytes()
 
-    def _mm_reduce(self, x: torch.Tensor, W: _Weight) -> torch.Tensor:
-        """x @ W^T summed over the tensor-parallel ranks (row-parallel projection)."""
+    def _mm_reduce(self, x: torch.Tensor, W: _Weight):
+        """x @ W^T of a row-parallel projection. Returns the product summed over the tensor-parallel ranks, or --
+        for batches that fit the peer-memory all-reduce -- ``None`` after leaving this rank's partial product in the
+        all-reduce input buffer: the caller then finishes with ``_norm`` (sum + residual + RMSNorm in one kernel)."""
         tp = self.tp
         if tp is None:
             return self._mm(x, W)
         T, N = x.shape[0], W.shape[0]
         if T <= tp.max_rows and x.dtype == torch.bfloat16:
             self._mm(x, W, out=tp.ar.input_view(T, N))
-            return tp.ar.reduce(T, N)
+            return None
         return tp.all_reduce_big(self._mm(x, W))
+
+    def _norm(self, x, res, norm, rows: int):
+        """(rmsnorm(x + res) * weight, x + res); ``x is None`` means the partial sums wait in the all-reduce buffer."""
+        if x is None:
+            return self.tp.ar.reduce_norm(rows, norm.weight.shape[0], res, norm.weight, norm.eps)
+        if res is None:
+            return ops.rms_norm(x, norm.weight, norm.eps), x
+        return ops.rms_norm(x, norm.weight, norm.eps, residual=res)
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_ids, gen: Optional[GenerateConfig] = None) -> int:
@@ -332,12 +342,9 @@ class ServingEngine:
     def _layer(self, li: int, x, res, positions, slots, tables, lens, prefill_bounds=None):
         blk = self.model.layers[li]
         H, Hkv, D = self.H, self.Hkv, self.D
-        if res is None:
-            h, res = ops.rms_norm(x, blk.norm_1.weight, blk.norm_1.eps), x
-        else:
-            h, res = ops.rms_norm(x, blk.norm_1.weight, blk.norm_1.eps, residual=res)
+        T = positions.shape[0]
+        h, res = self._norm(x, res, blk.norm_1, T)
         qkv = self._mm(h, self.wqkv[li])
-        T = qkv.shape[0]
         ks = self.k_scale[li] if self.k_scale is not None else None
         vs = self.v_scale[li] if self.v_scale is not None else None
         rope = self.model.rope
@@ -370,7 +377,7 @@ class ServingEngine:
                         for (a, b) in spans]
                 o = torch.cat(outs, dim=0) if len(outs) > 1 else outs[0]
         a_out = self._mm_reduce(o, self.wo[li])
-        h2, res = ops.rms_norm(a_out, blk.norm_2.weight, blk.norm_2.eps, residual=res)
+        h2, res = self._norm(a_out, res, blk.norm_2, T)
         gu = self._mm(h2, self.wgu[li])
         f = self._mm_reduce(ops.swiglu(gu), self.wdown[li])
         return f, res
@@ -407,7 +414,7 @@ class ServingEngine:
         res = None
         for li in range(self.L):
             x, res = self._layer(li, x, res, positions, slots, tables, lens, prefill_bounds)
-        h, _ = ops.rms_norm(x, m.norm.weight, m.norm.eps, residual=res)
+        h, _ = self._norm(x, res, m.norm, tokens.shape[0])
         if last_rows is not None:
             h = h.index_select(0, last_rows)
         return self._mm(h.contiguous(), self.w_head)

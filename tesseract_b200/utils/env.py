@@ -37,6 +37,10 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_DP_COMM", "symm", "data-parallel gradient all-reduce: symm (two-shot peer-memory kernel) | nccl"),
     EnvVar("TESSERACT_DP_CTAS", "0", "CTAs of the gradient all-reduce kernel (0 = 48)"),
     EnvVar("TESSERACT_PEAKS_FILE", "", "benchmarks: JSON file with the measured hbm_gbs / bf16_tflops of this GPU (roofline denominators)"),
+    EnvVar("TESSERACT_TP_FUSED_MIN_AG", "8192", "tokens per step from which all-gather -> GEMM runs as the fused kernel"),
+    EnvVar("TESSERACT_TP_FUSED_MIN_RS", "1024", "tokens per step from which GEMM -> reduce-scatter runs as the fused kernel"),
+    EnvVar("TESSERACT_PDL", "1", "serving decode GEMMs: 1 (programmatic dependent launch) | 0"),
+    EnvVar("TESSERACT_CPU_GEMM", "torch", "2-D fp32 CPU products of ops.cpu_gemm.matmul_f32 callers: torch | native (host-runtime AVX2 GEMM)"),
     EnvVar("TESSERACT_SWIGLU", "2", "SwiGLU kernels: 2 (row-wise, two vector pairs per thread) | 0 (flat kernel, for A/B runs)"),
 ]}
 

@@ -1,0 +1,38 @@
+"""Native CPU FP32 GEMM of the host runtime against a float64 product (cf. the reference's CPU matmul cases,
+tests/ops/test_matmul.cpp, and its thread-cap rule, src/ops/cpu/GemmAvx2.cpp:25-55)."""
+import pytest
+import torch
+
+from tesseract_b200.ops import cpu_gemm
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 7, 3), (6, 16, 256), (7, 17, 257), (97, 2049, 33), (200, 130, 600)])
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_matmul_f32_matches_float64(M, N, K, b_is_nk):
+    g = torch.Generator().manual_seed(M * 31 + N)
+    a = torch.randn(M, K, generator=g)
+    b = torch.randn(K, N, generator=g)
+    want = (a.double() @ b.double()).float()
+    got = cpu_gemm.matmul_f32(a, b.t().contiguous() if b_is_nk else b, b_is_nk=b_is_nk)
+    assert got.shape == (M, N)
+    assert (got - want).abs().max() <= 2e-5 * max(1.0, float(want.abs().max())) * max(1, K // 64)
+
+
+def test_thread_count_grows_with_work_and_respects_the_cap(monkeypatch):
+    assert cpu_gemm.gemm_num_threads(8, 8, 8) == 1                      # tiny problems stay on one thread
+    big = cpu_gemm.gemm_num_threads(2048, 2048, 2048)
+    assert big >= 1
+    monkeypatch.setenv("TESSERACT_GEMM_MAX_THREADS", "1")
+    assert cpu_gemm.gemm_num_threads(2048, 2048, 2048) == 1
+    monkeypatch.setenv("TESSERACT_GEMM_MAX_THREADS", "2")
+    assert cpu_gemm.gemm_num_threads(2048, 2048, 2048, requested=1) == 1
+    a = torch.randn(64, 64)
+    assert torch.allclose(cpu_gemm.matmul_f32(a, a, threads=1), a @ a, atol=1e-4)
+
+
+def test_python_twin_and_errors(monkeypatch):
+    monkeypatch.setenv("TESSERACT_HOST", "python")
+    a, b = torch.randn(9, 5), torch.randn(5, 4)
+    assert torch.allclose(cpu_gemm.matmul_f32(a, b), a @ b, atol=1e-6)
+    with pytest.raises(ValueError):
+        cpu_gemm.matmul_f32(a, torch.randn(6, 4))

@@ -104,7 +104,7 @@ def _free_port():
 def _worker(rank, world, port, q):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      NCCL_NVLS_ENABLE="0")
+                      NCCL_NVLS_ENABLE="0", TESSERACT_TP_FUSED_MIN_AG="0", TESSERACT_TP_FUSED_MIN_RS="0")
     try:
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)
