@@ -96,15 +96,21 @@ def quantize_weight(w: torch.Tensor):
     return q, sb
 
 
-def fp8_gemm(qa: torch.Tensor, sa: torch.Tensor, qb: torch.Tensor, sb: torch.Tensor) -> torch.Tensor:
-    """bf16 [M, N] = block-scaled qa [M, K] @ qb [N, K]^T on the tensor cores (fp32 accumulation)."""
+def fp8_gemm(qa: torch.Tensor, sa: torch.Tensor, qb: torch.Tensor, sb: torch.Tensor,
+             out: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 [M, N] = block-scaled qa [M, K] @ qb [N, K]^T on the tensor cores (fp32 accumulation); ``out`` (bf16,
+    unit stride in the last dimension) receives the result when given."""
     M, K = qa.shape
     N = qb.shape[0]
     if not _native_ok(qa):
-        return fp8_gemm_ref(qa, sa, qb, sb)
+        r = fp8_gemm_ref(qa, sa, qb, sb)
+        return r if out is None else out.copy_(r)
     if not (qa.is_contiguous() and qb.is_contiguous() and sa.is_contiguous() and sb.is_contiguous()):
         raise ValueError("fp8_gemm: operands must be contiguous")
-    out = torch.empty((M, N), dtype=torch.bfloat16, device=qa.device)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=qa.device)
+    elif out.shape != (M, N) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise ValueError("fp8_gemm: out must be a bf16 [M, N] tensor with contiguous rows")
     check(lib().tsb_gemm_fp8_blockscaled(qa.data_ptr(), qb.data_ptr(), out.data_ptr(), sa.data_ptr(), sb.data_ptr(), M, N,
                                          K, out.stride(0), stream_ptr(qa.device)), "tsb_gemm_fp8_blockscaled")
     return out

@@ -120,28 +120,70 @@ _native.register_signatures({
 })
 
 
+_native.register_signatures({
+    "tsb_gemm_decode_wq_plan": [_native.I, _native.I, _native.I, _native.I, _native.P, _native.P, _native.P, _native.P],
+})
+
+
+def stream_linear_plan(M: int, N: int, K: int, fp8: bool, bn: int = 0):
+    """(tile width, K split) the streaming kernel chooses on the current device (``bn`` > 0 fixes the width)."""
+    import ctypes
+    b, s_, st, res = ctypes.c_int(bn), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+    _native.check(_native.lib().tsb_gemm_decode_wq_plan(M, N, K, int(fp8), ctypes.byref(b), ctypes.byref(s_),
+                                                        ctypes.byref(st), ctypes.byref(res)), "tsb_gemm_decode_wq_plan")
+    return b.value, s_.value
+
+
+def pack_fp8_weight(q: torch.Tensor, bn: int) -> torch.Tensor:
+    """E4M3 payload [N, K] -> tile-major [ceil(N / bn), K / 64, bn, 64] (rows past N zero): the layout in which every
+    tile the streaming kernel loads is one contiguous run of HBM. K must be a multiple of 64."""
+    N, K = q.shape
+    if K % 64 or bn % 16 or not 32 <= bn <= 256:
+        raise ValueError("pack_fp8_weight: K % 64 == 0 and bn a multiple of 16 in [32, 256]")
+    tiles = (N + bn - 1) // bn
+    qp = q.view(torch.uint8)
+    if tiles * bn != N:
+        qp = torch.cat([qp, torch.zeros(tiles * bn - N, K, dtype=torch.uint8, device=q.device)], dim=0)
+    return qp.view(tiles, bn, K // 64, 64).permute(0, 2, 1, 3).contiguous()
+
+
+def unpack_fp8_weight(packed: torch.Tensor, N: int) -> torch.Tensor:
+    """Inverse of ``pack_fp8_weight``: uint8 [N, K]."""
+    tiles, nkb, bn, _ = packed.shape
+    return packed.permute(0, 2, 1, 3).reshape(tiles * bn, nkb * 64)[:N]
+
+
 def stream_linear(x: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor | None = None,
-                  out: torch.Tensor | None = None, pdl: bool = False, bn: int = 0, split: int = 0) -> torch.Tensor:
+                  out: torch.Tensor | None = None, pdl: bool = False, bn: int = 0, split: int = 0,
+                  packed_n: int = 0) -> torch.Tensor:
     """x [M, K] (bf16) @ W^T for decode-sized M with the weight-streaming kernel (``csrc/gemm_decode_wq.cu``).
 
     ``w`` is bf16 [N, K], or -- with ``w_scale`` (fp32 [ceil(N/128), ceil(K/128)]) -- the E4M3 payload (uint8 /
-    float8_e4m3fn [N, K]) of a 128 x 128 block-scaled weight as ``ops.fp8.quantize_weight`` produces it. Activations
-    are not quantised. ``pdl=True`` launches with programmatic stream serialisation: the kernel may begin (and
-    prefetch weights) while the previous kernel of the stream is still running. CPU tensors / other dtypes run the
-    torch restatement."""
+    float8_e4m3fn [N, K]) of a 128 x 128 block-scaled weight as ``ops.fp8.quantize_weight`` produces it, or that
+    payload packed tile-major by ``pack_fp8_weight`` (then ``packed_n`` = N and ``bn`` = the packing width).
+    Activations are not quantised. ``pdl=True`` launches with programmatic stream serialisation: the kernel may begin
+    (and prefetch weights) while the previous kernel of the stream is still running. CPU tensors / other dtypes run
+    the torch restatement."""
     M, K = x.shape
-    N = w.shape[0]
+    packed = packed_n > 0
+    if packed:
+        if w_scale is None or w.dim() != 4 or w.shape[3] != 64 or w.shape[1] * 64 != K or w.shape[2] != bn:
+            raise ValueError("stream_linear: packed weights are [tiles, K / 64, bn, 64] with their block scales")
+        N = packed_n
+    else:
+        N = w.shape[0]
     fp8 = w_scale is not None
     if not (x.is_cuda and x.dtype == torch.bfloat16 and _native.available()):
-        wf = w.float() if not fp8 else _dequant_block128(w, w_scale)
+        wf = w.float() if not fp8 else _dequant_block128(unpack_fp8_weight(w, N) if packed else w, w_scale)
         r = (x.float() @ wf.t()).to(x.dtype)
         return r if out is None else out.copy_(r)
-    if x.stride(1) != 1 or w.stride(1) != 1:
+    if x.stride(1) != 1 or (not packed and w.stride(1) != 1) or (packed and not w.is_contiguous()):
         raise ValueError("stream_linear: rows must be contiguous")
     res = out if out is not None else torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
     rc = _native.lib().tsb_gemm_decode_wq(x.data_ptr(), w.data_ptr(), w_scale.data_ptr() if fp8 else None,
-                                          res.data_ptr(), M, N, K, x.stride(0), w.stride(0), res.stride(0), int(fp8),
-                                          bn, split, int(pdl), _native.stream_ptr(x.device))
+                                          res.data_ptr(), M, N, K, x.stride(0), 64 if packed else w.stride(0),
+                                          res.stride(0), 2 if packed else int(fp8), bn, split,
+                                          int(pdl) if isinstance(pdl, bool) else pdl, _native.stream_ptr(x.device))
     _native.check(rc, "tsb_gemm_decode_wq")
     return res
 

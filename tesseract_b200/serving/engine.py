@@ -161,7 +161,8 @@ class ServingEngine:
         # programmatic dependent launch of the decode GEMMs: they start (and prefetch weights) under the tail of the
         # kernel before them
         self.pdl = os.environ.get("TESSERACT_PDL", "1") == "1"
-        self.stream_rows = 256       # batches up to this many rows go through the weight-streaming GEMM
+        self.stream_rows = 256       # batches up to this many rows count as decode-sized
+        self.decode_gemm = os.environ.get("TESSERACT_SERVE_DECODE_GEMM", "auto")   # auto | stream (always the streaming kernel)
         c, mc = self.cfg, model.config
         self.device = model._device()
         if self.device.type != "cuda" or mc.dtype not in (torch.bfloat16, torch.float16):
@@ -389,15 +390,25 @@ class ServingEngine:
         if x.dtype != torch.bfloat16:
             r = x @ W.w.t()
             return r if out is None else out.copy_(r)
-        if x.shape[0] <= self.stream_rows:
-            if W.q is not None:
+        M = x.shape[0]
+        if M <= self.stream_rows:
+            # measured on B200 (layer shapes of the 8 B model): up to 128 rows the streaming kernel is the fastest
+            # path for both weight formats; above, it streams (and widens) the weights once per 128-row block, and
+            # the cluster split-K kernel (bf16) / the block-scaled fp8 tensor-core GEMM (fp8) are faster
+            N, K = W.shape
+            if W.q is None:
+                if M <= 128 or self.decode_gemm == "stream":
+                    return ops.stream_linear(x, W.w, out=out, pdl=self.pdl)
+                return ops.decode_linear(x, W.w, out=out)
+            # fp8 weights: the streaming kernel (bf16 activations, weights widened on the fly) pays off for the
+            # K-heavy row-parallel products; elsewhere the block-scaled fp8 GEMM with 1 x 128 activation scales is as
+            # fast and streams the weights once whatever the batch
+            if self.decode_gemm == "stream" or (M <= 128 and K >= 2 * N):
                 return ops.stream_linear(x, W.q, W.s, out=out, pdl=self.pdl)
-            return ops.stream_linear(x, W.w, out=out, pdl=self.pdl)
         if W.q is not None:
             from ..ops import fp8
             qa, sa = fp8.quantize_act(x.contiguous())
-            r = fp8.fp8_gemm(qa, sa, W.q, W.s)
-            return r if out is None else out.copy_(r)
+            return fp8.fp8_gemm(qa, sa, W.q, W.s, out=out)
         w8 = self._w8.get(id(W))
         if w8 is not None:
             from ..ops import fp8

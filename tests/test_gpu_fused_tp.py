@@ -357,7 +357,8 @@ def test_twoshot_allreduce_emulated_ranks_on_one_gpu():
         code = 1 if dtype == torch.bfloat16 else 0
         for phase in (1, 2, 4):
             for r in range(world):
-                if phase == 4:                       # the peers' "done" flags, as concurrent ranks would have set them
+                flags[r][:world] = 1                 # the peers' "ready" flags, as concurrent ranks would have set them
+                if phase == 4:                       # ... and their "done" flags
                     flags[r][16:16 + world] = 1
                 _native.check(_native.lib().tsb_allreduce_twoshot(parr, farr, states[r].data_ptr(), n, code, r, world, 1,
                                                                   1.0 / world, 7, phase, 200_000_000, stream),
