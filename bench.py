@@ -264,7 +264,7 @@ def _mesh_list(spec: str, world: int):
     if world == 1:
         return [("auto", 0, "single")]
     if spec == "auto":
-        spec = {2: "tp2", 4: "tp4,tp2", 8: "tp8,tp2"}.get(world, f"tp{world}")
+        spec = {2: "tp2", 4: "tp4,tp2", 8: "tp8,tp4,tp2"}.get(world, f"tp{world}")
     out = []
     for item in spec.split(","):
         item = item.strip().lower()

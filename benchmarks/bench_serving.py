@@ -106,7 +106,8 @@ def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, tempera
         "requests": requests, "kv": "int8" if kv_int8 else "bf16", "fp8_prefill": bool(fp8_prefill), "sampling": "greedy" if temperature <= 0 else f"top_p={top_p}",
         "prefill_tok_s": m["prefill_tok_s"], "decode_tok_s": m["decode_tok_s"], "ttft_p50_ms": m["ttft_p50_ms"],
         "end_to_end_s": wall, "generated_tokens": gen_tokens, "total_tok_s": (total_tokens) / wall,
-        "steps": m["steps"], "max_batch": max_batch, "block_size": block, "cuda_graph": cuda_graph,
+        "steps": m["steps"], "decode_ms_per_step": m["decode_ms_per_step"],
+        "decode_gpu_ms_per_step": m["decode_gpu_ms_per_step"], "max_batch": max_batch, "block_size": block, "cuda_graph": cuda_graph,
         "weights": "fp8-e4m3-block128 (bf16 activations on the decode path, 1x128 fp8 on the prompt path)"
                    if eng.weights == "fp8" else "bf16",
         "weight_bytes_per_rank": eng.weight_bytes(), "layers": len(model.layers),

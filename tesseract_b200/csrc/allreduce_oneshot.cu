@@ -24,6 +24,7 @@ struct ArArgs {
 
 __global__ void __launch_bounds__(256)
 allreduce_oneshot_kernel(ArArgs a, __nv_bfloat16* __restrict__ out, long long nvec, int rank, int world, int* status) {
+  pdl_trigger();
   __shared__ int s_epoch;
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
@@ -103,6 +104,7 @@ __global__ void __launch_bounds__(kNormThreads)
 allreduce_norm_oneshot_kernel(ArArgs a, const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ weight,
                               __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h, int cols, float eps, int rank,
                               int world, int* status) {
+  pdl_trigger();
   __shared__ int s_epoch;
   __shared__ int s_ok;
   __shared__ float s_red[kNormThreads / 32];

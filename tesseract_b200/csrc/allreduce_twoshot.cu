@@ -124,19 +124,35 @@ allreduce_twoshot_kernel(Ar2Args a, long long nvec, int rank, int world, int epo
     const long long lo = rank * per;
     const long long hi = lo + per < nvec ? lo + per : nvec;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    for (long long i = lo + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < hi; i += stride) {
-      uint4 raw[kMaxWorld];
+    // two vectors per thread and pass: 2 * world 16-byte loads are in flight before the first sum (NVLink latency is
+    // a few microseconds; the kernel runs on few CTAs, so every thread has to keep several requests outstanding)
+    for (long long i0 = lo + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < hi; i0 += 2 * stride) {
+      const long long i1 = i0 + stride;
+      const bool two = i1 < hi;
+      uint4 raw0[kMaxWorld], raw1[kMaxWorld];
 #pragma unroll
       for (int r = 0; r < kMaxWorld; ++r)
-        if (r < world) raw[r] = reinterpret_cast<const uint4*>(a.peer[r])[i];
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (r < world) raw0[r] = reinterpret_cast<const uint4*>(a.peer[r])[i0];
 #pragma unroll
       for (int r = 0; r < kMaxWorld; ++r)
-        if (r < world) Vec16<T>::add(acc, raw[r]);
-      const uint4 o = Vec16<T>::pack(acc, scale);
+        if (r < world && two) raw1[r] = reinterpret_cast<const uint4*>(a.peer[r])[i1];
+      float acc0[8] = {0, 0, 0, 0, 0, 0, 0, 0}, acc1[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
       for (int r = 0; r < kMaxWorld; ++r)
-        if (r < world) reinterpret_cast<uint4*>(a.peer[r])[i] = o;
+        if (r < world) Vec16<T>::add(acc0, raw0[r]);
+      const uint4 o0 = Vec16<T>::pack(acc0, scale);
+#pragma unroll
+      for (int r = 0; r < kMaxWorld; ++r)
+        if (r < world) reinterpret_cast<uint4*>(a.peer[r])[i0] = o0;
+      if (two) {
+#pragma unroll
+        for (int r = 0; r < kMaxWorld; ++r)
+          if (r < world) Vec16<T>::add(acc1, raw1[r]);
+        const uint4 o1 = Vec16<T>::pack(acc1, scale);
+#pragma unroll
+        for (int r = 0; r < kMaxWorld; ++r)
+          if (r < world) reinterpret_cast<uint4*>(a.peer[r])[i1] = o1;
+      }
     }
   }
   __syncthreads();
@@ -163,7 +179,7 @@ allreduce_twoshot_kernel(Ar2Args a, long long nvec, int rank, int world, int epo
 //   peer[r]: the bucket inside rank r's symmetric buffer as mapped in this process (16-byte aligned);
 //   peer_flags[r]: rank r's flag pad, int32 [32], zero at allocation, used by this call sequence only;
 //   state: local int32 [2], zero at allocation; epoch: number of this call (1, 2, ...; compared modulo 2^32);
-//   dtype: 1 bf16 (n % 8 == 0), 0 fp32 (n % 4 == 0); ctas: grid size (<= 0: 48); limit_cycles <= 0: about a second.
+//   dtype: 1 bf16 (n % 8 == 0), 0 fp32 (n % 4 == 0); ctas: grid size (<= 0: 64); limit_cycles <= 0: about a second.
 //   Every rank issues the same calls in the same order.
 TSB_EXPORT int tsb_allreduce_twoshot(void* const* peer, void* const* peer_flags, int* state, long long n, int dtype,
                                      int rank, int world, int epoch, float scale, int ctas, int phase_mask,
@@ -179,7 +195,7 @@ TSB_EXPORT int tsb_allreduce_twoshot(void* const* peer, void* const* peer_flags,
   }
   a.state = state;
   const long long nvec = n / (dtype == 1 ? 8 : 4);
-  int grid = ctas > 0 ? ctas : 48;
+  int grid = ctas > 0 ? ctas : 64;
   const long long need = (nvec / world + 255) / 256;
   if (need < grid) grid = static_cast<int>(need > 0 ? need : 1);
   const long long limit = limit_cycles > 0 ? limit_cycles : kWaitCycleLimit;

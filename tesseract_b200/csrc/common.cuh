@@ -94,6 +94,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel that calls this lets a successor launched with programmatic stream serialisation start its prologue (and
+// whatever does not depend on this kernel's results) while this kernel is still running; successors launched the
+// ordinary way are unaffected. Called first thing by the small kernels that precede the decode GEMMs.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -275,6 +275,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(D)
 decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, T* __restrict__ out,
                     int splits) {
+  pdl_trigger();
   const long long ah = blockIdx.x;  // a * H + h
   const int d = threadIdx.x;
   float nm = -INFINITY;

@@ -89,6 +89,7 @@ struct MmaDecParams {
 template <typename T, int D, bool INT8>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_mma_kernel(MmaDecParams p) {
+  pdl_trigger();
   // INT8 pools run their products in fp16 whatever the model type: int8 -> fp16 is one byte-permute and half a
   // subtract per element (1024 + u is exact in fp16), and |k|, |v| <= 128 with fp32 accumulation loses nothing.
   using MT = typename std::conditional<INT8, __half, T>::type;

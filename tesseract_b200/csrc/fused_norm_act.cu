@@ -62,6 +62,7 @@ template <typename T, int MAXV>
 __global__ void __launch_bounds__(256)
 rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w, T* __restrict__ y,
                    T* __restrict__ h_out, float* __restrict__ rstd_out, int rows, int D, float eps) {
+  pdl_trigger();
   __shared__ float red[32];
   const int nvec = D / 8;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -134,6 +135,7 @@ template <typename T, int MAXV>
 __global__ void __launch_bounds__(256)
 rmsnorm_fwd_pf_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w, T* __restrict__ y,
                       T* __restrict__ h_out, float* __restrict__ rstd_out, int rows, int D, float eps) {
+  pdl_trigger();
   __shared__ float red[32];
   const int nvec = D / 8;
   Raw8<T> nx[MAXV], nr[MAXV];
@@ -273,6 +275,7 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, T* __r
 template <typename T>
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows, int F) {
+  pdl_trigger();
   const long long nvec = rows * (F / 8);
   const int vpr = F / 8;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
@@ -291,6 +294,7 @@ swiglu_fwd_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long 
 template <typename T, int UNR>
 __global__ void __launch_bounds__(256)
 swiglu_fwd_rows_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int F) {
+  pdl_trigger();
   const int vpr = F / 8;
   for (int row = blockIdx.y; row < rows; row += gridDim.y) {
     const T* gp = gate_up + static_cast<size_t>(row) * 2 * F;

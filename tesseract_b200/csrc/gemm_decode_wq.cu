@@ -175,7 +175,7 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     mbar_fence_init();
     tma_prefetch_desc(&tmX);
     tma_prefetch_desc(&tmW);
-    pdl_launch_dependents();     // whatever follows in the stream may start its own prologue
+    pdl_trigger();     // whatever follows in the stream may start its own prologue
   }
   if (warp == 1) {
     tmem_alloc(&tmem_base_smem, kMaxBN);

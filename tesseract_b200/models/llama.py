@@ -246,6 +246,10 @@ class LlamaModel(Module):
                 if res is not None:
                     res = red.mark(res, red.block_bucket0 + li)
             x, res = blk.forward_fused(x, res)
+        if red is not None:
+            tail = red.tail_buckets(len(self.layers))
+            if tail:
+                x = red.mark(x, tail)
         if res is None:
             return self.norm(x)
         h, _ = self.norm(x, res)

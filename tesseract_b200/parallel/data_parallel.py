@@ -27,7 +27,9 @@ class _BucketMarker(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        ctx.reducer._bucket_ready(ctx.bucket_id)
+        ids = ctx.bucket_id if isinstance(ctx.bucket_id, (tuple, list)) else (ctx.bucket_id,)
+        for bid in ids:
+            ctx.reducer._bucket_ready(bid)
         return g, None, None
 
 
@@ -38,6 +40,7 @@ class GradReducer:
         import torch.distributed as dist
         self.arena, self.group, self.buckets, self.average = arena, group, buckets, average
         self.symm = symm
+        self.block_bucket0 = 0
         self.world = dist.get_world_size(group)
         self._dist = dist
         self._last = False
@@ -75,10 +78,18 @@ class GradReducer:
             out[0] = (0, out[0][1])
         return out
 
-    def mark(self, x: torch.Tensor, bucket_id: int) -> torch.Tensor:
+    def mark(self, x: torch.Tensor, bucket_id) -> torch.Tensor:
+        """Identity whose backward announces that the gradients of bucket ``bucket_id`` (an index or several) are
+        complete."""
         if not (torch.is_grad_enabled() and x.requires_grad) or self.world == 1:
             return x
         return _BucketMarker.apply(x, self, bucket_id)
+
+    def tail_buckets(self, num_blocks: int):
+        """Buckets behind the last transformer block (final norm, head). With the fused head + loss their gradients are
+        complete as soon as the backward pass has left the final norm, so they are reduced under the whole rest of
+        the backward pass instead of after it."""
+        return tuple(range(self.block_bucket0 + num_blocks, len(self.buckets)))
 
     def begin_step(self) -> None:
         self._done = [False] * len(self.buckets)

@@ -202,7 +202,9 @@ class ServingEngine:
         self.use_cuda_graph = use_cuda_graph
         self._graphs: Dict[int, dict] = {}
         self._host_inputs: Dict[int, torch.Tensor] = {}
-        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0}
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "decode_gpu_s": 0.0,
+                      "decode_steps": 0}
+        self._step_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
 
     # ------------------------------------------------------------------ weights
     def _fuse_weights(self) -> None:
@@ -548,15 +550,20 @@ class ServingEngine:
             g = self._graphs.get(A)
             if g is None:
                 g = self._capture(A, host)
+            ev = self._step_events
             g["inp"].copy_(host, non_blocking=True)
+            ev[0].record()
             g["graph"].replay()
+            ev[1].record()
             nxt = g["next"][:n].cpu().tolist()
+            self.stats["decode_gpu_s"] += ev[0].elapsed_time(ev[1]) * 1e-3   # device time of the captured step
         else:
             logits = self._run_packed(host.to(self.device, non_blocking=True))
             nxt = self._pick(logits, reqs)[:n].cpu().tolist()
         for r, t in zip(reqs, nxt):
             self._emit(r, int(t))
         self.stats["decode_tokens"] += n
+        self.stats["decode_steps"] += 1
         self.stats["decode_s"] += time.perf_counter() - t0
 
     def _capture(self, A: int, host: torch.Tensor) -> dict:
@@ -606,4 +613,7 @@ class ServingEngine:
             "decode_tok_s": s["decode_tokens"] / s["decode_s"] if s["decode_s"] > 0 else 0.0,
             "ttft_p50_ms": ttft[len(ttft) // 2] if ttft else 0.0,
             "steps": self.steps,
+            # wall time of a decode step against the device time of its captured graph: the difference is host work
+            "decode_ms_per_step": 1e3 * s["decode_s"] / max(1, s["decode_steps"]),
+            "decode_gpu_ms_per_step": 1e3 * s["decode_gpu_s"] / max(1, s["decode_steps"]),
         }

@@ -35,7 +35,7 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_REF_TIME_BUDGET", "780", "bench.py --impl reference: seconds the reference arm may take in total"),
     EnvVar("TESSERACT_REFERENCE_DIR", "/root/reference", "baseline/build_reference.py: source tree of the reference to build"),
     EnvVar("TESSERACT_DP_COMM", "symm", "data-parallel gradient all-reduce: symm (two-shot peer-memory kernel) | nccl"),
-    EnvVar("TESSERACT_DP_CTAS", "0", "CTAs of the gradient all-reduce kernel (0 = 48)"),
+    EnvVar("TESSERACT_DP_CTAS", "0", "CTAs of the gradient all-reduce kernel (0 = 64)"),
     EnvVar("TESSERACT_PEAKS_FILE", "", "benchmarks: JSON file with the measured hbm_gbs / bf16_tflops of this GPU (roofline denominators)"),
     EnvVar("TESSERACT_TP_FUSED_MIN_AG", "8192", "tokens per step from which all-gather -> GEMM runs as the fused kernel"),
     EnvVar("TESSERACT_TP_FUSED_MIN_RS", "1024", "tokens per step from which GEMM -> reduce-scatter runs as the fused kernel"),

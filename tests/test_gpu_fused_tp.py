@@ -195,9 +195,9 @@ def _worker(rank, world, port, q):
             want = part.float().clone()
             dist.all_reduce(want)
             errs.append(((got.float() - want).norm() / want.norm()).item())
-        scfg = LlamaConfig(vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=4 * world,
+        scfg = LlamaConfig(vocab_size=2048, hidden_size=64 * 4 * world, num_hidden_layers=2, num_attention_heads=4 * world,
                            num_key_value_heads=world, intermediate_size=1024, max_position_embeddings=256,
-                           dtype=torch.bfloat16)
+                           dtype=torch.bfloat16)            # head_dim 64 at every world size
         ecfg = EngineConfig(block_size=16, num_blocks=256, max_seq_len=256, max_batch_size=8)
         prompts = [[(7 * i + j) % 2048 for j in range(20 + 9 * i)] for i in range(5)]
         outs = {}
