@@ -50,17 +50,19 @@ struct Layout {
   int r_stages;     // raw ring (fp8 path)
 };
 
-inline Layout make_layout(int M, int bn, bool fp8) {
+// rb: 128-row blocks of the batch that one CTA multiplies with the weight tile it streams (1, or 2 for 129 .. 256 rows:
+// the tile is then loaded -- and, for fp8, widened -- once for both blocks, into two accumulators).
+inline Layout make_layout(int M, int bn, bool fp8, int rb) {
   Layout L{};
-  const int rows = M >= BM ? BM : ((M + 7) / 8) * 8;
+  const int rows = (M >= BM || rb > 1) ? BM : ((M + 7) / 8) * 8;
   L.x_rows = rows;
-  L.x_pitch = ((rows * BK * 2 + 1023) / 1024) * 1024;
+  L.x_pitch = rb * (((rows * BK * 2 + 1023) / 1024) * 1024);
   L.c_pitch = ((bn * BK * 2 + 1023) / 1024) * 1024;
   // the MMA reads 128 activation rows from a stage whatever x_rows is; the bytes past the box belong to later
   // buffers (their content only reaches accumulator rows that are never stored), but must lie inside the allocation
-  L.x_stages = L.x_pitch <= 8192 ? 8 : 4;
+  L.x_stages = L.x_pitch <= 8192 ? 8 : ((rb > 1 && fp8) ? 3 : 4);
   const int x_ring = L.x_stages * L.x_pitch;
-  const int x_overread = BM * BK * 2 - L.x_pitch;     // > 0 when x_rows < 128
+  const int x_overread = rb * BM * BK * 2 - L.x_pitch;     // > 0 when x_rows < 128
   int avail = kSmemBudget - 1024 - x_ring;
   if (!fp8) {
     L.r_pitch = 0;
@@ -113,7 +115,6 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
                : "memory");
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Two E4M3 bytes, already spread to bits [7:0] and [23:16] of `y` -> packed bf16x2 holding value * 2^-120 each:
 // exponent and mantissa move up by four bits, the sign by eight. (Both MMA operands must have the same 16-bit format:
@@ -128,7 +129,7 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   return d;
 }
 
-template <int S, bool FP8>
+template <int S, bool FP8, int RB>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                       const uint8_t* __restrict__ w_packed, const float* __restrict__ w_scale,
@@ -153,7 +154,8 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   const int slice = static_cast<int>(cluster_ctarank());
   const int tile = static_cast<int>(blockIdx.x) / S;
   const int n0 = tile * BN;
-  const int m0 = static_cast<int>(blockIdx.y) * BM;
+  const int m0 = static_cast<int>(blockIdx.y) * BM * RB;
+  constexpr int kXBlock = BM * BK * 2;             // one 128-row activation tile inside a stage
   const int total_kb = (K + BK - 1) / BK;
   const int kb_per = (total_kb + S - 1) / S;
   const int kb0 = slice * kb_per;
@@ -178,7 +180,7 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     pdl_trigger();     // whatever follows in the stream may start its own prologue
   }
   if (warp == 1) {
-    tmem_alloc(&tmem_base_smem, kMaxBN);
+    tmem_alloc(&tmem_base_smem, RB * kMaxBN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -191,7 +193,7 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     if (lane == 0) {
       const int WST = FP8 ? L.r_stages : L.c_stages;
       const bool packed = (flags & 2) != 0;
-      const uint32_t x_bytes = static_cast<uint32_t>(L.x_rows) * BK * 2;
+      const uint32_t x_bytes = static_cast<uint32_t>(RB * L.x_rows) * BK * 2;
       uint64_t* w_full = FP8 ? full_r : full_c;
       uint64_t* w_empty = FP8 ? empty_r : empty_c;
       uint8_t* w_base = FP8 ? sR : sC;
@@ -227,7 +229,9 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         }
         if (x_issued < nk && mbar_test_wait(&empty_x[xs], xphase ^ 1u)) {
           mbar_expect_tx(&full_x[xs], x_bytes);
-          tma_load_2d(sX + xs * L.x_pitch, &tmX, &full_x[xs], (kb0 + x_issued) * BK, m0);
+#pragma unroll
+          for (int rb = 0; rb < RB; ++rb)
+            tma_load_2d(sX + xs * L.x_pitch + rb * kXBlock, &tmX, &full_x[xs], (kb0 + x_issued) * BK, m0 + rb * BM);
           ++x_issued;
           if (++xs == L.x_stages) {
             xs = 0;
@@ -265,9 +269,13 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
           mbar_arrive(&empty_c[cs]);
         } else {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_f16(tmem_base, umma_smem_desc_sw128(a_base + k * 32, 16, 1024),
-                     umma_smem_desc_sw128(b_base + k * 32, 16, 1024), idesc, (i | k) != 0 ? 1u : 0u);
+          for (int rb = 0; rb < RB; ++rb) {
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              umma_f16(tmem_base + static_cast<uint32_t>(rb * kMaxBN),
+                       umma_smem_desc_sw128(a_base + rb * kXBlock + k * 32, 16, 1024),
+                       umma_smem_desc_sw128(b_base + k * 32, 16, 1024), idesc, (i | k) != 0 ? 1u : 0u);
+          }
           umma_commit(&empty_x[xs]);
           umma_commit(&empty_c[cs]);
         }
@@ -349,20 +357,23 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     const bool ok = mbar_wait(&acc_bar, 0, &cta_abort, status);
     const bool warp_ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
     tc_fence_after();
-    // the rings are idle now: park this CTA's partial tile over them
-    uint8_t* prow = smem + row * part_pitch;
-    for (int c = 0; c < BN; c += 32) {
-      uint32_t r[32];
-      if (warp_ok && nk > 0) {
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c), r);
-        tmem_ld_wait();
-      } else {
+    // the rings are idle now: park this CTA's partial tile (RB * 128 rows) over them
 #pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = 0u;
+    for (int rb = 0; rb < RB; ++rb) {
+      uint8_t* prow = smem + (rb * BM + row) * part_pitch;
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        if (warp_ok && nk > 0) {
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(rb * kMaxBN + c), r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          if (c + i < BN) *reinterpret_cast<uint4*>(prow + (c + i) * 4) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
       }
-#pragma unroll
-      for (int i = 0; i < 32; i += 4)
-        if (c + i < BN) *reinterpret_cast<uint4*>(prow + (c + i) * 4) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
     }
     tc_fence_before();
   }
@@ -370,8 +381,8 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   cluster_sync_all();
 
   if (warp >= 2 && warp < 6) {
-    // CTA `slice` sums batch rows [slice * 128 / S, (slice + 1) * 128 / S) of all S partial tiles
-    constexpr int kRows = BM / S;
+    // CTA `slice` sums batch rows [slice * R / S, (slice + 1) * R / S) of all S partial tiles, R = RB * 128
+    constexpr int kRows = RB * BM / S;
     const int t = (warp - 2) * 32 + lane;        // 0 .. 127
     const int vec_per_row = BN / 4;
     const int total = kRows * vec_per_row;
@@ -416,13 +427,13 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     }
     tc_fence_after();
-    tmem_dealloc(tmem_base, kMaxBN);
+    tmem_dealloc(tmem_base, RB * kMaxBN);
   }
 }
 
-template <int S, bool FP8>
+template <int S, bool FP8, int RB>
 cudaError_t config_wq(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at, int grid_x, int grid_y, int pdl, cudaStream_t s) {
-  auto kern = gemm_decode_wq_kernel<S, FP8>;
+  auto kern = gemm_decode_wq_kernel<S, FP8, RB>;
   static PerDeviceFlag attr;
   if (attr.unset()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
@@ -449,7 +460,7 @@ cudaError_t config_wq(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at, int grid
   return cudaSuccess;
 }
 
-template <int S, bool FP8>
+template <int S, bool FP8, int RB>
 int launch_wq(const CUtensorMap& tx, const CUtensorMap& tw, const void* w_packed, const float* w_scale, void* Y, int M,
               int N, int K,
               long long ldy, int BN, int scale_cols, int scale_rows, const Layout& L, int pdl, int flags,
@@ -459,9 +470,9 @@ int launch_wq(const CUtensorMap& tx, const CUtensorMap& tw, const void* w_packed
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute at[2];
   const int tiles = (N + BN - 1) / BN;
-  cudaError_t e = config_wq<S, FP8>(&cfg, at, tiles * S, (M + BM - 1) / BM, pdl, s);
+  cudaError_t e = config_wq<S, FP8, RB>(&cfg, at, tiles * S, (M + RB * BM - 1) / (RB * BM), pdl, s);
   if (e != cudaSuccess) return static_cast<int>(e);
-  return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_decode_wq_kernel<S, FP8>, tx, tw,
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_decode_wq_kernel<S, FP8, RB>, tx, tw,
                                              static_cast<const uint8_t*>(w_packed), w_scale,
                                              static_cast<__nv_bfloat16*>(Y), M, N, K, ldy, BN, scale_cols, scale_rows, L,
                                              flags, device_status_word()));
@@ -478,8 +489,8 @@ int resident_ctas() {
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute at[2];
     int clusters = 0;
-    if (config_wq<S, FP8>(&cfg, at, S * 64, 1, 0, nullptr) != cudaSuccess ||
-        cudaOccupancyMaxActiveClusters(&clusters, gemm_decode_wq_kernel<S, FP8>, &cfg) != cudaSuccess || clusters <= 0) {
+    if (config_wq<S, FP8, 1>(&cfg, at, S * 64, 1, 0, nullptr) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&clusters, gemm_decode_wq_kernel<S, FP8, 1>, &cfg) != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
       clusters = sm_count() / S * 3 / 4;
     }
@@ -502,9 +513,14 @@ int resident_ctas_for(int split, bool fp8) {
 // them the one that keeps the most SMs streaming wins (K slices of fewer than 16 steps and very narrow tiles are
 // marked down: their fixed costs show). Measured on B200 at 16 .. 256 rows: 138 CTAs of 208 rows for N = 28672,
 // 32 x 4 CTAs of 128 rows for N = 4096.
-void plan_tiles(int M, int N, int kb, bool fp8, int fixed_bn, int* bn_out, int* split_out) {
-  const int row_blocks = (M + BM - 1) / BM;
-  int best_bn = 128, best_s = 1;
+bool layout_ok(const Layout& L, bool fp8, int bn, int rb) {
+  return (fp8 ? L.r_stages : L.c_stages) >= (fp8 ? kConvGroups : 3) && rb * BM * (bn * 4 + 16) <= kSmemBudget - 1024;
+}
+
+// One candidate family: tile widths and K splits for a given number of row blocks per CTA. Returns the score of the
+// best single-wave plan (< 0 if there is none).
+double plan_family(int M, int N, int kb, bool fp8, int fixed_bn, int rb, int* bn_out, int* split_out) {
+  const int row_ctas = (M + rb * BM - 1) / (rb * BM);
   double best = -1.0;
   for (int s : {1, 2, 4, 8}) {
     if (s > 1 && kb / s < 8) break;
@@ -514,10 +530,10 @@ void plan_tiles(int M, int N, int kb, bool fp8, int fixed_bn, int* bn_out, int* 
     if (cap <= 0 || cap > sms) cap = safe;
     for (int bn = 256; bn >= 32; bn -= 16) {
       if (fixed_bn > 0 && bn != fixed_bn) continue;
-      const Layout L = make_layout(M, bn, fp8);
-      if ((fp8 ? L.r_stages : L.c_stages) < (fp8 ? kConvGroups : 3) || BM * (bn * 4 + 16) > kSmemBudget - 1024) continue;
+      const Layout L = make_layout(M, bn, fp8, rb);
+      if (!layout_ok(L, fp8, bn, rb)) continue;
       const int tiles = (N + bn - 1) / bn;
-      const int ctas = tiles * s * row_blocks;
+      const int ctas = tiles * s * row_ctas;
       if (ctas > cap) continue;
       const double useful = static_cast<double>(N) / (static_cast<double>(tiles) * bn);
       // at equal CTA counts the plan with fewer K steps per CTA wins (a step costs about the same whatever its width)
@@ -527,24 +543,57 @@ void plan_tiles(int M, int N, int kb, bool fp8, int fixed_bn, int* bn_out, int* 
       if (bn < 64) score *= 0.85;
       if (score > best + 1e-9) {
         best = score;
-        best_bn = bn;
-        best_s = s;
+        *bn_out = bn;
+        *split_out = s;
       }
     }
   }
+  return best;
+}
+
+// Tile width, K split and row blocks per CTA for M batch rows, N weight rows and `kb` K steps. The kernel is not
+// persistent, and a second wave of CTAs costs about as much as the first, so only plans whose CTAs are all resident
+// at once are considered; among them the one that keeps the most SMs streaming wins (K slices of fewer than 16 steps
+// and very narrow tiles are marked down: their fixed costs show). 129 .. 256 rows: one CTA takes both 128-row blocks
+// when the rings still fit, so the weights are streamed once. Measured on B200 at 16 .. 128 rows: 138 CTAs of 208
+// rows for N = 28672, 32 x 4 CTAs of 128 rows for N = 4096.
+void plan_tiles(int M, int N, int kb, bool fp8, int fixed_bn, int* bn_out, int* split_out, int* rb_out) {
+  int bn = 128, s = 1, rb = 1;
+  double best = -1.0;
+  if (M > BM && M <= 2 * BM) {
+    int b2 = 0, s2 = 0;
+    const double sc2 = plan_family(M, N, kb, fp8, fixed_bn, 2, &b2, &s2);
+    if (sc2 > 0.0) {
+      best = sc2;
+      bn = b2;
+      s = s2;
+      rb = 2;
+    }
+  }
+  if (best < 0.0) {
+    int b1 = 0, s1 = 0;
+    const double sc1 = plan_family(M, N, kb, fp8, fixed_bn, 1, &b1, &s1);
+    if (sc1 > 0.0) {
+      best = sc1;
+      bn = b1;
+      s = s1;
+      rb = 1;
+    }
+  }
   if (best < 0.0) {   // more tiles than resident CTAs at every width: several waves of the widest tile that has room
-    best_bn = fixed_bn > 0 ? fixed_bn : 32;
-    best_s = 1;
-    for (int bn = 256; bn >= 32 && fixed_bn <= 0; bn -= 16) {
-      const Layout L = make_layout(M, bn, fp8);
-      if ((fp8 ? L.r_stages : L.c_stages) >= (fp8 ? kConvGroups : 3) && BM * (bn * 4 + 16) <= kSmemBudget - 1024) {
-        best_bn = bn;
+    rb = (M > BM && M <= 2 * BM && !fp8) ? 2 : 1;
+    bn = fixed_bn > 0 ? fixed_bn : 32;
+    s = 1;
+    for (int b = 256; b >= 32 && fixed_bn <= 0; b -= 16) {
+      if (layout_ok(make_layout(M, b, fp8, rb), fp8, b, rb)) {
+        bn = b;
         break;
       }
     }
   }
-  *bn_out = best_bn;
-  *split_out = best_s;
+  *bn_out = bn;
+  *split_out = s;
+  *rb_out = rb;
 }
 
 }  // namespace
@@ -569,15 +618,22 @@ TSB_EXPORT int tsb_gemm_decode_wq(const void* X, const void* W, const float* w_s
   const bool fp8 = w_fp8 != 0, packed = w_fp8 == 2;
   if (packed ? (K % 64 || !w_scale || bn <= 0) : (fp8 ? (ldw % 16 || K % 64 || !w_scale) : (ldw % 8 || K % 16))) return -2;
   const int kb = (K + BK - 1) / BK;
-  if (bn <= 0 || split <= 0) {
-    int pbn = 0, ps = 0;
-    plan_tiles(M, N, kb, fp8, bn > 0 ? bn : 0, &pbn, &ps);
+  int rb = 1;
+  {
+    int pbn = 0, ps = 0, prb = 1;
+    plan_tiles(M, N, kb, fp8, bn > 0 ? bn : 0, &pbn, &ps, &prb);
     if (bn <= 0) bn = pbn;
     if (split <= 0) split = ps;
+    rb = prb;
   }
   if (bn < 32 || bn > kMaxBN || bn % 16 || (split != 1 && split != 2 && split != 4 && split != 8)) return -2;
-  const Layout L = make_layout(M, bn, fp8);
-  if ((fp8 ? L.r_stages : L.c_stages) < (fp8 ? kConvGroups : 2)) return -2;   // no room for the rings at this width
+  Layout L = make_layout(M, bn, fp8, rb);
+  if (!layout_ok(L, fp8, bn, rb) && rb == 2) {   // a caller-given width that has no room for two row blocks
+    rb = 1;
+    L = make_layout(M, bn, fp8, rb);
+  }
+  if ((fp8 ? L.r_stages : L.c_stages) < (fp8 ? kConvGroups : 2) || rb * BM * (bn * 4 + 16) > kSmemBudget - 1024)
+    return -2;   // no room for the rings at this width
   if (fp8 && (kb + split - 1) / split * BK / 128 + 2 > kMaxScaleSteps) return -2;
   CUtensorMap tx, tw;
   if (!make_tmap_2d(&tx, X, 2, M, K, ldx * 2, L.x_rows, BK, true)) return -3;
@@ -593,9 +649,10 @@ TSB_EXPORT int tsb_gemm_decode_wq(const void* X, const void* W, const float* w_s
   const int scale_cols = (K + 127) / 128, scale_rows = (N + 127) / 128;
   const int flags = packed ? 2 : 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-#define TSB_WQ(S_)                                                                                                       \
-  return fp8 ? launch_wq<S_, true>(tx, tw, W, w_scale, Y, M, N, K, ldy, bn, scale_cols, scale_rows, L, pdl, flags, s)  \
-             : launch_wq<S_, false>(tx, tw, W, w_scale, Y, M, N, K, ldy, bn, scale_cols, scale_rows, L, pdl, flags, s)
+#define TSB_WQ_ARGS tx, tw, W, w_scale, Y, M, N, K, ldy, bn, scale_cols, scale_rows, L, pdl, flags, s
+#define TSB_WQ(S_)                                                                            \
+  return fp8 ? (rb == 2 ? launch_wq<S_, true, 2>(TSB_WQ_ARGS) : launch_wq<S_, true, 1>(TSB_WQ_ARGS))  \
+             : (rb == 2 ? launch_wq<S_, false, 2>(TSB_WQ_ARGS) : launch_wq<S_, false, 1>(TSB_WQ_ARGS))
   switch (split) {
     case 1: TSB_WQ(1);
     case 2: TSB_WQ(2);
@@ -603,6 +660,7 @@ TSB_EXPORT int tsb_gemm_decode_wq(const void* X, const void* W, const float* w_s
     default: TSB_WQ(8);
   }
 #undef TSB_WQ
+#undef TSB_WQ_ARGS
 }
 
 // The plan the call above makes for a problem (host only): *bn (pass a positive value to fix the tile width, as for
@@ -612,9 +670,10 @@ TSB_EXPORT int tsb_gemm_decode_wq_plan(int M, int N, int K, int w_fp8, int* bn, 
   using namespace tsb;
   if (M <= 0 || N <= 0 || K <= 0 || !bn || !split) return -2;
   const int fixed = *bn > 0 ? *bn : 0;
-  plan_tiles(M, N, (K + BK - 1) / BK, w_fp8 != 0, fixed, bn, split);
-  const Layout L = make_layout(M, *bn, w_fp8 != 0);
-  if (w_stages) *w_stages = w_fp8 ? L.r_stages : L.c_stages;
+  int rb = 1;
+  plan_tiles(M, N, (K + BK - 1) / BK, w_fp8 != 0, fixed, bn, split, &rb);
+  const Layout L = make_layout(M, *bn, w_fp8 != 0, rb);
+  if (w_stages) *w_stages = (w_fp8 ? L.r_stages : L.c_stages) * (rb == 2 ? -1 : 1);   // negative: two row blocks per CTA
   if (resident) *resident = resident_ctas_for(*split, w_fp8 != 0);   // what the runtime reports for that cluster size
   return 0;
 }

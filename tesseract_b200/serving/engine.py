@@ -162,7 +162,7 @@ class ServingEngine:
         # kernel before them
         self.pdl = os.environ.get("TESSERACT_PDL", "1") == "1"
         self.stream_rows = 256       # batches up to this many rows count as decode-sized
-        self.decode_gemm = os.environ.get("TESSERACT_SERVE_DECODE_GEMM", "auto")   # auto | stream (always the streaming kernel)
+        self.decode_gemm = os.environ.get("TESSERACT_SERVE_DECODE_GEMM", "auto")   # auto | stream | splitk (A/B runs)
         c, mc = self.cfg, model.config
         self.device = model._device()
         if self.device.type != "cuda" or mc.dtype not in (torch.bfloat16, torch.float16):
@@ -394,12 +394,11 @@ class ServingEngine:
             return r if out is None else out.copy_(r)
         M = x.shape[0]
         if M <= self.stream_rows:
-            # measured on B200 (layer shapes of the 8 B model): up to 128 rows the streaming kernel is the fastest
-            # path for both weight formats; above, it streams (and widens) the weights once per 128-row block, and
-            # the cluster split-K kernel (bf16) / the block-scaled fp8 tensor-core GEMM (fp8) are faster
+            # measured on B200 (layer shapes of the 8 B model, 16 .. 256 rows): bf16 weights go through the streaming
+            # kernel (one CTA takes both 128-row blocks of a 129 .. 256-row batch)
             N, K = W.shape
             if W.q is None:
-                if M <= 128 or self.decode_gemm == "stream":
+                if self.decode_gemm != "splitk":
                     return ops.stream_linear(x, W.w, out=out, pdl=self.pdl)
                 return ops.decode_linear(x, W.w, out=out)
             # fp8 weights: the streaming kernel (bf16 activations, weights widened on the fly) pays off for the

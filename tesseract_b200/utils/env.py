@@ -41,7 +41,7 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_TP_FUSED_MIN_RS", "1024", "tokens per step from which GEMM -> reduce-scatter runs as the fused kernel"),
     EnvVar("TESSERACT_PDL", "1", "serving decode GEMMs: 1 (programmatic dependent launch) | 0"),
     EnvVar("TESSERACT_CPU_GEMM", "torch", "2-D fp32 CPU products of ops.cpu_gemm.matmul_f32 callers: torch | native (host-runtime AVX2 GEMM)"),
-    EnvVar("TESSERACT_SERVE_DECODE_GEMM", "auto", "serving decode GEMMs above 128 rows: auto (split-K / fp8 tensor-core GEMM) | stream"),
+    EnvVar("TESSERACT_SERVE_DECODE_GEMM", "auto", "serving decode GEMMs: auto | stream (always the weight-streaming kernel) | splitk (bf16: the cluster split-K kernel)"),
     EnvVar("TESSERACT_SWIGLU", "2", "SwiGLU kernels: 2 (row-wise, two vector pairs per thread) | 0 (flat kernel, for A/B runs)"),
 ]}
 

@@ -689,8 +689,11 @@ def test_serving_engine_fp8_block_scaled_weights(dev, kv_int8):
     x = torch.randn(600, 512, device=dev, generator=torch.Generator(device=dev).manual_seed(0)).bfloat16()
     W = eng8.wgu[1]
     ref = x.float() @ _dequant_block128(W.q, W.s).t()
-    assert _rel_err(eng8._mm(x[:48], W).float(), ref[:48]) < 1.2e-2          # streaming kernel, bf16 activations
-    assert _rel_err(eng8._mm(x, W).float(), ref) < 0.05                      # fp8 x fp8 block-scaled GEMM
+    assert _rel_err(eng8._mm(x[:48], W).float(), ref[:48]) < 0.05           # fp8 x fp8 block-scaled GEMM (1 x 128 scales)
+    assert _rel_err(eng8._mm(x, W).float(), ref) < 0.05
+    Wd = eng8.wdown[1]                                                       # K-heavy: the streaming kernel, bf16 activations
+    xd = torch.randn(48, Wd.shape[1], device=dev, generator=torch.Generator(device=dev).manual_seed(1)).bfloat16()
+    assert _rel_err(eng8._mm(xd, Wd).float(), xd.float() @ _dequant_block128(Wd.q, Wd.s).t()) < 1.2e-2
     _, out16 = run("bf16")
     same = sum(a == b for x8, x16 in zip(out8, out16) for a, b in zip(x8, x16))
     assert all(len(o) == 10 for o in out8)
