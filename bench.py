@@ -100,6 +100,8 @@ def parse_args():
     ap.add_argument("--serve", type=int, default=-1,
                     help="also run the serving benchmark, tensor-parallel over all ranks (-1 = when all 32 layers run)")
     ap.add_argument("--serve-requests", type=int, default=256)
+    ap.add_argument("--serve-tp", type=int, default=0,
+                    help="tensor-parallel ranks per serving replica (0 = serving.default_tp); the other ranks form replicas")
     ap.add_argument("--serve-weights", default="fp8", choices=["fp8", "bf16"],
                     help="serving weights: E4M3 with 128x128 block scales (the named configuration) | bf16")
     ap.add_argument("--layers", type=int, default=32, help="(debug only) fewer layers; invalidates the metric")
@@ -433,15 +435,20 @@ def main():
         try:
             sys.path.insert(0, os.path.join(REPO_ROOT, "benchmarks"))
             from bench_serving import run_serving_variants
-            variants = run_serving_variants(requests=args.serve_requests, layers=args.layers, device=device,
-                                            tp_group=dist.group.WORLD if world > 1 else None, rank=rank, world=world,
-                                            weights=args.serve_weights)
+            variants = run_serving_variants(requests=args.serve_requests, layers=args.layers, device=device, rank=rank,
+                                            world=world, tp_size=args.serve_tp, weights=args.serve_weights)
             # headline = the first variant (bf16 KV, greedy); the other three ride along under "variants"
             first = next(iter(variants))
             serve = dict(variants[first])
-            serve["variants"] = {k: {kk: v[kk] for kk in ("kv", "sampling", "prefill_tok_s", "decode_tok_s", "ttft_p50_ms",
-                                                           "end_to_end_s", "total_tok_s", "kernel_status")}
-                                 for k, v in variants.items()}
+            keys = ("parallelism", "kv", "sampling", "prefill_tok_s", "decode_tok_s", "ttft_p50_ms", "end_to_end_s",
+                    "total_tok_s", "decode_gpu_ms_per_step", "kernel_status")
+            serve["variants"] = {k: {kk: v[kk] for kk in keys} for k, v in variants.items()}
+            if world > 1 and serve["tp"] != world:
+                # the same workload behind ONE tensor-parallel engine over all ranks (lowest latency per request)
+                one = run_serving_variants(requests=args.serve_requests, layers=args.layers, device=device, rank=rank,
+                                           world=world, tp_size=world, weights=args.serve_weights,
+                                           variants=(("bf16", "greedy"),))
+                serve["variants"][f"bf16_greedy_tp{world}"] = {kk: one["bf16_greedy"][kk] for kk in keys}
         except Exception as e:  # the training number stands on its own
             serve = {"error": f"{type(e).__name__}: {e}"[:300]}
 

@@ -43,7 +43,8 @@ def main() -> int:
     use_batched = a.engine == "batched" or (a.engine == "auto" and dev.type == "cuda")
     if use_batched:
         from tesseract_b200.serving.engine import ServingEngine
-        engine = ServingEngine(model, ecfg)
+        from tesseract_b200.parallel.launch import job_metrics
+        engine = ServingEngine(model, ecfg).instrument(metrics=job_metrics())    # TESSERACT_METRICS_FILE / TESSERACT_NVTX
     else:
         engine = ContinuousBatchingScheduler(model, ecfg)
     prompts = [p for p in a.prompts.split("|") if p]

@@ -51,6 +51,10 @@ def main() -> int:
     cfg = preset(a.model, dtype, a.seq + 1)
     tcfg = TrainConfig(lr=a.lr, micro_batch=a.micro_batch or min(a.batch, 4))
     trainer, plan = build_parallel_trainer(cfg, tcfg, world, rank, dev, a.parallelism, seed=a.seed)
+    from tesseract_b200.parallel.launch import job_metrics, job_watchdog
+    # TESSERACT_METRICS_FILE: one JSON record per step; TESSERACT_WATCHDOG_S: heartbeat + peer check before every step;
+    # TESSERACT_NVTX=1: ranges around forward / backward / optimizer
+    trainer.instrument(metrics=job_metrics(), watchdog=job_watchdog())
     if a.batch % plan["dp"]:
         raise SystemExit(f"error: --batch {a.batch} is not divisible by the data-parallel degree {plan['dp']}")
     g = torch.Generator().manual_seed(1234)

@@ -21,6 +21,9 @@ _native.register_signatures({
     "tsb_quant_weight_128x128": [P, P, P, I, I, L, I, P],
     "tsb_gemm_fp8_pertensor": [P, P, P, P, P, I, I, I, L, P],
     "tsb_quant_tensor_e4m3": [P, P, P, L, I, P],
+    "tsb_quant_act_mx": [P, L, P, P, I, I, P],
+    "tsb_gemm_decode_mx": [P, P, P, P, P, I, I, I, L, L, I, I, I, P],
+    "tsb_gemm_decode_mx_plan": [I, I, I, P, P, P, P],
 })
 
 E4M3_MAX = 448.0
@@ -40,7 +43,7 @@ def quantize_act_ref(x: torch.Tensor):
     return q.view(torch.uint8), scale.t().contiguous()
 
 
-def quantize_weight_ref(w: torch.Tensor):
+def quantize_weight_ref(w: torch.Tensor, pow2: bool = False):
     N, K = w.shape
     nb = (N + 127) // 128
     wp = torch.zeros(nb * 128, K, dtype=torch.float32, device=w.device)
@@ -48,6 +51,8 @@ def quantize_weight_ref(w: torch.Tensor):
     blk = wp.view(nb, 128, K // 128, 128)
     amax = blk.abs().amax(dim=(1, 3))
     scale = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+    if pow2:
+        scale = torch.exp2(torch.ceil(torch.log2(scale)))
     q = (blk / scale[:, None, :, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(nb * 128, K)[:N]
     return q.contiguous().view(torch.uint8), scale.contiguous()
 
@@ -82,11 +87,16 @@ def quantize_act(x: torch.Tensor):
     return q, sa
 
 
-def quantize_weight(w: torch.Tensor):
-    """w [N, K] (K % 128 == 0) -> (e4m3 bytes uint8 [N, K], scales fp32 [ceil(N / 128), K / 128])."""
+def quantize_weight(w: torch.Tensor, pow2: bool = False):
+    """w [N, K] (K % 128 == 0) -> (e4m3 bytes uint8 [N, K], scales fp32 [ceil(N / 128), K / 128]).
+    ``pow2=True`` rounds every block scale up to a power of two (the block then uses at most one binade less of the
+    E4M3 range; the relative precision of a floating-point payload does not depend on the scale). Such weights can be
+    multiplied by ``mx_linear``, where the tensor core applies the scales itself."""
     N, K = w.shape
     if K % 128:
         raise ValueError("quantize_weight: K must be a multiple of 128")
+    if pow2:
+        return quantize_weight_ref(w, pow2=True)
     if not _native_ok(w) or w.stride(1) != 1:
         return quantize_weight_ref(w)
     q = torch.empty((N, K), dtype=torch.uint8, device=w.device)
@@ -171,3 +181,95 @@ def fp8_gemm_pertensor(qa: torch.Tensor, sa: torch.Tensor, qb: torch.Tensor, sb:
     check(lib().tsb_gemm_fp8_pertensor(qa.data_ptr(), qb.data_ptr(), out.data_ptr(), sa.data_ptr(), sb.data_ptr(), M, N, K,
                                        out.stride(0), stream_ptr(qa.device)), "tsb_gemm_fp8_pertensor")
     return out
+
+
+# ----------------------------------------------------------------------------------------- MX path (decode-sized M)
+def _mx_m_pad(M: int) -> int:
+    return (M + 127) // 128 * 128
+
+
+def scales_are_pow2(scale: torch.Tensor) -> bool:
+    """True when every fp32 scale is a positive power of two (mantissa bits zero)."""
+    bits = scale.contiguous().view(torch.int32)
+    return bool(((bits & 0x7FFFFF) == 0).all() and (bits > 0).all())
+
+
+def quantize_act_mx_ref(x: torch.Tensor):
+    M, K = x.shape
+    xb = x.float().view(M, K // 32, 32)
+    amax = xb.abs().amax(dim=2)
+    e = torch.ceil(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax)) / E4M3_MAX)) + 127
+    e = torch.where(amax > 0, e, torch.full_like(e, 127)).clamp(1, 254)
+    q = (xb * torch.exp2(127 - e)[:, :, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(M, K)
+    eb = e.to(torch.int64).view(M, K // 128, 4)
+    words = eb[:, :, 0] | (eb[:, :, 1] << 8) | (eb[:, :, 2] << 16) | (eb[:, :, 3] << 24)          # [M, K / 128]
+    sf = torch.full((K // 128, _mx_m_pad(M)), 0x7F7F7F7F, dtype=torch.int64, device=x.device)
+    sf[:, :M] = words.t()
+    sf = torch.where(sf >= 2 ** 31, sf - 2 ** 32, sf).to(torch.int32)
+    return q.view(torch.uint8), sf
+
+
+def quantize_act_mx(x: torch.Tensor, out=None):
+    """x [M, K] bf16 (K % 128 == 0) -> (E4M3 bytes uint8 [M, K], scale words int32 [K / 128, ceil(M / 128) * 128]):
+    one power-of-two scale per row and 32 columns, ``q = x * 2^(127 - e)`` with the smallest exponent byte ``e`` that
+    keeps the block within +-448; byte j of word [k / 128, m] is the exponent of columns 128 (k / 128) + 32 j .. + 31.
+    ``out`` = (q, sf) buffers of those shapes to write into."""
+    M, K = x.shape
+    if K % 128:
+        raise ValueError("quantize_act_mx: K must be a multiple of 128")
+    if not (_native_ok(x) and x.dtype == torch.bfloat16):
+        q, sf = quantize_act_mx_ref(x)
+        if out is not None:
+            out[0].copy_(q)
+            out[1].copy_(sf)
+            return out
+        return q, sf
+    if x.stride(1) != 1:
+        raise ValueError("quantize_act_mx: rows must be contiguous")
+    if out is None:
+        q = torch.empty((M, K), dtype=torch.uint8, device=x.device)
+        sf = torch.empty((K // 128, _mx_m_pad(M)), dtype=torch.int32, device=x.device)
+    else:
+        q, sf = out
+    check(lib().tsb_quant_act_mx(x.data_ptr(), x.stride(0), q.data_ptr(), sf.data_ptr(), M, K, stream_ptr(x.device)),
+          "tsb_quant_act_mx")
+    return q, sf
+
+
+def dequantize_act_mx(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+    M, K = q.shape
+    words = sf[:, :M].t().to(torch.int64) & 0xFFFFFFFF                                            # [M, K / 128]
+    e = torch.stack([(words >> (8 * j)) & 0xFF for j in range(4)], dim=2).view(M, K // 32).float()
+    return (q.view(torch.float8_e4m3fn).float().view(M, K // 32, 32) * torch.exp2(e - 127)[:, :, None]).view(M, K)
+
+
+def mx_linear(q: torch.Tensor, sf: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, out=None, pdl: bool = False,
+              bn: int = 0, split: int = 0) -> torch.Tensor:
+    """bf16 [M, N] = dequant(q, sf) @ dequant(wq, w_scale)^T for decode-sized M, with the scales applied by the tensor
+    core (``csrc/gemm_decode_mx.cu``: tcgen05.mma kind::mxf8f6f4.block_scale). ``q, sf`` from ``quantize_act_mx``;
+    ``wq, w_scale`` from ``quantize_weight(w, pow2=True)`` (the scales must be powers of two: only their exponent
+    reaches the hardware)."""
+    M, K = q.shape
+    N = wq.shape[0]
+    if not _native_ok(q):
+        r = (dequantize_act_mx(q, sf) @ dequantize_weight(wq, w_scale).t()).to(torch.bfloat16)
+        return r if out is None else out.copy_(r)
+    if not (q.is_contiguous() and wq.stride(1) == 1 and w_scale.is_contiguous() and sf.is_contiguous()):
+        raise ValueError("mx_linear: operands must be contiguous")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=q.device)
+    elif out.shape != (M, N) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise ValueError("mx_linear: out must be a bf16 [M, N] tensor with contiguous rows")
+    check(lib().tsb_gemm_decode_mx(q.data_ptr(), sf.data_ptr(), wq.data_ptr(), w_scale.data_ptr(), out.data_ptr(), M, N,
+                                   K, wq.stride(0), out.stride(0), bn, split, int(pdl), stream_ptr(q.device)),
+          "tsb_gemm_decode_mx")
+    return out
+
+
+def mx_linear_plan(M: int, N: int, K: int, bn: int = 0):
+    """(tile width, K split, ring depth [negative: two row blocks per CTA], resident CTAs) on the current device."""
+    import ctypes
+    b, s_, st, res = ctypes.c_int(bn), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+    check(lib().tsb_gemm_decode_mx_plan(M, N, K, ctypes.byref(b), ctypes.byref(s_), ctypes.byref(st), ctypes.byref(res)),
+          "tsb_gemm_decode_mx_plan")
+    return b.value, s_.value, st.value, res.value

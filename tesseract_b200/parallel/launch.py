@@ -77,6 +77,13 @@ def _worker(fn, rank: int, world: int, port: int, backend: str, timeout_s: float
             dist.init_process_group(backend, rank=rank, world_size=world, timeout=datetime.timedelta(seconds=timeout_s), **kw)
         try:
             q.put((rank, "ok", fn(rank, world, *args)))
+        except Skip:
+            raise
+        except BaseException as e:
+            wd = job_watchdog(timeout_s=60.0)          # tell the peers on the host before this rank goes away
+            if wd is not None:
+                wd.report_failure(f"{type(e).__name__}: {e}")
+            raise
         finally:
             if dist.is_initialized():
                 dist.destroy_process_group()
@@ -87,6 +94,34 @@ def _worker(fn, rank: int, world: int, port: int, backend: str, timeout_s: float
         q.put((rank, "error", traceback.format_exc()))
         code = 1
     sys.exit(code)
+
+
+def job_watchdog(timeout_s: Optional[float] = None):
+    """A ``utils.watchdog.RankWatchdog`` over the key-value store of the default process group, or None when no group
+    is initialised or the timeout (default: ``TESSERACT_WATCHDOG_S``) is not positive. Hand it to
+    ``Trainer.instrument`` / ``ServingEngine.instrument``: every step then beats, and raises ``RankLost`` on the host
+    when a peer stopped beating or posted an error, before the next collective is launched."""
+    import torch.distributed as dist
+    from ..utils.watchdog import RankWatchdog
+    if timeout_s is None:
+        timeout_s = float(os.environ.get("TESSERACT_WATCHDOG_S", "0") or 0)
+    if timeout_s <= 0 or not dist.is_available() or not dist.is_initialized():
+        return None
+    try:
+        store = dist.distributed_c10d._get_default_store()
+    except Exception:
+        return None
+    return RankWatchdog(store, dist.get_rank(), dist.get_world_size(), timeout_s=timeout_s)
+
+
+def job_metrics(path: Optional[str] = None):
+    """A ``utils.metrics.MetricsLogger`` writing to ``path`` (default: ``TESSERACT_METRICS_FILE``) on rank 0, or None
+    when neither names a file."""
+    from ..utils.metrics import MetricsLogger
+    path = path or os.environ.get("TESSERACT_METRICS_FILE", "")
+    if not path:
+        return None
+    return MetricsLogger(path, rank=int(os.environ.get("RANK", "0")))
 
 
 def launch(fn: Callable, world: int, *args: Any, backend: Optional[str] = None, timeout_s: float = 600.0,

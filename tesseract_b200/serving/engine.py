@@ -585,21 +585,61 @@ class ServingEngine:
         self._graphs[A] = g
         return g
 
+    def instrument(self, metrics=None, watchdog=None, nvtx_ranges: Optional[bool] = None) -> "ServingEngine":
+        """Attach a ``utils.metrics.MetricsLogger`` (``run`` writes one summary record; every ``log_every`` steps a
+        progress record), a ``utils.watchdog.RankWatchdog`` (tensor-parallel serving: every step beats and checks the
+        peers on the host before it launches a collective) and / or NVTX ranges around prefill and decode (default:
+        the ``TESSERACT_NVTX`` environment variable)."""
+        import os
+        if metrics is not None:
+            self.metrics_logger = metrics
+        if watchdog is not None:
+            self.watchdog = watchdog
+        self.nvtx = bool(nvtx_ranges) if nvtx_ranges is not None else os.environ.get("TESSERACT_NVTX", "0") == "1"
+        return self
+
+    def _range(self, name: str):
+        import contextlib
+        if not getattr(self, "nvtx", False):
+            return contextlib.nullcontext()
+        from ..utils import nvtx
+        return nvtx.range_(name)
+
     def step(self) -> bool:
+        wd = getattr(self, "watchdog", None)
+        if wd is not None:
+            wd.step()
         admitted = self._admit()
         if admitted:
-            self._prefill(admitted)
+            with self._range(f"prefill[{len(admitted)}]"):
+                self._prefill(admitted)
             self.running += [r for r in admitted if not r.finished]
         live = [r for r in self.running if not r.finished]
         if live:
-            self._decode(live)
+            with self._range(f"decode[{len(live)}]"):
+                self._decode(live)
         self.running = [r for r in self.running if not r.finished]
         self.steps += 1
+        ml = getattr(self, "metrics_logger", None)
+        if ml is not None and self.steps % self.log_every == 0:
+            ml.log(event="serve_progress", step=self.steps, running=len(self.running), waiting=len(self.waiting),
+                   decode_tokens=self.stats["decode_tokens"], prefill_tokens=self.stats["prefill_tokens"])
         return self.has_pending()
 
+    log_every = 100
+
     def run(self) -> None:
-        while self.has_pending():
-            self.step()
+        try:
+            while self.has_pending():
+                self.step()
+        except Exception as e:
+            wd = getattr(self, "watchdog", None)
+            if wd is not None:
+                wd.report_failure(f"{type(e).__name__}: {e}")
+            raise
+        ml = getattr(self, "metrics_logger", None)
+        if ml is not None:
+            ml.log(event="serve_summary", **self.metrics())
 
     # ------------------------------------------------------------------ metrics
     def metrics(self) -> dict:

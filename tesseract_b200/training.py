@@ -18,6 +18,7 @@ from typing import Optional
 import torch
 
 from .optim import Adam, ParamArena
+from .utils import nvtx
 
 
 @dataclass
@@ -49,6 +50,27 @@ class Trainer:
         self._dev_batch: Optional[torch.Tensor] = None
         self._loss_host = torch.zeros((), dtype=torch.float32).pin_memory() if self.device.type == "cuda" else None
         self.steps_done = 0
+        self.metrics = None             # utils.metrics.MetricsLogger: one record per train_step
+        self.watchdog = None            # utils.watchdog.RankWatchdog: heartbeat + peer check before every step
+        self.nvtx = False               # NVTX ranges around the phases of a step (visible in a timeline profiler)
+        self._last_step_t = None
+
+    def instrument(self, metrics=None, watchdog=None, nvtx_ranges: Optional[bool] = None) -> "Trainer":
+        """Attach a metrics logger (rank 0 writes step, loss, step time and tokens/s per ``train_step``), a rank
+        watchdog (``train_step`` beats and checks the peers before it launches anything: a lost peer raises
+        ``RankLost`` on the host instead of a hang in the next collective; an exception in the step is reported to
+        the peers) and / or NVTX ranges (default: the ``TESSERACT_NVTX`` environment variable)."""
+        import os
+        if metrics is not None:
+            self.metrics = metrics
+        if watchdog is not None:
+            self.watchdog = watchdog
+        self.nvtx = bool(nvtx_ranges) if nvtx_ranges is not None else os.environ.get("TESSERACT_NVTX", "0") == "1"
+        return self
+
+    def _range(self, name: str):
+        import contextlib
+        return nvtx.range_(name) if self.nvtx else contextlib.nullcontext()
 
     # -------------------------------------------------------------------------------------------
     def step_on_device(self, batch: torch.Tensor) -> torch.Tensor:
@@ -69,9 +91,11 @@ class Trainer:
             inputs, targets = chunk[:, :-1], chunk[:, 1:]
             if self.grad_reducer is not None:
                 self.grad_reducer.set_last_microbatch(i == n_micro - 1)
-            loss = self.model.loss(inputs.contiguous(), targets.contiguous(), chunk_rows=cfg.ce_chunk_rows,
-                                   loss_scale=1.0 / n_micro)
-            loss.backward()
+            with self._range(f"forward[{i}]"):
+                loss = self.model.loss(inputs.contiguous(), targets.contiguous(), chunk_rows=cfg.ce_chunk_rows,
+                                       loss_scale=1.0 / n_micro)
+            with self._range(f"backward[{i}]"):
+                loss.backward()
             total += loss.detach()
         if hasattr(self.model, "sync_replicated_grads"):
             self.arena.fold_autograd_grads()
@@ -90,12 +114,33 @@ class Trainer:
             if world > 1:
                 self.arena.grad.div_(world)
                 dist.all_reduce(self.arena.grad, group=self.dp_group)
-        self.opt.step()
+        with self._range("optimizer"):
+            self.opt.step()
         self.steps_done += 1
         return total / n_micro
 
     def train_step(self, host_batch: torch.Tensor) -> float:
         """End-to-end step from a (pinned) host batch; returns the loss as a float."""
+        if self.watchdog is None and self.metrics is None:
+            return self._train_step(host_batch)
+        import time
+        if self.watchdog is not None:
+            self.watchdog.step()                         # raises RankLost before anything is launched
+        t0 = time.perf_counter()
+        try:
+            loss = self._train_step(host_batch)
+        except Exception as e:
+            if self.watchdog is not None:
+                self.watchdog.report_failure(f"{type(e).__name__}: {e}")
+            raise
+        if self.metrics is not None:
+            dt = time.perf_counter() - t0
+            tokens = host_batch.shape[0] * (host_batch.shape[1] - 1)
+            self.metrics.log(step=self.steps_done, loss=loss, step_ms=round(dt * 1e3, 3),
+                             tokens_per_s_rank=round(tokens / dt, 1))
+        return loss
+
+    def _train_step(self, host_batch: torch.Tensor) -> float:
         if self.device.type == "cuda":
             if self._dev_batch is None or self._dev_batch.shape != host_batch.shape:
                 self._dev_batch = torch.empty(host_batch.shape, dtype=host_batch.dtype, device=self.device)

@@ -39,6 +39,9 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_PEAKS_FILE", "", "benchmarks: JSON file with the measured hbm_gbs / bf16_tflops of this GPU (roofline denominators)"),
     EnvVar("TESSERACT_TP_FUSED_MIN_AG", "8192", "tokens per step from which all-gather -> GEMM runs as the fused kernel"),
     EnvVar("TESSERACT_TP_FUSED_MIN_RS", "1024", "tokens per step from which GEMM -> reduce-scatter runs as the fused kernel"),
+    EnvVar("TESSERACT_NVTX", "0", "1: Trainer and ServingEngine open NVTX ranges around the phases of a step"),
+    EnvVar("TESSERACT_METRICS_FILE", "", "examples and the launcher: rank 0 appends one JSON record per step to this file"),
+    EnvVar("TESSERACT_WATCHDOG_S", "0", "launcher and examples: > 0 attaches a rank watchdog with this heartbeat timeout in seconds"),
     EnvVar("TESSERACT_PDL", "1", "serving decode GEMMs: 1 (programmatic dependent launch) | 0"),
     EnvVar("TESSERACT_CPU_GEMM", "torch", "2-D fp32 CPU products of ops.cpu_gemm.matmul_f32 callers: torch | native (host-runtime AVX2 GEMM)"),
     EnvVar("TESSERACT_SERVE_DECODE_GEMM", "auto", "serving decode GEMMs: auto | stream (always the weight-streaming kernel) | splitk (bf16: the cluster split-K kernel)"),

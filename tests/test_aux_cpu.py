@@ -132,3 +132,41 @@ def test_every_environment_variable_read_by_the_code_is_registered():
     missing = sorted(used - set(env.REGISTRY))
     assert not missing, f"not in utils/env.py: {missing}"
     assert "TESSERACT_SWIGLU" in used and len(used) >= 12
+
+
+def test_trainer_writes_metrics_and_stops_on_a_lost_peer(tmp_path):
+    """The instrumented Trainer: one metrics record per step; a peer's posted error or silence raises RankLost on the
+    host BEFORE the step launches anything (the step counter does not move); its own exception reaches the store."""
+    import json
+
+    from tesseract_b200.models import LlamaConfig, LlamaModel
+    from tesseract_b200.training import TrainConfig, Trainer
+    from tesseract_b200.utils.metrics import MetricsLogger
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1,
+                      intermediate_size=48, max_position_embeddings=16)
+    trainer = Trainer(LlamaModel(cfg, init_std=0.02, seed=0), TrainConfig(lr=1e-3))
+    now = [0.0]
+    store = DictStore()
+    me = RankWatchdog(store, 0, 2, timeout_s=5.0, clock=lambda: now[0])
+    peer = RankWatchdog(store, 1, 2, timeout_s=5.0, clock=lambda: now[0])
+    path = tmp_path / "m.jsonl"
+    trainer.instrument(metrics=MetricsLogger(str(path)), watchdog=me, nvtx_ranges=True)
+    batch = torch.randint(0, 64, (2, 9))
+    for _ in range(2):
+        peer.beat()
+        trainer.train_step(batch)
+    recs = [json.loads(line) for line in path.read_text().splitlines()]
+    assert [r["step"] for r in recs] == [1, 2] and all(r["step_ms"] > 0 and r["tokens_per_s_rank"] > 0 for r in recs)
+    now[0] = 10.0                                    # the peer has been silent for longer than the timeout
+    with pytest.raises(RankLost, match="no heartbeat"):
+        trainer.train_step(batch)
+    assert trainer.steps_done == 2
+    peer.beat()
+    peer.report_failure("ValueError: boom")
+    with pytest.raises(RankLost, match="boom"):
+        trainer.train_step(batch)
+    # this rank's own failure is posted for the others
+    with pytest.raises(Exception):
+        trainer.watchdog = RankWatchdog(DictStore(), 0, 1)
+        trainer.train_step(torch.randint(0, 64, (2, 40)))        # longer than max_position_embeddings
+    assert trainer.watchdog.store.get("tsb/hb/error/0")

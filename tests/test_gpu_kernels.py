@@ -766,6 +766,78 @@ def test_stream_linear_bf16_and_fp8_block_scaled(dev, M, N, K, bn, split, fp8):
     assert _native.read_status(torch.cuda.current_stream().cuda_stream) == 0
 
 
+@pytest.mark.parametrize("M,K", [(5, 256), (130, 4096), (256, 1024)])
+def test_quantize_act_mx_matches_the_torch_restatement(dev, M, K):
+    """The activation quantiser of the MX path: E4M3 payload and UE8M0 exponent words equal to the torch restatement
+    (powers of two make the scaling exact, so the bytes must agree), and the round trip stays within E4M3 precision."""
+    from tesseract_b200.ops import fp8 as f8
+    g = torch.Generator(device=dev).manual_seed(M + K)
+    x = (torch.randn(M, K, device=dev, generator=g) * torch.exp(torch.randn(M, 1, device=dev, generator=g) * 2)).bfloat16()
+    x[0, :64] = 0                                                          # two all-zero blocks
+    q, sf = f8.quantize_act_mx(x)
+    q_ref, sf_ref = f8.quantize_act_mx_ref(x)
+    assert torch.equal(sf, sf_ref)
+    assert torch.equal(q, q_ref)
+    back = f8.dequantize_act_mx(q, sf)
+    assert ((back - x.float()).abs() <= x.float().abs() * 2 ** -4 + 1e-30).all()
+
+
+@pytest.mark.parametrize("M,N,K,bn,split", [(16, 4096, 4096, 0, 0), (141, 6144, 4096, 0, 0), (64, 28672, 4096, 0, 0),
+                                            (128, 4096, 14336, 0, 0), (8, 200, 256, 0, 0), (300, 1024, 1024, 0, 0),
+                                            (37, 1000, 512, 48, 2), (256, 768, 4096, 0, 0), (24, 520, 1024, 240, 8),
+                                            (200, 4096, 4096, 208, 4), (1, 4096, 4096, 128, 1)])
+def test_mx_linear_block_scaled_fp8_on_the_tensor_core(dev, M, N, K, bn, split):
+    """tcgen05.mma kind::mxf8f6f4.block_scale decode GEMM against an fp32 product of the same dequantised operands.
+    The operands are drawn directly in their quantised form with a different exponent for every (row, 32-column) block
+    of the activations and every 128 x 128 block of the weights, so that a scale that reaches the wrong row, column
+    block or byte shows up as an error of a factor of two or more."""
+    from tesseract_b200 import _native
+    from tesseract_b200.ops import fp8 as f8
+    g = torch.Generator(device=dev).manual_seed(M * 11 + N + K)
+
+    def payload(rows, cols):
+        b = torch.randint(0, 256, (rows, cols), device=dev, generator=g, dtype=torch.int32)
+        b = torch.where((b & 0x7F) == 0x7F, b & 0x80 | 0x30, b)           # no NaN encodings
+        return b.to(torch.uint8)
+
+    q = payload(M, K)
+    ea = torch.randint(120, 131, (M, K // 32), device=dev, generator=g, dtype=torch.int64).view(M, K // 128, 4)
+    words = ea[:, :, 0] | (ea[:, :, 1] << 8) | (ea[:, :, 2] << 16) | (ea[:, :, 3] << 24)
+    sf = torch.full((K // 128, (M + 127) // 128 * 128), 0x7F7F7F7F, dtype=torch.int64, device=dev)
+    sf[:, :M] = words.t()
+    sf = sf.to(torch.int32)
+    wq = payload(N, K)
+    ws = torch.exp2(torch.randint(-12, -4, ((N + 127) // 128, K // 128), device=dev, generator=g).float())
+    want = f8.dequantize_act_mx(q, sf) @ f8.dequantize_weight(wq, ws).t()
+    got = f8.mx_linear(q, sf, wq, ws, bn=bn, split=split)
+    got_pdl = f8.mx_linear(q, sf, wq, ws, bn=bn, split=split, pdl=True)
+    torch.cuda.synchronize()
+    assert got.shape == (M, N)
+    err = ((got.float() - want).norm() / want.norm()).item()
+    assert err < 4e-3, err                                                 # bf16 rounding of the result only
+    assert (got.float() - want).abs().max().item() < 0.01 * want.abs().max().item()
+    assert torch.equal(got, got_pdl)
+    buf = torch.zeros(M, N + 8, device=dev, dtype=torch.bfloat16)
+    f8.mx_linear(q, sf, wq, ws, out=buf[:, :N], bn=bn, split=split)
+    assert torch.equal(buf[:, :N], got) and float(buf[:, N:].abs().max()) == 0.0
+    assert _native.read_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
+def test_mx_linear_from_bf16_operands(dev):
+    """Quantise-then-multiply against the bf16 product: the error is that of rounding both operands to E4M3."""
+    from tesseract_b200.ops import fp8 as f8
+    g = torch.Generator(device=dev).manual_seed(5)
+    for M, N, K in [(32, 4096, 4096), (160, 14336, 4096)]:
+        x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+        wq, ws = f8.quantize_weight(w, pow2=True)
+        assert f8.scales_are_pow2(ws)
+        q, sf = f8.quantize_act_mx(x)
+        got = f8.mx_linear(q, sf, wq, ws)
+        full = x.float() @ w.float().t()
+        assert ((got.float() - full).norm() / full.norm()).item() < 0.06
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("B,L,d,N", [(2, 1, 64, 16), (1, 50, 96, 8), (2, 300, 128, 16), (1, 1000, 64, 32)])
 def test_selective_scan_and_conv1d(dev, dtype, B, L, d, N):

@@ -255,3 +255,76 @@ def test_zero1_sharded_adam_matches_replicated_adam_over_gloo_ranks():
         assert r[0][0] == 0 and r[-1][1] == numel and all(a[1] == b[0] for a, b in zip(r, r[1:]))
         assert all(a % 64 == 0 for a, _ in r if a < numel)
     _run_ranks(_zero_worker, 3)
+
+
+def _replica_worker(rank, world):
+    from tesseract_b200.serving import make_replica_plan, split_requests
+    plan = make_replica_plan(world, rank, 2)
+    assert (plan.replicas, plan.replica, plan.tp_rank) == (world // 2, rank // 2, rank % 2)
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, group=plan.group)                        # the group holds exactly this replica's two ranks
+    assert t.item() == 4 * plan.replica + 1
+    mine = split_requests(list(range(10)), plan)
+    assert mine == [i for i in range(10) if i % plan.replicas == plan.replica]
+    return plan.is_leader
+
+
+def test_serving_replica_plan_over_gloo_ranks():
+    from tesseract_b200.serving import default_tp, make_replica_plan, split_requests
+    solo = make_replica_plan(1, 0, 1)
+    assert solo.replicas == 1 and solo.group is None and split_requests([3, 4], solo) == [3, 4]
+    assert [default_tp(w) for w in (1, 2, 4, 8)] == [1, 1, 2, 2]
+    with pytest.raises(ValueError):
+        make_replica_plan(8, 0, 3)
+    leaders = _run_ranks(_replica_worker, 4)
+    assert leaders == {0: True, 1: False, 2: True, 3: False}
+
+
+def _ep_model_worker(rank, world):
+    from tesseract_b200.models import LlamaConfig, LlamaModel
+    from tesseract_b200.parallel.ep_model import EPMoELlama
+    cfg = LlamaConfig(vocab_size=128, hidden_size=32, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, intermediate_size=48, max_position_embeddings=32, rope_theta=10000.0,
+                      num_experts=4, num_experts_per_tok=2)
+    full = LlamaModel(cfg, init_std=0.05, seed=11)                         # every expert, same on every rank
+    g = torch.Generator().manual_seed(5)
+    tok = torch.randint(0, 128, (world, 2, 16), generator=g)               # [rank, micro-batch, seq]
+    tgt = torch.randint(0, 128, (world, 2, 16), generator=g)
+    ref = sum(full.loss(tok[r, m:m + 1], tgt[r, m:m + 1]) for r in range(world) for m in range(2)) / (2 * world)
+    ref.backward()
+    ep = EPMoELlama(cfg, dist.group.WORLD, rank, world, None, max_tokens=16, exchange="nccl")
+    ep.load_full_state_dict(full.state_dict())
+    ep.zero_grad()
+    mine = sum(ep.forward_backward(tok[rank, m:m + 1], tgt[rank, m:m + 1], scale=1.0 / (2 * world)) for m in range(2))
+    ep.reduce_replicated_grads()
+    total = mine.clone()
+    dist.all_reduce(total)
+    assert abs(total.item() / (2 * world) - ref.item()) < 1e-5
+    want = dict(full.named_parameters())
+    el = cfg.num_experts // world
+    worst = 0.0
+    for name, p in ep.model.named_parameters():
+        parts = name.split(".")
+        if "experts" in parts:
+            at = parts.index("experts")
+            parts[at + 1] = str(int(parts[at + 1]) + rank * el)
+            got = p.grad
+        else:
+            got = p.main_grad
+        w = want[".".join(parts)].grad
+        w = torch.zeros_like(got) if w is None else w
+        got = torch.zeros_like(w) if got is None else got
+        d = (got - w).abs().max().item()
+        if d > 2e-5: print('BAD', rank, name, d, w.abs().max().item(), flush=True)
+        worst = max(worst, d)
+    assert worst < 2e-5, worst
+    # one decode step through caches equals the full model's
+    caches, fcaches = ep.make_kv_caches(1, 32), full.make_kv_caches(1, 32)
+    a = ep.decode_step(tok[rank, :1, :5], caches)
+    b = full.forward_step(tok[rank, :1, :5], fcaches)
+    assert (a - b).abs().max() < 1e-4
+    return worst
+
+
+def test_expert_parallel_moe_llama_matches_full_model_over_gloo_ranks():
+    _run_ranks(_ep_model_worker, 2)
