@@ -141,7 +141,7 @@ def run_serving_bench(requests=256, layers=32, kv_int8=False, top_p=1.0, tempera
         "steps": m["steps"], "decode_ms_per_step": m["decode_ms_per_step"],
         "decode_gpu_ms_per_step": m["decode_gpu_ms_per_step"], "max_batch": max_batch, "max_batch_per_replica": rep_batch,
         "block_size": block, "cuda_graph": cuda_graph,
-        "weights": "fp8-e4m3-block128 (bf16 activations on the K-heavy decode products, 1x128 fp8 elsewhere)"
+        "weights": "fp8-e4m3-block128, power-of-two scales (decode: E4M3 activations with 1x32 power-of-two scales on mxf8f6f4; prefill: 1x128 fp8)"
                    if eng.weights == "fp8" else "bf16",
         "weight_bytes_per_rank": eng.weight_bytes(), "layers": len(model.layers),
         "max_prefill_tokens": max_prefill_tokens, "_state": state,

@@ -121,65 +121,175 @@ __device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&v)
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// ------------------------------------------------------------------------------------------------ activation quantiser
+// ------------------------------------------------------------------------------------------------ activation quantisers
 // X [M, K] bf16 -> Xq [M, K] E4M3 and one UE8M0 exponent per row and 32 columns: q = x * 2^-(e - 127) with the smallest
 // e that keeps the block inside +-448. The exponents are stored as one 32-bit word per row and 128 columns (byte j =
 // columns 32 j .. 32 j + 31), laid out [K / 128][m_pad]: the word a GEMM CTA needs for (stage, row) is one load, and
-// the 32 rows a warp needs are contiguous. Rows M .. m_pad - 1 get exponent 127 (scale 1); the GEMM's tensor map fills
-// their activations with zeros.
-__global__ void __launch_bounds__(256)
-quant_act_mx_kernel(const __nv_bfloat16* __restrict__ X, long long ldx, uint8_t* __restrict__ Xq,
-                    uint32_t* __restrict__ sf, int M, int K, int m_pad) {
-  pdl_trigger();
-  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int per_row = K / 8;                         // threads per row: 8 elements each
-  const int row = static_cast<int>(t / per_row);
-  const int c8 = static_cast<int>(t - static_cast<long long>(row) * per_row);
-  if (row >= m_pad) return;                          // whole warps only: per_row is a multiple of 16 (K % 128 == 0)
-  const int lane = threadIdx.x & 31;
-  float v[8];
-  if (row < M) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(X + static_cast<long long>(row) * ldx + c8 * 8);
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(p[j]);
-      v[2 * j] = f.x;
-      v[2 * j + 1] = f.y;
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = 0.f;
-  }
+// the 32 rows a warp needs are contiguous. The GEMM reads no word of a row past M.
+//
+// All three kernels below give consecutive lanes consecutive 8-column vectors of one row, so four lanes share a
+// 32-column block and sixteen lanes a scale word; every lane of a warp calls the two helpers (lanes without data pass
+// zeros and writer = false).
+__device__ __forceinline__ uint32_t mx_quant8(const float (&v)[8], uint2* packed) {
   float amax = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));       // four threads share a 32-column block
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   // smallest power of two s with amax / s <= 448: exponent of amax / 448, rounded up
   const uint32_t bits = __float_as_uint(amax * (1.0f / 448.0f));
   int e = static_cast<int>((bits >> 23) & 0xffu) + ((bits & 0x7fffffu) ? 1 : 0);
   if (!(amax > 0.f)) e = 127;                        // an all-zero block: any scale does
   e = max(1, min(254, e));
-  const uint32_t byte = static_cast<uint32_t>(e);
-  if (row < M) {
-    const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);   // 2^(127 - e)
-    uint32_t w[4];
+  const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);   // 2^(127 - e)
+  uint32_t w[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      w[j] = __nv_cvt_float2_to_fp8x2(make_float2(v[2 * j] * inv, v[2 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-    uint2 o;
-    o.x = w[0] | (w[1] << 16);
-    o.y = w[2] | (w[3] << 16);
-    *reinterpret_cast<uint2*>(Xq + static_cast<long long>(row) * K + c8 * 8) = o;
-  }
-  // 16 threads cover 128 columns: lanes 0 and 16 of the warp assemble the word of their half
+  for (int j = 0; j < 4; ++j)
+    w[j] = __nv_cvt_float2_to_fp8x2(make_float2(v[2 * j] * inv, v[2 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+  packed->x = w[0] | (w[1] << 16);
+  packed->y = w[2] | (w[3] << 16);
+  return static_cast<uint32_t>(e);
+}
+// Assembles the scale word of every 16-lane group from its four exponent bytes; the group's first lane stores it.
+__device__ __forceinline__ void mx_store_word(uint32_t byte, int lane, bool writer, uint32_t* dst) {
   const int base = lane & 16;
   const uint32_t b0 = __shfl_sync(0xffffffffu, byte, base);
   const uint32_t b1 = __shfl_sync(0xffffffffu, byte, base + 4);
   const uint32_t b2 = __shfl_sync(0xffffffffu, byte, base + 8);
   const uint32_t b3 = __shfl_sync(0xffffffffu, byte, base + 12);
-  if ((lane & 15) == 0) sf[static_cast<long long>(c8 / 16) * m_pad + row] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+  if (writer && (lane & 15) == 0) *dst = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+}
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&v)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(p[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float block_sum(float v, float* red) {      // same order of additions as the RMSNorm kernel
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+__global__ void __launch_bounds__(256)
+quant_act_mx_kernel(const __nv_bfloat16* __restrict__ X, long long ldx, uint8_t* __restrict__ Xq,
+                    uint32_t* __restrict__ sf, int M, int K, int m_pad) {
+  pdl_trigger();
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int per_row = K / 8;                         // threads per row: 8 elements each, a multiple of 16
+  const int row = static_cast<int>(t / per_row);
+  const int c8 = static_cast<int>(t - static_cast<long long>(row) * per_row);
+  if (row >= m_pad) return;                          // whole warps only: m_pad * per_row is a multiple of 32
+  const int lane = threadIdx.x & 31;
+  float v[8];
+  if (row < M) {
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(X + static_cast<long long>(row) * ldx + c8 * 8), v);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  }
+  uint2 o;
+  const uint32_t byte = mx_quant8(v, &o);
+  if (row < M) *reinterpret_cast<uint2*>(Xq + static_cast<long long>(row) * K + c8 * 8) = o;
+  mx_store_word(byte, lane, true, sf + static_cast<long long>(c8 / 16) * m_pad + row);
+}
+
+// RMSNorm (+ residual add) whose bf16 result exists only as the quantised operand of the next GEMM: one CTA per row.
+// h = x (+ res), rounded to bf16 and written to h_out when a residual is given; y = bf16(h * rstd * w) -> (Xq, sf).
+// Same arithmetic as the stand-alone RMSNorm kernel followed by quant_act_mx_kernel.
+template <int MAXV>
+__global__ void __launch_bounds__(256)
+rmsnorm_quant_mx_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
+                        uint8_t* __restrict__ Xq, uint32_t* __restrict__ sf, int D, int m_pad, float eps) {
+  pdl_trigger();
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int nvec = D / 8;
+  const size_t off = static_cast<size_t>(row) * D;
+  float f[MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < nvec) {
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(x + off + v * 8), f[i]);
+      if (res) {
+        float g[8];
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(res + off + v * 8), g);
+        uint4 o;
+        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[i][j] = round_bf16(f[i][j] + g[j]);      // normalise what is stored
+#pragma unroll
+        for (int j = 0; j < 4; ++j) op[j] = pack_bf16x2(f[i][2 * j], f[i][2 * j + 1]);
+        *reinterpret_cast<uint4*>(h_out + off + v * 8) = o;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[i][j] * f[i][j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[i][j] = 0.f;
+    }
+  }
+  const float tot = block_sum(ss, red);
+  const float rstd = rsqrtf(tot / static_cast<float>(D) + eps);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * 256;
+    const bool have = v < nvec;
+    float y[8];
+    if (have) {
+      float g[8];
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(w + v * 8), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = round_bf16(f[i][j] * rstd * g[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = 0.f;
+    }
+    uint2 o;
+    const uint32_t byte = mx_quant8(y, &o);
+    if (have) *reinterpret_cast<uint2*>(Xq + off + v * 8) = o;
+    mx_store_word(byte, lane, have, sf + static_cast<long long>(v / 16) * m_pad + row);
+  }
+}
+
+// silu(gate) * up of a packed [rows, 2F] tensor, rounded to bf16 and quantised: grid (column chunks, rows).
+__global__ void __launch_bounds__(256)
+swiglu_quant_mx_kernel(const __nv_bfloat16* __restrict__ gate_up, uint8_t* __restrict__ Xq, uint32_t* __restrict__ sf,
+                       int F, int m_pad) {
+  pdl_trigger();
+  const int row = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const int v = blockIdx.x * 256 + threadIdx.x;
+  const bool have = v < F / 8;
+  const __nv_bfloat16* gp = gate_up + static_cast<size_t>(row) * 2 * F;
+  float y[8];
+  if (have) {
+    float g[8], u[8];
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(gp + v * 8), g);
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(gp + F + v * 8), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = round_bf16(__fdividef(g[j], 1.f + __expf(-g[j])) * u[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = 0.f;
+  }
+  uint2 o;
+  const uint32_t byte = mx_quant8(y, &o);
+  if (have) *reinterpret_cast<uint2*>(Xq + static_cast<size_t>(row) * F + v * 8) = o;
+  mx_store_word(byte, lane, have, sf + static_cast<long long>(v / 16) * m_pad + row);
 }
 
 // ------------------------------------------------------------------------------------------------ the GEMM
@@ -331,7 +441,10 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 #pragma unroll
     for (int c = 0; c < 8; ++c) blk[c] = min(((n0 + 32 * c + lane) >> 7) - rblk0, 2);
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    uint32_t a_next[RB][4];
+    // Activation scale words come from global memory (L2): kDepth stages are kept in flight in registers, so that a
+    // stage costs a quarter of a load latency instead of a whole one.
+    constexpr int kDepth = 4;
+    uint32_t ring[kDepth][RB][4];
     auto load_a = [&](int i, uint32_t (&dst)[RB][4]) {
       const uint32_t* src = sfa + static_cast<long long>(kb0 + i) * m_pad + m0 + lane;
 #pragma unroll
@@ -339,113 +452,181 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int r = rb * BM + 32 * c;
-          dst[rb][c] = (m0 + r + lane < m_pad) ? __ldg(src + r) : 0x7f7f7f7fu;
+          dst[rb][c] = (m0 + r + lane < M) ? __ldg(src + r) : 0x7f7f7f7fu;   // rows past M: scale 1 on zeros
         }
     };
     pdl_wait();                                     // the activation scales come from the kernel before this one
-    if (nk > 0) load_a(0, a_next);
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d)
+      if (d < nk) load_a(d, ring[d]);
     int s = 0;
     uint32_t phase = 0;
-    for (int i = 0; i < nk; ++i) {
-      uint32_t a_cur[RB][4];
+    bool alive = true;
+    for (int i0 = 0; i0 < nk && alive; i0 += kDepth) {
 #pragma unroll
-      for (int rb = 0; rb < RB; ++rb)
+      for (int d = 0; d < kDepth; ++d) {
+        const int i = i0 + d;
+        if (i >= nk || !alive) break;
+        uint32_t a_cur[RB][4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) a_cur[rb][c] = a_next[rb][c];
-      if (i + 1 < nk) load_a(i + 1, a_next);
-      const bool ok = mbar_wait(&empty[s], phase ^ 1u, &cta_abort, status);
-      if (!__all_sync(0xffffffffu, ok ? 1 : 0)) break;
-      tc_fence_after();
-      const uint32_t col = lane_addr + static_cast<uint32_t>(sf_base(RB) + s * kSfCols);
+        for (int rb = 0; rb < RB; ++rb)
 #pragma unroll
-      for (int rb = 0; rb < RB; ++rb) tmem_st_32x4(col + rb * 4, a_cur[rb][0], a_cur[rb][1], a_cur[rb][2], a_cur[rb][3]);
-      const int kk = min(i, kMaxSteps - 1);
-      uint32_t b[8];
+          for (int c = 0; c < 4; ++c) a_cur[rb][c] = ring[d][rb][c];
+        if (i + kDepth < nk) load_a(i + kDepth, ring[d]);
+        const bool ok = mbar_wait(&empty[s], phase ^ 1u, &cta_abort, status);
+        if (!__all_sync(0xffffffffu, ok ? 1 : 0)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t col = lane_addr + static_cast<uint32_t>(sf_base(RB) + s * kSfCols);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) b[c] = static_cast<uint32_t>(s_exp[blk[c] * kMaxSteps + kk]) * 0x01010101u;
-      tmem_st_32x8(col + 8, b);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&full[s]);
-      if (++s == ST) {
-        s = 0;
-        phase ^= 1u;
+        for (int rb = 0; rb < RB; ++rb)
+          tmem_st_32x4(col + rb * 4, a_cur[rb][0], a_cur[rb][1], a_cur[rb][2], a_cur[rb][3]);
+        const int kk = min(i, kMaxSteps - 1);
+        uint32_t b[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) b[c] = static_cast<uint32_t>(s_exp[blk[c] * kMaxSteps + kk]) * 0x01010101u;
+        tmem_st_32x8(col + 8, b);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+        if (++s == ST) {
+          s = 0;
+          phase ^= 1u;
+        }
       }
     }
   }
 
   // ---------------------------------------------------------------- epilogue (warps 2..5)
+  // Only the batch rows that exist are moved: a 16-row batch occupies one warp's lanes, the other three have nothing
+  // to do. Without a K split the bf16 result goes from the accumulator registers straight to global memory; with one,
+  // every CTA parks its fp32 partial rows in shared memory (over the idle rings) and sums an equal share of the rows
+  // from all S partials through distributed shared memory, several vectors in flight per thread.
   const int part_pitch = BN * 4 + 16;            // fp32 partial row, padded against bank conflicts
+  const int m_valid = min(M - m0, RB * BM);      // batch rows of this CTA that exist
   if (warp >= 2) {
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const bool ok = mbar_wait(&acc_bar, 0, &cta_abort, status);
     const bool warp_ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
     tc_fence_after();
-    // the rings are idle now: park this CTA's partial tile (RB * 128 rows) over them
 #pragma unroll
     for (int rb = 0; rb < RB; ++rb) {
-      uint8_t* prow = smem + (rb * BM + row) * part_pitch;
-      for (int c = 0; c < BN; c += 16) {
-        uint32_t r[16];
-        if (warp_ok && nk > 0) {
-          tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(rb * d_stride(RB) + c), r);
-          tmem_ld_wait();
-        } else {
+      const int rows_here = m_valid - rb * BM;
+      if (q * 32 >= rows_here) continue;         // warp-uniform
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(rb * d_stride(RB));
+      if (S == 1) {
+        const int grow = m0 + rb * BM + row;
+        __nv_bfloat16* yrow = Y + static_cast<long long>(grow) * ldy + n0;
+        const bool vec_ok = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          if (warp_ok && nk > 0) {
+            tmem_ld_32x16(t_row + static_cast<uint32_t>(c), r);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) r[i] = 0u;
+            for (int i = 0; i < 16; ++i) r[i] = 0u;
+          }
+          if (row < rows_here) {
+            if (vec_ok && n0 + c + 16 <= N) {
+              uint4 o0, o1;
+              o0.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+              o0.y = pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+              o0.z = pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+              o0.w = pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+              o1.x = pack_bf16x2(__uint_as_float(r[8]), __uint_as_float(r[9]));
+              o1.y = pack_bf16x2(__uint_as_float(r[10]), __uint_as_float(r[11]));
+              o1.z = pack_bf16x2(__uint_as_float(r[12]), __uint_as_float(r[13]));
+              o1.w = pack_bf16x2(__uint_as_float(r[14]), __uint_as_float(r[15]));
+              *reinterpret_cast<uint4*>(yrow + c) = o0;
+              *reinterpret_cast<uint4*>(yrow + c + 8) = o1;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (n0 + c + i < N) yrow[c + i] = __float2bfloat16(__uint_as_float(r[i]));
+            }
+          }
         }
+      } else {
+        uint8_t* prow = smem + (rb * BM + row) * part_pitch;
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          if (warp_ok && nk > 0) {
+            tmem_ld_32x16(t_row + static_cast<uint32_t>(c), r);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-        for (int i = 0; i < 16; i += 4)
-          *reinterpret_cast<uint4*>(prow + (c + i) * 4) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+            for (int i = 0; i < 16; ++i) r[i] = 0u;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<uint4*>(prow + (c + i) * 4) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+        }
       }
     }
     tc_fence_before();
   }
   __syncthreads();
-  cluster_sync_all();
-
-  if (warp >= 2) {
-    // CTA `slice` sums batch rows [slice * R / S, (slice + 1) * R / S) of all S partial tiles, R = RB * 128
-    constexpr int kRows = RB * BM / S;
-    const int t = (warp - 2) * 32 + lane;        // 0 .. 127
-    const int vec_per_row = BN / 4;
-    const int total = kRows * vec_per_row;
-    const bool vec_ok = (ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 7) == 0);
-    for (int it = t; it < total; it += 128) {
-      const int rr = it / vec_per_row;
-      const int cv = it - rr * vec_per_row;
-      const int row = slice * kRows + rr;
-      const int grow = m0 + row;
-      if (grow >= M) break;                      // rows are visited in increasing order
-      const uint32_t local = smem_u32(smem + row * part_pitch + cv * 16);
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (S > 1) {
+    cluster_sync_all();
+    if (warp >= 2) {
+      // CTA `slice` sums an equal share of the existing batch rows from all S partial tiles
+      const int rows_per = (m_valid + S - 1) / S;
+      const int row_lo = slice * rows_per;
+      const int row_hi = min(m_valid, row_lo + rows_per);
+      const int t = (warp - 2) * 32 + lane;        // 0 .. 127
+      const int vec_per_row = BN / 4;
+      const int total = max(0, row_hi - row_lo) * vec_per_row;
+      const bool vec_ok = (ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 7) == 0);
+      constexpr int U = S >= 8 ? 2 : 4;            // vectors per thread and pass: U * S remote loads in flight
+      for (int it0 = t; it0 < total; it0 += 128 * U) {
+        float4 v[U][S];
 #pragma unroll
-      for (int r = 0; r < S; ++r) {
-        const float4 v = ld_cluster_f4(map_to_cta(local, static_cast<uint32_t>(r)));
-        acc.x += v.x;
-        acc.y += v.y;
-        acc.z += v.z;
-        acc.w += v.w;
-      }
-      const int col = n0 + cv * 4;
-      __nv_bfloat16* dst = Y + static_cast<long long>(grow) * ldy + col;
-      if (vec_ok && col + 4 <= N) {
-        uint2 o;
-        o.x = pack_bf16x2(acc.x, acc.y);
-        o.y = pack_bf16x2(acc.z, acc.w);
-        *reinterpret_cast<uint2*>(dst) = o;
-      } else {
-        const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
-        for (int j = 0; j < 4; ++j)
-          if (col + j < N) dst[j] = __float2bfloat16(a4[j]);
+        for (int u = 0; u < U; ++u) {
+          const int it = it0 + u * 128;
+          if (it < total) {
+            const int rr = it / vec_per_row;
+            const uint32_t local = smem_u32(smem + (row_lo + rr) * part_pitch + (it - rr * vec_per_row) * 16);
+#pragma unroll
+            for (int r = 0; r < S; ++r) v[u][r] = ld_cluster_f4(map_to_cta(local, static_cast<uint32_t>(r)));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int it = it0 + u * 128;
+          if (it >= total) break;
+          const int rr = it / vec_per_row;
+          const int cv = it - rr * vec_per_row;
+          float4 acc = v[u][0];
+#pragma unroll
+          for (int r = 1; r < S; ++r) {
+            acc.x += v[u][r].x;
+            acc.y += v[u][r].y;
+            acc.z += v[u][r].z;
+            acc.w += v[u][r].w;
+          }
+          const int col = n0 + cv * 4;
+          __nv_bfloat16* dst = Y + static_cast<long long>(m0 + row_lo + rr) * ldy + col;
+          if (vec_ok && col + 4 <= N) {
+            uint2 o;
+            o.x = pack_bf16x2(acc.x, acc.y);
+            o.y = pack_bf16x2(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(dst) = o;
+          } else {
+            const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+            for (int j = 0; j < 4; ++j)
+              if (col + j < N) dst[j] = __float2bfloat16(a4[j]);
+          }
+        }
       }
     }
+    // nobody leaves (and frees its shared memory) before every CTA of the cluster has finished reading
+    cluster_sync_all();
   }
-
-  // nobody leaves (and frees its shared memory) before every CTA of the cluster has finished reading
-  cluster_sync_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -622,6 +803,39 @@ TSB_EXPORT int tsb_quant_act_mx(const void* X, long long ldx, void* Xq, void* sf
   const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
   quant_act_mx_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(X), ldx, static_cast<uint8_t*>(Xq), static_cast<uint32_t*>(sf), M, K, m_pad);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Fused producers of the same (Xq, sf) pair, bf16 only, D (F) % 128 == 0, dense rows:
+//   tsb_rmsnorm_quant_mx: y = rmsnorm(x + res) * w; h_out receives x + res when res is given (may alias x or res).
+//   tsb_swiglu_quant_mx:  y = silu(gate_up[:, :F]) * gate_up[:, F:].
+TSB_EXPORT int tsb_rmsnorm_quant_mx(const void* x, const void* res, const void* w, void* h_out, void* Xq, void* sf,
+                                    int rows, int D, float eps, void* stream) {
+  using namespace tsb;
+  if (rows <= 0 || D <= 0 || D % 128 || D > 8 * 256 * 4 || !x || !w || !Xq || !sf || (res && !h_out)) return -2;
+  const int m_pad = tsb_mx_m_pad(rows);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int maxv = (D / 8 + 255) / 256;
+#define TSB_RQ(MV)                                                                                                 \
+  rmsnorm_quant_mx_kernel<MV><<<rows, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),                            \
+                                                   static_cast<const __nv_bfloat16*>(res),                          \
+                                                   static_cast<const __nv_bfloat16*>(w),                            \
+                                                   static_cast<__nv_bfloat16*>(h_out), static_cast<uint8_t*>(Xq),   \
+                                                   static_cast<uint32_t*>(sf), D, m_pad, eps)
+  if (maxv <= 1) TSB_RQ(1);
+  else if (maxv <= 2) TSB_RQ(2);
+  else TSB_RQ(4);
+#undef TSB_RQ
+  return static_cast<int>(cudaGetLastError());
+}
+
+TSB_EXPORT int tsb_swiglu_quant_mx(const void* gate_up, void* Xq, void* sf, int rows, int F, void* stream) {
+  using namespace tsb;
+  if (rows <= 0 || rows > 65535 || F <= 0 || F % 128 || !gate_up || !Xq || !sf) return -2;
+  const dim3 grid(static_cast<unsigned>((F / 8 + 255) / 256), static_cast<unsigned>(rows));
+  swiglu_quant_mx_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), static_cast<uint8_t*>(Xq), static_cast<uint32_t*>(sf), F,
+      tsb_mx_m_pad(rows));
   return static_cast<int>(cudaGetLastError());
 }
 

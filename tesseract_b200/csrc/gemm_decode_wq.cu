@@ -350,76 +350,132 @@ gemm_decode_wq_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   }
 
   // ---------------------------------------------------------------- epilogue (warps 2..5)
+  // Only the batch rows that exist are moved: a 16-row batch occupies one warp's lanes, the other three have nothing
+  // to do. Without a K split the bf16 result goes from the accumulator registers straight to global memory; with one,
+  // every CTA parks its fp32 partial rows in shared memory (over the idle rings) and sums an equal share of the rows
+  // from all S partials through distributed shared memory, several vectors in flight per thread.
   const int part_pitch = BN * 4 + 16;            // fp32 partial row, padded against bank conflicts
+  const int m_valid = min(M - m0, RB * BM);      // batch rows of this CTA that exist
   if (warp >= 2 && warp < 6) {
     const int q = warp & 3;
     const int row = q * 32 + lane;
     const bool ok = mbar_wait(&acc_bar, 0, &cta_abort, status);
     const bool warp_ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
     tc_fence_after();
-    // the rings are idle now: park this CTA's partial tile (RB * 128 rows) over them
 #pragma unroll
     for (int rb = 0; rb < RB; ++rb) {
-      uint8_t* prow = smem + (rb * BM + row) * part_pitch;
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        if (warp_ok && nk > 0) {
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(rb * kMaxBN + c), r);
-          tmem_ld_wait();
-        } else {
+      const int rows_here = m_valid - rb * BM;
+      if (q * 32 >= rows_here) continue;         // warp-uniform
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(rb * kMaxBN);
+      if (S == 1) {
+        const int grow = m0 + rb * BM + row;
+        __nv_bfloat16* yrow = Y + static_cast<long long>(grow) * ldy + n0;
+        const bool vec_ok = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          if (warp_ok && nk > 0) {
+            tmem_ld_32x16(t_row + static_cast<uint32_t>(c), r);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+            for (int i = 0; i < 16; ++i) r[i] = 0u;
+          }
+          if (row < rows_here) {
+            if (vec_ok && n0 + c + 16 <= N) {
+              uint4 o0, o1;
+              o0.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+              o0.y = pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+              o0.z = pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+              o0.w = pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+              o1.x = pack_bf16x2(__uint_as_float(r[8]), __uint_as_float(r[9]));
+              o1.y = pack_bf16x2(__uint_as_float(r[10]), __uint_as_float(r[11]));
+              o1.z = pack_bf16x2(__uint_as_float(r[12]), __uint_as_float(r[13]));
+              o1.w = pack_bf16x2(__uint_as_float(r[14]), __uint_as_float(r[15]));
+              *reinterpret_cast<uint4*>(yrow + c) = o0;
+              *reinterpret_cast<uint4*>(yrow + c + 8) = o1;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (n0 + c + i < N) yrow[c + i] = __float2bfloat16(__uint_as_float(r[i]));
+            }
+          }
         }
+      } else {
+        uint8_t* prow = smem + (rb * BM + row) * part_pitch;
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          if (warp_ok && nk > 0) {
+            tmem_ld_32x16(t_row + static_cast<uint32_t>(c), r);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          if (c + i < BN) *reinterpret_cast<uint4*>(prow + (c + i) * 4) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+            for (int i = 0; i < 16; ++i) r[i] = 0u;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<uint4*>(prow + (c + i) * 4) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+        }
       }
     }
     tc_fence_before();
   }
   __syncthreads();
-  cluster_sync_all();
-
-  if (warp >= 2 && warp < 6) {
-    // CTA `slice` sums batch rows [slice * R / S, (slice + 1) * R / S) of all S partial tiles, R = RB * 128
-    constexpr int kRows = RB * BM / S;
-    const int t = (warp - 2) * 32 + lane;        // 0 .. 127
-    const int vec_per_row = BN / 4;
-    const int total = kRows * vec_per_row;
-    const bool vec_ok = (ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 7) == 0);
-    for (int it = t; it < total; it += 128) {
-      const int rr = it / vec_per_row;
-      const int cv = it - rr * vec_per_row;
-      const int row = slice * kRows + rr;
-      const int grow = m0 + row;
-      if (grow >= M) break;                      // rows are visited in increasing order
-      const uint32_t local = smem_u32(smem + row * part_pitch + cv * 16);
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (S > 1) {
+    cluster_sync_all();
+    if (warp >= 2 && warp < 6) {
+      // CTA `slice` sums an equal share of the existing batch rows from all S partial tiles
+      const int rows_per = (m_valid + S - 1) / S;
+      const int row_lo = slice * rows_per;
+      const int row_hi = min(m_valid, row_lo + rows_per);
+      const int t = (warp - 2) * 32 + lane;        // 0 .. 127
+      const int vec_per_row = BN / 4;
+      const int total = max(0, row_hi - row_lo) * vec_per_row;
+      const bool vec_ok = (ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 7) == 0);
+      constexpr int U = S >= 8 ? 2 : 4;            // vectors per thread and pass: U * S remote loads in flight
+      for (int it0 = t; it0 < total; it0 += 128 * U) {
+        float4 v[U][S];
 #pragma unroll
-      for (int r = 0; r < S; ++r) {
-        const float4 v = ld_cluster_f4(map_to_cta(local, static_cast<uint32_t>(r)));
-        acc.x += v.x;
-        acc.y += v.y;
-        acc.z += v.z;
-        acc.w += v.w;
-      }
-      const int col = n0 + cv * 4;
-      __nv_bfloat16* dst = Y + static_cast<long long>(grow) * ldy + col;
-      if (vec_ok && col + 4 <= N) {
-        uint2 o;
-        o.x = pack_bf16x2(acc.x, acc.y);
-        o.y = pack_bf16x2(acc.z, acc.w);
-        *reinterpret_cast<uint2*>(dst) = o;
-      } else {
-        const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
-        for (int j = 0; j < 4; ++j)
-          if (col + j < N) dst[j] = __float2bfloat16(a4[j]);
+        for (int u = 0; u < U; ++u) {
+          const int it = it0 + u * 128;
+          if (it < total) {
+            const int rr = it / vec_per_row;
+            const uint32_t local = smem_u32(smem + (row_lo + rr) * part_pitch + (it - rr * vec_per_row) * 16);
+#pragma unroll
+            for (int r = 0; r < S; ++r) v[u][r] = ld_cluster_f4(map_to_cta(local, static_cast<uint32_t>(r)));
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int it = it0 + u * 128;
+          if (it >= total) break;
+          const int rr = it / vec_per_row;
+          const int cv = it - rr * vec_per_row;
+          float4 acc = v[u][0];
+#pragma unroll
+          for (int r = 1; r < S; ++r) {
+            acc.x += v[u][r].x;
+            acc.y += v[u][r].y;
+            acc.z += v[u][r].z;
+            acc.w += v[u][r].w;
+          }
+          const int col = n0 + cv * 4;
+          __nv_bfloat16* dst = Y + static_cast<long long>(m0 + row_lo + rr) * ldy + col;
+          if (vec_ok && col + 4 <= N) {
+            uint2 o;
+            o.x = pack_bf16x2(acc.x, acc.y);
+            o.y = pack_bf16x2(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(dst) = o;
+          } else {
+            const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+            for (int j = 0; j < 4; ++j)
+              if (col + j < N) dst[j] = __float2bfloat16(a4[j]);
+          }
+        }
       }
     }
+    // nobody leaves (and frees its shared memory) before every CTA of the cluster has finished reading
+    cluster_sync_all();
   }
-
-  // nobody leaves (and frees its shared memory) before every CTA of the cluster has finished reading
-  cluster_sync_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {

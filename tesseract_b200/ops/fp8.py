@@ -23,6 +23,8 @@ _native.register_signatures({
     "tsb_quant_tensor_e4m3": [P, P, P, L, I, P],
     "tsb_quant_act_mx": [P, L, P, P, I, I, P],
     "tsb_gemm_decode_mx": [P, P, P, P, P, I, I, I, L, L, I, I, I, P],
+    "tsb_rmsnorm_quant_mx": [P, P, P, P, P, P, I, I, _native.F, P],
+    "tsb_swiglu_quant_mx": [P, P, P, I, I, P],
     "tsb_gemm_decode_mx_plan": [I, I, I, P, P, P, P],
 })
 
@@ -233,6 +235,48 @@ def quantize_act_mx(x: torch.Tensor, out=None):
         q, sf = out
     check(lib().tsb_quant_act_mx(x.data_ptr(), x.stride(0), q.data_ptr(), sf.data_ptr(), M, K, stream_ptr(x.device)),
           "tsb_quant_act_mx")
+    return q, sf
+
+
+def _mx_buffers(M: int, K: int, device):
+    return (torch.empty((M, K), dtype=torch.uint8, device=device),
+            torch.empty((K // 128, _mx_m_pad(M)), dtype=torch.int32, device=device))
+
+
+def rms_norm_quant_mx(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
+    """RMSNorm whose result exists only as the MX-quantised operand of the next GEMM (one kernel):
+    returns ``(q, sf, h)`` with ``h = x + residual`` (``x`` itself without a residual) and ``(q, sf)`` =
+    ``quantize_act_mx(rmsnorm(h) * weight)``. x [M, D] bf16, D % 128 == 0."""
+    M, D = x.shape
+    fused = _native_ok(x) and x.dtype == torch.bfloat16 and D % 128 == 0 and D <= 8192 and x.is_contiguous() \
+        and (residual is None or residual.is_contiguous())
+    if not fused:
+        from . import fused as F_
+        if residual is None:
+            y, h = F_.rms_norm(x, weight, eps), x
+        else:
+            y, h = F_.rms_norm(x, weight, eps, residual=residual)
+        q, sf = quantize_act_mx(y)
+        return q, sf, h
+    q, sf = _mx_buffers(M, D, x.device)
+    h = torch.empty_like(x) if residual is not None else x
+    check(lib().tsb_rmsnorm_quant_mx(x.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                     weight.data_ptr(), h.data_ptr() if residual is not None else None, q.data_ptr(),
+                                     sf.data_ptr(), M, D, float(eps), stream_ptr(x.device)), "tsb_rmsnorm_quant_mx")
+    return q, sf, h
+
+
+def swiglu_quant_mx(gate_up: torch.Tensor):
+    """``quantize_act_mx(swiglu(gate_up))`` in one kernel: gate_up [M, 2F] bf16 (gate first), F % 128 == 0."""
+    M, F2 = gate_up.shape
+    F = F2 // 2
+    if not (_native_ok(gate_up) and gate_up.dtype == torch.bfloat16 and F % 128 == 0 and gate_up.is_contiguous()
+            and M <= 65535):
+        from . import fused as F_
+        return quantize_act_mx(F_.swiglu(gate_up))
+    q, sf = _mx_buffers(M, F, gate_up.device)
+    check(lib().tsb_swiglu_quant_mx(gate_up.data_ptr(), q.data_ptr(), sf.data_ptr(), M, F, stream_ptr(gate_up.device)),
+          "tsb_swiglu_quant_mx")
     return q, sf
 
 

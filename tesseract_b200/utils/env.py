@@ -42,9 +42,10 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_NVTX", "0", "1: Trainer and ServingEngine open NVTX ranges around the phases of a step"),
     EnvVar("TESSERACT_METRICS_FILE", "", "examples and the launcher: rank 0 appends one JSON record per step to this file"),
     EnvVar("TESSERACT_WATCHDOG_S", "0", "launcher and examples: > 0 attaches a rank watchdog with this heartbeat timeout in seconds"),
+    EnvVar("TESSERACT_MX_FUSED_QUANT", "1", "serving, fp8 weights: 1 (RMSNorm / SwiGLU write the quantised GEMM operand directly) | 0 (separate quantiser kernel)"),
     EnvVar("TESSERACT_PDL", "1", "serving decode GEMMs: 1 (programmatic dependent launch) | 0"),
     EnvVar("TESSERACT_CPU_GEMM", "torch", "2-D fp32 CPU products of ops.cpu_gemm.matmul_f32 callers: torch | native (host-runtime AVX2 GEMM)"),
-    EnvVar("TESSERACT_SERVE_DECODE_GEMM", "auto", "serving decode GEMMs: auto | stream (always the weight-streaming kernel) | splitk (bf16: the cluster split-K kernel)"),
+    EnvVar("TESSERACT_SERVE_DECODE_GEMM", "auto", "serving decode GEMMs: auto | mx (fp8 weights: tensor-core block scaling) | stream (always the weight-streaming kernel) | splitk (bf16: the cluster split-K kernel) | fp8gemm (fp8 weights: never mx)"),
     EnvVar("TESSERACT_SWIGLU", "2", "SwiGLU kernels: 2 (row-wise, two vector pairs per thread) | 0 (flat kernel, for A/B runs)"),
 ]}
 
