@@ -175,6 +175,8 @@ def main():
             status = _native.read_status(torch.cuda.current_stream().cuda_stream)
             kind = "rs" if op == "gemm_rs" else "ag"
             choice = "fused" if (fused_ok and M >= prod_min[kind]) else "nccl"
+            if kind == "ag" and N < 1024 and M < 32768:
+                choice = "nccl"                    # the rule of parallel.tp_layers for gathers with few columns per rank
             if rank == 0:
                 r4 = lambda v: None if v is None else round(v, 4)   # noqa: E731
                 best_unfused = min(tn, tc)

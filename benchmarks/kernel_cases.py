@@ -167,6 +167,33 @@ def case_stream_linear(b: Bench):
             report(f"stream_linear_layer_{key}_M{M}", tot[key][0], bytes_=tot[key][1])
 
 
+def case_mx_linear(b: Bench):
+    """The block-scaled fp8 decode GEMM on tcgen05.mma kind::mxf8f6f4 (E4M3 activations and weights, power-of-two
+    scales applied by the tensor core) on the layer shapes of one decode step; bytes = the fp8 weight matrix once.
+    ``with_quant`` adds the stand-alone activation quantiser in front (the serving engine fuses it into RMSNorm /
+    SwiGLU instead); ``TESSERACT_KERNEL_CASES_SMALL=1`` runs one shape only (a profiler capture)."""
+    import os
+
+    from tesseract_b200.ops import fp8
+    small = os.environ.get("TESSERACT_KERNEL_CASES_SMALL", "0") == "1"
+    shapes = (("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336))
+    for M in ((32,) if small else (16, 32, 64, 128, 256)):
+        tot = [0.0, 0.0, 0]
+        for name, N, K in (shapes[2:3] if small else shapes):
+            x, w = b.randn(M, K), b.randn(N, K, scale=0.02)
+            wq, ws = fp8.quantize_weight(w, pow2=True)
+            q, sf = fp8.quantize_act_mx(x)
+            ms = b.time(lambda: fp8.mx_linear(q, sf, wq, ws))
+            ms_q = b.time(lambda: fp8.mx_linear(*fp8.quantize_act_mx(x, out=(q, sf)), wq, ws, pdl=True))
+            tot[0] += ms
+            tot[1] += ms_q
+            tot[2] += N * K
+            bn, split, stages, _ = fp8.mx_linear_plan(M, N, K)
+            report(f"mx_linear_{name}_M{M}", ms, bytes_=N * K, shape=[M, N, K], with_quant_ms=round(ms_q, 4),
+                   tile=bn, k_split=split, stages=stages)
+        report(f"mx_linear_layer_M{M}", tot[0], bytes_=tot[2], with_quant_ms=round(tot[1], 4))
+
+
 def case_grouped_gemm(b: Bench):
     from tesseract_b200.ops import moe
     E, N, K, per = 8, 4096, 4096, 2048
@@ -360,7 +387,7 @@ CASES = {"gemm": case_gemm, "gemm_fp8": case_gemm_fp8, "gemm_fp8_pertensor": cas
          "flash_fwd": case_flash_fwd, "flash_bwd": case_flash_bwd, "decode": case_decode,
          "decode_int8": case_decode_int8, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu, "swiglu_bwd": case_swiglu_bwd, "adam": case_adam,
          "ce_stats": case_ce, "selective_scan": case_scan, "gemv_w8": case_gemv, "gemm_rs_emul": case_gemm_rs_emul,
-         "ag_gemm_emul": case_ag_gemm_emul, "stream_linear": case_stream_linear}
+         "ag_gemm_emul": case_ag_gemm_emul, "stream_linear": case_stream_linear, "mx_linear": case_mx_linear}
 
 
 def main():

@@ -20,6 +20,7 @@ enum : int {
   kStatusMbarTimeout = 1,    // an mbarrier wait inside a kernel ran out
   kStatusFlagTimeout = 2,    // a cross-CTA / cross-GPU flag wait ran out
   kStatusBadArgument = 3,
+  kStatusBadIndex = 4,       // a data-dependent index (token id, block-table entry) was out of range; the access was redirected or skipped
 };
 
 // ~1 s at 1.9 GHz; long enough for any legitimate wait, short enough to keep a context alive.

@@ -81,6 +81,7 @@ struct MmaDecParams {
   float* part_ml;
   int A, H, Hkv, bs, nb, max_logical, splits, gh;  // gh = query heads per CTA (<= 8)
   float scale_log2;
+  int* status;           // device status word: a block-table entry outside the pool is reported there
 };
 
 // INT8 pools: the raw int8 rows (and their scales) travel through the cp.async ring and are widened to T in a
@@ -156,7 +157,10 @@ paged_decode_mma_kernel(MmaDecParams p) {
   // one shuffle per 16-byte piece, no divisions and no table reads.
   auto row_of = [&](int t, bool valid) -> long long {
     int blk = valid ? table[t / p.bs] : 0;
-    blk = (blk < 0 || blk >= p.nb) ? 0 : blk;
+    if (blk < 0 || blk >= p.nb) {       // never read outside the pool: block 0 instead, and the host hears of it
+      if (p.status) atomicCAS(p.status, kStatusOk, kStatusBadIndex);
+      blk = 0;
+    }
     return (static_cast<long long>(blk) * p.Hkv + hk) * p.bs + (valid ? t % p.bs : 0);
   };
   auto issue = [&](int j) {
@@ -392,6 +396,7 @@ int paged_decode_mma_dispatch(const void* q, const void* k_pool, const void* v_p
   p.part_o = part_o; p.part_ml = part_ml;
   p.A = A; p.H = H; p.Hkv = Hkv; p.bs = bs; p.nb = nb; p.max_logical = max_logical; p.splits = splits; p.gh = gh;
   p.scale_log2 = scale_log2;
+  p.status = device_status_word();
   const bool i8 = k_scale != nullptr;
   if (dtype == 1) {
     if (D == 128) return i8 ? launch_mma<__nv_bfloat16, 128, true>(p, s) : launch_mma<__nv_bfloat16, 128, false>(p, s);

@@ -415,7 +415,7 @@ rope_qkv_kernel(T* __restrict__ qkv, const float* __restrict__ cos_t, const floa
 template <typename T>
 __global__ void __launch_bounds__(256)
 embedding_fwd_kernel(const long long* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
-                     long long tokens, int D, int vocab) {
+                     long long tokens, int D, int vocab, int* status) {
   const int vpr = D / 8;
   const long long nvec = tokens * vpr;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
@@ -423,7 +423,10 @@ embedding_fwd_kernel(const long long* __restrict__ ids, const T* __restrict__ ta
     const long long t = i / vpr;
     const int c = static_cast<int>(i - t * vpr) * 8;
     long long id = ids[t];
-    if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; clamp as defence in depth
+    if (id < 0 || id >= vocab) {        // never read outside the table: row 0 instead, and the host hears of it
+      if (c == 0 && status) atomicCAS(status, kStatusOk, kStatusBadIndex);
+      id = 0;
+    }
     float f[8];
     load8<T>(table + id * D + c, f);
     store8<T>(out + t * D + c, f);
@@ -433,7 +436,7 @@ embedding_fwd_kernel(const long long* __restrict__ ids, const T* __restrict__ ta
 template <typename T, typename G>
 __global__ void __launch_bounds__(256)
 embedding_bwd_kernel(const long long* __restrict__ ids, const T* __restrict__ dy, G* __restrict__ dtable,
-                     long long tokens, int D, int vocab) {
+                     long long tokens, int D, int vocab, int* status) {
   const int vpr = D / 8;
   const long long nvec = tokens * vpr;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
@@ -441,7 +444,10 @@ embedding_bwd_kernel(const long long* __restrict__ ids, const T* __restrict__ dy
     const long long t = i / vpr;
     const int c = static_cast<int>(i - t * vpr) * 8;
     const long long id = ids[t];
-    if (id < 0 || id >= vocab) continue;
+    if (id < 0 || id >= vocab) {
+      if (status) atomicCAS(status, kStatusOk, kStatusBadIndex);
+      continue;
+    }
     float f[8];
     load8<T>(dy + t * D + c, f);
     G* dst = dtable + id * D + c;
@@ -632,7 +638,7 @@ TSB_EXPORT int tsb_embedding_fwd(const long long* ids, const void* table, void* 
   const int grid = tsb::ew_grid(tokens * (D / 8), 256);
   TSB_DISPATCH_FLOAT(dtype, (tsb::embedding_fwd_kernel<T><<<grid, 256, 0, s>>>(ids, static_cast<const T*>(table),
                                                                               static_cast<T*>(out), tokens, D,
-                                                                              vocab)));
+                                                                              vocab, tsb::device_status_word())));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -644,11 +650,12 @@ TSB_EXPORT int tsb_embedding_bwd(const long long* ids, const void* dy, void* dta
   const int grid = tsb::ew_grid(tokens * (D / 8), 256);
   if (grad_f32) {
     TSB_DISPATCH_FLOAT(dtype, (tsb::embedding_bwd_kernel<T, float><<<grid, 256, 0, s>>>(
-                                  ids, static_cast<const T*>(dy), static_cast<float*>(dtable), tokens, D, vocab)));
+                                  ids, static_cast<const T*>(dy), static_cast<float*>(dtable), tokens, D, vocab,
+                                  tsb::device_status_word())));
   } else {
     TSB_DISPATCH_FLOAT(dtype, (tsb::embedding_bwd_kernel<T, __nv_bfloat16><<<grid, 256, 0, s>>>(
                                   ids, static_cast<const T*>(dy), static_cast<__nv_bfloat16*>(dtable), tokens, D,
-                                  vocab)));
+                                  vocab, tsb::device_status_word())));
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -298,8 +298,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                       const uint32_t* __restrict__ sfa, const float* __restrict__ w_scale,
                       __nv_bfloat16* __restrict__ Y, int M, int N, int K, int m_pad, long long ldy, int BN,
-                      int scale_cols, int scale_rows, const Layout L, int* status) {
+                      int scale_cols, int scale_rows, const Layout L, int* status, long long* trace) {
   const int ST = L.stages;
+  // diagnostics: per-CTA phase timestamps (ns) when the host installed a trace buffer [CTAs][8]
+  auto stamp = [&](int slot) {
+    if (trace) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");   // the clobber keeps it behind the barriers
+      trace[static_cast<long long>(blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = static_cast<long long>(t);
+    }
+  };
+  if (threadIdx.x == 0) stamp(0);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sX = smem;
@@ -345,6 +354,7 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
+  if (threadIdx.x == 0) stamp(1);                  // set-up done
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -403,6 +413,7 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       uint32_t phase = 0;
       for (int i = 0; i < nk; ++i) {
         if (!mbar_wait(&full[s], phase, &cta_abort, status)) break;
+        if (i == 0) stamp(2);                      // first stage complete (weights, activations, scales)
         tc_fence_after();
         const uint32_t a_base = smem_u32(sX + s * L.x_pitch);
         const uint32_t b_base = smem_u32(sW + s * L.w_pitch);
@@ -423,19 +434,27 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         }
       }
       umma_commit(&acc_bar);
+      stamp(3);                                    // last MMA issued
     }
   } else {
     // ------------------------------------------------------------ scale warps (2 .. 5): one lane quadrant each
     const int q = warp & 3;
     const int t = (warp - 2) * 32 + lane;
     const int rblk0 = n0 >> 7;
-    for (int e = t; e < 3 * nk && e < 3 * kMaxSteps; e += 128) {
-      const int b3 = e / nk, kk = e - b3 * nk;
-      const float sc = __ldg(w_scale + static_cast<long long>(min(rblk0 + b3, scale_rows - 1)) * scale_cols +
-                             min(kb0 + kk, scale_cols - 1));
-      s_exp[b3 * kMaxSteps + kk] = static_cast<uint8_t>((__float_as_uint(sc) >> 23) & 0xffu);
+    // The weight exponents (cold: they come from HBM) and the first activation scale words (written by the kernel
+    // before this one) are requested together; the exponents are parked in shared memory once both are under way.
+    constexpr int kExpPerThread = 3 * kMaxSteps / 128;
+    float w_sc[kExpPerThread];
+#pragma unroll
+    for (int j = 0; j < kExpPerThread; ++j) {
+      const int e = t + j * 128;
+      w_sc[j] = 1.f;
+      if (e < 3 * nk && e < 3 * kMaxSteps) {
+        const int b3 = e / nk, kk = e - b3 * nk;
+        w_sc[j] = __ldg(w_scale + static_cast<long long>(min(rblk0 + b3, scale_rows - 1)) * scale_cols +
+                        min(kb0 + kk, scale_cols - 1));
+      }
     }
-    asm volatile("bar.sync 2, 128;" ::: "memory");
     // which of the CTA's (at most three) 128-row weight blocks each of this thread's eight scale rows belongs to
     int blk[8];
 #pragma unroll
@@ -459,6 +478,15 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 #pragma unroll
     for (int d = 0; d < kDepth; ++d)
       if (d < nk) load_a(d, ring[d]);
+#pragma unroll
+    for (int j = 0; j < kExpPerThread; ++j) {
+      const int e = t + j * 128;
+      if (e < 3 * nk && e < 3 * kMaxSteps) {
+        const int b3 = e / nk, kk = e - b3 * nk;
+        s_exp[b3 * kMaxSteps + kk] = static_cast<uint8_t>((__float_as_uint(w_sc[j]) >> 23) & 0xffu);
+      }
+    }
+    asm volatile("bar.sync 2, 128;" ::: "memory");
     int s = 0;
     uint32_t phase = 0;
     bool alive = true;
@@ -492,6 +520,7 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&full[s]);
+        if (i == 0 && threadIdx.x == 64) stamp(5);   // scales of the first stage in tensor memory
         if (++s == ST) {
           s = 0;
           phase ^= 1u;
@@ -513,6 +542,7 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     const bool ok = mbar_wait(&acc_bar, 0, &cta_abort, status);
     const bool warp_ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
     tc_fence_after();
+    if (threadIdx.x == 64) stamp(4);               // accumulator complete
 #pragma unroll
     for (int rb = 0; rb < RB; ++rb) {
       const int rows_here = m_valid - rb * BM;
@@ -573,6 +603,7 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   __syncthreads();
   if (S > 1) {
     cluster_sync_all();
+    if (threadIdx.x == 0) stamp(6);
     if (warp >= 2) {
       // CTA `slice` sums an equal share of the existing batch rows from all S partial tiles
       const int rows_per = (m_valid + S - 1) / S;
@@ -629,6 +660,7 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) stamp(7);
   if (warp == 1) {
     if (cta_abort) {
       for (int i = 0; i < 1000; ++i) __nanosleep(1000);
@@ -637,6 +669,8 @@ gemm_decode_mx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     tmem_dealloc(tmem_base, kTmemCols);
   }
 }
+
+long long* g_trace = nullptr;   // diagnostics: see tsb_gemm_decode_mx_trace
 
 template <int S, int RB>
 cudaError_t config_mx(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at, int grid_x, int grid_y, int pdl, cudaStream_t s) {
@@ -678,7 +712,7 @@ int launch_mx(const CUtensorMap& tx, const CUtensorMap& tw, const uint32_t* sfa,
   if (e != cudaSuccess) return static_cast<int>(e);
   return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_decode_mx_kernel<S, RB>, tx, tw, sfa, w_scale,
                                              static_cast<__nv_bfloat16*>(Y), M, N, K, m_pad, ldy, BN, scale_cols,
-                                             scale_rows, L, device_status_word()));
+                                             scale_rows, L, device_status_word(), g_trace));
 }
 
 // CTAs that can be resident at once when launched as clusters of S (a GPC takes whole clusters only).
@@ -887,6 +921,11 @@ TSB_EXPORT int tsb_gemm_decode_mx(const void* Xq, const void* sf, const void* W,
 #undef TSB_MX
 #undef TSB_MX_ARGS
 }
+
+// Diagnostics: the launches that follow write eight nanosecond timestamps per CTA into `buf` (int64 [CTAs][8]: start,
+// set-up done, first stage landed, last MMA issued, accumulator complete, first scales written, cluster synchronised, end);
+// nullptr switches it off again.
+TSB_EXPORT void tsb_gemm_decode_mx_trace(void* buf) { tsb::g_trace = static_cast<long long*>(buf); }
 
 // The plan the call above makes (host only): *bn (a positive value fixes the width), *split, ring depth (negative: two
 // row blocks per CTA), resident CTAs for that cluster size.

@@ -54,12 +54,19 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
 //           coordinate advances by b_group_rows per group; row blocks at or beyond offsets[groups] are skipped.
 //   mode 2  reduction grouped (expert weight gradient, A and B both MN-major): work item (g, m_blk, n_blk) reduces
 //           over rows [offsets[g], offsets[g + 1]) and writes C + g * c_group_stride; an empty group adds nothing.
+//   mode 1 with `row_tags` (expert-parallel return path): the result rows do not go to C but straight to the rank
+//           each row came from -- row r with tag t >= 0 is stored at peer_out[t >> 24] + (t & 0xFFFFFF) * ldc (peer-mapped
+//           memory of that rank, over NVLink), rows with a negative tag (padding) are dropped. The all-to-all that
+//           returns expert results is the epilogue of the down projection; nothing is written locally.
 struct GroupArgs {
   const int* offsets;
   int groups;
   int mode;
   long long b_group_rows;
   long long c_group_stride;
+  const int* row_tags = nullptr;
+  long long peer_rows = 0;
+  void* peer_out[8] = {};
 };
 
 __device__ __forceinline__ int group_of_row(const GroupArgs& g, int row) {
@@ -242,6 +249,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = m0 + row_in_tile;
       OutT* crow = Cg + static_cast<long long>(row) * ldc;
+      bool row_ok = row < M;
+      if (gmode == 1 && grp.row_tags) {
+        const int tag = row_ok ? __ldg(grp.row_tags + row) : -1;
+        const long long slot = tag & 0xFFFFFF;
+        row_ok = tag >= 0 && slot < grp.peer_rows;
+        if (row_ok) {
+          const int owner = (tag >> 24) & 7;
+          void* base = grp.peer_out[0];      // selected by comparison: a dynamic index would move the array to local memory
+#pragma unroll
+          for (int r = 1; r < 8; ++r)
+            if (owner == r) base = grp.peer_out[r];
+          crow = static_cast<OutT*>(base) + slot * ldc;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -252,7 +273,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
         const int col0 = n0 + c * 32;
-        if (row < M && col0 < N) {
+        if (row_ok && col0 < N) {
           if (vec_ok && col0 + 32 <= N) {
             if constexpr (sizeof(OutT) == 2) {
               uint4* dst = reinterpret_cast<uint4*>(crow + col0);
@@ -526,6 +547,50 @@ TSB_EXPORT int tsb_gemm_grouped(const void* A, const void* B, void* C, const int
     return go(std::integral_constant<int, 64>{});
   }
   return -2;
+}
+
+// Row-grouped GEMM (mode 1 above) whose result rows are scattered to peer-mapped buffers instead of a local C:
+// row r goes to peer_out[tags[r] >> 24] + (tags[r] & 0xFFFFFF) * ld_out when tags[r] >= 0 (and the slot is below
+// peer_rows), nowhere otherwise. peer_out: `world` (<= 8) device pointers as mapped in this process, 16-byte aligned,
+// ld_out % 8 == 0. Plain stores: the caller orders them with its own barrier (e.g. tsb_symm_barrier).
+TSB_EXPORT int tsb_gemm_grouped_scatter(const void* A, const void* B, const int* offsets, int groups, int rows_cap, int N,
+                                        int K, long long lda, long long ldb, int b_mn, long long b_group_stride,
+                                        const int* tags, void* const* peer_out, int world, long long peer_rows,
+                                        long long ld_out, void* stream) {
+  using namespace tsb;
+  if (!offsets || !tags || !peer_out || world < 1 || world > 8 || groups < 1 || groups > 1024 || rows_cap <= 0 ||
+      rows_cap % BM || N <= 0 || K <= 0 || K % 8 || ld_out % 8 || peer_rows <= 0 || peer_rows > 0xFFFFFF)
+    return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % 8) || (ldb % 8)) return -2;
+  if (b_mn && (K % BK)) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUtensorMap ta, tb;
+  const int bn = (N >= 256) ? 256 : (N >= 128 ? 128 : 64);
+  if (!cached_tmap_2d(&ta, A, rows_cap, K, lda * 2, BM, BK)) return -3;
+  if (b_group_stride <= 0 || b_group_stride % ldb) return -2;
+  const long long grows = b_group_stride / ldb;
+  if (grows < (b_mn ? K : N)) return -2;
+  const uint64_t map_rows = static_cast<uint64_t>(groups - 1) * grows + (b_mn ? K : N);
+  const bool ok = b_mn ? cached_tmap_2d(&tb, B, map_rows, N, ldb * 2, BK, 64)
+                       : cached_tmap_2d(&tb, B, map_rows, K, ldb * 2, bn, BK);
+  if (!ok) return -3;
+  GroupArgs g{offsets, groups, 1, grows, 0};
+  g.row_tags = tags;
+  g.peer_rows = peer_rows;
+  for (int r = 0; r < world; ++r) {
+    if (!peer_out[r] || (reinterpret_cast<uintptr_t>(peer_out[r]) & 15)) return -2;
+    g.peer_out[r] = peer_out[r];
+  }
+  void* C = peer_out[0];   // only its alignment is looked at
+  auto go = [&](auto bn_tag, auto bmn_tag) {
+    return launch_cfg<decltype(bn_tag)::value, false, decltype(bmn_tag)::value, __nv_bfloat16, false>(
+        ta, tb, C, rows_cap, N, K, ld_out, 0, s, 1, g);
+  };
+  using T = std::true_type;
+  using F = std::false_type;
+  if (bn == 256) return b_mn ? go(std::integral_constant<int, 256>{}, T{}) : go(std::integral_constant<int, 256>{}, F{});
+  if (bn == 128) return b_mn ? go(std::integral_constant<int, 128>{}, T{}) : go(std::integral_constant<int, 128>{}, F{});
+  return b_mn ? go(std::integral_constant<int, 64>{}, T{}) : go(std::integral_constant<int, 64>{}, F{});
 }
 
 // Split-K variant for decode-shaped calls (few rows, the weight matrix is streamed once): the K range is cut into

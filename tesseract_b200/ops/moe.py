@@ -27,6 +27,8 @@ _native.register_signatures({
     "tsb_moe_combine": [P, P, P, P, I, I, I, P],
     "tsb_moe_gate_grad": [P, P, P, P, I, I, I, P],
     "tsb_gemm_grouped": [P, P, P, P, I, I, I, I, I, I, L, L, L, I, L, L, I, I, P],
+    "tsb_gemm_grouped_scatter": [P, P, P, I, I, I, I, L, L, I, L, P, _native.ctypes.POINTER(_native.ctypes.c_void_p), I, L,
+                                 L, P],
     "tsb_ep_publish_counts": [_native.ctypes.POINTER(_native.ctypes.c_void_p), P, I, I, I, P],
     "tsb_ep_plan": [P, P, P, P, I, I, I, I, P],
     "tsb_ep_fill_i32": [P, L, I, P],
@@ -116,6 +118,19 @@ def grouped_gemm_rows(a: torch.Tensor, w0: torch.Tensor, group_stride: int, offs
                                  0, N, K, a.stride(0), w0.stride(0), out.stride(0), int(b_mn), group_stride, 0, 0, 0,
                                  stream_ptr(a.device)), "tsb_gemm_grouped")
     return out
+
+
+def grouped_gemm_rows_scatter(a: torch.Tensor, w0: torch.Tensor, group_stride: int, offsets: torch.Tensor, groups: int,
+                              tags: torch.Tensor, peer_out, world: int, peer_rows: int, b_mn: bool = False) -> None:
+    """``grouped_gemm_rows`` whose result rows leave through the GEMM epilogue for peer-mapped buffers: row r is
+    stored at ``peer_out[tags[r] >> 24] + (tags[r] & 0xFFFFFF) * N`` when ``tags[r] >= 0`` (``peer_out``: a ctypes
+    array of ``world`` device pointers, each [peer_rows, N] bf16); rows with a negative tag are dropped and nothing
+    is written locally. The expert-parallel return exchange as the epilogue of the down projection."""
+    rows_cap, K = a.shape
+    N = w0.shape[1] if b_mn else w0.shape[0]
+    check(lib().tsb_gemm_grouped_scatter(a.data_ptr(), w0.data_ptr(), offsets.data_ptr(), groups, rows_cap, N, K,
+                                         a.stride(0), w0.stride(0), int(b_mn), group_stride, tags.data_ptr(), peer_out,
+                                         world, peer_rows, N, stream_ptr(a.device)), "tsb_gemm_grouped_scatter")
 
 
 def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, offsets: torch.Tensor, groups: int, out: torch.Tensor,

@@ -155,9 +155,14 @@ class _FusedEPFn(torch.autograd.Function):
                                       offsets[El:].data_ptr(), D, s), "tsb_ep_clean_copy")
         h = M.grouped_gemm_rows(xs, w_gu0, stride, offsets, El)
         a = swiglu(h)
-        ys = M.grouped_gemm_rows(a, w_dn0, stride, offsets, El)
-        check(lib().tsb_ep_return(ys.data_ptr(), tags.data_ptr(), ep.ret.ptr_array, ep.cap_rows, offsets[El:].data_ptr(), D,
-                                  ep.ret_rows, W, s), "tsb_ep_return")
+        if ep.scatter_epilogue:
+            # the return exchange is the epilogue of the down projection: every result row goes from the accumulator
+            # straight to the return buffer of the rank it came from (NVLink stores); no local copy of the results
+            M.grouped_gemm_rows_scatter(a, w_dn0, stride, offsets, El, tags, ep.ret.ptr_array, W, ep.ret_rows)
+        else:
+            ys = M.grouped_gemm_rows(a, w_dn0, stride, offsets, El)
+            check(lib().tsb_ep_return(ys.data_ptr(), tags.data_ptr(), ep.ret.ptr_array, ep.cap_rows,
+                                      offsets[El:].data_ptr(), D, ep.ret_rows, W, s), "tsb_ep_return")
         ep.barrier()                                            # every result row of this rank's tokens is back
         back = ep.ret_view(T * k, D).clone()
         gates32 = gates.float().contiguous()
@@ -226,6 +231,8 @@ class FusedExpertParallel(ExpertParallel):
         self.pads = SymmetricMemory(group, rank, world, 256, device)
         self.epoch = 0
         self.calls = 0
+        import os
+        self.scatter_epilogue = os.environ.get("TESSERACT_EP_SCATTER_EPILOGUE", "1") == "1"
         self._ident = torch.arange(self.ret_rows, dtype=torch.int32, device=self.device)
 
     def barrier(self) -> None:

@@ -163,7 +163,9 @@ def _worker(rank, world, port, q):
         from tesseract_b200.parallel.expert import FusedExpertParallel
         fep = FusedExpertParallel(dist.group.WORLD, rank, world, dev, 256, 2 * world, 2, max_tokens=512)
         fep.shard_(fused_l)
-        for it in range(2):                                          # twice: buffers and tags are reused
+        for it in range(3):                                          # several calls: buffers and tags are reused
+            # result rows returned by the down projection's own epilogue (peer stores), then by the separate kernel
+            fep.scatter_epilogue = it != 1
             xc = xe.clone().requires_grad_(True)
             yc = fused_l(xc)
             yc.backward(ge)
@@ -177,9 +179,9 @@ def _worker(rank, world, port, q):
                 el_ = 2
                 if ge_i // el_ == rank:
                     got = getattr(fused_l.experts[ge_i - rank * el_], name).weight.grad.float()
-                    # two backward passes accumulated into .grad
-                    errs.append(((got / 2 - want).norm() / want.norm().clamp_min(1e-6)).item())
-        assert fep.calls == 2
+                    # three backward passes accumulated into .grad
+                    errs.append(((got / 3 - want).norm() / want.norm().clamp_min(1e-6)).item())
+        assert fep.calls == 3
         status |= _native.read_status(torch.cuda.current_stream().cuda_stream)
         # tensor-parallel serving: sharded engine (one-shot all-reduce kernel inside the decode CUDA graph) against
         # the single-GPU engine on the same seeded model and requests

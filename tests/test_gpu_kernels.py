@@ -494,6 +494,38 @@ def test_paged_decode_attention(dev, A, H, Hkv, D, bs, lens, int8):
     assert (got.float() - ref).abs().max() < 3e-3 * max(1.0, ref.abs().max().item()) + 2e-2, (got.float() - ref).abs().max()
 
 
+def test_out_of_range_indices_are_redirected_and_reported(dev):
+    """Data-dependent indices are checked in the kernels: a token id outside the vocabulary reads row 0, a block-table
+    entry outside the pool reads block 0 (never memory outside the tensor), the rows that had valid indices are
+    unaffected, and the status word tells the host (code 4)."""
+    from tesseract_b200 import _native, ops
+    stream = torch.cuda.current_stream().cuda_stream
+    assert _native.read_status(stream) == 0
+    V, D = 64, 128
+    table = torch.randn(V, D, device=dev).bfloat16()
+    ids = torch.tensor([[3, V + 5, 7, -2]], device=dev)
+    out = ops.embedding(ids, table)
+    torch.cuda.synchronize()
+    assert torch.equal(out[0, 0], table[3]) and torch.equal(out[0, 2], table[7])
+    assert torch.equal(out[0, 1], table[0]) and torch.equal(out[0, 3], table[0])
+    assert _native.read_status(stream) == 4                              # reading clears it
+    assert _native.read_status(stream) == 0
+    A, H, Hkv, Dh, bs = 3, 8, 2, 128, 16
+    lens = [40, 100, 17]
+    k_pool, v_pool, _, _, tables, lens_t = _make_paged(dev, A, Hkv, Dh, bs, lens, torch.bfloat16, False)
+    q = torch.randn(A, H, Dh, device=dev).bfloat16()
+    good = ops.paged_decode_attention(q, k_pool, v_pool, tables, lens_t)
+    bad_tables = tables.clone()
+    bad_tables[1, 2] = k_pool.shape[0] + 7                                # a block that does not exist
+    got = ops.paged_decode_attention(q, k_pool, v_pool, bad_tables, lens_t)
+    torch.cuda.synchronize()
+    assert _native.read_status(stream) == 4
+    assert torch.isfinite(got.float()).all() and torch.equal(got[0], good[0]) and torch.equal(got[2], good[2])
+    again = ops.paged_decode_attention(q, k_pool, v_pool, tables, lens_t)  # the context is intact
+    torch.cuda.synchronize()
+    assert torch.equal(again, good) and _native.read_status(stream) == 0
+
+
 @pytest.mark.parametrize("int8", [False, True])
 def test_kv_append_paged_rope_and_quant(dev, int8):
     from tesseract_b200 import _native, ops

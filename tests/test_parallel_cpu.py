@@ -273,7 +273,7 @@ def test_serving_replica_plan_over_gloo_ranks():
     from tesseract_b200.serving import default_tp, make_replica_plan, split_requests
     solo = make_replica_plan(1, 0, 1)
     assert solo.replicas == 1 and solo.group is None and split_requests([3, 4], solo) == [3, 4]
-    assert [default_tp(w) for w in (1, 2, 4, 8)] == [1, 1, 2, 2]
+    assert [default_tp(w) for w in (1, 2, 4, 8)] == [1, 1, 1, 1]
     with pytest.raises(ValueError):
         make_replica_plan(8, 0, 3)
     leaders = _run_ranks(_replica_worker, 4)
