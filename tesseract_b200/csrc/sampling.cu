@@ -1,8 +1,8 @@
 // Device-side token selection so that a decode step needs no logits transfer:
 //   * tsb_argmax_rows        greedy: index of the row maximum (lowest index on ties, like the host sampler)
 //   * tsb_sample_top_p_rows  temperature + nucleus sampling without sorting: the probability threshold of the
-//                            nucleus is found by bisection over the row (kept hot in L2), then one uniform draw
-//                            picks a token among the survivors in index order.
+//                            nucleus is found by a four-pass radix descent over the row (kept hot in L2), then one
+//                            uniform draw picks a token among the survivors in index order.
 // The host sampler (repetition penalty -> temperature -> top-k -> top-p -> mt19937_64 draw,
 // src/models/Sampler.cpp:29-116) stays the bit-exact path for seeded tests; these kernels are the serving fast
 // path. The reference copies the whole logits row to the host for every token (src/models/Llama.cpp:481-509).
@@ -154,17 +154,58 @@ repetition_penalty_kernel(T* __restrict__ logits, long long ld, int V, const int
   }
 }
 
+// Visits every element of a row once: f(index, value). 16-byte loads (two in flight per thread) when the row allows.
+template <typename T, typename F>
+__device__ __forceinline__ void for_each_elem(const T* __restrict__ x, int V, F f) {
+  int j0 = 0;
+  if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int nvec = V / 8;
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    for (int c0 = threadIdx.x; c0 < nvec; c0 += 2 * blockDim.x) {
+      uint4 v[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int c = c0 + u * blockDim.x;
+        if (c < nvec) v[u] = xv[c];
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int c = c0 + u * blockDim.x;
+        if (c < nvec) {
+          const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) f(c * 8 + k, to_f32<T>(e[k]));
+        }
+      }
+    }
+    j0 = nvec * 8;
+  }
+  for (int j = j0 + threadIdx.x; j < V; j += blockDim.x) f(j, to_f32<T>(x[j]));
+}
+
+// Temperature, top-k, top-p and the draw for one row per CTA, in a handful of passes over the row (which stays in
+// L2). The nucleus threshold is found exactly by a radix descent over the bit pattern of the unnormalised
+// probabilities e = exp(z - max) (positive floats order like their bits): four passes, each adding the mass of the
+// still-undecided elements into 256 bins of the next byte and picking, from the top, the bin in which the cumulative
+// mass reaches top_p * sum(e). (A bisection on the threshold needs two dozen passes for the same answer; on a
+// 128 K-entry vocabulary that was 1.8 ms per decode step.)
 template <typename T>
 __global__ void __launch_bounds__(kSampThreads)
 sample_top_p_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, long long ld, float inv_temp,
                     float top_p, int top_k, unsigned long long seed, unsigned long long step,
                     const unsigned long long* __restrict__ step_ptr) {
+  constexpr int kWarps = kSampThreads / 32;
   __shared__ float red[32];
   __shared__ float s_scan[kSampThreads];
+  __shared__ float s_hist[kWarps][256];
+  __shared__ float s_bins[256];
+  __shared__ unsigned int s_prefix;
+  __shared__ float s_above, s_sel;
   const T* x = logits + blockIdx.x * ld;
+  const int warp = threadIdx.x >> 5;
   if (step_ptr) step = *step_ptr;       // a device-resident counter: the launch can sit in a CUDA graph
   float m = -INFINITY;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) m = fmaxf(m, to_f32<T>(x[j]) * inv_temp);
+  for_each_elem(x, V, [&](int, float v) { m = fmaxf(m, v * inv_temp); });
   m = block_reduce_max(m, red);
   // top-k: the k-th largest scaled logit by bisection on the ordered integer image of the values (exact; ties at the
   // k-th value all survive, as in the host sampler). kth = -inf keeps everything.
@@ -175,52 +216,83 @@ sample_top_p_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, 
       const unsigned int mid = lo_k + ((hi_k - lo_k + 1u) >> 1);
       const float t = key_float(mid);
       float cnt = 0.f;
-      for (int j = threadIdx.x; j < V; j += blockDim.x) cnt += (to_f32<T>(x[j]) * inv_temp >= t) ? 1.f : 0.f;
+      for_each_elem(x, V, [&](int, float v) { cnt += (v * inv_temp >= t) ? 1.f : 0.f; });
       cnt = block_reduce_sum(cnt, red);
       if (cnt >= static_cast<float>(top_k)) lo_k = mid; else hi_k = mid - 1u;
     }
     kth = key_float(lo_k);
   }
   float s = 0.f;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) {
-    const float z = to_f32<T>(x[j]) * inv_temp;
+  for_each_elem(x, V, [&](int, float v) {
+    const float z = v * inv_temp;
     if (z >= kth) s += __expf(z - m);
-  }
+  });
   const float denom = block_reduce_sum(s, red);
-  // bisection on the probability threshold t: mass(p >= t) is non-increasing in t; find the largest t whose
-  // mass still reaches top_p (the smallest nucleus). p is in (0, 1]; the top token has p_max = 1 / denom.
-  float lo = 0.f, hi = 1.f / denom;
+  // nucleus: the smallest set {e >= thr} whose mass reaches top_p * denom
+  unsigned int thr_key = 0u;            // bit pattern of the threshold; 0 keeps every element with e > 0
+  float total = denom;
   if (top_p < 1.f) {
-    for (int it = 0; it < 24; ++it) {
-      const float mid = 0.5f * (lo + hi);
-      float mass = 0.f;
-      for (int j = threadIdx.x; j < V; j += blockDim.x) {
-        const float z = to_f32<T>(x[j]) * inv_temp;
-        const float p = z >= kth ? __expf(z - m) / denom : 0.f;
-        if (p >= mid && p > 0.f) mass += p;
-      }
-      mass = block_reduce_sum(mass, red);
-      if (mass >= top_p) lo = mid; else hi = mid;
+    const float goal = top_p * denom;
+    if (threadIdx.x == 0) {
+      s_prefix = 0u;
+      s_above = 0.f;
     }
+    for (int level = 0; level < 4; ++level) {
+      const int shift = 24 - 8 * level;
+      for (int i = threadIdx.x; i < kWarps * 256; i += blockDim.x) (&s_hist[0][0])[i] = 0.f;
+      __syncthreads();
+      const unsigned int prefix = s_prefix;
+      for_each_elem(x, V, [&](int, float v) {
+        const float z = v * inv_temp;
+        if (z >= kth) {
+          const float e = __expf(z - m);
+          const unsigned int key = __float_as_uint(e);
+          const bool undecided = level == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8));
+          if (e > 0.f && undecided) atomicAdd(&s_hist[warp][(key >> shift) & 255u], e);
+        }
+      });
+      __syncthreads();
+      if (threadIdx.x < 256) {
+        float h = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) h += s_hist[w][threadIdx.x];
+        s_bins[threadIdx.x] = h;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float above = s_above;
+        int pick = -1, lowest = -1;
+        for (int bin = 255; bin >= 0; --bin) {
+          const float h = s_bins[bin];
+          if (h > 0.f) lowest = bin;
+          if (h > 0.f && above + h >= goal) {
+            pick = bin;
+            break;
+          }
+          above += h;
+        }
+        if (pick < 0) {                 // rounding left the goal just out of reach: everything undecided survives
+          pick = lowest < 0 ? 0 : lowest;
+          above -= s_bins[pick];
+        }
+        s_above = above;
+        s_sel = s_bins[pick];
+        s_prefix = prefix | (static_cast<unsigned int>(pick) << shift);
+      }
+      __syncthreads();
+    }
+    thr_key = s_prefix;
+    total = s_above + s_sel;            // mass of {e >= thr}: everything above the last bin plus the bin itself
   }
-  const float thr = lo;
-  // mass of the survivors, then an inverse-CDF walk in index order
-  float keep = 0.f;
-  for (int j = threadIdx.x; j < V; j += blockDim.x) {
-    const float z = to_f32<T>(x[j]) * inv_temp;
-    const float p = z >= kth ? __expf(z - m) / denom : 0.f;
-    if (p >= thr && p > 0.f) keep += p;
-  }
-  const float total = block_reduce_sum(keep, red);
   const float target = uniform_from(seed, blockIdx.x, step) * total;
-  // each thread owns a contiguous span so that the walk is in index order
+  // inverse-CDF walk in index order: each thread owns a contiguous span
   const int per = (V + blockDim.x - 1) / blockDim.x;
   const int j0 = threadIdx.x * per, j1 = min(V, j0 + per);
   float mine = 0.f;
   for (int j = j0; j < j1; ++j) {
     const float z = to_f32<T>(x[j]) * inv_temp;
-    const float p = z >= kth ? __expf(z - m) / denom : 0.f;
-    if (p >= thr && p > 0.f) mine += p;
+    const float e = z >= kth ? __expf(z - m) : 0.f;
+    if (e > 0.f && __float_as_uint(e) >= thr_key) mine += e;
   }
   s_scan[threadIdx.x] = mine;
   __syncthreads();
@@ -239,10 +311,10 @@ sample_top_p_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, 
     int pick = -1, last = -1;
     for (int j = a0; j < a1; ++j) {
       const float z = to_f32<T>(x[j]) * inv_temp;
-      const float p = z >= kth ? __expf(z - m) / denom : 0.f;
-      if (p >= thr && p > 0.f) {
+      const float e = z >= kth ? __expf(z - m) : 0.f;
+      if (e > 0.f && __float_as_uint(e) >= thr_key) {
         last = j;
-        acc += p;
+        acc += e;
         if (acc >= target) {
           pick = j;
           break;

@@ -591,6 +591,22 @@ def test_device_sampling_kernels(dev):
     a = sample_top_p_rows(logits, 0.8, 0.95, 5, 1)
     b = sample_top_p_rows(logits, 0.8, 0.95, 5, 1)
     assert torch.equal(a, b) and int(a.min()) >= 0 and int(a.max()) < 5000
+    # every draw lies inside the smallest nucleus of the fp32 reference (sorted cumulative mass), on a vocabulary of
+    # Llama-3 size with a spread of logits that puts thousands of tokens into the nucleus
+    big = (torch.randn(12, 128256, device=dev) * 2.0).bfloat16()
+    probs = torch.softmax(big.float() / 0.9, dim=-1)
+    sp, _ = probs.sort(dim=-1, descending=True)
+    first = (sp.cumsum(-1) >= 0.5).float().argmax(-1)                  # index of the element that completes the nucleus
+    thr = sp.gather(1, first.view(-1, 1)).view(-1)
+    sizes = (probs >= thr.view(-1, 1)).sum(-1)
+    assert int(sizes.min()) > 100
+    seen = set()
+    for s in range(8):
+        pick = sample_top_p_rows(big, 0.9, 0.5, 77, s).long()
+        p_pick = probs.gather(1, pick.view(-1, 1)).view(-1)
+        assert (p_pick >= thr * (1 - 1e-3)).all()
+        seen |= set(pick.tolist())
+    assert len(seen) > 40                                              # and the draws do move around inside it
 
 
 def test_device_sampler_top_k_penalty_and_step_counter(dev):
