@@ -167,6 +167,23 @@ def case_stream_linear(b: Bench):
             report(f"stream_linear_layer_{key}_M{M}", tot[key][0], bytes_=tot[key][1])
 
 
+def case_gemm_mx(b: Bench):
+    """Block-scaled fp8 GEMM on the tensor core's own block scaling (E4M3 x E4M3, power-of-two scales, persistent
+    128 x 192 tiles), next to the bf16 GEMM of the same shape; the activation quantiser is timed separately."""
+    from tesseract_b200.ops import fp8, gemm_bf16
+    for M, N, K in ((8192, 8192, 8192), (16384, 4096, 4096), (16384, 28672, 4096), (16384, 4096, 14336)):
+        a, w = b.randn(M, K), b.randn(N, K, scale=0.02)
+        wq, ws = fp8.quantize_weight(w, pow2=True)
+        q, sf = fp8.quantize_act_mx(a, atoms=True)
+        wa = fp8.weight_scale_atoms(ws)
+        out = torch.empty(M, N, device=b.dev, dtype=torch.bfloat16)
+        ms = b.time(lambda: fp8.mx_linear(q, sf, wq, ws, out=out, w_atoms=wa))
+        ms_bf = b.time(lambda: gemm_bf16(a, w, out=out))
+        ms_q = b.time(lambda: fp8.quantize_act_mx(a, out=(q, sf), atoms=True))
+        report(f"gemm_mx_{M}x{N}x{K}", ms, flops=2.0 * M * N * K, shape=[M, N, K], bf16_gemm_ms=round(ms_bf, 4),
+               speedup_over_bf16=round(ms_bf / ms, 3), quantiser_ms=round(ms_q, 4))
+
+
 def case_mx_linear(b: Bench):
     """The block-scaled fp8 decode GEMM on tcgen05.mma kind::mxf8f6f4 (E4M3 activations and weights, power-of-two
     scales applied by the tensor core) on the layer shapes of one decode step; bytes = the fp8 weight matrix once.
@@ -388,7 +405,7 @@ CASES = {"gemm": case_gemm, "gemm_fp8": case_gemm_fp8, "gemm_fp8_pertensor": cas
          "flash_fwd": case_flash_fwd, "flash_bwd": case_flash_bwd, "decode": case_decode,
          "decode_int8": case_decode_int8, "rmsnorm": case_rmsnorm, "swiglu": case_swiglu, "swiglu_bwd": case_swiglu_bwd, "adam": case_adam,
          "ce_stats": case_ce, "selective_scan": case_scan, "gemv_w8": case_gemv, "gemm_rs_emul": case_gemm_rs_emul,
-         "ag_gemm_emul": case_ag_gemm_emul, "stream_linear": case_stream_linear, "mx_linear": case_mx_linear}
+         "ag_gemm_emul": case_ag_gemm_emul, "stream_linear": case_stream_linear, "mx_linear": case_mx_linear, "gemm_mx": case_gemm_mx}
 
 
 def main():

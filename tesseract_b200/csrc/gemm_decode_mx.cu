@@ -182,7 +182,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {      // same o
 
 __global__ void __launch_bounds__(256)
 quant_act_mx_kernel(const __nv_bfloat16* __restrict__ X, long long ldx, uint8_t* __restrict__ Xq,
-                    uint32_t* __restrict__ sf, int M, int K, int m_pad) {
+                    uint32_t* __restrict__ sf, int M, int K, int m_pad, int atoms) {
   pdl_trigger();
   const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int per_row = K / 8;                         // threads per row: 8 elements each, a multiple of 16
@@ -200,7 +200,12 @@ quant_act_mx_kernel(const __nv_bfloat16* __restrict__ X, long long ldx, uint8_t*
   uint2 o;
   const uint32_t byte = mx_quant8(v, &o);
   if (row < M) *reinterpret_cast<uint2*>(Xq + static_cast<long long>(row) * K + c8 * 8) = o;
-  mx_store_word(byte, lane, true, sf + static_cast<long long>(c8 / 16) * m_pad + row);
+  // atoms = 0: [K / 128][m_pad] words (the decode GEMM reads a word per row); atoms = 1: 512-byte atoms
+  // [m_pad / 128][K / 128][128 words], word (row % 32) * 4 + (row % 128) / 32 (what tcgen05.cp wants, gemm_mx.cu)
+  const long long kc = c8 / 16;
+  uint32_t* dst = atoms ? sf + ((static_cast<long long>(row >> 7) * (K / 128) + kc) << 7) + ((row & 31) << 2) + ((row & 127) >> 5)
+                        : sf + kc * m_pad + row;
+  mx_store_word(byte, lane, true, dst);
 }
 
 // RMSNorm (+ residual add) whose bf16 result exists only as the quantised operand of the next GEMM: one CTA per row.
@@ -827,7 +832,14 @@ TSB_EXPORT int tsb_mx_m_pad(int M) { return (M + 127) / 128 * 128; }
 
 // X [M, K] bf16 (row stride ldx) -> Xq [M, K] E4M3 (dense rows) and sf: uint32 [K / 128][tsb_mx_m_pad(M)], byte j of
 // word (k / 128, m) = UE8M0 exponent of X[m, 128 (k / 128) + 32 j .. + 31]. K % 128 == 0, X 16-byte aligned, ldx % 8 == 0.
+TSB_EXPORT int tsb_quant_act_mx_layout(const void* X, long long ldx, void* Xq, void* sf, int M, int K, int atoms,
+                                       void* stream);
 TSB_EXPORT int tsb_quant_act_mx(const void* X, long long ldx, void* Xq, void* sf, int M, int K, void* stream) {
+  return tsb_quant_act_mx_layout(X, ldx, Xq, sf, M, K, 0, stream);
+}
+// atoms != 0: sf receives 512-byte scale atoms [tsb_mx_m_pad(M) / 128][K / 128][128 words] (the operand of tsb_gemm_mx).
+TSB_EXPORT int tsb_quant_act_mx_layout(const void* X, long long ldx, void* Xq, void* sf, int M, int K, int atoms,
+                                       void* stream) {
   using namespace tsb;
   if (M <= 0 || K <= 0 || K % 128 || !X || !Xq || !sf || (ldx % 8) || (reinterpret_cast<uintptr_t>(X) & 15) ||
       (reinterpret_cast<uintptr_t>(Xq) & 7))
@@ -836,7 +848,8 @@ TSB_EXPORT int tsb_quant_act_mx(const void* X, long long ldx, void* Xq, void* sf
   const long long threads = static_cast<long long>(m_pad) * (K / 8);
   const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
   quant_act_mx_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(X), ldx, static_cast<uint8_t*>(Xq), static_cast<uint32_t*>(sf), M, K, m_pad);
+      static_cast<const __nv_bfloat16*>(X), ldx, static_cast<uint8_t*>(Xq), static_cast<uint32_t*>(sf), M, K, m_pad,
+      atoms);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -26,6 +26,9 @@ _native.register_signatures({
     "tsb_rmsnorm_quant_mx": [P, P, P, P, P, P, I, I, _native.F, P],
     "tsb_swiglu_quant_mx": [P, P, P, I, I, P],
     "tsb_gemm_decode_mx_plan": [I, I, I, P, P, P, P],
+    "tsb_gemm_mx": [P, P, P, P, P, I, I, I, L, L, P],
+    "tsb_quant_act_mx_layout": [P, L, P, P, I, I, I, P],
+    "tsb_mx_weight_scale_atoms": [P, P, I, I, P],
 })
 
 E4M3_MAX = 448.0
@@ -196,7 +199,36 @@ def scales_are_pow2(scale: torch.Tensor) -> bool:
     return bool(((bits & 0x7FFFFF) == 0).all() and (bits > 0).all())
 
 
-def quantize_act_mx_ref(x: torch.Tensor):
+def _words_to_atoms(sf: torch.Tensor) -> torch.Tensor:
+    """[K / 128, m_pad] scale words -> 512-byte atoms [m_pad / 128, K / 128, 128]: word (r % 32) * 4 + (r % 128) / 32."""
+    kb, m_pad = sf.shape
+    a = sf.t().reshape(m_pad // 128, 4, 32, kb)                # [mb, r / 32, r % 32, kb]
+    return a.permute(0, 3, 2, 1).reshape(m_pad // 128, kb, 128).contiguous()
+
+
+def _atoms_to_words(atoms: torch.Tensor) -> torch.Tensor:
+    mb, kb, _ = atoms.shape
+    return atoms.view(mb, kb, 32, 4).permute(1, 0, 3, 2).reshape(kb, mb * 128).contiguous()
+
+
+def weight_scale_atoms(w_scale: torch.Tensor) -> torch.Tensor:
+    """fp32 power-of-two block scales [N / 128, K / 128] -> scale atoms int32 [N / 128, K / 128, 128] for ``mx_linear``
+    above 256 rows (every word = the scale's exponent byte four times)."""
+    rows, cols = w_scale.shape
+    if _native_ok(w_scale):
+        out = torch.empty((rows, cols, 128), dtype=torch.int32, device=w_scale.device)
+        check(lib().tsb_mx_weight_scale_atoms(w_scale.contiguous().data_ptr(), out.data_ptr(), rows, cols,
+                                              stream_ptr(w_scale.device)), "tsb_mx_weight_scale_atoms")
+        return out
+    e = ((w_scale.contiguous().view(torch.int32).to(torch.int64) >> 23) & 0xFF) * 0x01010101
+    e = torch.where(e >= 2 ** 31, e - 2 ** 32, e).to(torch.int32)
+    return e[:, :, None].expand(rows, cols, 128).contiguous()
+
+
+def quantize_act_mx_ref(x: torch.Tensor, atoms: bool = False):
+    if atoms:
+        q, sf = quantize_act_mx_ref(x)
+        return q, _words_to_atoms(sf)
     M, K = x.shape
     xb = x.float().view(M, K // 32, 32)
     amax = xb.abs().amax(dim=2)
@@ -211,16 +243,18 @@ def quantize_act_mx_ref(x: torch.Tensor):
     return q.view(torch.uint8), sf
 
 
-def quantize_act_mx(x: torch.Tensor, out=None):
+def quantize_act_mx(x: torch.Tensor, out=None, atoms: bool = False):
     """x [M, K] bf16 (K % 128 == 0) -> (E4M3 bytes uint8 [M, K], scale words int32 [K / 128, ceil(M / 128) * 128]):
     one power-of-two scale per row and 32 columns, ``q = x * 2^(127 - e)`` with the smallest exponent byte ``e`` that
     keeps the block within +-448; byte j of word [k / 128, m] is the exponent of columns 128 (k / 128) + 32 j .. + 31.
+    ``atoms=True`` lays the same words out as 512-byte atoms int32 [ceil(M / 128), K / 128, 128] (word
+    (m % 32) * 4 + (m % 128) / 32): the form the persistent GEMM behind ``mx_linear`` copies into tensor memory.
     ``out`` = (q, sf) buffers of those shapes to write into."""
     M, K = x.shape
     if K % 128:
         raise ValueError("quantize_act_mx: K must be a multiple of 128")
     if not (_native_ok(x) and x.dtype == torch.bfloat16):
-        q, sf = quantize_act_mx_ref(x)
+        q, sf = quantize_act_mx_ref(x, atoms)
         if out is not None:
             out[0].copy_(q)
             out[1].copy_(sf)
@@ -230,11 +264,12 @@ def quantize_act_mx(x: torch.Tensor, out=None):
         raise ValueError("quantize_act_mx: rows must be contiguous")
     if out is None:
         q = torch.empty((M, K), dtype=torch.uint8, device=x.device)
-        sf = torch.empty((K // 128, _mx_m_pad(M)), dtype=torch.int32, device=x.device)
+        sf = torch.empty((_mx_m_pad(M) // 128, K // 128, 128) if atoms else (K // 128, _mx_m_pad(M)), dtype=torch.int32,
+                         device=x.device)
     else:
         q, sf = out
-    check(lib().tsb_quant_act_mx(x.data_ptr(), x.stride(0), q.data_ptr(), sf.data_ptr(), M, K, stream_ptr(x.device)),
-          "tsb_quant_act_mx")
+    check(lib().tsb_quant_act_mx_layout(x.data_ptr(), x.stride(0), q.data_ptr(), sf.data_ptr(), M, K, int(atoms),
+                                        stream_ptr(x.device)), "tsb_quant_act_mx_layout")
     return q, sf
 
 
@@ -281,6 +316,8 @@ def swiglu_quant_mx(gate_up: torch.Tensor):
 
 
 def dequantize_act_mx(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+    if sf.dim() == 3:
+        sf = _atoms_to_words(sf)
     M, K = q.shape
     words = sf[:, :M].t().to(torch.int64) & 0xFFFFFFFF                                            # [M, K / 128]
     e = torch.stack([(words >> (8 * j)) & 0xFF for j in range(4)], dim=2).view(M, K // 32).float()
@@ -288,11 +325,14 @@ def dequantize_act_mx(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
 
 
 def mx_linear(q: torch.Tensor, sf: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, out=None, pdl: bool = False,
-              bn: int = 0, split: int = 0) -> torch.Tensor:
-    """bf16 [M, N] = dequant(q, sf) @ dequant(wq, w_scale)^T for decode-sized M, with the scales applied by the tensor
-    core (``csrc/gemm_decode_mx.cu``: tcgen05.mma kind::mxf8f6f4.block_scale). ``q, sf`` from ``quantize_act_mx``;
-    ``wq, w_scale`` from ``quantize_weight(w, pow2=True)`` (the scales must be powers of two: only their exponent
-    reaches the hardware)."""
+              bn: int = 0, split: int = 0, w_atoms: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 [M, N] = dequant(q, sf) @ dequant(wq, w_scale)^T with the scales applied by the tensor core
+    (tcgen05.mma kind::mxf8f6f4.block_scale). ``q, sf`` from ``quantize_act_mx``; ``wq, w_scale`` from
+    ``quantize_weight(w, pow2=True)`` (the scales must be powers of two: only their exponent reaches the hardware).
+    ``sf`` as scale words (2-D) selects the weight-streaming kernel ``csrc/gemm_decode_mx.cu`` (meant for up to 256
+    rows); ``sf`` as scale atoms (3-D, ``quantize_act_mx(..., atoms=True)``) selects the persistent 128 x 192-tile
+    kernel ``csrc/gemm_mx.cu`` (prompt-sized M), which also wants the weight scales as atoms (``w_atoms`` =
+    ``weight_scale_atoms(w_scale)``; made on the fly when not given)."""
     M, K = q.shape
     N = wq.shape[0]
     if not _native_ok(q):
@@ -304,6 +344,12 @@ def mx_linear(q: torch.Tensor, sf: torch.Tensor, wq: torch.Tensor, w_scale: torc
         out = torch.empty((M, N), dtype=torch.bfloat16, device=q.device)
     elif out.shape != (M, N) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         raise ValueError("mx_linear: out must be a bf16 [M, N] tensor with contiguous rows")
+    if sf.dim() == 3:
+        if w_atoms is None:
+            w_atoms = weight_scale_atoms(w_scale)
+        check(lib().tsb_gemm_mx(q.data_ptr(), sf.data_ptr(), wq.data_ptr(), w_atoms.data_ptr(), out.data_ptr(), M, N, K,
+                                wq.stride(0), out.stride(0), stream_ptr(q.device)), "tsb_gemm_mx")
+        return out
     check(lib().tsb_gemm_decode_mx(q.data_ptr(), sf.data_ptr(), wq.data_ptr(), w_scale.data_ptr(), out.data_ptr(), M, N,
                                    K, wq.stride(0), out.stride(0), bn, split, int(pdl), stream_ptr(q.device)),
           "tsb_gemm_decode_mx")

@@ -50,17 +50,18 @@ _native.register_signatures({
 class _Weight:
     """A projection weight as the engine holds it: bf16 [N, K] (``w``), or the E4M3 payload ``q`` [N, K] with its
     fp32 128 x 128 block scales ``s`` [ceil(N / 128), K / 128]."""
-    __slots__ = ("w", "q", "s", "shape", "pow2")
+    __slots__ = ("w", "q", "s", "shape", "pow2", "atoms")
 
-    def __init__(self, w=None, q=None, s=None, pow2=False):
+    def __init__(self, w=None, q=None, s=None, pow2=False, atoms=None):
         self.w, self.q, self.s = w, q, s
+        self.atoms = atoms          # the block scales as 512-byte scale atoms (prompt-sized MX GEMM)
         self.pow2 = pow2            # every block scale is a power of two: the MX decode GEMM can take the weight
         self.shape = tuple((w if w is not None else q).shape)
 
     def nbytes(self) -> int:
         if self.w is not None:
             return self.w.numel() * self.w.element_size()
-        return self.q.numel() + self.s.numel() * 4
+        return self.q.numel() + self.s.numel() * 4      # (the scale atoms of the prompt-sized GEMM are 1 / 32 more)
 
 
 @dataclass
@@ -223,7 +224,7 @@ class ServingEngine:
                 from ..ops import fp8
                 # power-of-two block scales: decode-sized batches then run on the tensor core's own block scaling
                 q, sc = fp8.quantize_weight(w.contiguous(), pow2=True)
-                return _Weight(q=q, s=sc, pow2=True)
+                return _Weight(q=q, s=sc, pow2=True, atoms=fp8.weight_scale_atoms(sc))
             return _Weight(w=w)
 
         with torch.no_grad():
@@ -441,6 +442,11 @@ class ServingEngine:
                 return ops.stream_linear(x, W.q, W.s, out=out, pdl=self.pdl)
         if W.q is not None:
             from ..ops import fp8
+            if W.pow2 and self.decode_gemm in ("auto", "mx") and x.stride(1) == 1 and x.stride(0) % 8 == 0:
+                # prompt-sized batches: the same operand formats on the persistent MX GEMM (the whole K range
+                # accumulates in tensor memory; the fp32-scaled GEMM below has to scale every 128-deep block in registers)
+                qa, sf = fp8.quantize_act_mx(x, atoms=True)
+                return fp8.mx_linear(qa, sf, W.q, W.s, out=out, w_atoms=W.atoms)
             qa, sa = fp8.quantize_act(x.contiguous())
             return fp8.fp8_gemm(qa, sa, W.q, W.s, out=out)
         w8 = self._w8.get(id(W))
@@ -555,16 +561,35 @@ class ServingEngine:
         arr = buf.numpy()
         for r in reqs:
             self._grow(r, len(r.tokens))
-        pos = np.fromiter((len(r.tokens) - 1 for r in reqs), dtype=np.int32, count=n)
-        arr[:n, 0] = np.fromiter((r.tokens[-1] for r in reqs), dtype=np.int32, count=n)
-        arr[:n, 1] = pos
-        arr[:n, 4:] = np.stack([r.table_row for r in reqs])
-        arr[:n, 2] = arr[np.arange(n), 4 + pos // bs] * bs + pos % bs
-        arr[:n, 3] = pos + 1
+        if n:
+            pos = np.fromiter((len(r.tokens) - 1 for r in reqs), dtype=np.int32, count=n)
+            arr[:n, 0] = np.fromiter((r.tokens[-1] for r in reqs), dtype=np.int32, count=n)
+            arr[:n, 1] = pos
+            arr[:n, 4:] = np.stack([r.table_row for r in reqs])
+            arr[:n, 2] = arr[np.arange(n), 4 + pos // bs] * bs + pos % bs
+            arr[:n, 3] = pos + 1
         arr[n:, 0:2] = 0
         arr[n:, 2] = -1
         arr[n:, 3] = 0
         return buf
+
+    @torch.no_grad()
+    def warm_graphs(self, max_batch: int = 0) -> int:
+        """Captures the decode graph of every batch bucket up to ``max_batch`` (default: the configured maximum) with
+        all-padding inputs (slot -1, length 0: nothing is appended or attended), so that no request pays for a capture
+        (about 0.1 s per bucket) in the middle of serving. Returns the number of graphs captured."""
+        if not self.use_cuda_graph or self.repetition_penalty != 1.0:
+            return 0
+        top = self._bucket(max_batch or self.cfg.max_batch_size)
+        made = 0
+        for A in self.BUCKETS:
+            if A > top:
+                break
+            if A in self._graphs:
+                continue
+            self._capture(A, self._decode_inputs([], A))
+            made += 1
+        return made
 
     def _run_packed(self, inp: torch.Tensor) -> torch.Tensor:
         tokens = inp[:, 0].long()

@@ -653,9 +653,11 @@ def test_serving_engine_graph_vs_eager_and_generate(dev, kv_int8):
     for graph in (True, False):
         eng = ServingEngine(model, EngineConfig(block_size=16, num_blocks=64, max_seq_len=256, max_batch_size=4,
                                                 kv_int8=kv_int8), use_cuda_graph=graph)
+        # every bucket (1, 2, 4) captured up front on padding rows; nothing is captured while requests run
+        assert eng.warm_graphs() == (3 if graph else 0)
         ids = [eng.add_request(p, GenerateConfig(max_new_tokens=12)) for p in prompts]
         eng.run()
-        assert eng.free_blocks() == 64
+        assert eng.free_blocks() == 64 and eng.warm_graphs() == 0
         outs[graph] = [eng.result(i) for i in ids]
         m = eng.metrics()
         assert m["requests"] == len(prompts) and m["decode_tok_s"] > 0
@@ -832,6 +834,8 @@ def test_quantize_act_mx_matches_the_torch_restatement(dev, M, K):
     q_ref, sf_ref = f8.quantize_act_mx_ref(x)
     assert torch.equal(sf, sf_ref)
     assert torch.equal(q, q_ref)
+    q_a, sf_a = f8.quantize_act_mx(x, atoms=True)                         # the same words laid out as 512-byte atoms
+    assert torch.equal(q_a, q) and torch.equal(f8._atoms_to_words(sf_a), sf) and torch.equal(sf_a, f8._words_to_atoms(sf))
     back = f8.dequantize_act_mx(q, sf)
     # three mantissa bits for normal values; values far below their block's maximum land on the subnormal grid
     amax = x.float().abs().view(M, K // 32, 32).amax(dim=2, keepdim=True).expand(M, K // 32, 32).reshape(M, K)
@@ -841,9 +845,12 @@ def test_quantize_act_mx_matches_the_torch_restatement(dev, M, K):
 @pytest.mark.parametrize("M,N,K,bn,split", [(16, 4096, 4096, 0, 0), (141, 6144, 4096, 0, 0), (64, 28672, 4096, 0, 0),
                                             (128, 4096, 14336, 0, 0), (8, 200, 256, 0, 0), (300, 1024, 1024, 0, 0),
                                             (37, 1000, 512, 48, 2), (256, 768, 4096, 0, 0), (24, 520, 1024, 240, 8),
-                                            (200, 4096, 4096, 208, 4), (1, 4096, 4096, 128, 1)])
+                                            (200, 4096, 4096, 208, 4), (1, 4096, 4096, 128, 1),
+                                            (1000, 1000, 512, 0, 0), (4096, 4096, 4096, 0, 0), (257, 96, 256, 0, 0),
+                                            (2048, 14336, 1024, 0, 0), (640, 200, 384, 0, 0)])
 def test_mx_linear_block_scaled_fp8_on_the_tensor_core(dev, M, N, K, bn, split):
-    """tcgen05.mma kind::mxf8f6f4.block_scale decode GEMM against an fp32 product of the same dequantised operands.
+    """tcgen05.mma kind::mxf8f6f4.block_scale GEMMs (the weight-streaming kernel up to 256 rows, the persistent
+    tiled kernel above) against an fp32 product of the same dequantised operands.
     The operands are drawn directly in their quantised form with a different exponent for every (row, 32-column) block
     of the activations and every 128 x 128 block of the weights, so that a scale that reaches the wrong row, column
     block or byte shows up as an error of a factor of two or more."""
@@ -865,6 +872,8 @@ def test_mx_linear_block_scaled_fp8_on_the_tensor_core(dev, M, N, K, bn, split):
     wq = payload(N, K)
     ws = torch.exp2(torch.randint(-12, -4, ((N + 127) // 128, K // 128), device=dev, generator=g).float())
     want = f8.dequantize_act_mx(q, sf) @ f8.dequantize_weight(wq, ws).t()
+    if M > 256:                                                          # the persistent tiled kernel takes scale atoms
+        sf = f8._words_to_atoms(sf)
     got = f8.mx_linear(q, sf, wq, ws, bn=bn, split=split)
     got_pdl = f8.mx_linear(q, sf, wq, ws, bn=bn, split=split, pdl=True)
     torch.cuda.synchronize()
@@ -913,12 +922,12 @@ def test_mx_linear_from_bf16_operands(dev):
     """Quantise-then-multiply against the bf16 product: the error is that of rounding both operands to E4M3."""
     from tesseract_b200.ops import fp8 as f8
     g = torch.Generator(device=dev).manual_seed(5)
-    for M, N, K in [(32, 4096, 4096), (160, 14336, 4096)]:
+    for M, N, K in [(32, 4096, 4096), (160, 14336, 4096), (3000, 6144, 4096)]:
         x = torch.randn(M, K, device=dev, generator=g).bfloat16()
         w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
         wq, ws = f8.quantize_weight(w, pow2=True)
         assert f8.scales_are_pow2(ws)
-        q, sf = f8.quantize_act_mx(x)
+        q, sf = f8.quantize_act_mx(x, atoms=M > 256)
         got = f8.mx_linear(q, sf, wq, ws)
         full = x.float() @ w.float().t()
         assert ((got.float() - full).norm() / full.norm()).item() < 0.06
