@@ -170,8 +170,13 @@ def case_stream_linear(b: Bench):
 def case_gemm_mx(b: Bench):
     """Block-scaled fp8 GEMM on the tensor core's own block scaling (E4M3 x E4M3, power-of-two scales, persistent
     128 x 192 tiles), next to the bf16 GEMM of the same shape; the activation quantiser is timed separately."""
+    import os
+
     from tesseract_b200.ops import fp8, gemm_bf16
-    for M, N, K in ((8192, 8192, 8192), (16384, 4096, 4096), (16384, 28672, 4096), (16384, 4096, 14336)):
+    shapes = ((8192, 8192, 8192), (16384, 4096, 4096), (16384, 28672, 4096), (16384, 4096, 14336))
+    if os.environ.get("TESSERACT_KERNEL_CASES_SMALL", "0") == "1":
+        shapes = shapes[:1]                                   # one shape for a profiler capture
+    for M, N, K in shapes:
         a, w = b.randn(M, K), b.randn(N, K, scale=0.02)
         wq, ws = fp8.quantize_weight(w, pow2=True)
         q, sf = fp8.quantize_act_mx(a, atoms=True)

@@ -22,6 +22,12 @@ Cases and bars (reference source beside each):
   mamba_scaling          Mamba decode step faster than attention decode at the largest L   bench_cuda_mamba_scaling.cpp:125-127
   graph_replay           CUDA-graph replay of a recorded chain faster than interpreting it  bench_cuda_graph.cpp:173
   pinned                 async H2D submit <= 10 us; copy overlapped with compute <= 0.85 of serial  bench_cuda_pinned.cpp:154-285
+  paged_kv               paged resident bytes <= 0.10 of the contiguous reservation (256 of 8192 tokens); append + gather
+                         of one decode step at L = 512 <= 250 us                            bench_cuda_paged_kv.cpp:25-35,100-186
+  transformer_block      no bar (dashboard): forward and forward + backward tokens/s of one block, d 512, 8 heads,
+                         d_ff 2048, batch 16 x 1024                                        bench_cuda_transformer_block.cpp:3,102
+  llama_decode_block     no bar (dashboard): one Llama-7B block decode step (d 4096, 32 heads, d_ff 11008, 129 keys) with
+                         bf16 / INT8 / INT4-group weights                                  bench_cuda_llama_decode.cpp:120-298
 """
 from __future__ import annotations
 
@@ -324,10 +330,98 @@ def case_pinned(h: Harness):
          bar="async submit <= 10 us; overlapped / serial <= 0.85")
 
 
+def case_paged_kv(h: Harness):
+    from tesseract_b200.nn.kv_cache import KVCache, PagedKVCache, PagedKVPool
+    B, H, Dh, BLK = 1, 32, 128, 16                                          # Llama-7B head geometry, one request
+    MAX, L = 8192, 256
+    pool = PagedKVPool(B * ((MAX + BLK - 1) // BLK), H, BLK, Dh, torch.bfloat16, h.dev)
+    paged = PagedKVCache(pool, MAX)
+    z = torch.zeros(B, H, L, Dh, device=h.dev, dtype=torch.bfloat16)
+    paged.append(z, z)
+    resident = 2 * len(paged.block_table) * H * BLK * Dh * 2
+    reserved = 2 * B * H * MAX * Dh * 2
+    frac = resident / reserved
+    MAX, L = 4096, 512
+    pool = PagedKVPool(B * ((MAX + BLK - 1) // BLK), H, BLK, Dh, torch.bfloat16, h.dev)
+    paged, contig = PagedKVCache(pool, MAX), KVCache(B, H, MAX, Dh, torch.bfloat16, h.dev)
+    pre = torch.zeros(B, H, L + 1, Dh, device=h.dev, dtype=torch.bfloat16)
+    paged.append(pre, pre)
+    contig.append(pre, pre)
+    one = torch.zeros(B, H, 1, Dh, device=h.dev, dtype=torch.bfloat16)
+
+    def step(cache):
+        cache.set_current_len(L)
+        cache.append(one, one)
+        return cache.keys_view(), cache.values_view()
+
+    with torch.no_grad():
+        tp = h.time_ms(lambda: step(paged)) * 1e3
+        tc = h.time_ms(lambda: step(contig)) * 1e3
+    emit("paged_kv", frac <= 0.10 and tp <= 250.0, resident_over_reserved=round(frac, 4), paged_step_us=round(tp, 1),
+         contiguous_step_us=round(tc, 1), note="the serving engine attends over the pool in place (no gather at all)",
+         bar="resident / reserved <= 0.10; paged append + gather <= 250 us")
+
+
+def case_transformer_block(h: Harness):
+    from tesseract_b200.nn.modules import TransformerBlock
+    d, heads, ff, B, S = 512, 8, 2048, 16, 1024
+    torch.manual_seed(0)
+    blk = TransformerBlock(d, heads, ff, heads, S, 10000.0, 1e-5, torch.bfloat16, h.dev)
+    x = h.randn(B, S, d).requires_grad_(True)
+    dy = h.randn(B, S, d)
+    with torch.no_grad():
+        fwd = h.time_ms(lambda: blk(x))
+
+    def both():
+        x.grad = None
+        for p in blk.parameters():
+            p.grad = None
+        blk(x).backward(dy)
+
+    tot = h.time_ms(both)
+    emit("transformer_block", True, shape=[B, S, d, heads, ff], dtype="bf16", fwd_ms=round(fwd, 3),
+         fwd_tok_s=round(B * S / fwd * 1e3), fwd_bwd_ms=round(tot, 3), fwd_bwd_tok_s=round(B * S / tot * 1e3),
+         reference_published="fp32 on RTX 5880 Ada: fwd 24.30 ms = 674264 tok/s, fwd + bwd 87.01 ms = 188295 tok/s",
+         bar="none (dashboard)")
+
+
+def case_llama_decode_block(h: Harness):
+    import copy
+
+    from tesseract_b200.nn.kv_cache import KVCache
+    from tesseract_b200.nn.modules import TransformerBlock
+    from tesseract_b200.quant import Scheme
+    d, heads, ff, keys = 4096, 32, 11008, 129
+    torch.manual_seed(0)
+    base = TransformerBlock(d, heads, ff, heads, 4096, 10000.0, 1e-5, torch.bfloat16, h.dev)
+    out = {}
+    for name, scheme in (("bf16", None), ("int8", Scheme.Int8Symmetric()), ("int4g", Scheme.Int4GroupSymmetric(128))):
+        blk = copy.deepcopy(base)
+        if scheme is not None:
+            blk.attn.quantize_(scheme)
+            blk.ffn.quantize_(scheme)
+        cache = KVCache(1, heads, 4096, d // heads, torch.bfloat16, h.dev)
+        pre = h.randn(1, heads, keys - 1, d // heads)
+        cache.append(pre, pre)
+        x = h.randn(1, 1, d)
+
+        def step():
+            cache.set_current_len(keys - 1)
+            return blk.forward_step(x, cache)
+
+        with torch.no_grad():
+            out[name] = h.time_ms(step) * 1e3
+        del blk
+    emit("llama_decode_block", True, shape=[d, heads, ff, keys], **{f"{k}_us": round(v, 1) for k, v in out.items()},
+         reference_published="RTX 5880 Ada: FP32 1123.7 us, INT8 510.2 us, INT4G 726.0 us (torch FP16 478.0 us)",
+         bar="none (dashboard)")
+
+
 CASES = {"rms_norm": case_rms_norm, "swiglu": case_swiglu, "elementwise": case_elementwise, "fp8_gemm": case_fp8_gemm,
          "decode_attention": case_decode_attention, "attention_bwd": case_attention_bwd,
          "quantized_decode": case_quantized_decode, "moe": case_moe, "mamba_scaling": case_mamba_scaling,
-         "graph_replay": case_graph_replay, "pinned": case_pinned}
+         "graph_replay": case_graph_replay, "pinned": case_pinned, "paged_kv": case_paged_kv,
+         "transformer_block": case_transformer_block, "llama_decode_block": case_llama_decode_block}
 
 
 def main() -> int:

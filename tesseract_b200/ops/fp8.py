@@ -155,6 +155,36 @@ class Fp8Linear(torch.nn.Module):
         return y.view(*x.shape[:-1], self.out_features)
 
 
+class MxLinear(torch.nn.Module):
+    """Inference Linear with E4M3 weights whose 128 x 128 block scales are powers of two; activations are quantised per
+    call to E4M3 with one power-of-two scale per row and 32 columns, and the tensor core applies both scale sets
+    (``mx_linear``: the weight-streaming kernel up to 256 rows, the persistent tiled kernel above). bf16 in, bf16 out."""
+
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor = None):
+        super().__init__()
+        q, sb = quantize_weight(weight.detach(), pow2=True)
+        self.register_buffer("q_weight", q)
+        self.register_buffer("weight_scale", sb)
+        self.register_buffer("weight_scale_atoms", weight_scale_atoms(sb))
+        self.bias = None if bias is None else torch.nn.Parameter(bias.detach().clone(), requires_grad=False)
+        self.out_features, self.in_features = weight.shape
+
+    @classmethod
+    def from_linear(cls, lin) -> "MxLinear":
+        return cls(lin.weight, getattr(lin, "bias", None))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        if x2.dtype != torch.bfloat16:
+            x2 = x2.to(torch.bfloat16)
+        big = x2.shape[0] > 256
+        q, sf = quantize_act_mx(x2, atoms=big)
+        y = mx_linear(q, sf, self.q_weight, self.weight_scale, w_atoms=self.weight_scale_atoms if big else None).to(x.dtype)
+        if self.bias is not None:
+            y = y + self.bias.to(y.dtype)
+        return y.view(*x.shape[:-1], self.out_features)
+
+
 # ----------------------------------------------------------------------------------------- per-tensor scaling
 def quantize_tensor(x: torch.Tensor):
     """x -> (e4m3 bytes uint8 of the same shape, fp32 scale [1] on x's device): scale = absmax / 448 (1 for an all-zero

@@ -44,3 +44,13 @@ def test_power_of_two_weight_scales_and_mx_linear_restatement():
         y = fp8.mx_linear(q, sf, wq, ws)
         full = x.float() @ w.t()
         assert y.dtype == torch.bfloat16 and ((y.float() - full).norm() / full.norm()).item() < 0.06
+
+
+def test_mx_linear_layer_small_and_large_batches():
+    g = torch.Generator().manual_seed(2)
+    lin = torch.nn.Linear(256, 96, bias=True)
+    layer = fp8.MxLinear.from_linear(lin)
+    for rows in (5, 300):
+        x = torch.randn(rows, 256, generator=g)
+        y, want = layer(x), lin(x)
+        assert y.shape == want.shape and ((y - want).norm() / want.norm()).item() < 0.06
