@@ -60,6 +60,13 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+// S += Q K^T on the int8 tensor-core path: A = int8 queries (16 rows x 32), B = int8 keys (32 x 8 tokens), int32 sums.
+__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
 // 16-byte async copy; src_bytes = 0 zero-fills the destination (rows past the end of the sequence).
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -84,9 +91,10 @@ struct MmaDecParams {
   int* status;           // device status word: a block-table entry outside the pool is reported there
 };
 
-// INT8 pools: the raw int8 rows (and their scales) travel through the cp.async ring and are widened to T in a
-// per-warp conversion buffer right before the MMAs; int8 values are exact in bf16 / fp16, K scales multiply S after
-// the product and V scales multiply P before it, so no precision is lost to the staging.
+// INT8 pools: the raw int8 rows (and their scales) travel through the cp.async ring. S = Q K^T runs on the int8
+// tensor-core path straight from the raw key rows: the queries are quantised once per CTA (one scale per head,
+// |q| / 127), the sums are exact int32, and query scale x key scale multiply S afterwards. The values are widened to
+// fp16 in a per-warp conversion buffer (int8 is exact in fp16) for P V, with the V scales riding on P.
 template <typename T, int D, bool INT8>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_mma_kernel(MmaDecParams p) {
@@ -98,8 +106,10 @@ paged_decode_mma_kernel(MmaDecParams p) {
   constexpr int kTileBytes = kTile * kRowBytes;   // one K (or V) tile as the tensor core reads it
   constexpr int kRawRow = INT8 ? D : D * 2;       // bytes per pool row
   constexpr int kRawTile = kTile * kRawRow;
-  constexpr int kStageBytes = INT8 ? (2 * kRawTile + 2 * kTile * 4) : 2 * kTileBytes;  // ring stage
-  constexpr int kConvBytes = INT8 ? 2 * kTileBytes : 0;                                // widened K, V
+  constexpr int kRawKRow = D + 16;                // INT8: raw key rows are padded in the ring (ldmatrix reads them)
+  constexpr int kRawKTile = kTile * kRawKRow;
+  constexpr int kStageBytes = INT8 ? (kRawKTile + kRawTile + 2 * kTile * 4) : 2 * kTileBytes;  // ring stage
+  constexpr int kConvBytes = INT8 ? kTileBytes : 0;                                            // widened V
   constexpr int kWarpBytes = kStagesD * kStageBytes + kConvBytes;
   constexpr int kChunks = kRawRow / 16;           // 16-byte pieces per pool row
   extern __shared__ uint8_t smem_raw[];
@@ -125,23 +135,54 @@ paged_decode_mma_kernel(MmaDecParams p) {
   const uint32_t wsmem_u32 = smem_u32(wsmem);
   const int* table = p.tables + static_cast<long long>(a) * p.max_logical;
 
-  // Q as the A operand (rows = heads, padded to 16 with zeros): per k-step a0 = (head g, d 2t..2t+1), a2 = (+8)
-  uint32_t qa[D / 16][2];
+  // Q as the A operand (rows = heads, padded to 16 with zeros). 16-bit pools: per k-step of 16, a0 = (head g,
+  // d 2t..2t+1), a2 = (+8). INT8 pools: the row is quantised to int8 with one scale (|q|max / 127) and a k-step covers
+  // 32 columns: a0 = (head g, d 4t..4t+3), a2 = (+16).
+  uint32_t qa[INT8 ? D / 32 : D / 16][2];
+  float q_scale = 1.f;
   {
     const T* qrow = static_cast<const T*>(p.q) + (static_cast<long long>(a) * p.H + h0 + g) * D;
+    if constexpr (INT8) {
+      float qv[D / 32][8];
+      float amax = 0.f;
 #pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      if (g < p.gh) {
-        if constexpr (std::is_same<MT, T>::value) {
-          qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
-          qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8);
-        } else {
-          const T* q0 = qrow + ks * 16 + 2 * t4;
-          qa[ks][0] = MmaT<MT>::pack(to_f32<T>(q0[0]), to_f32<T>(q0[1]));
-          qa[ks][1] = MmaT<MT>::pack(to_f32<T>(q0[8]), to_f32<T>(q0[9]));
+      for (int ks = 0; ks < D / 32; ++ks)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          qv[ks][e] = g < p.gh ? to_f32<T>(qrow[ks * 32 + (e >> 2) * 16 + 4 * t4 + (e & 3)]) : 0.f;
+          amax = fmaxf(amax, fabsf(qv[ks][e]));
         }
-      } else {
-        qa[ks][0] = qa[ks][1] = 0u;
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      q_scale = amax > 0.f ? amax / 127.f : 1.f;
+      const float inv = 1.f / q_scale;
+#pragma unroll
+      for (int ks = 0; ks < D / 32; ++ks)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t w = 0u;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int qi = max(-127, min(127, __float2int_rn(qv[ks][hh * 4 + e] * inv)));
+            w |= (static_cast<uint32_t>(qi) & 0xffu) << (8 * e);
+          }
+          qa[ks][hh] = w;
+        }
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        if (g < p.gh) {
+          if constexpr (std::is_same<MT, T>::value) {
+            qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
+            qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4 + 8);
+          } else {
+            const T* q0 = qrow + ks * 16 + 2 * t4;
+            qa[ks][0] = MmaT<MT>::pack(to_f32<T>(q0[0]), to_f32<T>(q0[1]));
+            qa[ks][1] = MmaT<MT>::pack(to_f32<T>(q0[8]), to_f32<T>(q0[9]));
+          }
+        } else {
+          qa[ks][0] = qa[ks][1] = 0u;
+        }
       }
     }
   }
@@ -167,7 +208,7 @@ paged_decode_mma_kernel(MmaDecParams p) {
     const int tile = warp + j * kWarps;
     const int tok0 = t_begin + tile * kTile;
     const uint32_t dstK = wsmem_u32 + (j % kStagesD) * kStageBytes;
-    const uint32_t dstV = dstK + (INT8 ? kRawTile : kTileBytes);
+    const uint32_t dstV = dstK + (INT8 ? kRawKTile : kTileBytes);
     const int my_t = tok0 + (lane & 15);
     const bool my_valid = my_t < t_end;
     const long long my_row = row_of(my_t, my_valid);           // lanes 16..31 duplicate lanes 0..15
@@ -179,14 +220,15 @@ paged_decode_mma_kernel(MmaDecParams p) {
       const long long row = __shfl_sync(0xffffffffu, my_row, r);
       const int valid = __shfl_sync(0xffffffffu, static_cast<int>(my_valid), r);
       const size_t off = static_cast<size_t>(row) * kRawRow + piece * 16;
-      const uint32_t d = r * (INT8 ? kRawRow : kRowBytes) + piece * 16;
-      cp_async16(dstK + d, static_cast<const char*>(p.k_pool) + off, valid ? 16 : 0);
-      cp_async16(dstV + d, static_cast<const char*>(p.v_pool) + off, valid ? 16 : 0);
+      const uint32_t dk = r * (INT8 ? kRawKRow : kRowBytes) + piece * 16;
+      const uint32_t dv = r * (INT8 ? kRawRow : kRowBytes) + piece * 16;
+      cp_async16(dstK + dk, static_cast<const char*>(p.k_pool) + off, valid ? 16 : 0);
+      cp_async16(dstV + dv, static_cast<const char*>(p.v_pool) + off, valid ? 16 : 0);
     }
     if constexpr (INT8) {
       // scales: 16 K + 16 V floats per tile, 4 bytes each -> one 4-byte async copy per lane
       const float* src = (lane < 16 ? p.k_scale : p.v_scale) + my_row;
-      const uint32_t dst = dstK + 2 * kRawTile + lane * 4;
+      const uint32_t dst = dstK + kRawKTile + kRawTile + lane * 4;
       asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(my_valid ? 4 : 0) : "memory");
     }
   };
@@ -207,16 +249,14 @@ paged_decode_mma_kernel(MmaDecParams p) {
     if constexpr (INT8) {
       const uint8_t* raw = wsmem + (j % kStagesD) * kStageBytes;
       uint8_t* conv = wsmem + kStagesD * kStageBytes;
-      sc = reinterpret_cast<const float*>(raw + 2 * kRawTile);
-      // widen 2 * kTile rows of D int8 to T: each lane converts 16-byte pieces
+      sc = reinterpret_cast<const float*>(raw + kRawKTile + kRawTile);
+      // widen the kTile value rows of D int8 to fp16: each lane converts 16-byte pieces (the keys stay int8)
 #pragma unroll
-      for (int i = 0; i < (2 * kTile * kChunks + 31) / 32; ++i) {
+      for (int i = 0; i < (kTile * kChunks + 31) / 32; ++i) {
         const int c = lane + 32 * i;
-        if (c >= 2 * kTile * kChunks) break;
-        const int which = c / (kTile * kChunks);           // 0 = K, 1 = V
-        const int cc = c - which * kTile * kChunks;
-        const int r = cc / kChunks, piece = cc % kChunks;
-        const uint4 v = *reinterpret_cast<const uint4*>(raw + which * kRawTile + r * kRawRow + piece * 16);
+        if (c >= kTile * kChunks) break;
+        const int r = c / kChunks, piece = c % kChunks;
+        const uint4 v = *reinterpret_cast<const uint4*>(raw + kRawKTile + r * kRawRow + piece * 16);
         const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
         uint32_t w[8];
 #pragma unroll
@@ -231,30 +271,50 @@ paged_decode_mma_kernel(MmaDecParams p) {
           w[2 * q4] = *reinterpret_cast<const uint32_t*>(&a);
           w[2 * q4 + 1] = *reinterpret_cast<const uint32_t*>(&b);
         }
-        uint8_t* dst = conv + which * kTileBytes + r * kRowBytes + piece * 32;
+        uint8_t* dst = conv + r * kRowBytes + piece * 32;
         *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
         *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
       }
       __syncwarp();
-      sK = smem_u32(conv);
-      sV = sK + kTileBytes;
+      sV = smem_u32(conv);
     }
     const int tok0 = t_begin + (warp + j * kWarps) * kTile;
 
     // ---- S = Q K^T : two 8-token column blocks
     float s[2][4];
+    if constexpr (INT8) {
+      int si[2][4];
 #pragma unroll
-    for (int b = 0; b < 2; ++b) s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.f;
+      for (int b = 0; b < 2; ++b) si[b][0] = si[b][1] = si[b][2] = si[b][3] = 0;
 #pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      // matrices: (tokens 0-7, d 0-7), (tokens 0-7, d 8-15), (tokens 8-15, d 0-7), (tokens 8-15, d 8-15)
-      uint32_t kb[4];
-      const int mat = lane >> 3;
-      const int r = (mat >> 1) * 8 + (lane & 7);
-      ldsm_x4(kb, sK + r * kRowBytes + ks * 32 + (mat & 1) * 16);
-      const uint32_t afrag[4] = {qa[ks][0], 0u, qa[ks][1], 0u};
-      MmaT<MT>::mma(s[0], afrag, kb[0], kb[1]);
-      MmaT<MT>::mma(s[1], afrag, kb[2], kb[3]);
+      for (int ks = 0; ks < D / 32; ++ks) {
+        // 8 x 16-byte matrices: (tokens 0-7, d 0-15), (tokens 0-7, d 16-31), (tokens 8-15, d 0-15), (tokens 8-15, d 16-31)
+        uint32_t kb[4];
+        const int mat = lane >> 3;
+        const int r = (mat >> 1) * 8 + (lane & 7);
+        ldsm_x4(kb, sK + r * kRawKRow + ks * 32 + (mat & 1) * 16);
+        const uint32_t afrag[4] = {qa[ks][0], 0u, qa[ks][1], 0u};
+        mma_s8(si[0], afrag, kb[0], kb[1]);
+        mma_s8(si[1], afrag, kb[2], kb[3]);
+      }
+#pragma unroll
+      for (int b = 0; b < 2; ++b)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[b][e] = static_cast<float>(si[b][e]) * q_scale;
+    } else {
+#pragma unroll
+      for (int b = 0; b < 2; ++b) s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        // matrices: (tokens 0-7, d 0-7), (tokens 0-7, d 8-15), (tokens 8-15, d 0-7), (tokens 8-15, d 8-15)
+        uint32_t kb[4];
+        const int mat = lane >> 3;
+        const int r = (mat >> 1) * 8 + (lane & 7);
+        ldsm_x4(kb, sK + r * kRowBytes + ks * 32 + (mat & 1) * 16);
+        const uint32_t afrag[4] = {qa[ks][0], 0u, qa[ks][1], 0u};
+        MmaT<MT>::mma(s[0], afrag, kb[0], kb[1]);
+        MmaT<MT>::mma(s[1], afrag, kb[2], kb[3]);
+      }
     }
     // ---- online softmax for head row g (rows g + 8 are padding); this lane holds tokens b*8 + 2t, +1
     float mx = -INFINITY;
@@ -365,8 +425,8 @@ int launch_mma(const MmaDecParams& p, cudaStream_t s) {
   constexpr int kRowBytes = D * 2 + 16;
   constexpr int kTileBytes = kTile * kRowBytes;
   constexpr int kRawTile = kTile * (INT8 ? D : D * 2);
-  constexpr int kStageBytes = INT8 ? (2 * kRawTile + 2 * kTile * 4) : 2 * kTileBytes;
-  constexpr int ring = kWarps * (kStagesD * kStageBytes + (INT8 ? 2 * kTileBytes : 0));
+  constexpr int kStageBytes = INT8 ? (kTile * (D + 16) + kRawTile + 2 * kTile * 4) : 2 * kTileBytes;
+  constexpr int ring = kWarps * (kStagesD * kStageBytes + (INT8 ? kTileBytes : 0));
   constexpr int merge = (kWarps * 8 * D + 2 * kWarps * 8) * 4;
   constexpr int smem = (ring > merge ? ring : merge) + 128;
   auto kern = paged_decode_mma_kernel<T, D, INT8>;
