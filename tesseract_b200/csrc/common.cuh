@@ -100,6 +100,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // whatever does not depend on this kernel's results) while this kernel is still running; successors launched the
 // ordinary way are unaffected. Called first thing by the small kernels that precede the decode GEMMs.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Blocks until the kernel before this one in the stream has completed and its writes are visible (a no-op for a
+// launch without the programmatic-serialisation attribute). First statement of a kernel launched with launch_pdl.
+__device__ __forceinline__ void pdl_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -312,6 +315,28 @@ bool make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t r
 bool make_tmap_nd(CUtensorMap* out, const void* base, int elem_bytes, int rank, const uint64_t* dims,
                   const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
 int sm_count();
+// Whether the small kernels of a decode step are launched with programmatic stream serialisation
+// (TESSERACT_PDL_ALL, default 1): each then starts while its predecessor drains and waits for it with pdl_grid_wait.
+bool pdl_all_enabled();
+
+// kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-serialisation attribute when `pdl` is set: the
+// launch (and the scheduling of its CTAs) overlaps the tail of the previous kernel in the stream. The kernel must call
+// pdl_grid_wait() before it reads or writes anything its predecessors touch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 // "Done once" remembered per device: cudaFuncSetAttribute (and the like) applies to the current device only, so a
 // process that drives several GPUs has to repeat it on each. Racing threads may both run the guarded call; it is

@@ -276,6 +276,7 @@ __global__ void __launch_bounds__(D)
 decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, T* __restrict__ out,
                     int splits) {
   pdl_trigger();
+  pdl_grid_wait();
   const long long ah = blockIdx.x;  // a * H + h
   const int d = threadIdx.x;
   float nm = -INFINITY;
@@ -342,6 +343,8 @@ kv_append_kernel(T* __restrict__ qkv, const float* __restrict__ cos_t, const flo
                  const int* __restrict__ positions, const int* __restrict__ slots, void* __restrict__ k_pool,
                  void* __restrict__ v_pool, float* __restrict__ k_scale, float* __restrict__ v_scale,
                  T* __restrict__ q_out, int tokens, int H, int Hkv, int bs, int rotate) {
+  pdl_trigger();
+  pdl_grid_wait();
   constexpr int EPL = D / 32;  // 4 (D=128) or 2 (D=64): an even count, so rotation pairs stay in-lane
   const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -471,11 +474,13 @@ TSB_EXPORT int tsb_paged_decode(const void* q, const void* k_pool, const void* v
     if (rc != -100) {
       if (rc != 0 || splits == 1) return rc;
       if (dtype == 1) {
-        if (D == 128) decode_merge_kernel<__nv_bfloat16, 128><<<A * H, 128, 0, s>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), splits);
-        else decode_merge_kernel<__nv_bfloat16, 64><<<A * H, 64, 0, s>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+        const bool pdl = pdl_all_enabled();
+        if (D == 128) launch_pdl(decode_merge_kernel<__nv_bfloat16, 128>, dim3(A * H), dim3(128), 0, s, pdl, part_o, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+        else launch_pdl(decode_merge_kernel<__nv_bfloat16, 64>, dim3(A * H), dim3(64), 0, s, pdl, part_o, part_ml, static_cast<__nv_bfloat16*>(out), splits);
       } else {
-        if (D == 128) decode_merge_kernel<__half, 128><<<A * H, 128, 0, s>>>(part_o, part_ml, static_cast<__half*>(out), splits);
-        else decode_merge_kernel<__half, 64><<<A * H, 64, 0, s>>>(part_o, part_ml, static_cast<__half*>(out), splits);
+        const bool pdl = pdl_all_enabled();
+        if (D == 128) launch_pdl(decode_merge_kernel<__half, 128>, dim3(A * H), dim3(128), 0, s, pdl, part_o, part_ml, static_cast<__half*>(out), splits);
+        else launch_pdl(decode_merge_kernel<__half, 64>, dim3(A * H), dim3(64), 0, s, pdl, part_o, part_ml, static_cast<__half*>(out), splits);
       }
       return static_cast<int>(cudaGetLastError());
     }
@@ -514,9 +519,9 @@ TSB_EXPORT int tsb_kv_append_paged(void* qkv, const float* cos_t, const float* s
   const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
   const bool i8 = k_scale != nullptr;
 #define TSB_KVA(TT, I8, DD)                                                                                      \
-  kv_append_kernel<TT, I8, DD><<<blocks, 256, 0, s>>>(static_cast<TT*>(qkv), cos_t, sin_t, positions, slots, k_pool, \
-                                                      v_pool, k_scale, v_scale, static_cast<TT*>(q_out), tokens, H, \
-                                                      Hkv, bs, rotate)
+  launch_pdl(kv_append_kernel<TT, I8, DD>, dim3(blocks), dim3(256), 0, s, pdl_all_enabled(), static_cast<TT*>(qkv), \
+             cos_t, sin_t, positions, slots, k_pool, v_pool, k_scale, v_scale, static_cast<TT*>(q_out), tokens, H, Hkv,  \
+             bs, rotate)
   if (dtype == 1) {
     if (D == 128) { if (i8) TSB_KVA(__nv_bfloat16, true, 128); else TSB_KVA(__nv_bfloat16, false, 128); }
     else { if (i8) TSB_KVA(__nv_bfloat16, true, 64); else TSB_KVA(__nv_bfloat16, false, 64); }

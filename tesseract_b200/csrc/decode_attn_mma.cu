@@ -99,6 +99,7 @@ template <typename T, int D, bool INT8>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_mma_kernel(MmaDecParams p) {
   pdl_trigger();
+  pdl_grid_wait();
   // INT8 pools run their products in fp16 whatever the model type: int8 -> fp16 is one byte-permute and half a
   // subtract per element (1024 + u is exact in fp16), and |k|, |v| <= 128 with fp32 accumulation loses nothing.
   using MT = typename std::conditional<INT8, __half, T>::type;
@@ -438,7 +439,7 @@ int launch_mma(const MmaDecParams& p, cudaStream_t s) {
   }
   const int G = p.H / p.Hkv;
   dim3 grid(p.splits, p.Hkv * (G / p.gh), p.A);
-  kern<<<grid, kWarps * 32, smem, s>>>(p);
+  launch_pdl(kern, grid, dim3(kWarps * 32), smem, s, pdl_all_enabled(), p);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -184,6 +184,7 @@ __global__ void __launch_bounds__(256)
 quant_act_mx_kernel(const __nv_bfloat16* __restrict__ X, long long ldx, uint8_t* __restrict__ Xq,
                     uint32_t* __restrict__ sf, int M, int K, int m_pad, int atoms) {
   pdl_trigger();
+  pdl_grid_wait();
   const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int per_row = K / 8;                         // threads per row: 8 elements each, a multiple of 16
   const int row = static_cast<int>(t / per_row);
@@ -217,6 +218,7 @@ rmsnorm_quant_mx_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
                         const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
                         uint8_t* __restrict__ Xq, uint32_t* __restrict__ sf, int D, int m_pad, float eps) {
   pdl_trigger();
+  pdl_grid_wait();
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int lane = threadIdx.x & 31;
@@ -275,6 +277,7 @@ __global__ void __launch_bounds__(256)
 swiglu_quant_mx_kernel(const __nv_bfloat16* __restrict__ gate_up, uint8_t* __restrict__ Xq, uint32_t* __restrict__ sf,
                        int F, int m_pad) {
   pdl_trigger();
+  pdl_grid_wait();
   const int row = blockIdx.y;
   const int lane = threadIdx.x & 31;
   const int v = blockIdx.x * 256 + threadIdx.x;
@@ -847,10 +850,9 @@ TSB_EXPORT int tsb_quant_act_mx_layout(const void* X, long long ldx, void* Xq, v
   const int m_pad = tsb_mx_m_pad(M);
   const long long threads = static_cast<long long>(m_pad) * (K / 8);
   const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
-  quant_act_mx_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(X), ldx, static_cast<uint8_t*>(Xq), static_cast<uint32_t*>(sf), M, K, m_pad,
-      atoms);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(quant_act_mx_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                     pdl_all_enabled(), static_cast<const __nv_bfloat16*>(X), ldx,
+                                     static_cast<uint8_t*>(Xq), static_cast<uint32_t*>(sf), M, K, m_pad, atoms));
 }
 
 // Fused producers of the same (Xq, sf) pair, bf16 only, D (F) % 128 == 0, dense rows:
@@ -863,27 +865,24 @@ TSB_EXPORT int tsb_rmsnorm_quant_mx(const void* x, const void* res, const void* 
   const int m_pad = tsb_mx_m_pad(rows);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int maxv = (D / 8 + 255) / 256;
-#define TSB_RQ(MV)                                                                                                 \
-  rmsnorm_quant_mx_kernel<MV><<<rows, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),                            \
-                                                   static_cast<const __nv_bfloat16*>(res),                          \
-                                                   static_cast<const __nv_bfloat16*>(w),                            \
-                                                   static_cast<__nv_bfloat16*>(h_out), static_cast<uint8_t*>(Xq),   \
-                                                   static_cast<uint32_t*>(sf), D, m_pad, eps)
+#define TSB_RQ(MV)                                                                                                  \
+  return static_cast<int>(launch_pdl(rmsnorm_quant_mx_kernel<MV>, dim3(rows), dim3(256), 0, s, pdl_all_enabled(),    \
+                                     static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),   \
+                                     static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(h_out),       \
+                                     static_cast<uint8_t*>(Xq), static_cast<uint32_t*>(sf), D, m_pad, eps))
   if (maxv <= 1) TSB_RQ(1);
-  else if (maxv <= 2) TSB_RQ(2);
-  else TSB_RQ(4);
+  if (maxv <= 2) TSB_RQ(2);
+  TSB_RQ(4);
 #undef TSB_RQ
-  return static_cast<int>(cudaGetLastError());
 }
 
 TSB_EXPORT int tsb_swiglu_quant_mx(const void* gate_up, void* Xq, void* sf, int rows, int F, void* stream) {
   using namespace tsb;
   if (rows <= 0 || rows > 65535 || F <= 0 || F % 128 || !gate_up || !Xq || !sf) return -2;
   const dim3 grid(static_cast<unsigned>((F / 8 + 255) / 256), static_cast<unsigned>(rows));
-  swiglu_quant_mx_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(gate_up), static_cast<uint8_t*>(Xq), static_cast<uint32_t*>(sf), F,
-      tsb_mx_m_pad(rows));
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(swiglu_quant_mx_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream),
+                                     pdl_all_enabled(), static_cast<const __nv_bfloat16*>(gate_up),
+                                     static_cast<uint8_t*>(Xq), static_cast<uint32_t*>(sf), F, tsb_mx_m_pad(rows)));
 }
 
 // Y [M, N] bf16 (row stride ldy) = dequant(Xq, sf) * dequant(W, w_scale)^T.

@@ -74,6 +74,14 @@ int sm_count() {
   return g_sm_count[dev];
 }
 
+bool pdl_all_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("TESSERACT_PDL_ALL");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  return on;
+}
+
 bool make_tmap_nd(CUtensorMap* out, const void* base, int elem_bytes, int rank, const uint64_t* dims,
                   const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
   EncodeTiledFn enc = resolve_encode();

@@ -45,6 +45,7 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_MX_FUSED_QUANT", "1", "serving, fp8 weights: 1 (RMSNorm / SwiGLU write the quantised GEMM operand directly) | 0 (separate quantiser kernel)"),
     EnvVar("TESSERACT_KERNEL_CASES_SMALL", "0", "benchmarks/kernel_cases.py: 1 runs one small shape per case (for a profiler capture)"),
     EnvVar("TESSERACT_EP_SCATTER_EPILOGUE", "1", "expert parallelism: 1 (the down projection's epilogue stores result rows into the source ranks' buffers) | 0 (separate return kernel)"),
+    EnvVar("TESSERACT_PDL_ALL", "1", "decode-step kernels (quantisers, KV append, decode attention, merge): 1 (programmatic dependent launch) | 0"),
     EnvVar("TESSERACT_PDL", "1", "serving decode GEMMs: 1 (programmatic dependent launch) | 0"),
     EnvVar("TESSERACT_CPU_GEMM", "torch", "2-D fp32 CPU products of ops.cpu_gemm.matmul_f32 callers: torch | native (host-runtime AVX2 GEMM)"),
     EnvVar("TESSERACT_SERVE_DECODE_GEMM", "auto", "serving decode GEMMs: auto | mx (fp8 weights: tensor-core block scaling) | stream (always the weight-streaming kernel) | splitk (bf16: the cluster split-K kernel) | fp8gemm (fp8 weights: never mx)"),
