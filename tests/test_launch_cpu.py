@@ -74,3 +74,38 @@ def test_command_line_form_runs_a_torchrun_style_script(tmp_path):
     r = subprocess.run([sys.executable, "-m", "tesseract_b200.parallel.launch", "--nproc", "2", "--backend", "gloo", str(bad)],
                        cwd=ROOT, capture_output=True, text=True, timeout=300)
     assert r.returncode == 77
+
+
+def _peer_learns_of_a_failure(rank, world, out_path):
+    """Rank 1 fails on the host between steps; rank 0 learns of it from the job's store (the launcher posts the
+    failing rank's exception there) at its next watchdog step, before it would enter a collective."""
+    import time
+
+    import torch.distributed as dist
+
+    from tesseract_b200.parallel.launch import job_watchdog
+    from tesseract_b200.utils.watchdog import RankLost
+    wd = job_watchdog(timeout_s=30.0)
+    assert wd is not None and wd.world == world
+    dist.barrier()
+    if rank == 1:
+        raise RuntimeError("rank 1 gives up between steps")
+    try:
+        for _ in range(3000):
+            wd.step()
+            time.sleep(0.005)
+    except RankLost as e:
+        with open(out_path, "w") as f:
+            f.write(f"{e.rank}|{e.reason}")
+        return "lost"
+    return "never noticed"
+
+
+def test_watchdog_over_the_job_store_tells_peers_of_a_failed_rank(tmp_path):
+    out = tmp_path / "seen.txt"
+    with pytest.raises(LaunchError) as e:
+        launch(_peer_learns_of_a_failure, 2, str(out), backend="gloo")
+    assert e.value.rank == 1 and "gives up between steps" in e.value.detail
+    assert out.exists(), "rank 0 did not learn of the failure before the launcher took it down"
+    rank, reason = out.read_text().split("|", 1)
+    assert rank == "1" and "RuntimeError" in reason and "gives up between steps" in reason
