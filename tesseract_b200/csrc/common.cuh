@@ -262,6 +262,17 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t m, uint32_t n, uint32
          ((m >> 4) << 24);
 }
 
+// ---------------------------------------------------------------- MX (power-of-two block scale) helpers
+// UE8M0 exponent byte of a block whose largest magnitude is amax: the smallest power of two s = 2^(e - 127) with
+// amax / s <= 448 (the E4M3 range); 127 for an all-zero block. mx_inv_scale(e) = 2^(127 - e).
+__device__ __forceinline__ int mx_exponent_byte(float amax) {
+  const uint32_t bits = __float_as_uint(amax * (1.0f / 448.0f));
+  int e = static_cast<int>((bits >> 23) & 0xffu) + ((bits & 0x7fffffu) ? 1 : 0);
+  if (!(amax > 0.f)) e = 127;
+  return max(1, min(254, e));
+}
+__device__ __forceinline__ float mx_inv_scale(int e) { return __uint_as_float(static_cast<uint32_t>(254 - e) << 23); }
+
 // ---------------------------------------------------------------- small math helpers
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

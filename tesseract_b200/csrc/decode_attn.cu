@@ -17,6 +17,8 @@
 #include "common.cuh"
 #include "tsb_no_alloc.h"
 
+#include <cuda_fp8.h>
+
 #include <atomic>
 #include <mutex>
 
@@ -291,6 +293,42 @@ decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ 
   out[ah * D + d] = from_f32<T>(ll > 0.f ? acc / ll : 0.f);
 }
 
+// The merge of the key splits for head_dim 128 that hands its result on as the MX operand of the output projection:
+// the bf16-rounded head (what decode_merge_kernel stores) is quantised to E4M3 with one power-of-two scale per 32
+// values -- a warp of this CTA is one such block -- and the four exponent bytes of a head are the scale word of
+// (row a, 128-byte K chunk h), at sf[h * m_pad + a]: the layout quant_act_mx_kernel writes for a [A, H * 128] matrix.
+__global__ void __launch_bounds__(128)
+decode_merge_quant_mx_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                             uint8_t* __restrict__ xq, uint32_t* __restrict__ sf, int splits, int H, int m_pad) {
+  constexpr int D = 128;
+  pdl_trigger();
+  pdl_grid_wait();
+  __shared__ uint32_t s_exp[4];
+  const long long ah = blockIdx.x;  // a * H + h
+  const int d = threadIdx.x;
+  float nm = -INFINITY;
+  for (int s = 0; s < splits; ++s) nm = fmaxf(nm, part_ml[(ah * splits + s) * 2]);
+  float acc = 0.f, ll = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(ah * splits + s) * 2];
+    const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - nm);
+    acc += part_o[(ah * splits + s) * D + d] * c;
+    ll += part_ml[(ah * splits + s) * 2 + 1] * c;
+  }
+  const float v = __bfloat162float(__float2bfloat16(ll > 0.f ? acc / ll : 0.f));
+  float amax = fabsf(v);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const int e = mx_exponent_byte(amax);
+  xq[ah * D + d] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v * mx_inv_scale(e), __NV_SATFINITE, __NV_E4M3));
+  if ((d & 31) == 0) s_exp[d >> 5] = static_cast<uint32_t>(e);
+  __syncthreads();
+  if (d == 0) {
+    const int a = static_cast<int>(ah / H), h = static_cast<int>(ah % H);
+    sf[static_cast<long long>(h) * m_pad + a] = s_exp[0] | (s_exp[1] << 8) | (s_exp[2] << 16) | (s_exp[3] << 24);
+  }
+}
+
 int choose_splits(int A, int Hkv_groups, int max_len) {
   // enough CTAs for ~6 per SM (they are latency-bound and small), but never chunks shorter than 256 keys
   const int target = sm_count() * 6;
@@ -502,6 +540,42 @@ TSB_EXPORT int tsb_paged_decode(const void* q, const void* k_pool, const void* v
     return i8 ? launch_decode<__half, true, 64>(p, G, s) : launch_decode<__half, false, 64>(p, G, s);
   }
   return -2;
+}
+
+extern "C" int tsb_quant_act_mx_layout(const void* X, long long ldx, void* Xq, void* sf, int M, int K, int atoms,
+                                       void* stream);
+extern "C" int tsb_mx_m_pad(int M);
+
+// tsb_paged_decode whose result also leaves as the E4M3 + power-of-two-scale operand of an MX GEMM: xq [A, H * D]
+// bytes and sf [H * D / 128, tsb_mx_m_pad(A)] scale words (the layout of tsb_quant_act_mx). With head_dim 128, bf16
+// and more than one key split the merge kernel writes the operand itself and `out` is left untouched; otherwise the
+// attention runs as usual into `out` and the quantiser follows.
+TSB_EXPORT int tsb_paged_decode_mx(const void* q, const void* k_pool, const void* v_pool, const float* k_scale,
+                                   const float* v_scale, const int* tables, const int* lens, void* out,
+                                   float* scratch, void* xq, void* sf, int A, int H, int Hkv, int D, int bs, int nb,
+                                   int max_logical, float scale, int max_len, int dtype, void* stream) {
+  using namespace tsb;
+  if (A <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || (D != 64 && D != 128) || bs <= 0 || (H * D) % 128) return -2;
+  int gh = 1, splits = 1;
+  decode_plan(A, H, Hkv, max_len, k_scale != nullptr, &gh, &splits);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128 && dtype == 1 && splits > 1) {
+    float* part_o = scratch;
+    float* part_ml = scratch + static_cast<long long>(A) * H * splits * D;
+    const int rc = paged_decode_mma_dispatch(q, k_pool, v_pool, k_scale, v_scale, tables, lens, out, part_o, part_ml, A, H,
+                                             Hkv, D, bs, nb, max_logical, splits, gh, scale * 1.4426950408889634f,
+                                             dtype, s);
+    if (rc == 0) {
+      launch_pdl(decode_merge_quant_mx_kernel, dim3(A * H), dim3(128), 0, s, pdl_all_enabled(), part_o, part_ml,
+                 static_cast<uint8_t*>(xq), static_cast<uint32_t*>(sf), splits, H, tsb_mx_m_pad(A));
+      return static_cast<int>(cudaGetLastError());
+    }
+    if (rc != -100) return rc;
+  }
+  const int rc = tsb_paged_decode(q, k_pool, v_pool, k_scale, v_scale, tables, lens, out, scratch, A, H, Hkv, D, bs, nb,
+                                  max_logical, scale, max_len, dtype, stream);
+  if (rc != 0) return rc;
+  return tsb_quant_act_mx_layout(out, static_cast<long long>(H) * D, xq, sf, A, H * D, 0, stream);
 }
 
 // Rotate (adjacent-pair RoPE at positions[t]) the query and key heads of packed qkv [tokens, (H + 2 Hkv) * D],

@@ -136,12 +136,8 @@ __device__ __forceinline__ uint32_t mx_quant8(const float (&v)[8], uint2* packed
   for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  // smallest power of two s with amax / s <= 448: exponent of amax / 448, rounded up
-  const uint32_t bits = __float_as_uint(amax * (1.0f / 448.0f));
-  int e = static_cast<int>((bits >> 23) & 0xffu) + ((bits & 0x7fffffu) ? 1 : 0);
-  if (!(amax > 0.f)) e = 127;                        // an all-zero block: any scale does
-  e = max(1, min(254, e));
-  const float inv = __uint_as_float(static_cast<uint32_t>(254 - e) << 23);   // 2^(127 - e)
+  const int e = mx_exponent_byte(amax);
+  const float inv = mx_inv_scale(e);
   uint32_t w[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j)

@@ -15,7 +15,8 @@ constexpr int kSampThreads = 512;
 
 template <typename T>
 __global__ void __launch_bounds__(kSampThreads)
-argmax_rows_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, long long ld) {
+argmax_rows_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, long long ld,
+                   __nv_bfloat16* __restrict__ packed = nullptr, int rank = 0, int world = 1) {
   __shared__ float sv[kSampThreads / 32];
   __shared__ int si[kSampThreads / 32];
   const T* x = logits + blockIdx.x * ld;
@@ -86,8 +87,43 @@ argmax_rows_kernel(const T* __restrict__ logits, int* __restrict__ out, int V, l
         bi = oi;
       }
     }
-    if (lane == 0) out[blockIdx.x] = bi;
+    if (lane == 0) {
+      if (out) out[blockIdx.x] = bi;
+      if (packed) {
+        // vocabulary-parallel head: this rank's (best value, index as three base-256 digits) in its slot of a
+        // [4 * world] row, zeros in the other slots -- the element-wise sum over the ranks (a bf16 all-reduce; every
+        // entry is exact in bf16) then holds every rank's candidate
+        __nv_bfloat16* row = packed + static_cast<long long>(blockIdx.x) * 4 * world;
+        for (int j = 0; j < 4 * world; ++j) row[j] = __float2bfloat16(0.f);
+        const int i = bi == 0x7fffffff ? 0 : bi;
+        row[4 * rank + 0] = __float2bfloat16(best);
+        row[4 * rank + 1] = __float2bfloat16(static_cast<float>(i & 255));
+        row[4 * rank + 2] = __float2bfloat16(static_cast<float>((i >> 8) & 255));
+        row[4 * rank + 3] = __float2bfloat16(static_cast<float>((i >> 16) & 255));
+      }
+    }
   }
+}
+
+// The other half of the vocabulary-parallel arg-max: row r of `summed` holds (value, index digits) of every rank's
+// shard; the winner is the largest value, the lowest rank (= lowest global index) on ties.
+__global__ void argmax_unpack_kernel(const __nv_bfloat16* __restrict__ summed, int* __restrict__ out, int rows,
+                                     int world, int shard) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const __nv_bfloat16* row = summed + static_cast<long long>(r) * 4 * world;
+  float best = __bfloat162float(row[0]);
+  int bw = 0;
+  for (int w = 1; w < world; ++w) {
+    const float v = __bfloat162float(row[4 * w]);
+    if (v > best) {
+      best = v;
+      bw = w;
+    }
+  }
+  const int i = static_cast<int>(__bfloat162float(row[4 * bw + 1])) + (static_cast<int>(__bfloat162float(row[4 * bw + 2])) << 8) +
+                (static_cast<int>(__bfloat162float(row[4 * bw + 3])) << 16);
+  out[r] = bw * shard + i;
 }
 
 __device__ __forceinline__ float block_reduce_sum(float v, float* red) {
@@ -343,6 +379,23 @@ TSB_EXPORT int tsb_argmax_rows(const void* logits, int* out, int rows, int V, lo
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   TSB_DISPATCH_FLOAT(dtype, (tsb::argmax_rows_kernel<T><<<rows, tsb::kSampThreads, 0, s>>>(
                                 static_cast<const T*>(logits), out, V, ld)));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Vocabulary-parallel arg-max over a head whose rows are split over `world` ranks, `shard` rows per rank (the last
+// rank may hold fewer). Step 1: packed [rows, 4 * world] bf16 receives this rank's candidate per row (see the kernel);
+// the caller sums `packed` over the ranks. Step 2: out[row] = global index of the best candidate in the summed rows.
+TSB_EXPORT int tsb_argmax_rows_pack(const void* logits, void* packed, int rows, int V, long long ld, int rank, int world,
+                                    void* stream) {
+  if (rows <= 0 || V <= 0 || V >= (1 << 24) || world < 1 || rank < 0 || rank >= world || !packed) return -2;
+  tsb::argmax_rows_kernel<__nv_bfloat16><<<rows, tsb::kSampThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), nullptr, V, ld, static_cast<__nv_bfloat16*>(packed), rank, world);
+  return static_cast<int>(cudaGetLastError());
+}
+TSB_EXPORT int tsb_argmax_rows_unpack(const void* summed, int* out, int rows, int world, int shard, void* stream) {
+  if (rows <= 0 || world < 1 || shard <= 0 || !summed || !out) return -2;
+  tsb::argmax_unpack_kernel<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(summed), out, rows, world, shard);
   return static_cast<int>(cudaGetLastError());
 }
 

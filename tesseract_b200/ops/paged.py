@@ -21,6 +21,7 @@ from .._native import check, lib, stream_ptr
 P, I, L, F = _native.P, _native.I, _native.L, _native.F
 _native.register_signatures({
     "tsb_paged_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
+    "tsb_paged_decode_mx": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
     "tsb_paged_decode_scratch_floats": [I, I, I, I],
     "tsb_kv_append_paged": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
 })
@@ -112,6 +113,40 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         _native.add_launches(1)
         return out
     return paged_attention_ref(q.unsqueeze(1), k_pool, v_pool, block_tables, lens, scale, k_scale, v_scale).squeeze(1)
+
+
+def paged_decode_attention_mx(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
+                              lens: torch.Tensor, scale: Optional[float] = None,
+                              k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None,
+                              max_len_hint: int = 0):
+    """``quantize_act_mx(paged_decode_attention(...).view(A, H * D))``: the attention output as the E4M3 +
+    power-of-two-scale operand ``(q, sf)`` of the output projection's MX GEMM. With head_dim 128, bf16 and a split
+    key range the merge kernel of the splits writes the operand itself (no bf16 round trip, one launch fewer)."""
+    from . import fp8
+    A, H, D = q.shape
+    if not (_native_decode_ok(q, k_pool) and (k_scale is None or k_pool.dtype == torch.int8)
+            and q.dtype == torch.bfloat16 and (H * D) % 128 == 0 and hasattr(lib(), "tsb_paged_decode_mx")):
+        o = paged_decode_attention(q, k_pool, v_pool, block_tables, lens, scale, k_scale, v_scale, max_len_hint)
+        return fp8.quantize_act_mx(o.view(A, H * D))
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    nb, Hkv, bs, _ = k_pool.shape
+    out = torch.empty_like(q)
+    xq, sf = fp8._mx_buffers(A, H * D, q.device)
+    max_len = int(max_len_hint) if max_len_hint > 0 else block_tables.shape[1] * bs
+    scratch = _decode_scratch(q.device, lib().tsb_paged_decode_scratch_floats(A, H, D, max_len))
+    bt = block_tables if block_tables.dtype == torch.int32 else block_tables.to(torch.int32)
+    if bt.stride(1) != 1:
+        bt = bt.contiguous()
+    ln = lens if lens.dtype == torch.int32 else lens.to(torch.int32)
+    check(lib().tsb_paged_decode_mx(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+                                    k_scale.data_ptr() if k_scale is not None else None,
+                                    v_scale.data_ptr() if v_scale is not None else None,
+                                    bt.data_ptr(), ln.data_ptr(), out.data_ptr(), scratch.data_ptr(), xq.data_ptr(),
+                                    sf.data_ptr(), A, H, Hkv, D, bs, nb, bt.stride(0), float(scale), max_len, 1,
+                                    stream_ptr(q.device)), "tsb_paged_decode_mx")
+    _native.add_launches(1)
+    return xq, sf
 
 
 def paged_decode_attention_int8(q, k_pool, v_pool, k_scale, v_scale, block_tables, lens, scale=None):

@@ -41,6 +41,8 @@ from ..nn.kv_cache import BlockAllocator
 P, I, L, F = _native.P, _native.I, _native.L, _native.F
 _native.register_signatures({
     "tsb_argmax_rows": [P, P, I, I, L, I, P],
+    "tsb_argmax_rows_pack": [P, P, I, I, L, I, I, P],
+    "tsb_argmax_rows_unpack": [P, P, I, I, I, P],
     "tsb_sample_top_p_rows": [P, P, I, I, L, F, F, _native.ctypes.c_ulonglong, _native.ctypes.c_ulonglong, I, P],
     "tsb_sample_rows": [P, P, I, I, L, F, I, F, _native.ctypes.c_ulonglong, _native.ctypes.c_ulonglong, P, I, P],
     "tsb_repetition_penalty_rows": [P, I, I, L, P, L, P, F, I, P],
@@ -86,6 +88,29 @@ def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def argmax_rows_pack(logits: torch.Tensor, packed: torch.Tensor, rank: int, world: int) -> None:
+    """Vocabulary-parallel arg-max, step 1: ``packed`` [rows, 4 * world] bf16 receives this rank's best
+    (value, index in three base-256 digits) per row in slot ``rank`` and zeros elsewhere; summed over the ranks it
+    holds every rank's candidate exactly."""
+    check(lib().tsb_argmax_rows_pack(logits.data_ptr(), packed.data_ptr(), logits.shape[0], logits.shape[1],
+                                     logits.stride(0), rank, world, stream_ptr(logits.device)), "tsb_argmax_rows_pack")
+
+
+def argmax_rows_unpack(summed: torch.Tensor, world: int, shard: int) -> torch.Tensor:
+    """Step 2: global index of the best candidate of each summed row (rank r's shard starts at ``r * shard``)."""
+    out = torch.empty(summed.shape[0], dtype=torch.int32, device=summed.device)
+    check(lib().tsb_argmax_rows_unpack(summed.data_ptr(), out.data_ptr(), summed.shape[0], world, shard,
+                                       stream_ptr(summed.device)), "tsb_argmax_rows_unpack")
+    return out
+
+
+def vocab_shard_rows(vocab: int, world: int) -> int:
+    """Rows of the LM head per tensor-parallel rank (a multiple of 128, the last rank may hold fewer), or 0 when the
+    vocabulary is too small for every rank to hold some."""
+    shard = (vocab + world * 128 - 1) // (world * 128) * 128
+    return shard if (world - 1) * shard < vocab else 0
+
+
 def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, step: int = 0,
                 step_counter: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Temperature -> top-k (0 = off) -> top-p -> one draw per row, on the device. With ``step_counter`` (an int64
@@ -125,6 +150,9 @@ class TPServe:
         self.group, self.rank, self.world = group, rank, world
         self.max_rows = max_batch
         self.ar = SymmAllReduce(group, rank, world, device, max_batch * hidden_size)
+        # a second, small instance for the arg-max candidates of a vocabulary-parallel LM head: it always uses its
+        # first buffer; the all-reduces of the layers in between order two of its calls on every rank
+        self.head_ar = SymmAllReduce(group, rank, world, device, max_batch * 4 * world)
         self.nccl_calls = 0
 
     def all_reduce_big(self, x: torch.Tensor) -> torch.Tensor:
@@ -256,7 +284,20 @@ class ServingEngine:
                 self.wdown.append(pack(f.down_proj.weight[:, r * fl:(r + 1) * fl].contiguous()))
                 for lin in (a.q_proj, a.k_proj, a.v_proj, a.o_proj, f.gate_proj, f.up_proj, f.down_proj):
                     lin.weight.data = torch.empty(0, dtype=lin.weight.dtype, device=lin.weight.device)
-            self.w_head = pack(self.model.lm_head.weight)
+            # Greedy tensor-parallel serving splits the LM head over the ranks by vocabulary rows: each rank streams
+            # 1 / world of it, takes the arg-max of its logits and the ranks exchange (value, index) pairs through the
+            # peer-memory all-reduce. Sampling and the repetition penalty need whole rows of logits: replicated head.
+            V = self.model.lm_head.weight.shape[0]
+            self.vocab_shard = 0
+            if (tp is not None and tp.world % 2 == 0 and self.greedy and self.repetition_penalty == 1.0 and V < (1 << 24)
+                    and self.model.lm_head.weight.dtype == torch.bfloat16
+                    and os.environ.get("TESSERACT_SERVE_VOCAB_PARALLEL", "1") == "1"):
+                self.vocab_shard = vocab_shard_rows(V, tp.world)
+            if self.vocab_shard:
+                v0 = tp.rank * self.vocab_shard
+                self.w_head = pack(self.model.lm_head.weight[v0:min(V, v0 + self.vocab_shard)].contiguous())
+            else:
+                self.w_head = pack(self.model.lm_head.weight)
             tied = self.model.lm_head.weight.data_ptr() == self.model.embed_tokens.weight.data_ptr()
             if fp8_mode and self.w_head.q is not None and not tied:
                 self.model.lm_head.weight.data = torch.empty(0, dtype=self.model.lm_head.weight.dtype,
@@ -379,9 +420,15 @@ class ServingEngine:
                                             ks.data_ptr() if ks is not None else None,
                                             vs.data_ptr() if vs is not None else None, q.data_ptr(), T, H, Hkv, D,
                                             self.cfg.block_size, dt, 1, stream_ptr(qkv.device)), "tsb_kv_append_paged")
-            o = ops.paged_decode_attention(q, self.k_pool[li], self.v_pool[li], tables, lens, None, ks, vs,
-                                           max_len_hint=self.cfg.max_seq_len)
-            o = o.view(T, H * D)
+            if self._mx_ok(self.wo[li], T, q.dtype) and (H * D) % 128 == 0:
+                from ..ops import paged
+                # the split merge of the attention writes the quantised operand of the output projection
+                o = paged.paged_decode_attention_mx(q, self.k_pool[li], self.v_pool[li], tables, lens, None, ks, vs,
+                                                    max_len_hint=self.cfg.max_seq_len)
+            else:
+                o = ops.paged_decode_attention(q, self.k_pool[li], self.v_pool[li], tables, lens, None, ks, vs,
+                                               max_len_hint=self.cfg.max_seq_len)
+                o = o.view(T, H * D)
         else:
             qkv = ops.rope_qkv(qkv, rope.cos, rope.sin, num_heads=H, num_kv_heads=Hkv, head_dim=D, seq_len=1,
                                positions=positions)
@@ -482,6 +529,14 @@ class ServingEngine:
                 hist[i, :len(r.tokens)] = torch.tensor(r.tokens, dtype=torch.int32)
                 lens[i] = len(r.tokens)
             repetition_penalty_rows_(logits, hist.to(logits.device), lens.to(logits.device), self.repetition_penalty)
+        if self.greedy and self.vocab_shard:
+            tp, T = self.tp, logits.shape[0]
+            if T > tp.max_rows:
+                raise ValueError("ServingEngine: more rows than the head exchange buffer holds")
+            tp.head_ar.parity = 0
+            argmax_rows_pack(logits, tp.head_ar.input_view(T, 4 * tp.world), tp.rank, tp.world)
+            summed = tp.head_ar.reduce(T, 4 * tp.world)
+            return argmax_rows_unpack(summed, tp.world, self.vocab_shard)
         if self.greedy:
             return argmax_rows(logits)
         out = sample_rows(logits, self.temperature, self.top_k, self.top_p, self.seed, step_counter=self._step_dev)

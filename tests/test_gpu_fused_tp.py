@@ -210,6 +210,9 @@ def _worker(rank, world, port, q):
             ids = [eng.add_request(p, GenerateConfig(max_new_tokens=12)) for p in prompts]
             eng.run()
             outs[mode] = [eng.result(i)[len(p):] for i, p in zip(ids, prompts)]
+            if tp is not None:     # greedy tensor-parallel serving: the LM head is split by vocabulary rows
+                assert eng.vocab_shard == 2048 // world and eng.w_head.shape[0] == 2048 // world
+                assert tp.head_ar.calls > 0
         flat = torch.tensor([t for o in outs["tp"] for t in o], device=dev)
         lo, hi = flat.clone(), flat.clone()
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)

@@ -494,6 +494,50 @@ def test_paged_decode_attention(dev, A, H, Hkv, D, bs, lens, int8):
     assert (got.float() - ref).abs().max() < 3e-3 * max(1.0, ref.abs().max().item()) + 2e-2, (got.float() - ref).abs().max()
 
 
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("A,H,Hkv,D,lens", [(3, 8, 2, 128, [37, 500, 1]), (5, 4, 1, 128, [2000, 17, 256, 1024, 999]),
+                                              (2, 4, 4, 64, [100, 33]), (130, 8, 2, 128, [300] * 130)])
+def test_paged_decode_attention_mx_operand(dev, A, H, Hkv, D, lens, int8):
+    """The attention output leaving as the quantised operand of the output projection (the split merge writes E4M3
+    bytes and scale words itself) is bit-identical to the stand-alone quantiser applied to the bf16 attention output."""
+    from tesseract_b200 import ops
+    from tesseract_b200.ops import fp8
+    k_pool, v_pool, ks, vs, tables, lens_t = _make_paged(dev, A, Hkv, D, 16, lens, torch.bfloat16, int8)
+    q = torch.randn(A, H, D, device=dev).bfloat16()
+    o = ops.paged_decode_attention(q, k_pool, v_pool, tables, lens_t, None, ks, vs)
+    want_q, want_sf = fp8.quantize_act_mx(o.view(A, H * D))
+    got_q, got_sf = ops.paged_decode_attention_mx(q, k_pool, v_pool, tables, lens_t, None, ks, vs)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert torch.equal(got_q, want_q)
+    assert torch.equal(got_sf[:, :A], want_sf[:, :A])
+
+
+@pytest.mark.parametrize("world,V,rows", [(2, 2048, 5), (8, 128256, 33), (4, 1000, 1)])
+def test_vocab_parallel_argmax_candidates(dev, world, V, rows):
+    """The two kernels of the vocabulary-parallel arg-max with the ranks emulated on one GPU: every rank packs the
+    candidate of its shard, the packed rows are summed in bf16 (what the all-reduce does), the unpack kernel returns
+    the global arg-max -- ties included (lowest index wins)."""
+    from tesseract_b200.serving.engine import argmax_rows, argmax_rows_pack, argmax_rows_unpack, vocab_shard_rows
+    shard = vocab_shard_rows(V, world)
+    assert shard % 128 == 0 and (world - 1) * shard < V <= world * shard
+    logits = torch.randn(rows, V, device=dev).bfloat16()
+    logits[0, 7] = logits[0, V - 3] = 50.0                      # a tie across the first and the last shard
+    if rows > 2:
+        logits[2, V - 1] = 60.0                                 # the winner is the very last column
+    total = torch.zeros(rows, 4 * world, device=dev, dtype=torch.float32)
+    for r in range(world):
+        local = logits[:, r * shard:min(V, (r + 1) * shard)].contiguous()
+        packed = torch.full((rows, 4 * world), 7.0, device=dev, dtype=torch.bfloat16)
+        argmax_rows_pack(local, packed, r, world)
+        total += packed.float()
+    got = argmax_rows_unpack(total.bfloat16(), world, shard)
+    torch.cuda.synchronize()
+    want = argmax_rows(logits)
+    assert torch.equal(got, want) and got[0].item() == 7
+    assert torch.equal(logits.gather(1, got.long()[:, None])[:, 0], logits.max(dim=-1).values)
+
+
 def test_out_of_range_indices_are_redirected_and_reported(dev):
     """Data-dependent indices are checked in the kernels: a token id outside the vocabulary reads row 0, a block-table
     entry outside the pool reads block 0 (never memory outside the tensor), the rows that had valid indices are
