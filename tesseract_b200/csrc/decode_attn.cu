@@ -331,7 +331,12 @@ decode_merge_quant_mx_kernel(const float* __restrict__ part_o, const float* __re
 
 int choose_splits(int A, int Hkv_groups, int max_len) {
   // enough CTAs for ~6 per SM (they are latency-bound and small), but never chunks shorter than 256 keys
-  const int target = sm_count() * 6;
+  static const int per_sm = [] {
+    const char* e = getenv("TESSERACT_DECODE_CTAS_PER_SM");
+    const int v = e ? atoi(e) : 0;
+    return v > 0 && v <= 64 ? v : 6;
+  }();
+  const int target = sm_count() * per_sm;
   int s = (target + A * Hkv_groups - 1) / (A * Hkv_groups);
   const int max_s = max_len / 256 > 0 ? max_len / 256 : 1;
   if (s > max_s) s = max_s;

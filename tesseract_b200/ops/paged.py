@@ -23,9 +23,11 @@ _native.register_signatures({
     "tsb_paged_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
     "tsb_paged_decode_mx": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
     "tsb_paged_decode_scratch_floats": [I, I, I, I],
+    "tsb_paged_decode_static_need_floats": [I, I, I, I, I, I],
     "tsb_kv_append_paged": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
 })
 _native._RESTYPES["tsb_paged_decode_scratch_floats"] = _native.L
+_native._RESTYPES["tsb_paged_decode_static_need_floats"] = _native.L
 
 
 def _gather_request(pool: torch.Tensor, table: torch.Tensor, length: int) -> torch.Tensor:
@@ -87,6 +89,16 @@ def _decode_scratch(device, floats: int) -> torch.Tensor:
     return t
 
 
+def _scratch_floats(A: int, H: int, Hkv: int, D: int, max_len: int, int8: bool) -> int:
+    """fp32 elements of split scratch the kernel's plan asks for (the worst case over all plans when the library
+    has no plan query)."""
+    if hasattr(lib(), "tsb_paged_decode_static_need_floats"):
+        need = int(lib().tsb_paged_decode_static_need_floats(A, H, Hkv, D, max_len, 1 if int8 else 0))
+        if need >= 0:
+            return need
+    return int(lib().tsb_paged_decode_scratch_floats(A, H, D, max_len))
+
+
 def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
                            lens: torch.Tensor, scale: Optional[float] = None, k_scale: Optional[torch.Tensor] = None,
                            v_scale: Optional[torch.Tensor] = None, max_len_hint: int = 0) -> torch.Tensor:
@@ -98,7 +110,7 @@ def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         nb, Hkv, bs, _ = k_pool.shape
         out = torch.empty_like(q)
         max_len = int(max_len_hint) if max_len_hint > 0 else block_tables.shape[1] * bs
-        floats = lib().tsb_paged_decode_scratch_floats(A, H, D, max_len)
+        floats = _scratch_floats(A, H, Hkv, D, max_len, k_scale is not None)
         scratch = _decode_scratch(q.device, floats)
         bt = block_tables if block_tables.dtype == torch.int32 else block_tables.to(torch.int32)
         if bt.stride(1) != 1:
@@ -134,7 +146,7 @@ def paged_decode_attention_mx(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     out = torch.empty_like(q)
     xq, sf = fp8._mx_buffers(A, H * D, q.device)
     max_len = int(max_len_hint) if max_len_hint > 0 else block_tables.shape[1] * bs
-    scratch = _decode_scratch(q.device, lib().tsb_paged_decode_scratch_floats(A, H, D, max_len))
+    scratch = _decode_scratch(q.device, _scratch_floats(A, H, Hkv, D, max_len, k_scale is not None))
     bt = block_tables if block_tables.dtype == torch.int32 else block_tables.to(torch.int32)
     if bt.stride(1) != 1:
         bt = bt.contiguous()
@@ -153,14 +165,39 @@ def paged_decode_attention_int8(q, k_pool, v_pool, k_scale, v_scale, block_table
     return paged_decode_attention(q, k_pool, v_pool, block_tables, lens, scale, k_scale, v_scale)
 
 
+_PREFILL_QUERIES_PER_LAUNCH = 32768   # pseudo-requests per launch (the request index is a grid z coordinate)
+
+
 def paged_prefill_attention(q: torch.Tensor, k_pool, v_pool, block_tables, lens, scale: Optional[float] = None,
                             k_scale=None, v_scale=None) -> torch.Tensor:
-    """Chunked prefill: q [A, S, H, D] against each request's pooled keys (new tokens already appended)."""
-    return paged_attention_ref(q, k_pool, v_pool, block_tables, lens, scale, k_scale, v_scale)
+    """Chunked prefill: q [A, S, H, D] against each request's pooled keys (new tokens already appended).
+
+    On the GPU the pools are read in place by the paged decode kernel (bf16 / fp16 or INT8 with per-token scales;
+    no gathered or dequantised views): new token ``s`` of request ``a`` is a decode query with the request's block
+    table and its own causal length ``lens[a] - S + s + 1``. The reference's kernels for the same op:
+    src/cuda/PagedAttention.cu:275-439."""
+    A, S, H, D = q.shape
+    if not (_native_decode_ok(q, k_pool) and (k_scale is None or k_pool.dtype == torch.int8)) or A * S == 0:
+        return paged_attention_ref(q, k_pool, v_pool, block_tables, lens, scale, k_scale, v_scale)
+    qf = q.reshape(A * S, H, D)
+    if not qf.is_contiguous():
+        qf = qf.contiguous()
+    bt = block_tables if block_tables.dtype == torch.int32 else block_tables.to(torch.int32)
+    ln = lens if lens.dtype == torch.int32 else lens.to(torch.int32)
+    steps = torch.arange(S, device=q.device, dtype=torch.int32)
+    q_lens = (ln[:, None] - (S - 1) + steps[None, :]).clamp_min(0).reshape(-1).contiguous()
+    q_tables = bt.repeat_interleave(S, dim=0)
+    max_len = block_tables.shape[1] * k_pool.shape[2]
+    out = torch.empty_like(qf)
+    for lo in range(0, A * S, _PREFILL_QUERIES_PER_LAUNCH):
+        hi = min(A * S, lo + _PREFILL_QUERIES_PER_LAUNCH)
+        out[lo:hi] = paged_decode_attention(qf[lo:hi], k_pool, v_pool, q_tables[lo:hi], q_lens[lo:hi], scale, k_scale,
+                                            v_scale, max_len_hint=max_len)
+    return out.view(A, S, H, D)
 
 
 def paged_prefill_attention_int8(q, k_pool, v_pool, k_scale, v_scale, block_tables, lens, scale=None):
-    return paged_attention_ref(q, k_pool, v_pool, block_tables, lens, scale, k_scale, v_scale)
+    return paged_prefill_attention(q, k_pool, v_pool, block_tables, lens, scale, k_scale, v_scale)
 
 
 def decode_attention_gqa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None):

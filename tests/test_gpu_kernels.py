@@ -495,6 +495,26 @@ def test_paged_decode_attention(dev, A, H, Hkv, D, bs, lens, int8):
 
 
 @pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("A,S,H,Hkv,D,lens", [(3, 24, 8, 2, 128, [37, 500, 24]), (2, 7, 4, 4, 64, [100, 33]),
+                                                (1, 200, 8, 1, 128, [1000]), (2, 16, 4, 2, 128, [40, 9])])
+def test_paged_prefill_attention_reads_the_pool_in_place(dev, A, S, H, Hkv, D, lens, int8):
+    """Chunked prefill over paged keys (the S new tokens already appended): every new token runs as a decode query
+    with its own causal length, on the kernel that reads the pool (INT8 included) in place. The last case has a
+    request shorter than the chunk: its leading rows see no key and return zeros, as in the reference formulation."""
+    from tesseract_b200 import _native, ops
+    k_pool, v_pool, ks, vs, tables, lens_t = _make_paged(dev, A, Hkv, D, 16, lens, torch.bfloat16, int8)
+    q = torch.randn(A, S, H, D, device=dev).bfloat16()
+    before = _native.launch_count()
+    got = ops.paged_prefill_attention(q, k_pool, v_pool, tables, lens_t, None, ks, vs)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _native.launch_count() > before                         # the native kernel ran, not the gathered fallback
+    ref = ops.paged_attention_ref(q.float(), k_pool, v_pool, tables, lens_t, None, ks, vs)
+    assert got.shape == ref.shape
+    assert (got.float() - ref).abs().max() < 3e-3 * max(1.0, ref.abs().max().item()) + 2e-2, (got.float() - ref).abs().max()
+
+
+@pytest.mark.parametrize("int8", [False, True])
 @pytest.mark.parametrize("A,H,Hkv,D,lens", [(3, 8, 2, 128, [37, 500, 1]), (5, 4, 1, 128, [2000, 17, 256, 1024, 999]),
                                               (2, 4, 4, 64, [100, 33]), (130, 8, 2, 128, [300] * 130)])
 def test_paged_decode_attention_mx_operand(dev, A, H, Hkv, D, lens, int8):
