@@ -998,7 +998,8 @@ def test_mx_linear_from_bf16_operands(dev):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("B,L,d,N", [(2, 1, 64, 16), (1, 50, 96, 8), (2, 300, 128, 16), (1, 1000, 64, 32)])
+@pytest.mark.parametrize("B,L,d,N", [(2, 1, 64, 16), (1, 50, 96, 8), (2, 300, 128, 16), (1, 1000, 64, 32),
+                                      (2, 300, 1024, 16), (1, 333, 2080, 8), (3, 65, 704, 16)])   # single-pass kernel
 def test_selective_scan_and_conv1d(dev, dtype, B, L, d, N):
     from tesseract_b200.ops import ssm
     g = torch.Generator(device=dev).manual_seed(L + N)
