@@ -6,8 +6,8 @@ Two artefacts, both placed inside the package so that they travel with a source 
   ``sm_100a`` only (``-gencode arch=compute_100a,code=sm_100a -lineinfo``) and linked into one
   shared library that exports a C ABI (loaded with ctypes; no torch headers, so a full rebuild takes
   well under a minute).
-* ``tesseract_b200/_lib/_tsb_host*.so`` -- the host runtime (safetensors, tokenizer, sampler, regex
-  automaton, block allocator, scheduler core, CPU GEMV), a pybind11 module built from ``csrc/host``.
+* ``tesseract_b200/_lib/_tsb_host*.so`` -- the host runtime (safetensors reads, BPE merge loop, sampler, regex
+  compiler and token mask, block allocator, CPU GEMV and GEMM), a pybind11 module built from ``csrc/host``.
 
 ``python -m tesseract_b200.build`` rebuilds whatever is out of date (``--force`` rebuilds everything).
 """

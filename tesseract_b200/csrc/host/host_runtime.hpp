@@ -91,6 +91,16 @@ std::pair<std::string, int64_t> safetensors_header(const std::string& path);
 void token_mask(const int32_t* table, int64_t num_states, int32_t state, const uint8_t* bytes, const int64_t* offsets,
                 int64_t n_tokens, uint8_t* allowed);
 
+// ---- byte-level regex -> complete DFA (regex.cpp). table: states x 256 next-state ids (-1 = dead), state 0 is the
+// start state, states numbered in breadth-first discovery order; accepting: one flag per state. Throws
+// std::invalid_argument on a malformed pattern, std::length_error when the DFA would exceed max_states.
+struct CompiledRegex {
+  std::vector<int32_t> table;
+  std::vector<uint8_t> accepting;
+  int64_t num_nfa_states = 0;
+};
+CompiledRegex compile_regex(const std::string& pattern, int64_t max_states);
+
 // ---- CPU FP32 GEMM (gemm_f32.cpp): C[M, N] = A[M, K] * op(B); b_nk = B stored [N, K] (a Linear weight)
 bool gemm_avx2_supported();
 int gemm_num_threads(int64_t M, int64_t N, int64_t K, int requested);

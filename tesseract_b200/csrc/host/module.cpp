@@ -70,6 +70,18 @@ PYBIND11_MODULE(_tsb_host, m) {
           return out;
         });
 
+  m.def("compile_regex",
+        [](py::bytes pattern, int64_t max_states) {
+          const CompiledRegex r = compile_regex(std::string(pattern), max_states);
+          const int64_t S = static_cast<int64_t>(r.accepting.size());
+          py::array_t<int32_t> table({S, static_cast<int64_t>(256)});
+          std::copy(r.table.begin(), r.table.end(), table.mutable_data());
+          py::array_t<uint8_t> acc(S);
+          std::copy(r.accepting.begin(), r.accepting.end(), acc.mutable_data());
+          return py::make_tuple(table, acc, r.num_nfa_states);
+        },
+        py::arg("pattern"), py::arg("max_states") = 65536);
+
   m.def("gemm_avx2_supported", &gemm_avx2_supported);
   m.def("gemm_num_threads", &gemm_num_threads, py::arg("M"), py::arg("N"), py::arg("K"), py::arg("requested") = 0);
   m.def("gemm_f32",

@@ -261,15 +261,63 @@ class _Parser:
         return frozenset(_ALL - items) if neg else frozenset(items)
 
 
+MAX_DFA_STATES = 65536
+
+
+def _host_module():
+    from .sampler import _host_module as hm
+    return hm()
+
+
 class RegexAutomaton(ByteAutomaton):
-    def __init__(self, pattern: str):
+    """Anchored byte-level regex. With the native host runtime the pattern is compiled in C++ (csrc/host/regex.cpp)
+    into a complete DFA table -- states numbered breadth first, state 0 the start state -- and ``step`` is a table
+    lookup; the token mask of a vocabulary is then one native walk over all token bytes (``GrammarConstraint``).
+    Without it (or when the DFA would exceed ``MAX_DFA_STATES``) the Python implementation below runs lazily:
+    a DFA state is an epsilon-closed set of NFA states, interned on first sight. ``dfa_table()`` of the Python
+    implementation builds the same table as the native compiler, entry for entry."""
+
+    def __init__(self, pattern: str, native: Optional[bool] = None):
         self.pattern = pattern
+        self._table: Optional[np.ndarray] = None        # int32 [states, 256], -1 = dead (native mode)
+        self._accepting: Optional[np.ndarray] = None
+        host = _host_module() if native in (None, True) else None
+        if native is True and host is None:
+            raise RuntimeError("RegexAutomaton: the native host runtime is not available")
+        if host is not None and hasattr(host, "compile_regex"):
+            try:
+                self._table, self._accepting, _ = host.compile_regex(pattern.encode("utf-8"), MAX_DFA_STATES)
+                return
+            except ValueError as e:
+                if "max_states" not in str(e):
+                    raise                                  # a malformed pattern: the same error class as the twin
         self._nfa = _Nfa()
         self._start_nfa, self._accept_nfa = _Parser(pattern, self._nfa).parse()
         self._ids: Dict[FrozenSet[int], int] = {}
         self._sets: List[FrozenSet[int]] = []
         self._memo: Dict[Tuple[int, int], int] = {}
         self._start = self._intern(self._closure({self._start_nfa}))
+
+    @property
+    def is_native(self) -> bool:
+        return self._table is not None
+
+    def dfa_table(self, max_states: int = MAX_DFA_STATES) -> Tuple[np.ndarray, np.ndarray]:
+        """The complete DFA as ``(table int32 [states, 256], accepting uint8 [states])``: state 0 is the start state,
+        states are numbered in breadth-first discovery order with the bytes visited 0 .. 255."""
+        if self._table is not None:
+            return self._table, self._accepting
+        fresh = RegexAutomaton(self.pattern, native=False)       # its lazy numbering starts from scratch
+        rows: List[List[int]] = []
+        q = 0
+        while q < len(fresh._sets):
+            if len(fresh._sets) > max_states:
+                raise ValueError("regex: more DFA states than max_states")
+            rows.append([fresh.step(q, b) for b in range(256)])
+            q += 1
+        table = np.asarray(rows, dtype=np.int32).reshape(len(rows), 256)
+        acc = np.asarray([1 if fresh.accepting(s) else 0 for s in range(len(rows))], dtype=np.uint8)
+        return table, acc
 
     def _closure(self, states) -> FrozenSet[int]:
         seen, stack = set(states), list(states)
@@ -290,11 +338,13 @@ class RegexAutomaton(ByteAutomaton):
         return i
 
     def start(self) -> int:
-        return self._start
+        return 0 if self._table is not None else self._start
 
     def step(self, state: int, byte: int) -> int:
         if state == K_DEAD:
             return K_DEAD
+        if self._table is not None:
+            return int(self._table[state, byte])
         key = (state, byte)
         hit = self._memo.get(key)
         if hit is not None:
@@ -309,14 +359,19 @@ class RegexAutomaton(ByteAutomaton):
         return res
 
     def accepting(self, state: int) -> bool:
-        return state != K_DEAD and self._accept_nfa in self._sets[state]
+        if state == K_DEAD:
+            return False
+        if self._table is not None:
+            return bool(self._accepting[state])
+        return self._accept_nfa in self._sets[state]
 
     def matches(self, s) -> bool:
         data = s.encode("utf-8") if isinstance(s, str) else bytes(s)
         return self.accepting(self.walk(self.start(), data))
 
     def num_dfa_states(self) -> int:
-        return len(self._sets)
+        """States of the complete DFA (native mode) or the states visited so far (lazy mode)."""
+        return int(self._table.shape[0]) if self._table is not None else len(self._sets)
 
 
 class GrammarConstraint:
@@ -326,6 +381,12 @@ class GrammarConstraint:
         self.eos_id = eos_id
         self.state = automaton.start()
         self._mask_cache: Dict[int, np.ndarray] = {}
+        # native mask: all token bytes in one buffer with offsets, walked over the DFA table in C++
+        self._packed: Optional[Tuple[bytes, np.ndarray]] = None
+        if getattr(automaton, "is_native", False) and _host_module() is not None:
+            offs = np.zeros(len(self.token_bytes) + 1, dtype=np.int64)
+            np.cumsum([len(b) for b in self.token_bytes], out=offs[1:])
+            self._packed = (b"".join(self.token_bytes), offs)
 
     @classmethod
     def from_tokenizer(cls, automaton: ByteAutomaton, tokenizer, eos_id: Optional[int] = None) -> "GrammarConstraint":
@@ -338,6 +399,12 @@ class GrammarConstraint:
 
     def allowed_mask(self) -> np.ndarray:
         m = self._mask_cache.get(self.state)
+        if m is None and self._packed is not None:
+            table, _ = self.automaton.dfa_table()
+            m = _host_module().token_mask(table, int(self.state), self._packed[0], self._packed[1]).astype(bool)
+            if 0 <= self.eos_id < m.shape[0]:
+                m[self.eos_id] = self.automaton.accepting(self.state)
+            self._mask_cache[self.state] = m
         if m is None:
             m = np.zeros(len(self.token_bytes), dtype=bool)
             for i, tb in enumerate(self.token_bytes):

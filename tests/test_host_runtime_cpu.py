@@ -104,3 +104,64 @@ def test_token_mask_kernel():
     offs = np.cumsum([0] + [len(t) for t in toks]).astype(np.int64)
     mask = host.token_mask(table, 0, b"".join(toks), offs)
     assert mask.tolist() == [1, 0, 0, 1, 0]
+
+
+REGEXES = [r"-?(0|[1-9]\d*)(\.\d+)?", r"(yes|no|maybe)", r"[a-c]{2,3}x?", r"[^0-9]+\s\w{2}", r"a{2,}", r"a{0,2}b{3}",
+           r"\{\"name\": \"[a-z]+\", \"age\": [1-9]\d?\}", r"[]a-]+", r"(ab|a)(bc|c)*", r"\D\W\S.", r"héllo[é-ü]?",
+           r"(\+|-)?\d{1,3}(,\d{3})*", r"[\d\s]+|x", r"((a|b)*c){2}", r""]
+
+
+@pytest.mark.parametrize("pattern", REGEXES)
+def test_regex_compiler_builds_the_same_dfa_as_the_python_twin(pattern):
+    """csrc/host/regex.cpp against models/structured.py: the complete DFA tables are equal entry for entry (same
+    breadth-first numbering), so are the accepting flags."""
+    from tesseract_b200.models.structured import RegexAutomaton
+    nat, twin = RegexAutomaton(pattern, native=True), RegexAutomaton(pattern, native=False)
+    assert nat.is_native and not twin.is_native
+    t_nat, a_nat = nat.dfa_table()
+    t_py, a_py = twin.dfa_table()
+    assert t_nat.shape == t_py.shape and np.array_equal(t_nat, t_py) and np.array_equal(a_nat, a_py)
+    assert nat.num_dfa_states() == t_py.shape[0]
+
+
+def test_regex_compiler_errors_and_matching_agree_with_the_twin():
+    from tesseract_b200.models.structured import K_DEAD, RegexAutomaton
+    for bad in ["(ab", "a)", "*a", "a{2", "a{3,1}", "[abc", "a\\", "[z-a]"]:
+        with pytest.raises(ValueError):
+            RegexAutomaton(bad, native=True)
+        with pytest.raises((ValueError, IndexError)):
+            RegexAutomaton(bad, native=False)
+    rng = np.random.default_rng(7)
+    alphabet = list(b"ab01 .-,x_c\xc3\xa9")
+    for pattern in REGEXES:
+        nat, twin = RegexAutomaton(pattern, native=True), RegexAutomaton(pattern, native=False)
+        for _ in range(200):
+            s = bytes(rng.choice(alphabet, size=int(rng.integers(0, 9))).tolist())
+            assert nat.matches(s) == twin.matches(s), (pattern, s)
+            live_n = nat.walk(nat.start(), s) != K_DEAD
+            live_t = twin.walk(twin.start(), s) != K_DEAD
+            assert live_n == live_t, (pattern, s)
+
+
+def test_grammar_mask_native_walk_equals_python_loop(monkeypatch):
+    """The vocabulary mask from one native walk over all token bytes equals the per-token Python loop, state by state
+    along a constrained generation."""
+    from tesseract_b200.models.structured import GrammarConstraint, RegexAutomaton
+    rng = np.random.default_rng(1)
+    pieces = [b"", b"0", b"1", b"12", b"7.", b".", b".5", b"-", b"-3", b"a", b"1a", b"00", b"<eos>"]
+    vocab = pieces + [bytes(rng.choice(list(b"0123456789.-a"), size=int(rng.integers(1, 5))).tolist()) for _ in range(300)]
+    eos = 12
+    pattern = r"-?(0|[1-9]\d*)(\.\d+)?"
+    g_nat = GrammarConstraint(RegexAutomaton(pattern, native=True), vocab, eos_id=eos)
+    g_py = GrammarConstraint(RegexAutomaton(pattern, native=False), vocab, eos_id=eos)
+    assert g_nat._packed is not None and g_py._packed is None
+    for step in range(12):
+        m_nat, m_py = g_nat.allowed_mask(), g_py.allowed_mask()
+        assert np.array_equal(m_nat, m_py), step
+        allowed = np.nonzero(m_py)[0]
+        allowed = allowed[allowed != eos]
+        if allowed.size == 0:
+            break
+        tok = int(allowed[int(rng.integers(0, allowed.size))])
+        g_nat.accept(tok)
+        g_py.accept(tok)
