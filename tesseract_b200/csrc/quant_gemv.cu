@@ -124,6 +124,51 @@ gemv_w4g_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const fl
   }
 }
 
+// Batches above kMaxM rows: the packed weights are widened to bf16 once per call and the product runs on the tcgen05
+// GEMM (the reference dequantises into its library GEMM the same way, src/cuda/DequantMatMul.cu:216-258). One thread
+// per 16 packed bytes: 16 INT8 values of one row, or 32 INT4 values of one scale group.
+__global__ void __launch_bounds__(256)
+dequant_w8_bf16_kernel(const int8_t* __restrict__ w, const float* __restrict__ scale, __nv_bfloat16* __restrict__ out,
+                       long long nvec, int K) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += stride) {
+    const long long e0 = i * 16;
+    const float s = scale[e0 / K];
+    const uint4 raw = *reinterpret_cast<const uint4*>(w + e0);
+    const int8_t* q = reinterpret_cast<const int8_t*>(&raw);
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = pack_bf16x2(static_cast<float>(q[2 * j]) * s, static_cast<float>(q[2 * j + 1]) * s);
+    *reinterpret_cast<uint4*>(out + e0) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(out + e0 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+dequant_w4g_bf16_kernel(const uint8_t* __restrict__ w, const float* __restrict__ scale, __nv_bfloat16* __restrict__ out,
+                        long long nvec, int K, int group) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec; i += stride) {
+    const long long e0 = i * 32;                       // 32 values = 16 packed bytes, inside one group (group % 32 == 0)
+    const long long row = e0 / K;
+    const int k = static_cast<int>(e0 - row * K);
+    const float gs = scale[row * (K / group) + k / group];
+    const uint4 raw = *reinterpret_cast<const uint4*>(w + e0 / 2);
+    const uint8_t* q = reinterpret_cast<const uint8_t*>(&raw);
+    uint32_t o[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      int lo = q[j] & 0xF, hi = q[j] >> 4;             // low nibble = even k; two's complement nibbles
+      lo = lo > 7 ? lo - 16 : lo;
+      hi = hi > 7 ? hi - 16 : hi;
+      o[j] = pack_bf16x2(static_cast<float>(lo) * gs, static_cast<float>(hi) * gs);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<uint4*>(out + e0 + 8 * j) = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+  }
+}
+
 template <typename T>
 int launch_w8(const void* x, const void* w, const float* scale, const void* bias, void* y, int M, int N, int K,
               cudaStream_t s) {
@@ -187,4 +232,33 @@ TSB_EXPORT int tsb_gemv_w4g(const void* x, const void* q_weight, const float* sc
     case 2: return launch_w4<__half>(x, q_weight, scale, bias, y, M, N, K, group, s);
     default: return -2;
   }
+}
+
+// out [N, K] bf16 = q_weight [N, K] int8 * scale[n]. K % 16 == 0; q_weight and out 16-byte aligned.
+TSB_EXPORT int tsb_dequant_w8_bf16(const void* q_weight, const float* scale, void* out, long long N, int K, void* stream) {
+  using namespace tsb;
+  if (N <= 0 || K <= 0 || K % 16 || !q_weight || !scale || !out) return -2;
+  if ((reinterpret_cast<uintptr_t>(q_weight) | reinterpret_cast<uintptr_t>(out)) & 15) return -2;
+  const long long nvec = N * K / 16;
+  long long blocks = (nvec + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  dequant_w8_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const int8_t*>(q_weight), scale, static_cast<__nv_bfloat16*>(out), nvec, K);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out [N, K] bf16 = INT4 nibbles [N, K / 2] * scale[n, k / group]. K % 32 == 0, group % 32 == 0, K % group == 0.
+TSB_EXPORT int tsb_dequant_w4g_bf16(const void* q_weight, const float* scale, void* out, long long N, int K, int group,
+                                    void* stream) {
+  using namespace tsb;
+  if (N <= 0 || K <= 0 || K % 32 || group <= 0 || group % 32 || K % group || !q_weight || !scale || !out) return -2;
+  if ((reinterpret_cast<uintptr_t>(q_weight) | reinterpret_cast<uintptr_t>(out)) & 15) return -2;
+  const long long nvec = N * K / 32;
+  long long blocks = (nvec + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  dequant_w4g_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(q_weight), scale, static_cast<__nv_bfloat16*>(out), nvec, K, group);
+  return static_cast<int>(cudaGetLastError());
 }

@@ -24,6 +24,8 @@ P, I, L, F = _native.P, _native.I, _native.L, _native.F
 _native.register_signatures({
     "tsb_gemv_w8": [P, P, P, P, P, I, I, I, I, P],
     "tsb_gemv_w4g": [P, P, P, P, P, I, I, I, I, I, P],
+    "tsb_dequant_w8_bf16": [P, P, P, L, I, P],
+    "tsb_dequant_w4g_bf16": [P, P, P, L, I, I, P],
 })
 
 
@@ -78,6 +80,12 @@ def _small_m(x2: torch.Tensor) -> bool:
     return x2.is_cuda and x2.shape[0] <= 16 and x2.dtype in (torch.bfloat16, torch.float16, torch.float32)
 
 
+def _large_m_native(x2: torch.Tensor, N: int, K: int) -> bool:
+    """More rows than the GEMV kernels take, bf16 on the GPU, shapes the tcgen05 GEMM accepts (16-byte rows)."""
+    return (x2.is_cuda and x2.dtype == torch.bfloat16 and x2.shape[0] > 16 and N % 8 == 0 and K % 8 == 0
+            and not (torch.is_grad_enabled() and x2.requires_grad) and _native.available())
+
+
 def dequantize_matmul_int8(x: torch.Tensor, q_weight: torch.Tensor, weight_scale: torch.Tensor) -> torch.Tensor:
     """x [..., in] @ dequant(q_weight [out, in])^T (src/ops/cpu/DequantMatMul.cpp)."""
     x2 = x.reshape(-1, x.shape[-1])
@@ -90,6 +98,13 @@ def dequantize_matmul_int8(x: torch.Tensor, q_weight: torch.Tensor, weight_scale
         check(lib().tsb_gemv_w8(xc.data_ptr(), q_weight.data_ptr(), weight_scale.data_ptr(), None, y.data_ptr(),
                                 x2.shape[0], N, K, _native.dtype_code(x.dtype), stream_ptr(x.device)), "tsb_gemv_w8")
         return y.view(*x.shape[:-1], N)
+    if _large_m_native(x2, N, K) and K % 16 == 0 and hasattr(lib(), "tsb_dequant_w8_bf16"):
+        # widen once to bf16 with the native kernel, multiply on the tcgen05 GEMM
+        w = torch.empty((N, K), device=x.device, dtype=torch.bfloat16)
+        check(lib().tsb_dequant_w8_bf16(q_weight.data_ptr(), weight_scale.data_ptr(), w.data_ptr(), N, K,
+                                        stream_ptr(x.device)), "tsb_dequant_w8_bf16")
+        from ..ops.gemm import gemm_bf16
+        return gemm_bf16(x2.contiguous(), w).view(*x.shape[:-1], N)
     w = (q_weight.float() * weight_scale[:, None].float()).to(x.dtype)
     return torch.nn.functional.linear(x, w)
 
@@ -108,6 +123,13 @@ def dequantize_matmul_int4_group(x: torch.Tensor, q_weight: torch.Tensor, weight
                                  x2.shape[0], N, K, group_size, _native.dtype_code(x.dtype), stream_ptr(x.device)),
               "tsb_gemv_w4g")
         return y.view(*x.shape[:-1], N)
+    if (_large_m_native(x2, N, K) and K % 32 == 0 and group_size % 32 == 0 and K % group_size == 0
+            and hasattr(lib(), "tsb_dequant_w4g_bf16")):
+        w = torch.empty((N, K), device=x.device, dtype=torch.bfloat16)
+        check(lib().tsb_dequant_w4g_bf16(q_weight.data_ptr(), weight_scale.data_ptr(), w.data_ptr(), N, K, group_size,
+                                         stream_ptr(x.device)), "tsb_dequant_w4g_bf16")
+        from ..ops.gemm import gemm_bf16
+        return gemm_bf16(x2.contiguous(), w).view(*x.shape[:-1], N)
     w = unpack_int4_group(q_weight, weight_scale, group_size).to(x.dtype)
     return torch.nn.functional.linear(x, w)
 

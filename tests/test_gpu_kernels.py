@@ -1041,6 +1041,37 @@ def test_quantized_gemv(dev, dtype, M):
     assert _rel_err(q4(xd), xd.float() @ w4.t() + q4.bias.float()) < tol
 
 
+@pytest.mark.parametrize("M", [17, 200, 1024])
+def test_quantized_linear_large_batch_runs_on_the_native_gemm(dev, M):
+    """More rows than the GEMV kernels take: the packed weights are widened to bf16 by the native kernel (bit-identical
+    to the reference dequantisation) and multiplied on the tcgen05 GEMM."""
+    from tesseract_b200 import _native, quant
+    from tesseract_b200.quant import unpack_int4_group
+    g = torch.Generator().manual_seed(M)
+    w = torch.randn(768, 1024, generator=g)
+    q8, s8 = (t.to(dev) for t in quant.pack_int8_symmetric(w))
+    q4, s4 = (t.to(dev) for t in quant.pack_int4_group(w, 128))
+    x = torch.randn(M, 1024, generator=g).to(dev).bfloat16()
+    w8 = torch.empty(768, 1024, device=dev, dtype=torch.bfloat16)
+    _native.check(_native.lib().tsb_dequant_w8_bf16(q8.data_ptr(), s8.data_ptr(), w8.data_ptr(), 768, 1024,
+                                                    _native.stream_ptr(x.device)), "tsb_dequant_w8_bf16")
+    assert torch.equal(w8, (q8.float() * s8[:, None].float()).bfloat16())
+    w4 = torch.empty(768, 1024, device=dev, dtype=torch.bfloat16)
+    _native.check(_native.lib().tsb_dequant_w4g_bf16(q4.data_ptr(), s4.data_ptr(), w4.data_ptr(), 768, 1024, 128,
+                                                     _native.stream_ptr(x.device)), "tsb_dequant_w4g_bf16")
+    assert torch.equal(w4, unpack_int4_group(q4.cpu(), s4.cpu(), 128).to(dev).bfloat16())
+    before = _native.launch_count()
+    with torch.no_grad():
+        y8 = quant.dequantize_matmul_int8(x, q8, s8)
+        y4 = quant.dequantize_matmul_int4_group(x, q4, s4, 128)
+    torch.cuda.synchronize()
+    _status_ok()
+    assert _native.launch_count() >= before + 4                 # two dequantisers, two GEMMs
+    assert _rel_err(y8, x.float() @ w8.float().t()) < 1e-2
+    assert _rel_err(y4, x.float() @ w4.float().t()) < 1e-2
+
+
+
 def test_moe_router_and_sort(dev):
     from tesseract_b200.nn.moe import route_topk
     from tesseract_b200.ops import moe
