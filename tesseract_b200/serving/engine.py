@@ -75,7 +75,7 @@ class _Req:
     generated: int = 0
     finished: bool = False
     blocks: List[int] = field(default_factory=list)
-    table_row: Optional[np.ndarray] = None
+    slot: int = -1                 # row of the engine's host-side state arrays while the request holds KV blocks
     t_submit: float = 0.0
     t_first: float = 0.0
     t_done: float = 0.0
@@ -234,6 +234,14 @@ class ServingEngine:
         self.use_cuda_graph = use_cuda_graph
         self._graphs: Dict[int, dict] = {}
         self._host_inputs: Dict[int, torch.Tensor] = {}
+        # Host-side state of the resident requests as arrays indexed by a stable slot (block table, block count, last
+        # token, length): a decode step packs its inputs with a few gathers instead of a Python loop over requests.
+        cap = self.cfg.max_batch_size
+        self._tab = np.zeros((cap, self.max_blocks), dtype=np.int32)
+        self._nblk = np.zeros(cap, dtype=np.int32)
+        self._last = np.zeros(cap, dtype=np.int32)
+        self._len = np.zeros(cap, dtype=np.int32)
+        self._free_slots = list(range(cap - 1, -1, -1))
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "prefill_s": 0.0, "decode_s": 0.0, "decode_gpu_s": 0.0,
                       "decode_steps": 0}
         self._step_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
@@ -388,17 +396,23 @@ class ServingEngine:
         return (n + self.cfg.block_size - 1) // self.cfg.block_size
 
     def _grow(self, r: _Req, new_len: int) -> None:
-        if r.table_row is None:
-            r.table_row = np.zeros(self.max_blocks, dtype=np.int32)
+        if r.slot < 0:
+            r.slot = self._free_slots.pop()
+            self._tab[r.slot] = 0
+            self._nblk[r.slot] = 0
         while len(r.blocks) < self._blocks_for(new_len):
             b = self.allocator.allocate()
-            r.table_row[len(r.blocks)] = b
+            self._tab[r.slot, len(r.blocks)] = b
             r.blocks.append(b)
+        self._nblk[r.slot] = len(r.blocks)
 
     def _retire(self, r: _Req) -> None:
         for b in r.blocks:
             self.allocator.free(b)
         r.blocks = []
+        if r.slot >= 0:
+            self._free_slots.append(r.slot)
+            r.slot = -1
         r.finished = True
         r.t_done = time.perf_counter()
 
@@ -595,6 +609,9 @@ class ServingEngine:
             return
         r.tokens.append(tok)
         r.generated += 1
+        if r.slot >= 0:
+            self._last[r.slot] = tok
+            self._len[r.slot] = len(r.tokens)
         if (r.gen.eos_token_id >= 0 and tok == r.gen.eos_token_id) or r.generated >= r.gen.max_new_tokens:
             self._retire(r)
 
@@ -614,15 +631,18 @@ class ServingEngine:
             buf = torch.zeros((A, 4 + self.max_blocks), dtype=torch.int32).pin_memory()
             self._host_inputs[A] = buf
         arr = buf.numpy()
-        for r in reqs:
-            self._grow(r, len(r.tokens))
         if n:
-            pos = np.fromiter((len(r.tokens) - 1 for r in reqs), dtype=np.int32, count=n)
-            arr[:n, 0] = np.fromiter((r.tokens[-1] for r in reqs), dtype=np.int32, count=n)
+            slots = np.fromiter((r.slot for r in reqs), dtype=np.int64, count=n)
+            lens = self._len[slots]
+            short = np.nonzero((lens + bs - 1) // bs > self._nblk[slots])[0]    # requests that cross into a new block
+            for i in short:
+                self._grow(reqs[i], int(lens[i]))
+            pos = lens - 1
+            arr[:n, 0] = self._last[slots]
             arr[:n, 1] = pos
-            arr[:n, 4:] = np.stack([r.table_row for r in reqs])
-            arr[:n, 2] = arr[np.arange(n), 4 + pos // bs] * bs + pos % bs
-            arr[:n, 3] = pos + 1
+            arr[:n, 4:] = self._tab[slots]
+            arr[:n, 2] = self._tab[slots, pos // bs] * bs + pos % bs
+            arr[:n, 3] = lens
         arr[n:, 0:2] = 0
         arr[n:, 2] = -1
         arr[n:, 3] = 0
