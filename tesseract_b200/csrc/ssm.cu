@@ -296,9 +296,7 @@ int run_scan(const void* u, const void* delta, const float* A, const void* Bm, c
     static const int stream_on = [] { const char* e = getenv("TESSERACT_SCAN_STREAM"); return e ? atoi(e) : 1; }();
     if (stream_on) {
       constexpr int smem = quad_smem_bytes<T>();
-      static const cudaError_t attr = cudaFuncSetAttribute(scan_stream_quad_kernel<T>,
-                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (attr != cudaSuccess) return static_cast<int>(attr);
+      static_assert(smem <= 48 * 1024, "within the default dynamic shared-memory limit: no per-device attribute needed");
       dim3 grid((d + kQuadCh - 1) / kQuadCh, Bsz);
       scan_stream_quad_kernel<T><<<grid, kQuadThreads, smem, s>>>(u_, dl, A, b_, c_, Dv, state_in, y_, state_out, L, d, N);
       return static_cast<int>(cudaGetLastError());

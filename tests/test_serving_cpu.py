@@ -229,3 +229,39 @@ def test_mt19937_64_known_values():
     for _ in range(9996):
         g.next_u64()
     assert g.next_u64() == 9981545732273789042   # 10000th draw of a default-seeded std::mt19937_64
+
+
+def test_vocab_shard_rows_cover_the_vocabulary_in_whole_scale_blocks():
+    """Vocabulary-parallel LM head: shards of a multiple of 128 rows (fp8 block scales stay whole), every rank holds
+    some rows, together they cover the vocabulary; too small a vocabulary keeps the head replicated (0)."""
+    from tesseract_b200.serving.engine import vocab_shard_rows
+    for vocab in (2048, 32000, 128256, 151936, 1000, 257):
+        for world in (2, 4, 8):
+            shard = vocab_shard_rows(vocab, world)
+            if shard == 0:
+                assert (world - 1) * ((vocab + world * 128 - 1) // (world * 128) * 128) >= vocab
+                continue
+            assert shard % 128 == 0 and (world - 1) * shard < vocab <= world * shard
+            sizes = [min(vocab, (r + 1) * shard) - r * shard for r in range(world)]
+            assert all(s > 0 for s in sizes) and sum(sizes) == vocab
+    assert vocab_shard_rows(128, 2) == 0 and vocab_shard_rows(128256, 8) == 16128
+
+
+def test_paged_prefill_every_new_token_is_a_decode_query_with_its_own_length():
+    """The formulation the GPU path of ``paged_prefill_attention`` uses -- new token s of a request attends the first
+    len - S + s + 1 pooled keys through the same block table -- equals the chunked-prefill reference."""
+    from tesseract_b200 import ops
+    torch.manual_seed(3)
+    A, S, H, Hkv, D, bs = 2, 5, 4, 2, 16, 4
+    lens = torch.tensor([13, 5])
+    nb = 12
+    k_pool, v_pool = torch.randn(nb, Hkv, bs, D), torch.randn(nb, Hkv, bs, D)
+    tables = torch.tensor([[0, 1, 2, 3], [4, 5, 0, 0]])
+    q = torch.randn(A, S, H, D)
+    ref = ops.paged_attention_ref(q, k_pool, v_pool, tables, lens)
+    steps = torch.arange(S)
+    q_lens = (lens[:, None] - (S - 1) + steps[None, :]).clamp_min(0).reshape(-1)
+    q_tables = tables.repeat_interleave(S, dim=0)
+    one = ops.paged_attention_ref(q.reshape(A * S, 1, H, D), k_pool, v_pool, q_tables, q_lens).view(A, S, H, D)
+    assert torch.allclose(one, ref, atol=1e-5)
+    assert torch.allclose(ops.paged_prefill_attention(q, k_pool, v_pool, tables, lens), ref, atol=1e-5)
