@@ -10,7 +10,7 @@
 //   pass 2  per (batch, channel, state): walk the chunks, turning local end states into chunk START states;
 //   pass 3  per (batch, chunk, channel): rescan from the start state and emit y.
 // Short sequences (decode steps, L <= 64) run as one pass with the state in registers; wide layers (batch x channels
-// >= 2048, N <= 16) run the whole sequence as one pass too (scan_stream_quad_kernel below). The reference has the same
+// >= 2048, N <= 16) run the whole sequence as one pass too (scan_stream_pair_kernel below). The reference has the same
 // three-pass structure with chunk 128 for fp32 prefill only (src/cuda/SelectiveScan.cu:95-228, N <= 32) and a
 // one-thread-per-output conv (src/cuda/CausalConv1d.cu:16-36).
 #include "common.cuh"
@@ -134,16 +134,16 @@ scan_output_kernel(const T* u, const T* delta, const float* A, const T* Bm, cons
 // Single pass for wide layers. The recurrence costs one exponential per (step, channel, state); the chunked passes
 // above evaluate every one twice, this kernel once, with the state in registers for the whole sequence. A thread's
 // steps are serial, so its inputs must be on chip before it gets there: u and delta travel through a four-stage
-// shared-memory ring of 32-step tiles filled by cp.async (three tiles in flight per CTA). B_t and C_t are shared by
+// shared-memory ring of 16-step tiles filled by cp.async (three tiles in flight per CTA). B_t and C_t are shared by
 // all channels of a batch row: staged as floats, double buffered, the next tile held in registers while the current
 // one is consumed. exp(delta * A) = 2^(delta * A * log2 e) with the constant folded into A.
-// Four lanes share a channel, each owning four of the (at most 16) states: one warp per scheduler (a lane per channel)
-// issues an instruction only every three cycles (dependent multiply-adds, the exponential unit's issue interval,
-// shared-memory latency); four times the warps for the same number of exponentials fill those gaps, and the four
-// partial sums of y meet in two shuffles. 32 channels per CTA, 40 KB of shared memory in fp32, several CTAs per SM.
-// Measured on [4, 4096, 4096, 16] fp32: 0.72 ms against 2.6 ms for the three chunked passes; the exponential unit is
-// 35 % busy, the rest is instruction issue (about 65 instructions per warp and step).
-constexpr int kStreamTile = 32;
+// Two lanes share a channel, each owning eight of the (at most 16) states: a lane per channel leaves one warp per
+// scheduler, which issues an instruction only every three cycles (dependent multiply-adds, the exponential unit's
+// issue interval, shared-memory latency); two lanes keep the instruction count per channel and step and double the
+// warps (four lanes double the instructions too: measured slower). The two partial sums of y meet in one shuffle; a
+// full tile runs as straight-line code. 64 channels per CTA, 36 KB of shared memory in fp32.
+// Measured on [4, 4096, 4096, 16] fp32: 0.66 ms against 2.6 ms for the three chunked passes (four lanes: 0.72 ms, one
+// lane: 0.74 - 0.78 ms); the exponential unit is about 35 % busy.
 constexpr int kStreamStages = 4;
 
 __device__ __forceinline__ void scan_cp_async16(void* dst_smem, const void* src, int src_bytes) {
@@ -151,57 +151,58 @@ __device__ __forceinline__ void scan_cp_async16(void* dst_smem, const void* src,
 }
 
 // Requires d * sizeof(T) % 16 == 0 and 16-byte aligned u / delta (every 16-byte piece of a row is whole).
-constexpr int kQuadThreads = 128;
-constexpr int kQuadCh = kQuadThreads / 4;
+constexpr int kPairTile = 16;
+constexpr int kPairThreads = 128;
+constexpr int kPairCh = kPairThreads / 2;
 
 template <typename T>
-constexpr int quad_smem_bytes() {
-  return 2 * kStreamStages * kStreamTile * kQuadCh * static_cast<int>(sizeof(T)) + 2 * 2 * kStreamTile * 16 * 4;
+constexpr int pair_smem_bytes() {
+  return 2 * kStreamStages * kPairTile * kPairCh * static_cast<int>(sizeof(T)) + 2 * 2 * kPairTile * 16 * 4;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kQuadThreads)
-scan_stream_quad_kernel(const T* __restrict__ u, const T* __restrict__ delta, const float* __restrict__ A,
+__global__ void __launch_bounds__(kPairThreads)
+scan_stream_pair_kernel(const T* __restrict__ u, const T* __restrict__ delta, const float* __restrict__ A,
                         const T* __restrict__ Bm, const T* __restrict__ Cm, const float* __restrict__ Dv,
                         const float* __restrict__ state_in, T* __restrict__ y, float* __restrict__ state_out, int L,
                         int d, int N) {
-  constexpr int NMAX = 16;
+  constexpr int NMAX = 16, SPL = 8;
   extern __shared__ __align__(16) uint8_t stream_smem[];
-  constexpr int kStageElems = kStreamTile * kQuadCh;
+  constexpr int kStageElems = kPairTile * kPairCh;
   T* su = reinterpret_cast<T*>(stream_smem);                       // [stages][tile][channels]
   T* sd = su + kStreamStages * kStageElems;
   float* sB = reinterpret_cast<float*>(sd + kStreamStages * kStageElems);   // [2][tile][NMAX]
-  float* sC = sB + 2 * kStreamTile * NMAX;
-  constexpr int kPerThread = kStreamTile * NMAX / kQuadThreads;    // staged B / C values per thread: 4
+  float* sC = sB + 2 * kPairTile * NMAX;
+  constexpr int kPerThread = kPairTile * NMAX / kPairThreads;      // staged B / C values per thread: 2
   constexpr int kVec = 16 / static_cast<int>(sizeof(T));
-  constexpr int kVecPerRow = kQuadCh / kVec;                       // 8 (fp32) or 4 (bf16)
-  constexpr int kPieces = kStreamTile * kVecPerRow;                // 16-byte pieces per tile and operand
+  constexpr int kVecPerRow = kPairCh / kVec;
+  constexpr int kPieces = kPairTile * kVecPerRow;
   const int tid = threadIdx.x;
-  const int part = tid & 3;                         // states 4 * part .. 4 * part + 3
-  const int cl = tid >> 2;                          // channel within the CTA
+  const int part = tid & 1;                         // states 8 * part .. 8 * part + 7
+  const int cl = tid >> 1;
   const int b = blockIdx.y;
-  const int ch0 = blockIdx.x * kQuadCh;
+  const int ch0 = blockIdx.x * kPairCh;
   const bool active = ch0 + cl < d;
-  const int ch = active ? ch0 + cl : d - 1;         // idle lanes shadow a valid channel and store nothing
+  const int ch = active ? ch0 + cl : d - 1;
   const long long base = static_cast<long long>(b) * L;
-  float a2[4], h[4];
+  float a2[SPL], h[SPL];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int n = part * 4 + j;
+  for (int j = 0; j < SPL; ++j) {
+    const int n = part * SPL + j;
     a2[j] = n < N ? A[static_cast<long long>(ch) * N + n] * 1.4426950408889634f : 0.f;
     h[j] = (state_in && n < N) ? state_in[(static_cast<long long>(b) * d + ch) * N + n] : 0.f;
   }
   const float Dval = Dv[ch];
-  const int ntiles = (L + kStreamTile - 1) / kStreamTile;
+  const int ntiles = (L + kPairTile - 1) / kPairTile;
 
   auto issue_tile = [&](int tile, int stage) {
-    for (int idx = tid; idx < kPieces; idx += kQuadThreads) {
+    for (int idx = tid; idx < kPieces; idx += kPairThreads) {
       const int row = idx / kVecPerRow, v = idx % kVecPerRow;
-      const int t = tile * kStreamTile + row;
+      const int t = tile * kPairTile + row;
       const int c0 = ch0 + v * kVec;
       const bool ok = tile < ntiles && t < L && c0 < d;
       const long long off = ok ? (base + t) * d + c0 : 0;
-      const int dst = (stage * kStreamTile + row) * kQuadCh + v * kVec;
+      const int dst = (stage * kPairTile + row) * kPairCh + v * kVec;
       scan_cp_async16(su + dst, u + off, ok ? 16 : 0);
       scan_cp_async16(sd + dst, delta + off, ok ? 16 : 0);
     }
@@ -211,9 +212,9 @@ scan_stream_quad_kernel(const T* __restrict__ u, const T* __restrict__ delta, co
   auto fetch_bc = [&](int tile) {
 #pragma unroll
     for (int k = 0; k < kPerThread; ++k) {
-      const int idx = tid + k * kQuadThreads;
+      const int idx = tid + k * kPairThreads;
       const int step = idx / NMAX, n = idx % NMAX;
-      const int t = tile * kStreamTile + step;
+      const int t = tile * kPairTile + step;
       const bool ok = n < N && t < L;
       rb[k] = ok ? to_f32<T>(Bm[(base + t) * N + n]) : 0.f;
       rc[k] = ok ? to_f32<T>(Cm[(base + t) * N + n]) : 0.f;
@@ -222,9 +223,9 @@ scan_stream_quad_kernel(const T* __restrict__ u, const T* __restrict__ delta, co
   auto park_bc = [&](int buf) {
 #pragma unroll
     for (int k = 0; k < kPerThread; ++k) {
-      const int idx = tid + k * kQuadThreads;
-      sB[buf * kStreamTile * NMAX + idx] = rb[k];
-      sC[buf * kStreamTile * NMAX + idx] = rc[k];
+      const int idx = tid + k * kPairThreads;
+      sB[buf * kPairTile * NMAX + idx] = rb[k];
+      sC[buf * kPairTile * NMAX + idx] = rc[k];
     }
   };
 
@@ -232,6 +233,7 @@ scan_stream_quad_kernel(const T* __restrict__ u, const T* __restrict__ delta, co
   for (int st = 0; st < kStreamStages - 1; ++st) issue_tile(st, st);
   fetch_bc(0);
   park_bc(0);
+  T* yp = y + base * d + ch;                        // advanced by d per step
   for (int tile = 0; tile < ntiles; ++tile) {
     const int stage = tile % kStreamStages;
     const int buf = tile & 1;
@@ -241,37 +243,48 @@ scan_stream_quad_kernel(const T* __restrict__ u, const T* __restrict__ delta, co
     if (tile + 1 < ntiles) fetch_bc(tile + 1);
     const T* tu = su + stage * kStageElems + cl;
     const T* td = sd + stage * kStageElems + cl;
-    const float* tb = sB + buf * kStreamTile * NMAX + part * 4;
-    const float* tc = sC + buf * kStreamTile * NMAX + part * 4;
-    const int steps = min(kStreamTile, L - tile * kStreamTile);   // uniform over the CTA: the shuffles stay whole
-#pragma unroll 4
-    for (int s = 0; s < steps; ++s) {
-      const float uv = to_f32<T>(tu[s * kQuadCh]);
-      const float dt = to_f32<T>(td[s * kQuadCh]);
+    const float* tb = sB + buf * kPairTile * NMAX + part * SPL;
+    const float* tc = sC + buf * kPairTile * NMAX + part * SPL;
+    auto one_step = [&](int s) {
+      const float uv = to_f32<T>(tu[s * kPairCh]);
+      const float dt = to_f32<T>(td[s * kPairCh]);
       const float du = dt * uv;
-      const float4 bv = *reinterpret_cast<const float4*>(tb + s * NMAX);
-      const float4 cv = *reinterpret_cast<const float4*>(tc + s * NMAX);
-      const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
-      const float cc[4] = {cv.x, cv.y, cv.z, cv.w};
-      float acc = 0.f;
+      const float4 b0 = *reinterpret_cast<const float4*>(tb + s * NMAX);
+      const float4 b1 = *reinterpret_cast<const float4*>(tb + s * NMAX + 4);
+      const float4 c0 = *reinterpret_cast<const float4*>(tc + s * NMAX);
+      const float4 c1 = *reinterpret_cast<const float4*>(tc + s * NMAX + 4);
+      const float bb[SPL] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      const float cc[SPL] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float e;
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(dt * a2[j]));
-        h[j] = e * h[j] + du * bb[j];
-        acc += h[j] * cc[j];
+      for (int j = 0; j < SPL; j += 2) {
+        float e0, e1;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(dt * a2[j]));
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(dt * a2[j + 1]));
+        h[j] = e0 * h[j] + du * bb[j];
+        h[j + 1] = e1 * h[j + 1] + du * bb[j + 1];
+        acc0 += h[j] * cc[j];
+        acc1 += h[j + 1] * cc[j + 1];
       }
+      float acc = acc0 + acc1;
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      if (active && part == 0) y[(base + tile * kStreamTile + s) * d + ch] = from_f32<T>(acc + Dval * uv);
+      if (active && part == 0) *yp = from_f32<T>(acc + Dval * uv);
+      yp += d;
+    };
+    const int steps = min(kPairTile, L - tile * kPairTile);   // uniform over the CTA: the shuffles stay whole
+    if (steps == kPairTile) {
+#pragma unroll
+      for (int s = 0; s < kPairTile; ++s) one_step(s);
+    } else {
+      for (int s = 0; s < steps; ++s) one_step(s);
     }
     if (tile + 1 < ntiles) park_bc(buf ^ 1);
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (active) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int n = part * 4 + j;
+    for (int j = 0; j < SPL; ++j) {
+      const int n = part * SPL + j;
       if (n < N) state_out[(static_cast<long long>(b) * d + ch) * N + n] = h[j];
     }
   }
@@ -295,10 +308,10 @@ int run_scan(const void* u, const void* delta, const float* A, const void* Bm, c
       ((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(delta)) & 15) == 0) {
     static const int stream_on = [] { const char* e = getenv("TESSERACT_SCAN_STREAM"); return e ? atoi(e) : 1; }();
     if (stream_on) {
-      constexpr int smem = quad_smem_bytes<T>();
+      constexpr int smem = pair_smem_bytes<T>();
       static_assert(smem <= 48 * 1024, "within the default dynamic shared-memory limit: no per-device attribute needed");
-      dim3 grid((d + kQuadCh - 1) / kQuadCh, Bsz);
-      scan_stream_quad_kernel<T><<<grid, kQuadThreads, smem, s>>>(u_, dl, A, b_, c_, Dv, state_in, y_, state_out, L, d, N);
+      dim3 grid((d + kPairCh - 1) / kPairCh, Bsz);
+      scan_stream_pair_kernel<T><<<grid, kPairThreads, smem, s>>>(u_, dl, A, b_, c_, Dv, state_in, y_, state_out, L, d, N);
       return static_cast<int>(cudaGetLastError());
     }
   }
