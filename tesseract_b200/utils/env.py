@@ -31,6 +31,7 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_AG_KEEP", "copy", "all-gather -> GEMM: how the gathered activations are kept for backward: copy (copy engine) | kernel"),
     EnvVar("TESSERACT_AG_NSUB", "0", "all-gather -> GEMM: sub-chunks signalled per rank (0 = chosen by size; at most 2)"),
     EnvVar("TESSERACT_RMS_PREFETCH", "1", "RMSNorm forward: 1 (next row prefetched across the reduction) | 0 (plain kernel, for A/B runs)"),
+    EnvVar("TESSERACT_GEMM_NO_AVX512", "0", "CPU fp32 GEMM: 1 = use the AVX2 6 x 16 tile even where AVX-512 (14 x 32) is available"),
     EnvVar("TESSERACT_SCAN_STREAM", "1", "selective scan of wide layers: 1 = single-pass kernel (state in registers, cp.async ring), 0 = three chunked passes"),
     EnvVar("TESSERACT_RMS_THREADS", "0", "RMSNorm forward threads per row: 0 (256) | 128 | 256, for A/B runs"),
     EnvVar("TESSERACT_REF_TIME_BUDGET", "780", "bench.py --impl reference: seconds the reference arm may take in total"),

@@ -18,6 +18,38 @@ def test_matmul_f32_matches_float64(M, N, K, b_is_nk):
     assert (got - want).abs().max() <= 2e-5 * max(1.0, float(want.abs().max())) * max(1, K // 64)
 
 
+def test_random_shapes_thread_counts_and_both_register_tiles():
+    """Edge tiles, both B layouts, every thread count, and the AVX2 tile next to the AVX-512 one (a child process:
+    the tile is chosen once per process)."""
+    import subprocess
+    import sys
+    code = """
+import numpy as np
+from tesseract_b200 import _native
+h = _native.host()
+rng = np.random.default_rng(0)
+for t in range(120):
+    M, N, K = [int(rng.integers(1, 200)) for _ in range(3)]
+    if t % 10 == 0:
+        M, N, K = int(rng.integers(200, 500)), int(rng.integers(1, 2300)), int(rng.integers(150, 450))
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    nk = bool(rng.integers(0, 2))
+    b = rng.standard_normal((N, K) if nk else (K, N)).astype(np.float32)
+    got = np.asarray(h.gemm_f32(a, b, nk, int(rng.integers(0, 9))))
+    ref = a @ (b.T if nk else b)
+    assert got.shape == ref.shape and np.allclose(got, ref, atol=2e-3, rtol=1e-4), (M, N, K, nk)
+print("ok")
+"""
+    if cpu_gemm._host() is None:
+        pytest.skip("native host runtime not built")
+    import os
+    for no512 in ("0", "1"):
+        env = dict(os.environ, TESSERACT_GEMM_NO_AVX512=no512)
+        out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300,
+                             cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]
+
+
 def test_thread_count_grows_with_work_and_respects_the_cap(monkeypatch):
     assert cpu_gemm.gemm_num_threads(8, 8, 8) == 1                      # tiny problems stay on one thread
     big = cpu_gemm.gemm_num_threads(2048, 2048, 2048)
