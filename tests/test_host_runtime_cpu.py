@@ -165,3 +165,59 @@ def test_grammar_mask_native_walk_equals_python_loop(monkeypatch):
         tok = int(allowed[int(rng.integers(0, allowed.size))])
         g_nat.accept(tok)
         g_py.accept(tok)
+
+
+def _random_pattern(rng, depth=0):
+    """A random pattern of the supported subset over the letters a .. c (valid for Python's ``re`` too)."""
+    def atom():
+        r = rng.integers(0, 10)
+        if r < 4:
+            return "abc"[int(rng.integers(0, 3))]
+        if r == 4:
+            return "."
+        if r == 5:
+            return ["[ab]", "[^a]", "[a-c]", "[b-c]", r"\w", r"\d"][int(rng.integers(0, 6))]
+        if depth < 2:
+            return "(" + _random_pattern(rng, depth + 1) + ")"
+        return "abc"[int(rng.integers(0, 3))]
+
+    def piece():
+        a = atom()
+        q = rng.integers(0, 8)
+        if q == 0:
+            return a + "*"
+        if q == 1:
+            return a + "+"
+        if q == 2:
+            return a + "?"
+        if q == 3:
+            lo = int(rng.integers(0, 3))
+            return a + "{%d,%d}" % (lo, lo + int(rng.integers(0, 3)))
+        if q == 4:
+            return a + "{%d}" % int(rng.integers(1, 3))
+        return a
+
+    def cat():
+        return "".join(piece() for _ in range(int(rng.integers(1, 4))))
+
+    return "|".join(cat() for _ in range(int(rng.integers(1, 3))))
+
+
+def test_regex_automata_agree_with_python_re_on_random_patterns():
+    """An independent oracle: anchored matching of both automata equals ``re.fullmatch`` for random patterns of the
+    supported subset and random strings."""
+    import re
+    from tesseract_b200.models.structured import RegexAutomaton
+    rng = np.random.default_rng(11)
+    checked = 0
+    for _ in range(150):
+        pattern = _random_pattern(rng)
+        oracle = re.compile(pattern, re.DOTALL | re.ASCII)
+        nat, twin = RegexAutomaton(pattern, native=True), RegexAutomaton(pattern, native=False)
+        for _ in range(40):
+            s = "".join("abc1_ "[int(i)] for i in rng.integers(0, 6, size=int(rng.integers(0, 7))))
+            want = oracle.fullmatch(s) is not None
+            assert nat.matches(s) == want, (pattern, s, want)
+            assert twin.matches(s) == want, (pattern, s, want)
+            checked += 1
+    assert checked == 6000
