@@ -52,10 +52,12 @@ def reduce_to_shape(x: torch.Tensor, shape: Sequence[int]) -> torch.Tensor:
 
 
 def _ce_backward(op: Op, logits, targets, grad):
+    # (softmax - one_hot) * grad / n, built in place on the softmax buffer
     n = logits.shape[0]
     p = torch.softmax(logits.float(), dim=-1)
-    p[torch.arange(n, device=logits.device), targets] -= 1.0
-    return (p * (grad.float() / n)).to(logits.dtype)
+    p.scatter_add_(1, targets.view(-1, 1), p.new_full((n, 1), -1.0))
+    p.mul_(grad.float() / n)
+    return p if p.dtype == logits.dtype else p.to(logits.dtype)
 
 
 _KERNELS: Dict[str, Callable] = {
@@ -84,13 +86,15 @@ _KERNELS: Dict[str, Callable] = {
     "broadcast_to": lambda op, x: x.broadcast_to(list(_need(op.attrs, "shape", op.kind))),
     "reduce_to_shape": lambda op, x: reduce_to_shape(x, _need(op.attrs, "shape", op.kind)),
     "cross_entropy_with_logits": lambda op, logits, targets: F.cross_entropy(logits, targets),
-    "relu_backward": lambda op, grad, x: grad * (x > 0).to(grad.dtype),
+    "relu_backward": lambda op, grad, x: torch.ops.aten.threshold_backward(grad, x, 0.0),
+    "fused_linear": lambda op, x, w, b: F.linear(x, w, b),         # produced by plan(), never recorded
+    "matmul_tn": lambda op, a, b: torch.mm(a.t(), b),              # likewise
     "cross_entropy_with_logits_backward": _ce_backward,
 }
 
 
 def supported_ops() -> List[str]:
-    return sorted(_KERNELS)
+    return sorted(k for k in _KERNELS if k not in ("fused_linear", "matmul_tn"))
 
 
 def _check_bindings(g: Graph, env: Dict[ValueId, torch.Tensor]) -> None:
@@ -108,8 +112,76 @@ def _check_bindings(g: Graph, env: Dict[ValueId, torch.Tensor]) -> None:
                                  f"tensor is {tuple(t.shape)} {t.dtype}")
 
 
+def _live(ops: Sequence[Op], outputs: Sequence[ValueId]) -> List[Op]:
+    """The ops whose results reach ``outputs`` (a backward-extended graph also carries the gradient of its inputs,
+    which graph-mode training never reads: the largest matmul of an MLP step)."""
+    needed = set(outputs)
+    keep: List[Op] = []
+    for op in reversed(ops):
+        if any(o in needed for o in op.outputs):
+            keep.append(op)
+            needed.update(op.inputs)
+    keep.reverse()
+    return keep
+
+
+def _is_2d_transpose(op: Optional[Op], g: Graph) -> bool:
+    if op is None or op.kind != "transpose" or len(g.value(op.inputs[0]).shape) != 2:
+        return False
+    return {int(op.attrs.get("dim_a", -9)), int(op.attrs.get("dim_b", -9))} in ({0, 1}, {-1, -2}, {0, -1}, {1, -2})
+
+
+def plan(g: Graph) -> List[Op]:
+    """The op list the interpreter actually walks: dead ops removed and two peepholes applied (the reference does this
+    kind of clean-up in its lowering passes, src/ir/passes/): ``add(matmul(x, transpose(W)), broadcast_to(bias))``
+    whose intermediates have no other reader becomes one ``fused_linear``; the result is cached on the graph."""
+    key = (len(g.ops), tuple(g.outputs))
+    cached = getattr(g, "_plan_cache", None)
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    ops = _live(g.ops, g.outputs)
+    uses: Dict[ValueId, int] = {}
+    for op in ops:
+        for i in op.inputs:
+            uses[i] = uses.get(i, 0) + 1
+    for o in g.outputs:
+        uses[o] = uses.get(o, 0) + 1
+    producer = {op.outputs[0]: op for op in ops}
+    folded = set()
+    rewritten: List[Op] = []
+    for op in ops:
+        if op.kind == "add" and len(op.inputs) == 2:
+            for a, b in (op.inputs, op.inputs[::-1]):
+                pm, pb = producer.get(a), producer.get(b)
+                if (pm is None or pb is None or pm.kind != "matmul" or pb.kind != "broadcast_to"
+                        or uses.get(a) != 1 or uses.get(b) != 1):
+                    continue
+                x, t = pm.inputs
+                pt = producer.get(t)
+                bias = pb.inputs[0]
+                out_shape = g.value(op.outputs[0]).shape
+                if (_is_2d_transpose(pt, g) and len(g.value(x).shape) == 2 and len(g.value(bias).shape) == 1
+                        and g.value(bias).shape[0] == out_shape[-1] and g.value(a).shape == out_shape):
+                    folded.update((id(pm), id(pb)))
+                    op = Op("fused_linear", [x, pt.inputs[0], bias], list(op.outputs), {})
+                    break
+        elif _is_2d_transpose(op, g):
+            # transpose(matmul(transpose(a), b)) = matmul(transpose(b), a): the weight gradient of a Linear comes out
+            # in the parameter's own layout, contiguous, instead of as a transposed view
+            pm = producer.get(op.inputs[0])
+            if pm is not None and pm.kind == "matmul" and uses.get(op.inputs[0]) == 1:
+                pt = producer.get(pm.inputs[0])
+                if _is_2d_transpose(pt, g) and len(g.value(pm.inputs[1]).shape) == 2:
+                    folded.add(id(pm))
+                    op = Op("matmul_tn", [pm.inputs[1], pt.inputs[0]], list(op.outputs), {})
+        rewritten.append(op)
+    final = _live([op for op in rewritten if id(op) not in folded], g.outputs)
+    g._plan_cache = (key, final)
+    return final
+
+
 def _execute(g: Graph, env: Dict[ValueId, torch.Tensor]) -> List[torch.Tensor]:
-    for op in g.ops:
+    for op in plan(g):
         kernel = _KERNELS.get(op.kind)
         if kernel is None:
             raise NotImplementedError(f"graph.run: no kernel for op kind '{op.kind}'")

@@ -42,8 +42,7 @@ class GraphTrainStep:
         outs = self.executor({self.x_id: x, self.y_id: y})
         loss, grads = outs[0], outs[1:]
         for p, g in zip(self.params, grads):
-            if p.grad is None or self.executor.cuda_graph:
-                p.grad = g              # CUDA-graph outputs are static buffers: hand them out as they are
-            else:
-                p.grad.copy_(g)
+            # CUDA-graph outputs are static buffers, interpreted outputs are fresh tensors: either way they are handed
+            # out as they are (a transposed view is made contiguous first: optimizers update it in place)
+            p.grad = g if g.is_contiguous() else g.contiguous()
         return loss
