@@ -228,3 +228,31 @@ def test_executor_on_cpu_interprets_and_shares_params():
     assert torch.equal(ex({x: 2 * torch.eye(2)})[0], 6 * torch.ones(2, 2))
     with pytest.raises(ValueError, match="needs the bindings on a CUDA device"):
         GraphExecutor(g, {x: torch.eye(2), p: w}, cuda_graph=True)
+
+
+def test_execution_plan_drops_dead_ops_and_fuses_linear_layers():
+    """The interpreter's plan: the gradient of the input batch never reaches an output and is dropped, a Linear layer
+    runs as one fused op, the weight gradient comes out contiguous in the parameter's layout -- and the results equal
+    autograd's."""
+    import torch.nn.functional as F
+    from tesseract_b200.graph import GraphTrainStep
+    from tesseract_b200.graph.interpreter import plan
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(36, 16), torch.nn.ReLU(), torch.nn.Linear(16, 5))
+    x, y = torch.rand(7, 1, 6, 6), torch.randint(0, 5, (7,))
+    step = GraphTrainStep(model, F.cross_entropy, x, y, cuda_graph=False)
+    kinds = [op.kind for op in plan(step.graph)]
+    assert kinds.count("fused_linear") == 2 and kinds.count("matmul_tn") == 2
+    assert len(kinds) < step.graph.num_ops()
+    assert kinds.count("matmul") == 1                       # only the hidden activation's gradient is left
+    assert set(step.graph.op_kinds()) <= set(supported_ops())   # the IR itself is untouched
+    loss = step(x, y)
+    got = [p.grad.clone() for p in model.parameters()]
+    assert all(g.is_contiguous() for g in got)
+    for p in model.parameters():
+        p.grad = None
+    ref = F.cross_entropy(model(x), y)
+    ref.backward()
+    assert torch.allclose(loss, ref.detach(), atol=1e-6)
+    for g, p in zip(got, model.parameters()):
+        assert torch.allclose(g, p.grad, atol=1e-5)
