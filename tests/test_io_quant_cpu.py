@@ -246,6 +246,34 @@ def test_tesseract_python_surface():
     assert len(mm.generate([1, 4, 2], gc)) == 7
 
 
+def test_tesseract_python_surface_models_and_tokenizer():
+    """The model and io part of the drop-in frontend (the reference's python/_core.cpp:247-360 surface): dense and
+    MoE Llama and Mamba generate greedily and deterministically from a bare config; the whitespace tokenizer
+    round-trips."""
+    import tesseract as ts
+    assert ts.__version__ and hasattr(ts.nn, "Linear") and hasattr(ts.models, "LlamaModel")
+    for experts in (0, 4):
+        cfg = ts.models.LlamaConfig()
+        cfg.vocab_size, cfg.hidden_size, cfg.num_hidden_layers = 40, 16, 2
+        cfg.num_attention_heads = cfg.num_key_value_heads = 4
+        cfg.intermediate_size, cfg.max_position_embeddings = 32, 64
+        if experts:
+            cfg.num_experts, cfg.num_experts_per_tok = experts, 2
+        model = ts.models.LlamaModel(cfg)
+        gc = ts.models.LlamaGenerateConfig()
+        gc.max_new_tokens = 6
+        first = model.generate([3, 7, 11], gc)
+        assert len(first) == 9 and first[:3] == [3, 7, 11] and model.generate([3, 7, 11], gc) == first
+        assert all(0 <= t < 40 for t in first)
+    tcfg = ts.io.WhitespaceTokenizerConfig()
+    tcfg.vocab = ["<unk>", "paged", "decode", "kernel"]
+    tcfg.unk = "<unk>"
+    tk = ts.io.WhitespaceTokenizer(tcfg)
+    ids = tk.encode("decode kernel paged", add_special_tokens=False)
+    assert ids == [2, 3, 1] and tk.decode(ids) == "decode kernel paged"
+    assert tk.encode("decode nothing", add_special_tokens=False) == [2, 0]
+
+
 def test_fp8_block_scaling_restatement_cpu():
     """1 x 128 / 128 x 128 E4M3 quantisation and the block-scaled matmul (torch restatement used as the oracle of
     the CUDA kernels): scales, zero blocks, ragged N, round trip error."""
