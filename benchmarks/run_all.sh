@@ -23,6 +23,8 @@ run kernel_cases    python "$here/kernel_cases.py" --case all --iters 10
 run reference_bars  python "$here/reference_bars.py"
 run serving         python "$here/bench_serving.py"
 run moe             python "$here/bench_moe.py"
+run decode_step     python "$here/bench_decode_step.py"
 run cpu_decode_vnni python "$here/bench_cpu_decode_vnni.py"
+run cpu             python "$here/bench_cpu.py"
 run bench           python "$here/../bench.py"
 exit $status
