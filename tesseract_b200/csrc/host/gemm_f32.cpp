@@ -1,14 +1,17 @@
 // Native CPU FP32 GEMM of the host runtime: C[M, N] = A[M, K] * op(B), row-major, B given as [K, N] or as
 // [N, K] (transposed use, the layout of a Linear weight).
 //
-// Design: the classic three-level blocking around a register tile chosen at run time: 14 x 32 on AVX-512 (28 zmm
-// accumulators + 2 loads of B + 1 broadcast of A = 31 of 32 registers), 6 x 16 on AVX2 (12 + 2 + 1 of 16). B is packed
-// once per (kc, nc) panel into NR-wide column strips -- by all threads, a strip each -- and A once per (mc, kc) block
-// into MR-high row strips, so the microkernel streams both with unit stride; edge tiles go through the same kernel on
-// a zero-padded pack and a masked write-back. Threads split the M range of every panel; the row block is sized so that
-// every thread gets the same number of blocks (whole strips, at most 8 per block), not a fixed 96 rows that leaves a
-// 128-row product on two threads or a 1024-row one with ten blocks for eight threads. Small problems stay on few threads, since waking a thread costs more than a share
-// of a 128^3 product, and TESSERACT_GEMM_MAX_THREADS caps the count for co-located jobs.
+// Design: a register tile chosen at run time: 14 x 32 on AVX-512 (28 zmm accumulators + 2 loads of B + 1 broadcast
+// of A = 31 of 32 registers), 6 x 16 on AVX2 (12 + 2 + 1 of 16).
+// Up to 512^3 (AVX-512) nothing is packed: the tile reads A rows and B rows where they lie and one parallel loop walks
+// the tiles of C; a weight-layout B is transposed once, by all threads, into a scratch that outlives the call.
+// Above that the classic three-level blocking: B is packed once per (kc, nc) panel into NR-wide column strips -- by
+// all threads, a strip each -- and A once per (mc, kc) block into MR-high row strips, so the microkernel streams both
+// with unit stride; edge tiles go through the same kernel on a zero-padded pack and a masked write-back. Threads
+// split the M range of every panel in row blocks sized so that every thread gets the same number of them (whole
+// strips, at most 8 per block). The panel buffers are kept between calls (fresh megabytes per call cost more in page
+// faults than a mid-sized product). Small problems stay on few threads, since waking a thread costs more than a share
+// of a 64^3 product, and TESSERACT_GEMM_MAX_THREADS caps the count for co-located jobs.
 // Counterpart in the reference: a 4 x 8 FMA microkernel with an adaptive thread cap (src/ops/cpu/GemmAvx2.cpp:25-150).
 #include <algorithm>
 #include <cstdlib>
@@ -168,6 +171,39 @@ __attribute__((target("avx512f,fma"))) void micro_avx512(const float* Ap, const 
   }
   write_back(tmp, NR, C, ldc, mr, nr, accumulate);
 }
+
+// Small products skip packing: the register tile reads A rows (one broadcast per row and k) and B rows (two vector
+// loads per k) where they lie. Rows beyond mr shadow the last valid row (computed, not stored); columns beyond nr are
+// masked out of the loads and stores.
+__attribute__((target("avx512f,fma"))) void micro_avx512_direct(const float* A, int64_t lda, const float* B, int64_t ldb,
+                                                                int64_t K, float* C, int64_t ldc, int64_t mr, int64_t nr) {
+  constexpr int MR = 14;
+  const __mmask16 m0 = static_cast<__mmask16>(nr >= 16 ? 0xFFFFu : ((1u << nr) - 1u));
+  const __mmask16 m1 = static_cast<__mmask16>(nr >= 32 ? 0xFFFFu : (nr > 16 ? ((1u << (nr - 16)) - 1u) : 0u));
+  const float* ar[MR];
+#pragma GCC unroll 14
+  for (int i = 0; i < MR; ++i) ar[i] = A + std::min<int64_t>(i, mr - 1) * lda;
+  __m512 acc[MR][2];
+#pragma GCC unroll 14
+  for (int i = 0; i < MR; ++i) acc[i][0] = acc[i][1] = _mm512_setzero_ps();
+  for (int64_t k = 0; k < K; ++k) {
+    const __m512 b0 = _mm512_maskz_loadu_ps(m0, B + k * ldb);
+    const __m512 b1 = _mm512_maskz_loadu_ps(m1, B + k * ldb + 16);
+#pragma GCC unroll 14
+    for (int i = 0; i < MR; ++i) {
+      const __m512 av = _mm512_set1_ps(ar[i][k]);
+      acc[i][0] = _mm512_fmadd_ps(av, b0, acc[i][0]);
+      acc[i][1] = _mm512_fmadd_ps(av, b1, acc[i][1]);
+    }
+  }
+#pragma GCC unroll 14
+  for (int i = 0; i < MR; ++i) {
+    if (i < mr) {
+      _mm512_mask_storeu_ps(C + i * ldc, m0, acc[i][0]);
+      _mm512_mask_storeu_ps(C + i * ldc + 16, m1, acc[i][1]);
+    }
+  }
+}
 #endif
 
 struct Tile {
@@ -213,6 +249,47 @@ void gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, bool b_n
     return;
   }
   static const Tile tile = pick_tile();
+#ifdef TSBH_HAVE_AVX2
+  // up to 512^3: no packed panels, one parallel loop over the register tiles of C. A weight-layout B ([N, K]) is
+  // transposed once, by all threads, into a [K, N] scratch whose row stride avoids multiples of 4 KB.
+  if (tile.kernel == micro_avx512 && static_cast<double>(M) * N * K <= 512.0 * 512.0 * 512.0 && K * N <= 512 * 512 &&
+      M * K <= 512 * 512) {
+    const int nt = gemm_num_threads(M, N, K, threads);
+    const int64_t tm = (M + 13) / 14, tn = (N + 31) / 32;
+    // scratch of the calling thread, kept between calls: a fresh megabyte per call costs more in page faults than
+    // the product itself
+    static thread_local std::vector<float> bt;
+    const float* Bd = B;
+    int64_t ldbd = ldb;
+    if (b_nk) {
+      ldbd = (N + 15) / 16 * 16;
+      if (ldbd % 1024 == 0) ldbd += 16;
+      if (bt.size() < static_cast<size_t>(K * ldbd)) bt.resize(static_cast<size_t>(K * ldbd));
+      Bd = bt.data();
+    }
+    float* const dst = b_nk ? bt.data() : nullptr;     // the caller's buffer: `bt` names another vector in a worker
+#pragma omp parallel num_threads(nt) if (nt > 1)
+    {
+      if (b_nk) {
+        const int64_t kb = (K + 15) / 16;
+#pragma omp for schedule(static)
+        for (int64_t blk = 0; blk < kb * ((N + 15) / 16); ++blk) {     // 16 x 16 blocks: both sides stay in cache lines
+          const int64_t k0 = (blk % kb) * 16, n0 = (blk / kb) * 16;
+          const int64_t k1 = std::min(K, k0 + 16), n1 = std::min(N, n0 + 16);
+          for (int64_t n = n0; n < n1; ++n)
+            for (int64_t k = k0; k < k1; ++k) dst[k * ldbd + n] = B[n * ldb + k];
+        }
+      }
+#pragma omp for schedule(static)
+      for (int64_t t = 0; t < tm * tn; ++t) {
+        const int64_t i0 = (t / tn) * 14, j0 = (t % tn) * 32;
+        micro_avx512_direct(A + i0 * lda, lda, Bd + j0, ldbd, K, C + i0 * ldc + j0, ldc, std::min<int64_t>(14, M - i0),
+                            std::min<int64_t>(32, N - j0));
+      }
+    }
+    return;
+  }
+#endif
   const int MR = tile.mr, NR = tile.nr;
   const int64_t KC = tile.kc;
   const int nt = gemm_num_threads(M, N, K, threads);
@@ -223,10 +300,14 @@ void gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, bool b_n
   const int64_t MC = per_block * MR;
   const int64_t m_blocks = (M + MC - 1) / MC;
   const int64_t max_strips_b = (std::min(N, NC) + NR - 1) / NR;
-  std::vector<float> bpack(static_cast<size_t>(KC * max_strips_b * NR));
+  // panels live in buffers that outlast the call (grow-only): the caller's for B, every worker's own for A
+  static thread_local std::vector<float> bpack_store;
+  if (bpack_store.size() < static_cast<size_t>(KC * max_strips_b * NR)) bpack_store.resize(static_cast<size_t>(KC * max_strips_b * NR));
+  float* const bpack_ptr = bpack_store.data();
 #pragma omp parallel num_threads(nt)
   {
-    std::vector<float> apack(static_cast<size_t>(MC * KC));
+    static thread_local std::vector<float> apack;
+    if (apack.size() < static_cast<size_t>(MC * KC)) apack.resize(static_cast<size_t>(MC * KC));
     for (int64_t jc = 0; jc < N; jc += NC) {
       const int64_t nc = std::min(NC, N - jc);
       const int64_t b_strips = (nc + NR - 1) / NR;
@@ -235,7 +316,7 @@ void gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, bool b_n
         const float* Bpanel = b_nk ? B + jc * ldb + pc : B + pc * ldb + jc;
 #pragma omp for schedule(static)
         for (int64_t sb = 0; sb < b_strips; ++sb)
-          pack_b_strip(Bpanel, ldb, b_nk, kc, nc, sb * NR, NR, bpack.data() + sb * kc * NR);
+          pack_b_strip(Bpanel, ldb, b_nk, kc, nc, sb * NR, NR, bpack_ptr + sb * kc * NR);
         // (the loop above ends with a barrier: the panel is complete before anyone multiplies)
         const bool accumulate = pc > 0;
         // few row blocks (a small M): the column strips of the panel are split over threads as well, each task
@@ -253,7 +334,7 @@ void gemm_f32(const float* A, int64_t lda, const float* B, int64_t ldb, bool b_n
           pack_a(A + ic * lda + pc, lda, mc, kc, MR, apack.data());
           for (int64_t jr = jr_begin; jr < jr_end; jr += NR) {
             const int64_t nr = std::min<int64_t>(NR, nc - jr);
-            const float* Bp = bpack.data() + (jr / NR) * kc * NR;
+            const float* Bp = bpack_ptr + (jr / NR) * kc * NR;
             for (int64_t ir = 0; ir < mc; ir += MR) {
               const int64_t mr = std::min<int64_t>(MR, mc - ir);
               tile.kernel(apack.data() + (ir / MR) * kc * MR, Bp, kc, C + (ic + ir) * ldc + jc + jr, ldc, mr, nr,
