@@ -107,7 +107,9 @@ def case_graph_vs_eager():
 
 def case_moe_sparse():
     from tesseract_b200.nn.moe import MoEFeedForward
-    for (T, D, F_, E, k) in ((512, 256, 512, 8, 2), (2048, 256, 512, 8, 2), (2048, 256, 512, 16, 1)):
+    # the last shape is the one the reference publishes (docs/design/moe-sparse.md:41-47: 300 ms sparse, 644 ms dense)
+    for (T, D, F_, E, k) in ((512, 256, 512, 8, 2), (2048, 256, 512, 8, 2), (2048, 256, 512, 16, 1),
+                             (4096, 512, 1024, 8, 2)):
         torch.manual_seed(0)
         moe = MoEFeedForward(D, F_, num_experts=E, num_experts_per_tok=k)
         x = torch.randn(1, T, D)
@@ -119,7 +121,30 @@ def case_moe_sparse():
             dense_ms=round(s_dense * 1e3, 2), speedup=round(s_dense / s_sparse, 2), max_abs_diff=round(err, 6))
 
 
-CASES = {"matmul": case_matmul, "python_overhead": case_python_overhead, "graph_vs_eager": case_graph_vs_eager,
+def case_mamba_vs_llama():
+    """Decode-step latency against context length (the reference's bench_mamba_vs_llama_scaling: d = 256, 4 layers;
+    docs/design/mamba-scaling.md:41-47 reports Mamba flat at 12.4 ms and Llama 14.6 -> 27.3 ms for 128 -> 2048)."""
+    from tesseract_b200.models import LlamaConfig, LlamaModel
+    from tesseract_b200.models.mamba import MambaConfig, MambaModel
+    torch.manual_seed(0)
+    lcfg = LlamaConfig(vocab_size=32000, hidden_size=256, num_hidden_layers=4, num_attention_heads=8,
+                       num_key_value_heads=8, intermediate_size=688, max_position_embeddings=4096, dtype=torch.float32)
+    llama = LlamaModel(lcfg)
+    mamba = MambaModel(MambaConfig(vocab_size=32000, hidden_size=256, num_hidden_layers=4))
+    tok = torch.tensor([[5]])
+    with torch.no_grad():
+        for L in (128, 512, 2048):
+            caches = llama.make_kv_caches(1, L + 64)
+            llama.forward_step(torch.randint(0, 32000, (1, L)), caches)          # fill the context
+            s_llama = best_of(lambda: (llama.forward_step(tok, caches), [c.set_current_len(L) for c in caches])[0], 20, reps=3)
+            states = mamba.make_state_caches(1)
+            for t in torch.randint(0, 32000, (8,)).tolist():                     # the recurrent state has no length
+                mamba.forward_step(torch.tensor([[t]]), states)
+            s_mamba = best_of(lambda: mamba.forward_step(tok, states), 20, reps=3)
+            out(case="mamba_vs_llama", context=L, llama_ms=round(s_llama * 1e3, 3), mamba_ms=round(s_mamba * 1e3, 3))
+
+
+CASES = {"mamba_vs_llama": case_mamba_vs_llama, "matmul": case_matmul, "python_overhead": case_python_overhead, "graph_vs_eager": case_graph_vs_eager,
          "moe_sparse": case_moe_sparse}
 
 
