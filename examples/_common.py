@@ -23,8 +23,8 @@ def pick_device(name: str) -> torch.device:
 
 def preset(name: str, dtype: torch.dtype, max_pos: int) -> LlamaConfig:
     if name == "tiny":        # the reference's llama_train config (examples/llama_train.cpp:117-125)
-        return LlamaConfig(vocab_size=128, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
-                           num_key_value_heads=2, intermediate_size=128, max_position_embeddings=max(max_pos, 64),
+        return LlamaConfig(vocab_size=64, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                           num_key_value_heads=4, intermediate_size=128, max_position_embeddings=max(max_pos, 128),
                            dtype=dtype)
     if name == "small":       # test-bed size with 128-wide heads (runs every native kernel)
         return LlamaConfig(vocab_size=4096, hidden_size=512, num_hidden_layers=4, num_attention_heads=4,

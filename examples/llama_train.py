@@ -50,7 +50,9 @@ def main() -> int:
     from tesseract_b200.training import TrainConfig
     cfg = preset(a.model, dtype, a.seq + 1)
     tcfg = TrainConfig(lr=a.lr, micro_batch=a.micro_batch or min(a.batch, 4))
-    trainer, plan = build_parallel_trainer(cfg, tcfg, world, rank, dev, a.parallelism, seed=a.seed)
+    # the tiny model on one process starts from the modules' own initialisers, like the reference's example
+    trainer, plan = build_parallel_trainer(cfg, tcfg, world, rank, dev, a.parallelism, seed=a.seed,
+                                           module_init=(a.model == "tiny" and world == 1))
     from tesseract_b200.parallel.launch import job_metrics, job_watchdog
     # TESSERACT_METRICS_FILE: one JSON record per step; TESSERACT_WATCHDOG_S: heartbeat + peer check before every step;
     # TESSERACT_NVTX=1: ranges around forward / backward / optimizer

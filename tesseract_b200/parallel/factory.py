@@ -74,11 +74,17 @@ def _attach_reducer(model, trainer, group, holder=None):
 
 
 def build_parallel_trainer(cfg: LlamaConfig, tcfg: TrainConfig, world: int, rank: int, device, mode: str = "auto",
-                           seed: int = 0, tp_size: int = 0):
+                           seed: int = 0, tp_size: int = 0, module_init: bool = False):
     """Returns ``(trainer, plan)``; ``plan`` has ``name`` (e.g. "tp8+sp", "dp4"), ``dp``, ``dp_rank``, ``tp``,
-    ``tp_rank``, ``fused_comm``, ``dp_comm`` and ``resources`` (see ``_resources``)."""
+    ``tp_rank``, ``fused_comm``, ``dp_comm`` and ``resources`` (see ``_resources``). Weights are N(0, 0.02) from
+    ``seed``; ``module_init`` (single process only) keeps the modules' own initialisers instead -- Linear
+    U(+-1/sqrt(in)), Embedding N(0, 1), the reference's rules (src/nn/Linear.cpp:19-60, src/nn/Embedding.cpp:64-85)."""
     if world == 1:
-        model = LlamaModel(cfg, device=device, init_std=0.02, seed=seed)
+        if module_init:
+            torch.manual_seed(seed)
+            model = LlamaModel(cfg, device=device)
+        else:
+            model = LlamaModel(cfg, device=device, init_std=0.02, seed=seed)
         return Trainer(model, tcfg), {"name": "single", "dp": 1, "dp_rank": 0, "tp": 1, "tp_rank": 0,
                                       "fused_comm": False, "dp_comm": None, "resources": []}
     import torch.distributed as dist
