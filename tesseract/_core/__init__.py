@@ -212,6 +212,11 @@ def _matmul(a: Tensor, b: Tensor) -> Tensor:
         raise ValueError(f"matmul: inner dimensions differ ({a.t.shape[-1]} vs {b.t.shape[-2]})")
     if a.t.is_cuda and a.t.dtype == torch.bfloat16 and a.t.dim() == 2 and b.t.dim() == 2:
         return _wrap(_LinearNN.apply(a.t, b.t))
+    if (not a.t.is_cuda and a.t.dtype == torch.float32 and b.t.dtype == torch.float32 and a.t.dim() == 2
+            and b.t.dim() == 2):
+        from tesseract_b200.ops import cpu_gemm
+        if cpu_gemm.native_selected():          # TESSERACT_CPU_GEMM=native: the host runtime's GEMM, with autograd
+            return _wrap(cpu_gemm.matmul(a.t, b.t))
     return _wrap(a.t @ b.t)
 
 

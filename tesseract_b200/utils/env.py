@@ -49,7 +49,7 @@ REGISTRY: Dict[str, EnvVar] = {v.name: v for v in [
     EnvVar("TESSERACT_EP_SCATTER_EPILOGUE", "1", "expert parallelism: 1 (the down projection's epilogue stores result rows into the source ranks' buffers) | 0 (separate return kernel)"),
     EnvVar("TESSERACT_PDL_ALL", "1", "decode-step kernels (quantisers, KV append, decode attention, merge): 1 (programmatic dependent launch) | 0"),
     EnvVar("TESSERACT_PDL", "1", "serving decode GEMMs: 1 (programmatic dependent launch) | 0"),
-    EnvVar("TESSERACT_CPU_GEMM", "torch", "2-D fp32 CPU products of ops.cpu_gemm.matmul_f32 callers: torch | native (host-runtime AVX2 GEMM)"),
+    EnvVar("TESSERACT_CPU_GEMM", "torch", "2-D fp32 CPU products of the frontend's ops.matmul: torch | native (the host runtime's GEMM, forward and backward)"),
     EnvVar("TESSERACT_DECODE_CTAS_PER_SM", "6", "paged decode attention: the key range is split until about this many CTAs per SM exist (never below 256 keys per split)"),
     EnvVar("TESSERACT_SERVE_VOCAB_PARALLEL", "1", "greedy tensor-parallel serving: 1 = the LM head is split over the ranks by vocabulary rows, 0 = replicated"),
     EnvVar("TESSERACT_SERVE_DECODE_GEMM", "auto", "serving decode GEMMs: auto | mx (fp8 weights: tensor-core block scaling) | stream (always the weight-streaming kernel) | splitk (bf16: the cluster split-K kernel) | fp8gemm (fp8 weights: never mx)"),
