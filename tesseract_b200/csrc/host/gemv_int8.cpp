@@ -14,6 +14,10 @@
 #include <immintrin.h>
 #endif
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
 #include "host_runtime.hpp"
 
 namespace tsbh {
@@ -111,19 +115,42 @@ void gemv_w8a8(const int8_t* W, const float* wscale, const int32_t* rowsum, cons
                int64_t N, int64_t K, int threads) {
   const int64_t work = N * K;
   int t = threads > 0 ? threads : static_cast<int>(std::min<unsigned>(16, std::max(1u, std::thread::hardware_concurrency())));
-  if (work < (int64_t(1) << 20) || N < 2 * t) t = 1;      // small matrices: one thread beats the fork
+#ifdef _OPENMP
+  t = std::min(t, omp_get_max_threads());
+#else
+  t = 1;
+#endif
+  if (work < (int64_t(1) << 20) || N < 2 * t) t = 1;      // small matrices: one thread beats waking the others
   if (t == 1) {
     gemv_w8a8_range(W, wscale, rowsum, xq, xscale, y, 0, N, K);
     return;
   }
-  std::vector<std::thread> pool;
+  // the OpenMP team persists between calls (a decode step makes hundreds of them; creating threads per call cost
+  // several times the product itself); the biased activation vector is built once and shared
+#if defined(__x86_64__)
+  const bool vnni = gemv_vnni_supported() && rowsum != nullptr;
+  std::vector<uint8_t> xu;
+  if (vnni) {
+    const int64_t Kp = (K + 63) & ~int64_t(63);
+    xu.assign(static_cast<size_t>(Kp), 128);
+    for (int64_t k = 0; k < K; ++k) xu[k] = static_cast<uint8_t>(static_cast<int>(xq[k]) + 128);
+  }
+#else
+  const bool vnni = false;
+#endif
   const int64_t per = (N + t - 1) / t;
+#pragma omp parallel for schedule(static, 1) num_threads(t)
   for (int i = 0; i < t; ++i) {
     const int64_t a = i * per, b = std::min<int64_t>(N, a + per);
-    if (a >= b) break;
-    pool.emplace_back([=] { gemv_w8a8_range(W, wscale, rowsum, xq, xscale, y, a, b, K); });
+    if (a >= b) continue;
+#if defined(__x86_64__)
+    if (vnni) {
+      rows_vnni(W, wscale, rowsum, xu.data(), xscale, y, a, b, K);
+      continue;
+    }
+#endif
+    rows_scalar(W, wscale, xq, xscale, y, a, b, K);
   }
-  for (auto& th : pool) th.join();
 }
 
 }  // namespace tsbh
