@@ -108,6 +108,8 @@ void BlockAllocator::free(int64_t block) {
 // ---------------------------------------------------------------------------------------------- automaton mask
 void token_mask(const int32_t* table, int64_t num_states, int32_t state, const uint8_t* bytes, const int64_t* offsets,
                 int64_t n_tokens, uint8_t* allowed) {
+  // tokens are independent: a large vocabulary is split over the OpenMP team
+#pragma omp parallel for schedule(static) if (n_tokens >= 16384)
   for (int64_t i = 0; i < n_tokens; ++i) {
     int32_t s = state;
     const int64_t b0 = offsets[i], b1 = offsets[i + 1];
