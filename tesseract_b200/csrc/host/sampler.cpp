@@ -43,37 +43,67 @@ int HostSampler::sample(const float* logits, int64_t V, const int64_t* prev, int
     for (int64_t i = 0; i < V; ++i)
       if (w[i] < kth) w[i] = ninf;
   }
+  bool have_e = false;
   if (params_.top_p < 1.f) {
-    order_.resize(V);
-    std::iota(order_.begin(), order_.end(), 0);
-    std::stable_sort(order_.begin(), order_.end(), [&](int32_t a, int32_t b) { return w[a] > w[b]; });
-    const float maxv = w[order_[0]];
+    have_e = true;
+    // The nucleus is a prefix of the order (value descending, index ascending on ties). Only that prefix is sorted:
+    // candidates are all entries not below the K-th largest value (K grows until the prefix reaches top_p); the
+    // probabilities come from one pass over the row in index order.
+    float mx = w[0];
+    for (int64_t i = 1; i < V; ++i) mx = std::max(mx, w[i]);
     e_.resize(V);
     double denom = 0.0;
     for (int64_t i = 0; i < V; ++i) {
-      const float v = w[order_[i]];
-      e_[i] = (v != ninf) ? std::exp(static_cast<double>(v - maxv)) : 0.0;
+      e_[i] = (w[i] != ninf) ? std::exp(static_cast<double>(w[i] - mx)) : 0.0;
       denom += e_[i];
     }
-    double cum = 0.0;
     int64_t cut = -1;
-    for (int64_t i = 0; i < V; ++i) {
-      cum += e_[i] / denom;
-      if (w[order_[i]] != ninf && cum >= static_cast<double>(params_.top_p)) {
-        cut = i + 1;
-        break;
+    for (int64_t K = 256;; K *= 8) {
+      order_.clear();
+      if (K >= V) {
+        order_.resize(V);
+        std::iota(order_.begin(), order_.end(), 0);
+      } else {
+        std::vector<float> tmp(work_);
+        std::nth_element(tmp.begin(), tmp.begin() + (V - K), tmp.end());
+        const float kth = tmp[V - K];
+        for (int64_t i = 0; i < V; ++i)
+          if (w[i] >= kth) order_.push_back(static_cast<int32_t>(i));
       }
+      std::stable_sort(order_.begin(), order_.end(), [&](int32_t a, int32_t b) { return w[a] > w[b]; });
+      double cum = 0.0;
+      for (size_t i = 0; i < order_.size(); ++i) {
+        cum += e_[order_[i]] / denom;
+        if (w[order_[i]] != ninf && cum >= static_cast<double>(params_.top_p)) {
+          cut = static_cast<int64_t>(i) + 1;
+          break;
+        }
+      }
+      if (cut >= 0 || static_cast<int64_t>(order_.size()) >= V) break;
     }
-    if (cut >= 0)
-      for (int64_t i = cut; i < V; ++i) w[order_[i]] = ninf;
+    if (cut >= 0) {
+      std::vector<char> keep(static_cast<size_t>(V), 0);
+      for (int64_t i = 0; i < cut; ++i) keep[order_[i]] = 1;
+      for (int64_t i = 0; i < V; ++i)
+        if (!keep[i]) w[i] = ninf;
+    }
   }
-  float maxv = w[0];
-  for (int64_t i = 1; i < V; ++i) maxv = std::max(maxv, w[i]);
-  e_.resize(V);
   double denom = 0.0;
-  for (int64_t i = 0; i < V; ++i) {
-    e_[i] = (w[i] != ninf) ? std::exp(static_cast<double>(w[i] - maxv)) : 0.0;
-    denom += e_[i];
+  if (have_e) {
+    // the largest entry always survives the nucleus cut, so the exponentials of the survivors are the ones already
+    // computed; the dropped entries count as zero
+    for (int64_t i = 0; i < V; ++i) {
+      if (w[i] == ninf) e_[i] = 0.0;
+      denom += e_[i];
+    }
+  } else {
+    float maxv = w[0];
+    for (int64_t i = 1; i < V; ++i) maxv = std::max(maxv, w[i]);
+    e_.resize(V);
+    for (int64_t i = 0; i < V; ++i) {
+      e_[i] = (w[i] != ninf) ? std::exp(static_cast<double>(w[i] - maxv)) : 0.0;
+      denom += e_[i];
+    }
   }
   if (!(denom > 0.0)) throw std::runtime_error("sample: degenerate distribution");
   double rem = uniform_double() * denom;

@@ -86,23 +86,33 @@ def sample_from_logits(logits: np.ndarray, params: SamplingParams, prev_tokens: 
                 work[t] = work[t] / pen if work[t] > 0 else work[t] * pen
     if params.temperature <= 1e-6:
         return argmax_lowest_index(work)
-    work *= np.float32(1.0 / params.temperature)
+    work *= np.float32(1.0) / np.float32(params.temperature)      # float arithmetic, as in the native sampler
     ninf = np.float32(-np.inf)
     if 0 < params.top_k < V:
         kth = np.partition(work, V - params.top_k)[V - params.top_k]
         work[work < kth] = ninf
     if params.top_p < 1.0:
-        order = np.argsort(-work, kind="stable")
-        sw = work[order]
-        finite = sw != ninf
-        maxv = sw.max()
-        e = np.where(finite, np.exp((sw - maxv).astype(np.float64)), 0.0)
-        denom = float(np.cumsum(e)[-1])
-        cum = np.cumsum(e / denom)
-        hit = np.nonzero(finite & (cum >= params.top_p))[0]
+        # the nucleus is a prefix of the order (value descending, index ascending on ties); only that prefix is
+        # sorted: all entries not below the K-th largest value, K growing until the prefix reaches top_p
+        finite_all = work != ninf
+        e_all = np.where(finite_all, np.exp((work - work.max()).astype(np.float64)), 0.0)
+        denom = float(np.cumsum(e_all)[-1])
+        K = 256
+        while True:
+            if K >= V:
+                cand = np.arange(V)
+            else:
+                kth = np.partition(work, V - K)[V - K]
+                cand = np.nonzero(work >= kth)[0]
+            order = cand[np.argsort(-work[cand], kind="stable")]
+            cum = np.cumsum(e_all[order] / denom)
+            hit = np.nonzero((work[order] != ninf) & (cum >= float(np.float32(params.top_p))))[0]   # top_p is a float
+            if hit.size or cand.size >= V:
+                break
+            K *= 8
         if hit.size:
-            cut = int(hit[0]) + 1
-            drop = order[cut:]
+            drop = np.ones(V, dtype=bool)
+            drop[order[:int(hit[0]) + 1]] = False
             work[drop] = ninf
     maxv = work.max()
     finite = work != ninf

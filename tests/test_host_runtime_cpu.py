@@ -221,3 +221,21 @@ def test_regex_automata_agree_with_python_re_on_random_patterns():
             assert twin.matches(s) == want, (pattern, s, want)
             checked += 1
     assert checked == 6000
+
+
+def test_sampler_twins_agree_on_flat_tied_and_peaked_rows():
+    """Nucleus sampling where the cut is decided by rounding (uniform rows, top_p next to 1), with many ties, and on a
+    128 K vocabulary where only a prefix of the order is sorted: native and Python samplers draw the same tokens."""
+    from tesseract_b200.models.sampler import Sampler, SamplingParams
+    rng = np.random.default_rng(0)
+    rows = [(rng.standard_normal(128256) * 3.0), (rng.standard_normal(128256) * 0.05), np.zeros(1000),
+            np.round(rng.standard_normal(300) * 2) / 4, rng.standard_normal(777) * 2.0]
+    settings = [dict(temperature=1.0, top_p=0.9), dict(temperature=0.7, top_k=40, top_p=0.5),
+                dict(temperature=1.3, top_p=0.999), dict(temperature=1.0, top_p=0.01),
+                dict(temperature=0.37, top_p=0.95, repetition_penalty=1.1)]
+    for row in rows:
+        logits = torch.from_numpy(row.astype(np.float32))
+        for kw in settings:
+            a, b = Sampler(SamplingParams(**kw), seed=7, native=True), Sampler(SamplingParams(**kw), seed=7, native=False)
+            for _ in range(4):
+                assert a.sample(logits, [1, 2, 3]) == b.sample(logits, [1, 2, 3]), (row.shape, kw)
