@@ -33,9 +33,10 @@ class HostSampler {
  private:
   SamplingParams params_;
   std::mt19937_64 rng_;
-  std::vector<float> work_;
+  std::vector<float> work_, tmp_;      // scratch kept between calls: no half-megabyte allocation per sampled token
   std::vector<int32_t> order_;
   std::vector<double> e_;
+  std::vector<char> keep_;
 };
 
 // ---- byte-level BPE merge loop (src/io/Tokenizer.cpp of the reference)

@@ -37,7 +37,8 @@ int HostSampler::sample(const float* logits, int64_t V, const int64_t* prev, int
   const float inv_t = 1.0f / params_.temperature;
   for (int64_t i = 0; i < V; ++i) w[i] *= inv_t;
   if (params_.top_k > 0 && params_.top_k < V) {
-    std::vector<float> tmp(work_);
+    std::vector<float>& tmp = tmp_;
+    tmp.assign(work_.begin(), work_.end());
     std::nth_element(tmp.begin(), tmp.begin() + (V - params_.top_k), tmp.end());
     const float kth = tmp[V - params_.top_k];
     for (int64_t i = 0; i < V; ++i)
@@ -64,7 +65,8 @@ int HostSampler::sample(const float* logits, int64_t V, const int64_t* prev, int
         order_.resize(V);
         std::iota(order_.begin(), order_.end(), 0);
       } else {
-        std::vector<float> tmp(work_);
+        std::vector<float>& tmp = tmp_;
+        tmp.assign(work_.begin(), work_.end());
         std::nth_element(tmp.begin(), tmp.begin() + (V - K), tmp.end());
         const float kth = tmp[V - K];
         for (int64_t i = 0; i < V; ++i)
@@ -82,7 +84,8 @@ int HostSampler::sample(const float* logits, int64_t V, const int64_t* prev, int
       if (cut >= 0 || static_cast<int64_t>(order_.size()) >= V) break;
     }
     if (cut >= 0) {
-      std::vector<char> keep(static_cast<size_t>(V), 0);
+      std::vector<char>& keep = keep_;
+      keep.assign(static_cast<size_t>(V), 0);
       for (int64_t i = 0; i < cut; ++i) keep[order_[i]] = 1;
       for (int64_t i = 0; i < V; ++i)
         if (!keep[i]) w[i] = ninf;
