@@ -203,6 +203,17 @@ class _FusedProj:
             if wv is not None and gv is not None:
                 need = torch.is_grad_enabled() and any(w.requires_grad for w in ws)
                 return ops.linear(x, wv, None, gv, force_wgrad=need)
+        need_grad = torch.is_grad_enabled() and any(w.requires_grad for w in ws)
+        if not need_grad:
+            # inference: weights that already sit back to back (an arena, or an engine that fused them in place) are one
+            # GEMM over a view; nothing is copied
+            wv = fused_rows_view(ws)
+            if wv is not None:
+                return ops.linear(x, wv)
+            if not x.is_cuda:
+                # separate weights on the CPU: three products and a cat of the (small) outputs, instead of copying all
+                # the weights into one matrix for every call
+                return torch.cat([ops.linear(x, w) for w in ws], dim=-1)
         w = torch.cat([ops.grad_to_buf(w, g) for w, g in zip(ws, grads)], dim=0)
         return ops.linear(x, w)
 
