@@ -173,7 +173,13 @@ def load_file_parallel(path: str, device=None, threads: int = 8, pin: bool = Tru
     out = {}
     for name, (dt, shape, b, e) in entries.items():
         tdt = _DTYPES[dt][0]
-        t = buf[b:e].view(tdt).reshape(shape) if e > b else torch.empty(shape, dtype=tdt)
+        if e > b:
+            raw = buf[b:e]
+            if b % tdt.itemsize:        # the format does not align tensors: a misaligned one is copied to offset 0
+                raw = raw.clone()
+            t = raw.view(tdt).reshape(shape)
+        else:
+            t = torch.empty(shape, dtype=tdt)
         out[name] = t.to(device, non_blocking=True) if device is not None else t
     if device is not None and torch.device(device).type == "cuda":
         torch.cuda.synchronize(device)
