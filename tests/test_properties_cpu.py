@@ -103,3 +103,61 @@ def test_block_allocator_twins_hand_out_the_same_blocks(num_blocks, script):
     if len(held) == num_blocks:
         with pytest.raises(RuntimeError):
             nat.allocate()
+
+
+@settings(**_SETTINGS)
+@given(st.integers(2, 400), st.floats(0.05, 3.0), st.sampled_from([0, 1, 5, 50]), st.sampled_from([1.0, 0.95, 0.5, 0.05]),
+       st.sampled_from([1.0, 1.3]), st.floats(0.01, 6.0), st.integers(0, 2 ** 31 - 1))
+def test_sampler_twins_draw_the_same_tokens(V, temperature, top_k, top_p, penalty, spread, seed):
+    from tesseract_b200 import _native
+    from tesseract_b200.models.sampler import Sampler, SamplingParams
+    if _native.host() is None:
+        pytest.skip("native host runtime not built")
+    rng = np.random.default_rng(seed)
+    logits = torch.from_numpy((rng.standard_normal(V) * spread).astype(np.float32))
+    if seed % 3 == 0:
+        logits = torch.round(logits * 2) / 2                     # ties
+    sp = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p, repetition_penalty=penalty)
+    a, b = Sampler(sp, seed=seed, native=True), Sampler(sp, seed=seed, native=False)
+    prev = rng.integers(0, V, size=5).tolist()
+    for _ in range(3):
+        ta, tb = a.sample(logits, prev), b.sample(logits, prev)
+        assert ta == tb and 0 <= ta < V
+        prev.append(ta)
+
+
+@settings(**_SETTINGS)
+@given(st.integers(1, 6), st.integers(1, 4), st.sampled_from([32, 64, 128]), st.integers(0, 2 ** 31 - 1))
+def test_int4_and_int8_packing_round_trip(rows, groups, group, seed):
+    from tesseract_b200 import quant
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(rows, groups * group, generator=g) * 3
+    q8, s8 = quant.pack_int8_symmetric(w)
+    assert q8.dtype == torch.int8 and int(q8.abs().max()) <= 127
+    assert (q8.float() * s8[:, None] - w).abs().max() <= s8.max() * 0.5 + 1e-6          # half a quantisation step
+    q4, s4 = quant.pack_int4_group(w, group)
+    back = quant.unpack_int4_group(q4, s4, group)
+    step = s4.repeat_interleave(group, dim=1)
+    assert back.shape == w.shape and ((back - w).abs() <= step * 0.5 + 1e-6).all()
+    q4b, s4b = quant.pack_int4_group(back, group)                                       # its own values re-pack exactly
+    assert torch.allclose(quant.unpack_int4_group(q4b, s4b, group), back, atol=1e-5)
+
+
+@settings(**_SETTINGS)
+@given(st.integers(1, 300), st.sampled_from([128, 256, 512]), st.integers(0, 2 ** 31 - 1))
+def test_mx_scale_layouts_are_inverse_and_quantisation_error_is_bounded(M, K, seed):
+    """The two scale-factor layouts of the MX activation quantiser carry the same exponents; dequantised values are
+    within one E4M3 step of the input; every scale is a power of two that keeps its block inside the E4M3 range."""
+    from tesseract_b200.ops import fp8
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(M, K, generator=g) * (10.0 ** float(torch.randint(-3, 3, (1,), generator=g)))).bfloat16()
+    q, sf = fp8.quantize_act_mx_ref(x)
+    qa, atoms = fp8.quantize_act_mx_ref(x, atoms=True)
+    assert torch.equal(q, qa) and atoms.dim() == 3
+    assert torch.equal(fp8._atoms_to_words(atoms)[:, :M], sf[:, :M])
+    assert torch.equal(fp8._atoms_to_words(fp8._words_to_atoms(sf)), sf)
+    back = fp8.dequantize_act_mx(q, sf).float()
+    blocks = x.float().view(M, K // 32, 32).abs().amax(-1)
+    tol = (blocks / 448.0 * 2 * 32).clamp_min(2.0 ** -20).repeat_interleave(32, dim=1)   # <= 2^-3 relative (3 mantissa bits) of the scaled block, with slack
+    assert ((back - x.float()).abs() <= tol).all()
+    assert torch.equal(fp8.dequantize_act_mx(qa, atoms).float(), back)
