@@ -161,3 +161,94 @@ def test_mx_scale_layouts_are_inverse_and_quantisation_error_is_bounded(M, K, se
     tol = (blocks / 448.0 * 2 * 32).clamp_min(2.0 ** -20).repeat_interleave(32, dim=1)   # <= 2^-3 relative (3 mantissa bits) of the scaled block, with slack
     assert ((back - x.float()).abs() <= tol).all()
     assert torch.equal(fp8.dequantize_act_mx(qa, atoms).float(), back)
+
+
+@settings(**_SETTINGS)
+@given(st.sampled_from([1, 3, 4, 16]), st.lists(st.tuples(st.sampled_from(["append", "rewind", "reset"]), st.integers(1, 9)),
+                                                  min_size=1, max_size=14), st.booleans(), st.integers(0, 2 ** 31 - 1))
+def test_paged_cache_behaves_like_the_contiguous_cache(block_size, script, int8, seed):
+    """A random script of appends (1 .. 9 tokens), rewinds (``set_current_len``) and resets: a paged view holds what the
+    contiguous cache of the same kind holds, uses ceil(len / block) blocks, and gives every block back on reset."""
+    from tesseract_b200.nn.kv_cache import (KVCache, PagedKVCache, PagedKVPool, QuantizedKVCache,
+                                            QuantizedPagedKVCache, QuantizedPagedKVPool)
+    H, D, max_len = 2, 8, 64
+    g = torch.Generator().manual_seed(seed)
+    if int8:
+        pool = QuantizedPagedKVPool(40, H, block_size, D)
+        paged, flat = QuantizedPagedKVCache(pool, max_len), QuantizedKVCache(1, H, max_len, D)
+    else:
+        pool = PagedKVPool(40, H, block_size, D)
+        paged, flat = PagedKVCache(pool, max_len), KVCache(1, H, max_len, D)
+    free0 = pool.allocator.num_free()
+    for action, n in script:
+        if action == "append":
+            if flat.current_len() + n > max_len:
+                continue
+            k, v = torch.randn(1, H, n, D, generator=g), torch.randn(1, H, n, D, generator=g)
+            paged.append(k, v)
+            flat.append(k, v)
+        elif action == "rewind":
+            keep = flat.current_len() * n // 10
+            paged.set_current_len(keep)
+            flat.set_current_len(keep)
+        else:
+            paged.reset()
+            flat.reset()
+            assert pool.allocator.num_free() == free0
+        L = flat.current_len()
+        assert paged.current_len() == L
+        assert paged.num_blocks_held() >= (L + block_size - 1) // block_size
+        assert torch.equal(paged.keys_view(), flat.keys_view()) and torch.equal(paged.values_view(), flat.values_view())
+    paged.reset()
+    assert pool.allocator.num_free() == free0
+
+
+_UNARY = ["relu", "sigmoid", "tanh", "exp", "neg"]
+_BINARY = ["add", "sub", "mul"]
+
+
+@settings(**_SETTINGS)
+@given(st.lists(st.tuples(st.sampled_from(_UNARY + _BINARY + ["matmul", "softmax", "transpose"]), st.integers(0, 7)),
+                min_size=1, max_size=8), st.integers(0, 2 ** 31 - 1))
+def test_recorded_graphs_replay_and_differentiate_like_eager(ops_script, seed):
+    """Random chains of recorded ops over two 4 x 4 inputs and a 4 x 4 parameter: the interpreter returns the eager
+    result, the text form parses back to a graph that runs the same, and the backward transform gives autograd's
+    gradient of the result with respect to the parameter (dead ops, fused patterns and all)."""
+    from tesseract_b200.graph import GraphScope, build_backward, emit_mlir, parse_mlir, run
+    g = torch.Generator().manual_seed(seed)
+    a, b = torch.randn(4, 4, generator=g) * 0.5, torch.randn(4, 4, generator=g) * 0.5
+    w = torch.randn(4, 4, generator=g) * 0.5
+
+    def program(x, y, p):
+        vals = [x, y, p]
+        for kind, pick in ops_script:
+            u, v = vals[pick % len(vals)], vals[(pick // 2) % len(vals)]
+            if kind in _UNARY:
+                r = -u if kind == "neg" else getattr(torch, kind)(u)
+            elif kind in _BINARY:
+                r = {"add": u + v, "sub": u - v, "mul": u * v}[kind]
+            elif kind == "matmul":
+                r = u @ v
+            elif kind == "softmax":
+                r = torch.softmax(u, dim=-1)
+            else:
+                r = u.transpose(0, 1)
+            vals.append(r)
+        return (vals[-1] * p).sum()
+
+    wg = w.clone().requires_grad_()
+    ref = program(a, b, wg)
+    (gw,) = torch.autograd.grad(ref, wg)
+    with GraphScope() as scope:
+        ia, ib, iw = scope.bind_input(a, "a"), scope.bind_input(b, "b"), scope.bind_param(w, "w")
+        scope.mark_output(program(a, b, w))
+    graph = scope.graph
+    bind = {ia: a, ib: b, iw: w}
+    assert torch.allclose(run(graph, bind)[0], ref.detach(), atol=1e-5, rtol=1e-5)
+    again = parse_mlir(emit_mlir(graph))
+    rebind = dict(zip(list(again.inputs) + list(again.params), [a, b, w]))
+    assert torch.allclose(run(again, rebind)[0], ref.detach(), atol=1e-5, rtol=1e-5)
+    res = build_backward(graph)
+    bind[res.cotangents[0]] = torch.ones(())
+    outs = run(graph, bind)
+    assert len(outs) == 2 and torch.allclose(outs[1], gw, atol=1e-4, rtol=1e-4)
