@@ -252,3 +252,43 @@ def test_recorded_graphs_replay_and_differentiate_like_eager(ops_script, seed):
     bind[res.cotangents[0]] = torch.ones(())
     outs = run(graph, bind)
     assert len(outs) == 2 and torch.allclose(outs[1], gw, atol=1e-4, rtol=1e-4)
+
+
+_MODEL = {}
+
+
+def _tiny_model():
+    if "m" not in _MODEL:
+        from tesseract_b200.models import LlamaConfig, LlamaModel
+        torch.manual_seed(21)
+        _MODEL["m"] = LlamaModel(LlamaConfig(vocab_size=48, hidden_size=32, num_hidden_layers=2, num_attention_heads=4,
+                                             num_key_value_heads=2, intermediate_size=64, max_position_embeddings=64,
+                                             dtype=torch.float32))
+    return _MODEL["m"]
+
+
+@settings(max_examples=25, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(st.lists(st.tuples(st.integers(1, 9), st.integers(0, 6), st.booleans(), st.integers(0, 47)), min_size=1, max_size=6),
+       st.sampled_from([2, 4]), st.integers(1, 4), st.booleans(), st.integers(0, 2 ** 31 - 1))
+def test_scheduler_results_equal_standalone_generation(requests, block_size, max_batch, kv_int8, seed):
+    """Random mixes of requests (prompt length, budget, greedy or seeded sampling, an EOS id that may or may not come
+    up) through the continuous-batching scheduler with a small pool and batch: every result equals a standalone
+    ``generate`` of the same request, and the pool is whole again at the end."""
+    from tesseract_b200.models import GenerateConfig
+    from tesseract_b200.models.sampler import SamplingParams
+    from tesseract_b200.models.scheduler import ContinuousBatchingScheduler, EngineConfig
+    m = _tiny_model()
+    rng = np.random.default_rng(seed)
+    sched = ContinuousBatchingScheduler(m, EngineConfig(block_size=block_size, num_blocks=24, max_seq_len=24,
+                                                        max_batch_size=max_batch, kv_int8=kv_int8))
+    jobs = []
+    for plen, budget, sample, eos in requests:
+        prompt = rng.integers(0, 48, size=plen).tolist()
+        gen = GenerateConfig(max_new_tokens=budget, kv_int8=kv_int8, eos_token_id=eos if eos % 3 == 0 else -1,
+                             do_sample=sample, seed=int(rng.integers(0, 1000)),
+                             sampling=SamplingParams(temperature=0.9, top_k=12, top_p=0.9))
+        jobs.append((sched.add_request(prompt, gen), prompt, gen))
+    sched.run()
+    assert sched.free_blocks() == 24 and not sched.has_pending()
+    for rid, prompt, gen in jobs:
+        assert sched.result(rid) == m.generate(prompt, gen)
