@@ -292,3 +292,51 @@ def test_scheduler_results_equal_standalone_generation(requests, block_size, max
     assert sched.free_blocks() == 24 and not sched.has_pending()
     for rid, prompt, gen in jobs:
         assert sched.result(rid) == m.generate(prompt, gen)
+
+
+@settings(max_examples=25, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(st.integers(1, 8), st.integers(1, 7), st.integers(0, 14), st.integers(0, 2 ** 31 - 1))
+def test_speculative_and_disaggregated_generation_equal_plain_greedy(plen, gamma, budget, seed):
+    """Whatever the draft length, the prompt and the budget: speculative decoding returns the target's greedy tokens
+    (with a draft model that disagrees and with the target as its own draft), and a prefill engine handing its KV to
+    a decode engine returns the monolithic result."""
+    from tesseract_b200.models import GenerateConfig, LlamaConfig, LlamaModel
+    from tesseract_b200.models.disaggregated import DisaggregatedEngine
+    from tesseract_b200.models.speculative import SpeculativeDecoder
+    target = _tiny_model()
+    if "draft" not in _MODEL:
+        torch.manual_seed(22)
+        _MODEL["draft"] = LlamaModel(LlamaConfig(vocab_size=48, hidden_size=32, num_hidden_layers=1, num_attention_heads=4,
+                                                 num_key_value_heads=2, intermediate_size=64, max_position_embeddings=64,
+                                                 dtype=torch.float32))
+    prompt = np.random.default_rng(seed).integers(0, 48, size=plen).tolist()
+    want = target.generate(prompt, GenerateConfig(max_new_tokens=budget))
+    for draft in (_MODEL["draft"], target):
+        res = SpeculativeDecoder(target, draft, gamma).generate(prompt, budget)
+        assert res.tokens == want and res.proposed >= res.accepted
+    assert DisaggregatedEngine(target, target).generate(prompt, budget) == want
+
+
+@settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(st.sampled_from([1, 2, 3, 4, 6]), st.integers(1, 5), st.integers(1, 4), st.integers(1, 6), st.booleans(),
+       st.integers(0, 2 ** 31 - 1))
+def test_simulated_tensor_parallel_mlp_equals_dense(world, rows, in_mult, hid_mult, bias, seed):
+    """Column-parallel up projection, row-parallel down projection over the in-process communication backend, any
+    shard count that divides the hidden width: forward values and every gradient equal the dense layers'."""
+    from tesseract_b200.nn import Linear
+    from tesseract_b200.parallel import ColumnParallelLinear, RowParallelLinear, SimCommBackend
+    torch.manual_seed(seed % 1000)
+    d_in, d_hid = 4 * in_mult, world * hid_mult
+    up, down = Linear(d_in, d_hid, bias=bias), Linear(d_hid, d_in, bias=bias)
+    comm = SimCommBackend(world)
+    col, row = ColumnParallelLinear.from_dense(up, comm), RowParallelLinear.from_dense(down, comm)
+    x = torch.randn(rows, d_in)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya = down(torch.relu(up(xa)))
+    yb = row(torch.relu(col(xb)))
+    assert torch.allclose(ya, yb, atol=1e-5)
+    ya.square().sum().backward()
+    yb.square().sum().backward()
+    assert torch.allclose(xa.grad, xb.grad, atol=1e-4)
+    gw = torch.cat([p.grad for n, p in col.named_parameters() if n.endswith("weight")], dim=0)
+    assert torch.allclose(gw, up.weight.grad, atol=1e-4)
