@@ -10,7 +10,8 @@ from hypothesis import HealthCheck, given, settings
 from hypothesis import strategies as st
 
 FIX = os.path.join(os.path.dirname(__file__), "fixtures", "hf_bpe", "tokenizer.json")
-_SETTINGS = dict(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+# derandomised: every run draws the same examples (explore with --hypothesis-seed=N and derandomize off)
+_SETTINGS = dict(max_examples=60, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
 
 
 @settings(**_SETTINGS)
@@ -267,7 +268,7 @@ def _tiny_model():
     return _MODEL["m"]
 
 
-@settings(max_examples=25, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=25, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
 @given(st.lists(st.tuples(st.integers(1, 9), st.integers(0, 6), st.booleans(), st.integers(0, 47)), min_size=1, max_size=6),
        st.sampled_from([2, 4]), st.integers(1, 4), st.booleans(), st.integers(0, 2 ** 31 - 1))
 def test_scheduler_results_equal_standalone_generation(requests, block_size, max_batch, kv_int8, seed):
@@ -294,7 +295,7 @@ def test_scheduler_results_equal_standalone_generation(requests, block_size, max
         assert sched.result(rid) == m.generate(prompt, gen)
 
 
-@settings(max_examples=25, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=25, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
 @given(st.integers(1, 8), st.integers(1, 7), st.integers(0, 14), st.integers(0, 2 ** 31 - 1))
 def test_speculative_and_disaggregated_generation_equal_plain_greedy(plen, gamma, budget, seed):
     """Whatever the draft length, the prompt and the budget: speculative decoding returns the target's greedy tokens
@@ -317,7 +318,7 @@ def test_speculative_and_disaggregated_generation_equal_plain_greedy(plen, gamma
     assert DisaggregatedEngine(target, target).generate(prompt, budget) == want
 
 
-@settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=30, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
 @given(st.sampled_from([1, 2, 3, 4, 6]), st.integers(1, 5), st.integers(1, 4), st.integers(1, 6), st.booleans(),
        st.integers(0, 2 ** 31 - 1))
 def test_simulated_tensor_parallel_mlp_equals_dense(world, rows, in_mult, hid_mult, bias, seed):
