@@ -341,3 +341,28 @@ def test_simulated_tensor_parallel_mlp_equals_dense(world, rows, in_mult, hid_mu
     assert torch.allclose(xa.grad, xb.grad, atol=1e-4)
     gw = torch.cat([p.grad for n, p in col.named_parameters() if n.endswith("weight")], dim=0)
     assert torch.allclose(gw, up.weight.grad, atol=1e-4)
+
+
+@settings(**_SETTINGS)
+@given(st.lists(st.integers(1, 4), min_size=1, max_size=3), st.sampled_from(["add", "sub", "mul", "div"]),
+       st.integers(0, 2 ** 31 - 1))
+def test_frontend_elementwise_ops_follow_numpy_and_their_gradients_sum_to_shape(shape, op, seed):
+    """``tesseract.ops`` binary ops on fp32 tensors: values equal numpy's, a broadcast operand receives a gradient of
+    its own shape (the sum over the broadcast axes), mismatched dtypes are refused."""
+    import tesseract as ts
+    rng = np.random.default_rng(seed)
+    a_np = rng.standard_normal(shape).astype(np.float32)
+    b_shape = [s if rng.integers(0, 2) else 1 for s in shape]
+    b_np = (rng.standard_normal(b_shape) + 3.0).astype(np.float32)            # away from zero for div
+    a, b = ts.Tensor(a_np), ts.Tensor(b_np)
+    a.requires_grad = True
+    b.requires_grad = True
+    y = getattr(ts.ops, op)(a, b)
+    want = {"add": a_np + b_np, "sub": a_np - b_np, "mul": a_np * b_np, "div": a_np / b_np}[op]
+    assert y.shape == list(want.shape) and np.allclose(y.numpy(), want, rtol=1e-5, atol=1e-6)
+    y.t.sum().backward()
+    assert a.grad().shape == list(a_np.shape) and b.grad().shape == list(b_np.shape)
+    if op == "add":
+        assert np.allclose(b.grad().numpy(), np.full(b_shape, a_np.size / b_np.size, dtype=np.float32))
+    with pytest.raises(TypeError):
+        getattr(ts.ops, op)(a, ts.Tensor(b_np.astype(np.float64)))
