@@ -366,3 +366,34 @@ def test_frontend_elementwise_ops_follow_numpy_and_their_gradients_sum_to_shape(
         assert np.allclose(b.grad().numpy(), np.full(b_shape, a_np.size / b_np.size, dtype=np.float32))
     with pytest.raises(TypeError):
         getattr(ts.ops, op)(a, ts.Tensor(b_np.astype(np.float64)))
+
+
+@settings(**_SETTINGS)
+@given(st.integers(1, 300), st.sampled_from([128, 256, 384]), st.booleans(), st.integers(-6, 4), st.integers(0, 2 ** 31 - 1))
+def test_block_scaled_weight_quantisation_bounds(N, K, pow2, decade, seed):
+    """128 x 128 block scales of an E4M3 weight: positive, powers of two when asked (never smaller than the exact
+    scale, less than twice it), zero blocks get scale 1, dequantised weights within one E4M3 step of the input, and the
+    scale atoms of the MX GEMM carry the exponent byte of every block."""
+    from tesseract_b200.ops import fp8
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(N, K, generator=g) * (10.0 ** decade)
+    if N > 130:
+        w[:128, :128] = 0                                          # an all-zero block
+    q, s = fp8.quantize_weight(w, pow2=pow2)
+    q0, s0 = fp8.quantize_weight_ref(w)
+    assert q.shape == (N, K) and q.dtype == torch.uint8 and s.shape == ((N + 127) // 128, K // 128)
+    assert (s > 0).all()
+    if pow2:
+        assert fp8.scales_are_pow2(s) and (s >= s0 * (1 - 1e-6)).all() and (s < 2 * s0 * (1 + 1e-6)).all()
+        atoms = fp8.weight_scale_atoms(s)
+        assert atoms.shape == (s.shape[0], s.shape[1], 128)
+        expo = (s.contiguous().view(torch.int32) >> 23) & 0xFF
+        assert torch.equal(atoms[:, :, 0] & 0xFF, expo) and torch.equal((atoms[:, :, 77] >> 24) & 0xFF, expo)
+    else:
+        assert torch.allclose(s, s0)
+    if N > 130:
+        assert s[0, 0] == 1.0
+    back = fp8.dequantize_weight(q, s)
+    rows = torch.arange(N) // 128
+    step = (s[rows].repeat_interleave(128, dim=1)[:, :K] * 32.0)         # the largest E4M3 step (at 448) is 32
+    assert ((back - w).abs() <= step * 0.5 + 1e-30).all()
