@@ -397,3 +397,43 @@ def test_block_scaled_weight_quantisation_bounds(N, K, pow2, decade, seed):
     rows = torch.arange(N) // 128
     step = (s[rows].repeat_interleave(128, dim=1)[:, :K] * 32.0)         # the largest E4M3 step (at 448) is 32
     assert ((back - w).abs() <= step * 0.5 + 1e-30).all()
+
+
+@settings(**_SETTINGS)
+@given(st.integers(1, 3), st.integers(1, 5), st.sampled_from([(4, 4), (4, 2), (6, 1)]), st.sampled_from([2, 4]),
+       st.booleans(), st.integers(0, 2 ** 31 - 1))
+def test_paged_attention_oracle_equals_dense_attention_on_gathered_keys(A, S, heads, bs, int8, seed):
+    """The paged-attention restatement (the oracle of the CUDA decode / prefill kernels) against plain softmax
+    attention over each request's keys gathered in order: GQA head map, per-request lengths, the last new token seeing
+    every key (bottom-right causal alignment), shuffled block tables, INT8 pools with per-token scales."""
+    from tesseract_b200 import ops
+    from tesseract_b200.nn.kv_cache import quantize_kv_per_token
+    H, Hkv = heads
+    D, max_blocks = 8, 5
+    rng = np.random.default_rng(seed)
+    g = torch.Generator().manual_seed(seed)
+    nb = A * max_blocks + 2
+    k_pool, v_pool = torch.randn(nb, Hkv, bs, D, generator=g), torch.randn(nb, Hkv, bs, D, generator=g)
+    perm = rng.permutation(nb)[:A * max_blocks].reshape(A, max_blocks)
+    tables = torch.from_numpy(perm.astype(np.int64))
+    lens = torch.from_numpy(rng.integers(S, max_blocks * bs + 1, size=A).astype(np.int64))
+    ks = vs = None
+    kd, vd = k_pool, v_pool
+    if int8:
+        kq, ks = quantize_kv_per_token(k_pool)
+        vq, vs = quantize_kv_per_token(v_pool)
+        kd, vd = kq.float() * ks[..., None], vq.float() * vs[..., None]
+        k_pool, v_pool = kq, vq
+    q = torch.randn(A, S, H, D, generator=g)
+    got = ops.paged_attention_ref(q, k_pool, v_pool, tables, lens, None, ks, vs)
+    for a in range(A):
+        L = int(lens[a])
+        keys = torch.cat([kd[tables[a, i]] for i in range(max_blocks)], dim=1)[:, :L]      # [Hkv, L, D]
+        vals = torch.cat([vd[tables[a, i]] for i in range(max_blocks)], dim=1)[:, :L]
+        for h in range(H):
+            kv = h // (H // Hkv)
+            s = (q[a, :, h] @ keys[kv].t()) / D ** 0.5                                    # [S, L]
+            i = torch.arange(S)[:, None] + (L - S)
+            s = s.masked_fill(torch.arange(L)[None, :] > i, float("-inf"))
+            want = torch.softmax(s, dim=-1) @ vals[kv]
+            assert torch.allclose(got[a, :, h], want, atol=1e-5)
